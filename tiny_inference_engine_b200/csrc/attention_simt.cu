@@ -1,0 +1,276 @@
+// Causal attention over the paged cache on the CUDA cores, for any head size that is a
+// multiple of 8, any number of heads and groups, any page size; float or bfloat16 storage,
+// float scores, softmax and accumulation. It is the attention of the 32-bit path and the
+// fallback of the bfloat16 path.
+//
+// What it computes is the reference's paged_attention (src/backend/cpu/cpu_backend.cpp:261-319):
+// query row t of sequence s has position pos = context_len[s] - n_queries(s) + (t - query_start[s])
+// and sees keys 0..pos (with a window w > 0: keys pos-w+1..pos); query head h reads kv head
+// h / (Hq/Hkv); online softmax of scale * q.k; out = acc / l.
+//
+// Two kernels share the inner loop:
+//   rows kernel   one warp per (row, head) over all of its keys: prompt portions.
+//   split kernel  one warp per (sequence, head, split of the keys) for sequences that bring
+//                 one token: each split of `split_keys` keys leaves (max, sum, acc) in
+//                 scratch memory and a merge kernel combines them in split order. The split
+//                 size is a constant of the call, so the order of the sums for a token
+//                 depends only on its own context, never on the batch around it.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace tie {
+
+struct AttnArgs {
+  const void* q;            // [T, ...] row stride q_stride, head h at h * head_dim
+  const void* k_cache;      // [pages, kv_heads, page_size, head_dim]
+  const void* v_cache;
+  void* out;                // [T, q_heads * head_dim]
+  const int* seq_of_row;    // [T]
+  const int* query_start;   // [S + 1]
+  const int* context_lens;  // [S]
+  const int* block_tables;  // [S, max_blocks]
+  long long q_stride;
+  int max_blocks;
+  int rows;                 // T
+  int seqs;                 // S
+  int q_heads, kv_heads, head_dim, page_size;
+  int window;               // 0 = all keys
+  float scale;
+};
+
+// One warp: online softmax over keys [lo, hi] of one (query vector, kv head).
+// q is in shared memory (float, already multiplied by nothing: scale is applied to the score).
+// Lane `l` owns output dims [l * DPL, (l + 1) * DPL). Returns m, l and acc in registers.
+template <typename T, int DPL>
+__device__ __forceinline__ void attend_range(const float* __restrict__ qs, const T* __restrict__ kc,
+                                             const T* __restrict__ vc, const int* __restrict__ table, int kvh,
+                                             int kv_heads, int head_dim, int page_size, float scale, int lo, int hi,
+                                             float& m, float& l, float (&acc)[DPL]) {
+  constexpr int V = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int d0 = lane * DPL;
+  for (int base = lo; base <= hi; base += 32) {
+    const int j = base + lane;
+    const bool valid = j <= hi;
+    int row = 0;  // index of the key's row in units of head_dim elements
+    float s = -INFINITY;
+    if (valid) {
+      const int page = table[j / page_size];
+      row = (page * kv_heads + kvh) * page_size + j % page_size;
+      const T* kr = kc + static_cast<long long>(row) * head_dim;
+      float dot = 0.0f;
+      for (int d = 0; d < head_dim; d += V) {
+        Vec16<T> kv;
+        kv.load(kr + d);
+#pragma unroll
+        for (int e = 0; e < V; ++e) dot = fmaf(qs[d + e], kv.v[e], dot);
+      }
+      s = scale * dot;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);  // m = -inf at the start gives 0
+    const float p = valid ? expf(s - m_new) : 0.0f;
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) acc[e] *= corr;
+    const int count = min(32, hi - base + 1);
+    for (int jj = 0; jj < count; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const int rj = __shfl_sync(0xffffffffu, row, jj);
+      if (d0 < head_dim) {
+        const T* vr = vc + static_cast<long long>(rj) * head_dim + d0;
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
+      }
+    }
+  }
+}
+
+template <typename T, int DPL>
+__global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (item >= static_cast<long long>(a.rows) * a.q_heads) return;
+  const int t = static_cast<int>(item / a.q_heads);
+  const int h = static_cast<int>(item % a.q_heads);
+  const int s = a.seq_of_row[t];
+  const int qs0 = a.query_start[s], qs1 = a.query_start[s + 1];
+  const int pos = a.context_lens[s] - (qs1 - qs0) + (t - qs0);
+  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int kvh = h / (a.q_heads / a.kv_heads);
+
+  float* qs = smem + warp * a.head_dim;
+  const T* qv = static_cast<const T*>(a.q) + static_cast<long long>(t) * a.q_stride + static_cast<long long>(h) * a.head_dim;
+  for (int d = lane; d < a.head_dim; d += 32) qs[d] = ld(qv + d);
+  __syncwarp();
+
+  float m = -INFINITY, l = 0.0f, acc[DPL] = {};
+  attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
+                       a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
+                       a.page_size, a.scale, lo, pos, m, l, acc);
+  const int d0 = lane * DPL;
+  if (d0 < a.head_dim) {
+    T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.head_dim + d0;
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // no keys (a padding row): zeros
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) st(o + e, acc[e] * inv);
+  }
+}
+
+// Split kernel: sequences listed in `seq_list` (each brings exactly one query row).
+// scratch: [n_list, q_heads, max_splits, head_dim + 2] floats (acc, then m, l).
+template <typename T, int DPL>
+__global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const int* __restrict__ seq_list, int n_list,
+                                                              int split_keys, int max_splits, float* __restrict__ scratch) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.y;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (item >= static_cast<long long>(n_list) * a.q_heads) return;
+  const int li = static_cast<int>(item / a.q_heads);
+  const int h = static_cast<int>(item % a.q_heads);
+  const int s = seq_list[li];
+  const int t = a.query_start[s];
+  const int pos = a.context_lens[s] - 1;
+  const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int lo = lo0 + split * split_keys;
+  if (lo > pos) return;  // this sequence has fewer splits
+  const int hi = min(pos, lo + split_keys - 1);
+  const int kvh = h / (a.q_heads / a.kv_heads);
+
+  float* qs = smem + warp * a.head_dim;
+  const T* qv = static_cast<const T*>(a.q) + static_cast<long long>(t) * a.q_stride + static_cast<long long>(h) * a.head_dim;
+  for (int d = lane; d < a.head_dim; d += 32) qs[d] = ld(qv + d);
+  __syncwarp();
+
+  float m = -INFINITY, l = 0.0f, acc[DPL] = {};
+  attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
+                       a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
+                       a.page_size, a.scale, lo, hi, m, l, acc);
+  float* dst = scratch + ((static_cast<long long>(li) * a.q_heads + h) * max_splits + split) * (a.head_dim + 2);
+  const int d0 = lane * DPL;
+  if (d0 < a.head_dim) {
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) dst[d0 + e] = acc[e];
+  }
+  if (lane == 0) {
+    dst[a.head_dim] = m;
+    dst[a.head_dim + 1] = l;
+  }
+}
+
+// Merge of the splits of one (sequence, head), in split order: one warp each.
+template <typename T>
+__global__ void attention_merge_kernel(AttnArgs a, const int* __restrict__ seq_list, int n_list, int split_keys,
+                                       int max_splits, const float* __restrict__ scratch) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (item >= static_cast<long long>(n_list) * a.q_heads) return;
+  const int li = static_cast<int>(item / a.q_heads);
+  const int h = static_cast<int>(item % a.q_heads);
+  const int s = seq_list[li];
+  const int t = a.query_start[s];
+  const int pos = a.context_lens[s] - 1;
+  const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int splits = (pos - lo0) / split_keys + 1;
+  const float* src = scratch + (static_cast<long long>(li) * a.q_heads + h) * max_splits * (a.head_dim + 2);
+  float m = -INFINITY;
+  for (int i = 0; i < splits; ++i) m = fmaxf(m, src[i * (a.head_dim + 2) + a.head_dim]);
+  float l = 0.0f;
+  for (int i = 0; i < splits; ++i) {
+    const float* p = src + i * (a.head_dim + 2);
+    l += p[a.head_dim + 1] * expf(p[a.head_dim] - m);
+  }
+  T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.head_dim;
+  for (int d = lane; d < a.head_dim; d += 32) {
+    float acc = 0.0f;
+    for (int i = 0; i < splits; ++i) {
+      const float* p = src + i * (a.head_dim + 2);
+      acc = fmaf(p[d], expf(p[a.head_dim] - m), acc);
+    }
+    st(o + d, l > 0.0f ? acc / l : 0.0f);
+  }
+}
+
+template <typename T>
+int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* seq_list, int n_list, int split_keys,
+                     int max_splits, float* scratch, int rows_kernel, cudaStream_t s) {
+  (void)row_seq_unused;
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * a.head_dim * sizeof(float);
+  const int dpl = (a.head_dim + 31) / 32;
+#define TIE_ATTN_CASE(D)                                                                                         \
+  do {                                                                                                           \
+    if (rows_kernel) {                                                                                           \
+      const long long items = static_cast<long long>(a.rows) * a.q_heads;                                        \
+      if (items > 0) attention_rows_kernel<T, D><<<ceil_div(items, warps), warps * 32, smem, s>>>(a);            \
+    } else {                                                                                                     \
+      const long long items = static_cast<long long>(n_list) * a.q_heads;                                        \
+      if (items > 0) {                                                                                           \
+        attention_split_kernel<T, D><<<dim3(ceil_div(items, warps), max_splits), warps * 32, smem, s>>>(          \
+            a, seq_list, n_list, split_keys, max_splits, scratch);                                               \
+        attention_merge_kernel<T><<<ceil_div(items, warps), warps * 32, 0, s>>>(a, seq_list, n_list, split_keys, \
+                                                                                 max_splits, scratch);           \
+      }                                                                                                          \
+    }                                                                                                            \
+  } while (0)
+  if (dpl <= 1) TIE_ATTN_CASE(1);
+  else if (dpl <= 2) TIE_ATTN_CASE(2);
+  else if (dpl <= 4) TIE_ATTN_CASE(4);
+  else if (dpl <= 8) TIE_ATTN_CASE(8);
+  else TIE_ATTN_CASE(16);
+#undef TIE_ATTN_CASE
+  TIE_RETURN_LAUNCH("paged_attention_simt");
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+static int check_attn(const AttnArgs& a) {
+  TIE_REQUIRE(a.q_heads > 0 && a.kv_heads > 0 && a.q_heads % a.kv_heads == 0,
+              "attention: %d query heads are not a multiple of %d kv heads", a.q_heads, a.kv_heads);
+  TIE_REQUIRE(a.head_dim > 0 && a.head_dim % 8 == 0 && a.head_dim <= 512,
+              "attention: head_dim %d must be a multiple of 8 and at most 512", a.head_dim);
+  TIE_REQUIRE(a.head_dim <= 256 || a.head_dim % 16 == 0, "attention: head_dim %d above 256 must be a multiple of 16",
+              a.head_dim);
+  TIE_REQUIRE(a.page_size > 0 && a.max_blocks > 0, "attention: bad page geometry");
+  TIE_REQUIRE(a.window >= 0, "attention: negative window");
+  return kOk;
+}
+
+// All rows of the step, each over all of its keys (prompt portions and, when no split is
+// wanted, single tokens too).
+TIE_API int tie_attention_rows(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                               void* out, const int* seq_of_row, const int* query_start, const int* context_lens,
+                               const int* block_tables, int max_blocks, int rows, int seqs, int q_heads, int kv_heads,
+                               int head_dim, int page_size, int window, float scale, cudaStream_t s) {
+  const AttnArgs a{q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_stride, max_blocks,
+                   rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
+  if (const int st = check_attn(a)) return st;
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
+  if (dtype == TIE_BF16) return launch_attention<__nv_bfloat16>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
+  set_error("attention: unknown dtype code %d", dtype);
+  return kBadArgument;
+}
+
+// The sequences of seq_list bring one token each; their keys are cut into splits of
+// `split_keys` keys. scratch holds n_list * q_heads * max_splits * (head_dim + 2) floats.
+TIE_API int tie_attention_split(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                void* out, const int* query_start, const int* context_lens, const int* block_tables,
+                                int max_blocks, int seqs, int q_heads, int kv_heads, int head_dim, int page_size,
+                                int window, float scale, const int* seq_list, int n_list, int split_keys,
+                                int max_splits, float* scratch, cudaStream_t s) {
+  const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
+                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
+  if (const int st = check_attn(a)) return st;
+  TIE_REQUIRE(split_keys > 0 && max_splits > 0 && scratch != nullptr, "attention split: bad split geometry");
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  if (dtype == TIE_BF16)
+    return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  set_error("attention: unknown dtype code %d", dtype);
+  return kBadArgument;
+}

@@ -1,0 +1,340 @@
+// Embedding, norms, rotary position encoding, cache append and SiLU*mul: the memory-bound
+// kernels between the matrix products. Each is templated on the storage type of the
+// activations (float for the 32-bit path, bfloat16 for serving); every sum, scale, angle
+// and the residual stream itself are float.
+//
+// What each computes follows the reference's CPU backend (src/backend/cpu/cpu_backend.cpp):
+// embed :51-76, rms_norm :141-159, rope_neox :161-193, silu_mul :195-207, add :209-221,
+// gather_rows :223-233, kv_write :235-259. The fusions are this engine's own.
+#include "common.cuh"
+
+namespace tie {
+
+// ---------------------------------------------------------------------------------------------
+// x[t, :] = float(table[ids[t], :]). The residual stream is float in both paths.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
+                             int dim, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; never read outside the table
+  const T* row = table + static_cast<size_t>(id) * dim;
+  float* out = x + static_cast<size_t>(t) * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = ld(row + i);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Residual add fused with the norm that follows it:
+//   x[t] += delta[t]  (float sum, written back; skipped when delta is null)
+//   out[t] = (x[t] * inv) * w,  inv = 1 / sqrt(mean(x[t]^2) + eps)
+// With `rows` non-null, row t of the output comes from row rows[t] of x and delta, and x is
+// not written back (the rows that reach the final norm are the last use of x).
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
+                                   const float* __restrict__ w, float eps, T* __restrict__ out, int dim) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[t] : t) * dim;
+  float* xr = x + src;
+  const T* dr = delta ? delta + src : nullptr;
+  T* o = out + static_cast<size_t>(t) * dim;
+  const bool write_back = dr != nullptr && rows == nullptr;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) v += ld(dr + i);
+    if (write_back) xr[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = xr[i];
+    if (dr && !write_back) v += ld(dr + i);
+    st(o + i, (v * inv) * w[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm of n rows of `size` elements of T (stride `row_stride`), one warp per row. Used for
+// norms over something else than the residual stream (per-head norms outside the fused kernel).
+template <typename T>
+__global__ void rmsnorm_rows_kernel(const T* __restrict__ x, long long row_stride, const float* __restrict__ w,
+                                    float eps, T* __restrict__ out, long long out_stride, int size, long long n) {
+  const long long r = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n) return;
+  const int lane = threadIdx.x & 31;
+  const T* xr = x + r * row_stride;
+  T* o = out + r * out_stride;
+  float ss = 0.0f;
+  for (int i = lane; i < size; i += 32) {
+    const float v = ld(xr + i);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(size) + eps);
+  for (int i = lane; i < size; i += 32) st(o + i, (ld(xr + i) * inv) * w[i]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(g) = g / (1 + exp(-g)).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, long long total) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / inter;
+  const int i = static_cast<int>(idx - t * inter);
+  const float g = ld(gu + t * 2 * inter + i);
+  const float u = ld(gu + t * 2 * inter + inter + i);
+  st(out + idx, g / (1.0f + expf(-g)) * u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rotate-half RoPE in place over the first `rot` dims of every head:
+//   angle = float(pos) * inv_freq[i];  (v[i], v[i + rot/2]) <- (v[i] c - v[i+rot/2] s, v[i+rot/2] c + v[i] s)
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ x, long long row_stride, const int* __restrict__ positions,
+                            const float* __restrict__ inv_freq, int heads, int head_dim, int rot, long long total) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int half = rot / 2;
+  const int i = static_cast<int>(idx % half);
+  const int h = static_cast<int>((idx / half) % heads);
+  const long long t = idx / (static_cast<long long>(half) * heads);
+  T* v = x + t * row_stride + static_cast<long long>(h) * head_dim;
+  const float angle = static_cast<float>(positions[t]) * inv_freq[i];
+  const float c = cosf(angle), s = sinf(angle);
+  const float x1 = ld(v + i), x2 = ld(v + i + half);
+  st(v + i, x1 * c - x2 * s);
+  st(v + i + half, x2 * c + x1 * s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// k, v rows of token t go to slot s = slots[t]: page s / page_size, offset s % page_size, in
+// planes laid out [page][kv_head][offset][head_dim]. A negative slot writes nothing.
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ v, long long k_stride,
+                                 long long v_stride, const int* __restrict__ slots, T* __restrict__ k_cache,
+                                 T* __restrict__ v_cache, int kv_heads, int head_dim, int page_size, long long total) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int d = static_cast<int>(idx % head_dim);
+  const int h = static_cast<int>((idx / head_dim) % kv_heads);
+  const long long t = idx / (static_cast<long long>(head_dim) * kv_heads);
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const long long page = slot / page_size, off = slot % page_size;
+  const long long dst = ((page * kv_heads + h) * page_size + off) * head_dim + d;
+  k_cache[dst] = k[t * k_stride + static_cast<long long>(h) * head_dim + d];
+  v_cache[dst] = v[t * v_stride + static_cast<long long>(h) * head_dim + d];
+}
+
+// ---------------------------------------------------------------------------------------------
+// The work between the q/k/v projection and attention, one warp per (token, head):
+//   q heads: RMSNorm over the head (weight qw, skipped when null), RoPE, written back in place;
+//   k heads: RMSNorm (kw), RoPE, written to the key plane at the token's slot;
+//   v heads: copied to the value plane at the token's slot.
+// qkv is [T, (Hq + 2 Hkv) * Dh] with q first, then k, then v. With write_kv == 0 only the q
+// heads are processed (a layer that reads another layer's cache). inv_freq null = no rotation.
+template <typename T>
+__global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ qw,
+                                           const float* __restrict__ kw, float q_eps, float k_eps,
+                                           const float* __restrict__ inv_freq, int rot,
+                                           const int* __restrict__ positions, const int* __restrict__ slots,
+                                           T* __restrict__ k_cache, T* __restrict__ v_cache, int q_heads, int kv_heads,
+                                           int head_dim, int page_size, int heads_per_token, long long total) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (item >= total) return;
+  const long long t = item / heads_per_token;
+  const int head = static_cast<int>(item - t * heads_per_token);
+  T* src = qkv + t * row_stride + static_cast<long long>(head) * head_dim;
+  float* buf = smem + warp * head_dim;
+
+  const bool is_q = head < q_heads;
+  const bool is_k = !is_q && head < q_heads + kv_heads;
+  T* dst = src;
+  if (!is_q) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int h = is_k ? head - q_heads : head - q_heads - kv_heads;
+    const long long page = slot / page_size, off = slot % page_size;
+    dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + h) * page_size + off) * head_dim;
+    if (!is_k) {  // values are stored as they are
+      for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+      return;
+    }
+  }
+
+  const float* w = is_q ? qw : kw;
+  float ss = 0.0f;
+  for (int i = lane; i < head_dim; i += 32) {
+    const float v = ld(src + i);
+    buf[i] = v;
+    ss += v * v;
+  }
+  if (w) {
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(head_dim) + (is_q ? q_eps : k_eps));
+    for (int i = lane; i < head_dim; i += 32) buf[i] = (buf[i] * inv) * w[i];
+  }
+  __syncwarp();
+  const int half = inv_freq ? rot / 2 : 0;
+  if (half > 0) {
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = lane; i < half; i += 32) {
+      const float angle = pos * inv_freq[i];
+      const float c = cosf(angle), s = sinf(angle);
+      const float x1 = buf[i], x2 = buf[i + half];
+      st(dst + i, x1 * c - x2 * s);
+      st(dst + i + half, x2 * c + x1 * s);
+    }
+  }
+  for (int i = 2 * half + lane; i < head_dim; i += 32) st(dst + i, buf[i]);
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+int launch_embed(const void* table, const int* ids, float* x, int tokens, int dim, int vocab, cudaStream_t s) {
+  if (tokens == 0) return kOk;
+  embed_kernel<T><<<tokens, dim >= 1024 ? 256 : 128, 0, s>>>(static_cast<const T*>(table), ids, x, dim, vocab);
+  TIE_RETURN_LAUNCH("embed");
+}
+
+template <typename T>
+int launch_add_rmsnorm(float* x, const void* delta, const int* rows, const float* w, float eps, void* out, int n,
+                       int dim, cudaStream_t s) {
+  if (n == 0) return kOk;
+  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  add_rmsnorm_kernel<T><<<n, threads, 0, s>>>(x, static_cast<const T*>(delta), rows, w, eps, static_cast<T*>(out), dim);
+  TIE_RETURN_LAUNCH("add_rmsnorm");
+}
+
+template <typename T>
+int launch_rmsnorm_rows(const void* x, long long xs, const float* w, float eps, void* out, long long os, int size,
+                        long long n, cudaStream_t s) {
+  if (n == 0) return kOk;
+  rmsnorm_rows_kernel<T><<<ceil_div(n, 4), 128, 0, s>>>(static_cast<const T*>(x), xs, w, eps, static_cast<T*>(out), os,
+                                                         size, n);
+  TIE_RETURN_LAUNCH("rmsnorm_rows");
+}
+
+template <typename T>
+int launch_silu_mul(const void* gu, void* out, int tokens, int inter, cudaStream_t s) {
+  const long long total = static_cast<long long>(tokens) * inter;
+  if (total == 0) return kOk;
+  silu_mul_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(static_cast<const T*>(gu), static_cast<T*>(out), inter, total);
+  TIE_RETURN_LAUNCH("silu_mul");
+}
+
+template <typename T>
+int launch_rope(void* x, long long stride, const int* pos, const float* inv_freq, int tokens, int heads, int head_dim,
+                int rot, cudaStream_t s) {
+  const long long total = static_cast<long long>(tokens) * heads * (rot / 2);
+  if (total == 0) return kOk;
+  rope_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(static_cast<T*>(x), stride, pos, inv_freq, heads, head_dim, rot,
+                                                      total);
+  TIE_RETURN_LAUNCH("rope");
+}
+
+template <typename T>
+int launch_kv_append(const void* k, const void* v, long long ks, long long vs, const int* slots, void* kc, void* vc,
+                     int tokens, int kv_heads, int head_dim, int page_size, cudaStream_t s) {
+  const long long total = static_cast<long long>(tokens) * kv_heads * head_dim;
+  if (total == 0) return kOk;
+  kv_append_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(static_cast<const T*>(k), static_cast<const T*>(v), ks, vs,
+                                                           slots, static_cast<T*>(kc), static_cast<T*>(vc), kv_heads,
+                                                           head_dim, page_size, total);
+  TIE_RETURN_LAUNCH("kv_append");
+}
+
+template <typename T>
+int launch_qk_norm_rope_append(void* qkv, long long stride, const float* qw, const float* kw, float q_eps, float k_eps,
+                               const float* inv_freq, int rot, const int* pos, const int* slots, void* kc, void* vc,
+                               int tokens, int q_heads, int kv_heads, int head_dim, int page_size, int write_kv,
+                               cudaStream_t s) {
+  const int heads_per_token = write_kv ? q_heads + 2 * kv_heads : q_heads;
+  const long long total = static_cast<long long>(tokens) * heads_per_token;
+  if (total == 0) return kOk;
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
+  qk_norm_rope_append_kernel<T><<<ceil_div(total, warps), warps * 32, smem, s>>>(
+      static_cast<T*>(qkv), stride, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots, static_cast<T*>(kc),
+      static_cast<T*>(vc), q_heads, kv_heads, head_dim, page_size, heads_per_token, total);
+  TIE_RETURN_LAUNCH("qk_norm_rope_append");
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+#define TIE_DISPATCH(dtype, call_f32, call_bf16)                       \
+  do {                                                                 \
+    if ((dtype) == TIE_F32) return call_f32;                           \
+    if ((dtype) == TIE_BF16) return call_bf16;                         \
+    set_error("unknown dtype code %d", (dtype));                       \
+    return kBadArgument;                                               \
+  } while (0)
+
+TIE_API int tie_embed(int dtype, const void* table, const int* ids, float* x, int tokens, int dim, int vocab,
+                      cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && dim > 0 && vocab > 0, "embed: bad sizes tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
+  TIE_DISPATCH(dtype, launch_embed<float>(table, ids, x, tokens, dim, vocab, s),
+               launch_embed<__nv_bfloat16>(table, ids, x, tokens, dim, vocab, s));
+}
+
+// rows may be null (row t of out from row t of x); delta may be null (no add).
+TIE_API int tie_add_rmsnorm(int dtype, float* x, const void* delta, const int* rows, const float* w, float eps,
+                            void* out, int n, int dim, cudaStream_t s) {
+  TIE_REQUIRE(n >= 0 && dim > 0, "add_rmsnorm: bad sizes n=%d dim=%d", n, dim);
+  TIE_DISPATCH(dtype, launch_add_rmsnorm<float>(x, delta, rows, w, eps, out, n, dim, s),
+               launch_add_rmsnorm<__nv_bfloat16>(x, delta, rows, w, eps, out, n, dim, s));
+}
+
+TIE_API int tie_rmsnorm_rows(int dtype, const void* x, long long x_stride, const float* w, float eps, void* out,
+                             long long out_stride, int size, long long n, cudaStream_t s) {
+  TIE_REQUIRE(n >= 0 && size > 0, "rmsnorm_rows: bad sizes n=%lld size=%d", n, size);
+  TIE_DISPATCH(dtype, launch_rmsnorm_rows<float>(x, x_stride, w, eps, out, out_stride, size, n, s),
+               launch_rmsnorm_rows<__nv_bfloat16>(x, x_stride, w, eps, out, out_stride, size, n, s));
+}
+
+TIE_API int tie_silu_mul(int dtype, const void* gu, void* out, int tokens, int inter, cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && inter > 0, "silu_mul: bad sizes tokens=%d inter=%d", tokens, inter);
+  TIE_DISPATCH(dtype, launch_silu_mul<float>(gu, out, tokens, inter, s),
+               launch_silu_mul<__nv_bfloat16>(gu, out, tokens, inter, s));
+}
+
+TIE_API int tie_rope(int dtype, void* x, long long stride, const int* pos, const float* inv_freq, int tokens,
+                     int heads, int head_dim, int rot, cudaStream_t s) {
+  TIE_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= head_dim, "rope: rotary dim %d must be even and at most head_dim %d",
+              rot, head_dim);
+  TIE_DISPATCH(dtype, launch_rope<float>(x, stride, pos, inv_freq, tokens, heads, head_dim, rot, s),
+               launch_rope<__nv_bfloat16>(x, stride, pos, inv_freq, tokens, heads, head_dim, rot, s));
+}
+
+TIE_API int tie_kv_append(int dtype, const void* k, const void* v, long long k_stride, long long v_stride,
+                          const int* slots, void* k_cache, void* v_cache, int tokens, int kv_heads, int head_dim,
+                          int page_size, cudaStream_t s) {
+  TIE_REQUIRE(kv_heads > 0 && head_dim > 0 && page_size > 0, "kv_append: bad geometry");
+  TIE_DISPATCH(dtype, launch_kv_append<float>(k, v, k_stride, v_stride, slots, k_cache, v_cache, tokens, kv_heads,
+                                              head_dim, page_size, s),
+               launch_kv_append<__nv_bfloat16>(k, v, k_stride, v_stride, slots, k_cache, v_cache, tokens, kv_heads,
+                                               head_dim, page_size, s));
+}
+
+TIE_API int tie_qk_norm_rope_append(int dtype, void* qkv, long long stride, const float* qw, const float* kw,
+                                    float q_eps, float k_eps, const float* inv_freq, int rot, const int* pos,
+                                    const int* slots, void* k_cache, void* v_cache, int tokens, int q_heads,
+                                    int kv_heads, int head_dim, int page_size, int write_kv, cudaStream_t s) {
+  TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_size > 0, "qk_norm_rope_append: bad geometry");
+  TIE_REQUIRE(head_dim <= 1024, "qk_norm_rope_append: head_dim %d above 1024", head_dim);
+  TIE_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= head_dim,
+              "qk_norm_rope_append: rotary dim %d must be even and at most head_dim %d", rot, head_dim);
+  TIE_DISPATCH(dtype,
+               launch_qk_norm_rope_append<float>(qkv, stride, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots, k_cache,
+                                                 v_cache, tokens, q_heads, kv_heads, head_dim, page_size, write_kv, s),
+               launch_qk_norm_rope_append<__nv_bfloat16>(qkv, stride, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots,
+                                                         k_cache, v_cache, tokens, q_heads, kv_heads, head_dim,
+                                                         page_size, write_kv, s));
+}

@@ -1,0 +1,254 @@
+"""The engine: admits requests, asks the scheduler for a batch, runs the step function, samples, finishes.
+
+The Python entry point follows the reference's Engine (src/engine/engine.h:18-86,
+src/engine/engine.cpp:11-235): add_request, step, generate, cancel, release, stats,
+set_token_callback, with the same meanings, errors and finish reasons.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Sequence as Seq
+
+import torch
+
+from ..cache.manager import CacheManager, blocks_for
+from ..cache.state_slots import StateSlots
+from ..errors import CapacityError, InvalidArgument
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .scheduler import ScheduledBatch, Scheduler, SchedulerConfig, ServingConfig
+from .sequence import FinishReason, SeqState, Sequence
+from .step import StepEntry, StepRunner
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    seqs_scheduled: int = 0    # summed over steps; divided by steps it is the mean batch size
+    prefill_tokens: int = 0    # prompt tokens, and tokens recomputed after preemption
+    decode_tokens: int = 0
+    step_seconds: float = 0.0  # time in the step function and sampling
+    preemptions: int = 0
+
+
+class Engine:
+    def __init__(self, model, cache: CacheManager, scheduler: Scheduler, serving: ServingConfig,
+                 stop_tokens: Seq[int] = (), states: StateSlots | None = None, runner: StepRunner | None = None):
+        serving.validate()
+        self.model, self.cache, self.scheduler, self.serving = model, cache, scheduler, serving
+        self.stop_tokens = set(int(t) for t in stop_tokens)
+        self.states = states
+        self.runner = runner or StepRunner(model, cache, serving.max_tokens_per_step, serving.max_seqs,
+                                           serving.max_seqs, states=states)
+        if self.runner.max_tokens < serving.max_tokens_per_step or self.runner.max_seqs < serving.max_seqs or \
+                self.runner.max_logit_rows < serving.max_seqs:
+            raise InvalidArgument(f"serving config ({serving.max_tokens_per_step} tokens, {serving.max_seqs} sequences "
+                                  f"per step) exceeds the step function's limits ({self.runner.max_tokens} tokens, "
+                                  f"{self.runner.max_seqs} sequences, {self.runner.max_logit_rows} logit rows)")
+        self.sampler = Sampler(serving.max_seqs)
+        self.sequences: dict[int, Sequence] = {}
+        self._next_id = 0
+        self._stepping = False
+        self._on_token: Callable[[int, int], None] | None = None
+        self._stats = EngineStats()
+        self.max_blocks_per_seq = blocks_for(model.spec.max_positions, cache.page_size)
+
+    # -- requests
+    def add_request(self, prompt: Seq[int], params: SamplingParams | None = None) -> int:
+        """Queues a request and returns its id. Only a prompt that can never run is rejected
+        (CapacityError) before any compute; otherwise max_tokens is clamped to what the
+        context and the pool can hold (src/engine/engine.cpp:26-63)."""
+        params = SamplingParams(**vars(params)) if params is not None else SamplingParams()
+        params.validate()
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise InvalidArgument("prompt is empty")
+        vocab = self.model.spec.vocab_size
+        for t in prompt:
+            if not 0 <= t < vocab:
+                raise InvalidArgument(f"prompt token {t} outside vocabulary of {vocab}")
+        page = self.cache.page_size
+        context_cap = self.model.spec.max_positions
+        pool_cap = self.cache.num_pages * page
+        n = len(prompt)
+        if n >= context_cap:
+            raise CapacityError(f"prompt of {n} tokens leaves no room to generate in the model context of {context_cap}")
+        if n >= pool_cap:
+            raise CapacityError(f"prompt of {n} tokens plus one generated token needs {blocks_for(n + 1, page)} KV pages "
+                                f"but the cache holds {self.cache.num_pages}; raise --kv-mem")
+        params.max_tokens = min(params.max_tokens, min(context_cap, pool_cap) - n)
+        seq = Sequence(id=self._next_id, tokens=prompt, prompt_len=n, params=params, cache=self.cache.new_request())
+        self._next_id += 1
+        self.scheduler.add(seq)
+        self.sequences[seq.id] = seq
+        return seq.id
+
+    def sequence(self, seq_id: int) -> Sequence:
+        try:
+            return self.sequences[seq_id]
+        except KeyError:
+            raise InvalidArgument(f"no sequence with id {seq_id}") from None
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def set_token_callback(self, callback: Callable[[int, int], None] | None) -> None:
+        self._on_token = callback
+
+    # -- one step
+    def _check_batch(self, batch: ScheduledBatch) -> None:
+        """A scheduler bug must fail loudly before any compute (src/engine/engine.cpp:65-92)."""
+        if len(batch.seqs) > self.serving.max_seqs:
+            raise InvalidArgument(f"scheduler gave {len(batch.seqs)} sequences; a step allows at most {self.serving.max_seqs}")
+        total, seen = 0, set()
+        for seq, n in batch.seqs:
+            if n <= 0 or n > seq.num_pending:
+                raise InvalidArgument(f"scheduler gave sequence {seq.id} {n} tokens; it has {seq.num_pending} pending")
+            if seq.id in seen:
+                raise InvalidArgument(f"scheduler gave sequence {seq.id} twice in one step")
+            seen.add(seq.id)
+            end = seq.num_computed + n
+            for t in seq.cache.tables:
+                if len(t) < blocks_for(end, self.cache.page_size):
+                    raise InvalidArgument(f"sequence {seq.id} has {len(t)} KV pages reserved; {end} tokens need "
+                                          f"{blocks_for(end, self.cache.page_size)}")
+            total += n
+        if total > self.serving.max_tokens_per_step:
+            raise InvalidArgument(f"scheduler gave {total} tokens; a step allows at most {self.serving.max_tokens_per_step}")
+
+    def step(self) -> None:
+        if self._stepping:
+            raise InvalidArgument("step() called during a step (e.g. from a token callback)")
+        batch = self.scheduler.schedule()
+        if batch.empty():
+            return
+        self._stepping = True
+        try:
+            self._run(batch)
+        finally:
+            self._stepping = False
+
+    def _run(self, batch: ScheduledBatch) -> None:
+        sampled: list[Sequence] = []
+        prefill = decode = 0
+        try:
+            self._check_batch(batch)
+            entries = []
+            for seq, n in batch.seqs:
+                begin, end = seq.num_computed, seq.num_computed + n
+                samples = end == len(seq.tokens)   # its whole pending input is in the cache after this step
+                entries.append(StepEntry(seq.cache, seq.tokens[begin:end], begin, (n - 1,) if samples else ()))
+                if samples:
+                    sampled.append(seq)
+                if seq.state == SeqState.DECODING and n == 1:
+                    decode += n
+                else:
+                    prefill += n
+            t0 = time.perf_counter()
+            logits = self.runner.run(entries)
+            if sampled:
+                tokens = self.sampler.sample(logits, [s.params for s in sampled], [s.num_generated for s in sampled])
+            else:
+                tokens = []
+            self._stats.step_seconds += time.perf_counter() - t0
+            self._stats.steps += 1
+            self._stats.seqs_scheduled += len(batch.seqs)
+            self._stats.prefill_tokens += prefill
+            self._stats.decode_tokens += decode
+        except BaseException:
+            # The step did not run: give back what the scheduler reserved and let it be scheduled again.
+            # State of fixed size may be half-updated, so requests that keep some start over.
+            for seq, _ in batch.seqs:
+                if seq.state == SeqState.FINISHED:
+                    continue
+                if self.states is not None and self.states.bytes_per_slot > 0:
+                    self.cache.reset(seq.cache)
+                    seq.num_computed = 0
+                else:
+                    self.cache.truncate(seq.cache, seq.num_computed)
+            self.scheduler.abandon(batch)
+            raise
+
+        for seq, n in batch.seqs:
+            seq.num_computed += n
+            self.cache.advance_window(seq.cache, seq.num_computed)
+        self.scheduler.complete(batch)
+
+        for i, seq in enumerate(sampled):
+            if seq.state == SeqState.FINISHED:
+                continue  # cancelled by an earlier token callback of this step
+            token = tokens[i]
+            try:
+                seq.tokens.append(token)
+                seq.state = SeqState.DECODING
+                if self._on_token is not None:
+                    self._on_token(seq.id, token)
+            except BaseException:
+                # The sequences after it count this step as computed but will never get their token.
+                for later in sampled[i:]:
+                    if later.state != SeqState.FINISHED:
+                        self._finish(later, FinishReason.ERROR)
+                raise
+            if seq.state == SeqState.FINISHED:
+                continue  # its own callback cancelled it
+            if token in self.stop_tokens:
+                self._finish(seq, FinishReason.STOP)
+            elif seq.num_generated >= seq.params.max_tokens:
+                self._finish(seq, FinishReason.LENGTH)
+
+    def _finish(self, seq: Sequence, reason: FinishReason) -> None:
+        seq.state = SeqState.FINISHED
+        seq.finish_reason = reason
+        self.cache.release(seq.cache)
+        self.scheduler.finish(seq)
+
+    def cancel(self, seq_id: int) -> None:
+        """Finishes a waiting, running or preempted request as CANCELLED; safe from a token callback."""
+        seq = self.sequence(seq_id)
+        if seq.state != SeqState.FINISHED:
+            self._finish(seq, FinishReason.CANCELLED)
+
+    def release(self, seq_id: int) -> None:
+        """Forgets a finished request; not allowed during step()."""
+        if self._stepping:
+            raise InvalidArgument(f"cannot release sequence {seq_id} during a step")
+        if self.sequence(seq_id).state != SeqState.FINISHED:
+            raise InvalidArgument(f"sequence {seq_id} is still running")
+        del self.sequences[seq_id]
+
+    def stats(self) -> EngineStats:
+        s = EngineStats(**vars(self._stats))
+        s.preemptions = self.scheduler.num_preemptions
+        return s
+
+    def generate(self, prompt: Seq[int], params: SamplingParams | None = None) -> list[int]:
+        """Runs one request to completion and returns its generated tokens, a final stop token included."""
+        seq_id = self.add_request(prompt, params)
+        try:
+            while self.sequence(seq_id).state != SeqState.FINISHED:
+                self.step()
+        except BaseException:
+            seq = self.sequences.get(seq_id)
+            if seq is not None:
+                if seq.state != SeqState.FINISHED:
+                    self._finish(seq, FinishReason.ERROR)
+                del self.sequences[seq_id]
+            raise
+        seq = self.sequence(seq_id)
+        out = seq.tokens[seq.prompt_len:]
+        self.release(seq_id)
+        return out
+
+    def generate_batch(self, prompts: Seq[Seq[int]], params: SamplingParams | Seq[SamplingParams] | None = None) -> list[list[int]]:
+        """Runs several requests together through the scheduler; returns their generated tokens in order."""
+        plist = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        ids = [self.add_request(p, q) for p, q in zip(prompts, plist)]
+        while any(self.sequence(i).state != SeqState.FINISHED for i in ids):
+            self.step()
+        outs = []
+        for i in ids:
+            seq = self.sequence(i)
+            outs.append(seq.tokens[seq.prompt_len:])
+            self.release(i)
+        return outs

@@ -1,0 +1,226 @@
+"""Python faces of the CUDA kernels: shape and dtype checks, then one launch on the current stream.
+
+Tensors are torch CUDA tensors used as typed device memory; nothing here computes with torch.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..errors import InvalidArgument
+from .library import call, check_device, library
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise InvalidArgument(f"dtype {t.dtype} is not one of float32, bfloat16") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise InvalidArgument(msg)
+
+
+def _dev(*ts) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise InvalidArgument("kernel arguments must be CUDA tensors: the engine has no CPU path")
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = float(table[ids[t]]); out is the float32 residual stream [T, D]."""
+    _dev(table, ids, out)
+    T, D = out.shape
+    _need(table.dim() == 2 and table.shape[1] == D and table.is_contiguous(), "embed: table must be [V, D] contiguous")
+    _need(ids.dtype == torch.int32 and ids.numel() == T and ids.is_contiguous(), "embed: ids must be int32 [T]")
+    _need(out.dtype == torch.float32 and out.is_contiguous(), "embed: output must be float32 contiguous")
+    call("tie_embed", dtype_code(table), table.data_ptr(), ids.data_ptr(), out.data_ptr(), T, D, table.shape[0], _stream())
+
+
+def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor, rows=None) -> None:
+    """x += delta (when given; float32, in place), out = rmsnorm(x) * weight in out's dtype.
+    With `rows` (int32 [R]), out[i] comes from row rows[i] and x is left as it is."""
+    _dev(x, delta, weight, out, rows)
+    D = x.shape[-1]
+    n = out.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "add_rmsnorm: x must be float32 contiguous")
+    _need(weight.dtype == torch.float32 and weight.numel() == D, "add_rmsnorm: weight must be float32 [D]")
+    _need(out.shape[-1] == D and out.is_contiguous(), "add_rmsnorm: out must be [n, D] contiguous")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.shape == x.shape and delta.is_contiguous(),
+              "add_rmsnorm: delta must match x's shape and out's dtype")
+    if rows is None:
+        _need(n == x.shape[0], "add_rmsnorm: out must have x's rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() == n, "add_rmsnorm: rows must be int32 [n]")
+    call("tie_add_rmsnorm", dtype_code(out), x.data_ptr(), _ptr(delta), _ptr(rows), weight.data_ptr(), float(eps),
+         out.data_ptr(), n, D, _stream())
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """RMSNorm over the last axis of a 2-D view whose rows may be strided (last axis contiguous)."""
+    _dev(x, weight, out)
+    _need(x.dim() == 2 and out.shape == x.shape and x.dtype == out.dtype, "rmsnorm_rows: x and out must be 2-D alike")
+    _need(x.stride(1) == 1 and out.stride(1) == 1, "rmsnorm_rows: last axis must be contiguous")
+    _need(weight.dtype == torch.float32 and weight.numel() == x.shape[1], "rmsnorm_rows: weight must be float32 [size]")
+    call("tie_rmsnorm_rows", dtype_code(x), x.data_ptr(), x.stride(0), weight.data_ptr(), float(eps), out.data_ptr(),
+         out.stride(0), x.shape[1], x.shape[0], _stream())
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _dev(gate_up, out)
+    T, I = out.shape
+    _need(gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous() and
+          gate_up.dtype == out.dtype, "silu_mul: gate_up must be [T, 2I] and out [T, I], same dtype, contiguous")
+    call("tie_silu_mul", dtype_code(out), gate_up.data_ptr(), out.data_ptr(), T, I, _stream())
+
+
+def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, heads: int, head_dim: int) -> None:
+    """Rotate-half RoPE in place over the first 2*len(inv_freq) dims of each head of x [T, >= heads*head_dim]."""
+    _dev(x, positions, inv_freq)
+    _need(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= heads * head_dim, "rope: x must be [T, heads*head_dim]")
+    _need(positions.dtype == torch.int32 and positions.numel() == x.shape[0], "rope: positions must be int32 [T]")
+    _need(inv_freq.dtype == torch.float32, "rope: inv_freq must be float32")
+    call("tie_rope", dtype_code(x), x.data_ptr(), x.stride(0), positions.data_ptr(), inv_freq.data_ptr(), x.shape[0],
+         heads, head_dim, 2 * inv_freq.numel(), _stream())
+
+
+def _check_planes(k_cache, v_cache, kv_heads, head_dim):
+    _need(k_cache.dim() == 4 and k_cache.shape == v_cache.shape and k_cache.is_contiguous() and v_cache.is_contiguous(),
+          "cache planes must be [pages, kv_heads, page_size, head_dim] contiguous")
+    _need(k_cache.shape[1] == kv_heads and k_cache.shape[3] == head_dim, "cache planes do not match the heads")
+    _need(k_cache.numel() // head_dim < 2 ** 31, "cache plane too large for 32-bit row indices")
+
+
+def kv_append(k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    """k, v [T, kv_heads*head_dim] (rows may be strided) into the planes at slots[t]; slot < 0 writes nothing."""
+    _dev(k, v, slots, k_cache, v_cache)
+    kv_heads, page_size, head_dim = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    _check_planes(k_cache, v_cache, kv_heads, head_dim)
+    _need(k.shape == v.shape and k.shape[1] == kv_heads * head_dim and k.stride(1) == 1 and v.stride(1) == 1,
+          "kv_append: k and v must be [T, kv_heads*head_dim]")
+    _need(k.dtype == k_cache.dtype and v.dtype == k_cache.dtype, "kv_append: dtype differs from the cache's")
+    _need(slots.dtype == torch.int32 and slots.numel() == k.shape[0], "kv_append: slots must be int32 [T]")
+    call("tie_kv_append", dtype_code(k), k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0), slots.data_ptr(),
+         k_cache.data_ptr(), v_cache.data_ptr(), k.shape[0], kv_heads, head_dim, page_size, _stream())
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, q_weight, k_weight, q_eps: float, k_eps: float, inv_freq,
+                        positions: torch.Tensor, slots, k_cache, v_cache, q_heads: int, kv_heads: int,
+                        head_dim: int, write_kv: bool = True) -> None:
+    """Per-head RMSNorm of q and k (weights may be None), RoPE (inv_freq may be None), q back in
+    place, k and v into the cache planes. qkv is [T, (q_heads + 2 kv_heads) * head_dim]; with
+    write_kv False it may hold q only and the planes are not touched."""
+    _dev(qkv, q_weight, k_weight, inv_freq, positions, slots, k_cache, v_cache)
+    T = qkv.shape[0]
+    width = (q_heads + (2 * kv_heads if write_kv else 0)) * head_dim
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= width, "qk_norm_rope_append: qkv too narrow")
+    _need(positions.dtype == torch.int32 and positions.numel() == T, "qk_norm_rope_append: positions must be int32 [T]")
+    for w in (q_weight, k_weight):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == head_dim),
+              "qk_norm_rope_append: norm weights must be float32 [head_dim]")
+    rot = 0
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32, "qk_norm_rope_append: inv_freq must be float32")
+        rot = 2 * inv_freq.numel()
+    page_size = 1
+    if write_kv:
+        _check_planes(k_cache, v_cache, kv_heads, head_dim)
+        _need(k_cache.dtype == qkv.dtype, "qk_norm_rope_append: dtype differs from the cache's")
+        _need(slots.dtype == torch.int32 and slots.numel() == T, "qk_norm_rope_append: slots must be int32 [T]")
+        page_size = k_cache.shape[2]
+    call("tie_qk_norm_rope_append", dtype_code(qkv), qkv.data_ptr(), qkv.stride(0), _ptr(q_weight), _ptr(k_weight),
+         float(q_eps), float(k_eps), _ptr(inv_freq), rot, positions.data_ptr(), _ptr(slots) if write_kv else 0,
+         _ptr(k_cache) if write_kv else 0, _ptr(v_cache) if write_kv else 0, T, q_heads, kv_heads, head_dim, page_size,
+         1 if write_kv else 0, _stream())
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] . w[N, K]^T on the CUDA cores with float accumulation (any sizes)."""
+    _dev(a, w, out)
+    _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "gemm: operands must be 2-D")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm: last axes must be contiguous")
+    _need(a.dtype == w.dtype, "gemm: a and w must have one dtype")
+    call("tie_gemm_simt", dtype_code(a), dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K,
+         a.stride(0), w.stride(0), out.stride(0), _stream())
+
+
+def _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim):
+    _check_planes(k_cache, v_cache, kv_heads, head_dim)
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= q_heads * head_dim, "attention: q too narrow")
+    _need(out.shape == (q.shape[0], q_heads * head_dim) and out.is_contiguous(), "attention: out must be [T, Hq*Dh]")
+    _need(q.dtype == k_cache.dtype and out.dtype == q.dtype, "attention: q, cache and out must have one dtype")
+    S = context_lens.numel()
+    _need(query_start.dtype == torch.int32 and query_start.numel() == S + 1, "attention: query_start must be int32 [S+1]")
+    _need(context_lens.dtype == torch.int32, "attention: context_lens must be int32 [S]")
+    _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.shape[0] == S and
+          block_tables.is_contiguous(), "attention: block_tables must be int32 [S, max_blocks]")
+    return S
+
+
+def attention_rows(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_heads, kv_heads,
+                   head_dim, scale: float, window: int = 0) -> None:
+    """Causal attention of every row of the step over the paged cache (CUDA cores)."""
+    _dev(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables)
+    S = _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    _need(seq_of_row.dtype == torch.int32 and seq_of_row.numel() == q.shape[0], "attention: seq_of_row must be int32 [T]")
+    call("tie_attention_rows", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+         out.data_ptr(), seq_of_row.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(),
+         block_tables.shape[1], q.shape[0], S, q_heads, kv_heads, head_dim, k_cache.shape[2], int(window), float(scale),
+         _stream())
+
+
+def attention_split_scratch_floats(n_list: int, q_heads: int, head_dim: int, max_splits: int) -> int:
+    return n_list * q_heads * max_splits * (head_dim + 2)
+
+
+def attention_split(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim,
+                    scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch,
+                    window: int = 0) -> None:
+    """Attention of sequences that bring one token each, their keys cut into splits of `split_keys`."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch)
+    S = _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
+    _need(scratch.dtype == torch.float32 and
+          scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, head_dim, max_splits),
+          "attention: scratch too small")
+    call("tie_attention_split", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+         out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+         S, q_heads, kv_heads, head_dim, k_cache.shape[2], int(window), float(scale), seq_list.data_ptr(), n_list,
+         split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None) -> None:
+    """out[r] = first maximum of row r (inv_temperature None or 0), or a draw from softmax(logits * inv_temperature)
+    with the Philox uniform of (seeds[r], counters[r])."""
+    _dev(logits, out, inv_temperature, seeds, counters)
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be float32 rows")
+    _need(out.dtype == torch.int32 and out.numel() >= R, "sample: out must be int32 [R]")
+    if inv_temperature is not None:
+        _need(inv_temperature.dtype == torch.float32 and seeds.dtype == torch.int64 and counters.dtype == torch.int64,
+              "sample: inv_temperature float32, seeds and counters int64")
+    call("tie_sample", logits.data_ptr(), logits.stride(0), R, V, _ptr(inv_temperature), _ptr(seeds), _ptr(counters),
+         out.data_ptr(), _stream())
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """The engine's matrix product: picks the kernel for the dtype and the sizes."""
+    from . import gemm_select
+    gemm_select.gemm(a, w, out)

@@ -1,0 +1,136 @@
+"""Grouped-query attention over the paged cache.
+
+    q, k, v = h Wq^T, h Wk^T, h Wv^T          one product with the three weights stacked
+    q, k    = norm over each head (optional), then the position encoding
+    k, v    -> cache pages at this step's slots
+    out     = softmax(scale q k^T, causal, optional window) v, then Wo
+
+Formulas: src/model/qwen3.cpp:218-230 and src/backend/cpu/cpu_backend.cpp:261-319. Every
+size and constant is a parameter: heads, kv heads, head size, scale, window, eps of the
+head norms, which position encoding.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..errors import InvalidArgument
+from ..weights.loader import TensorNeed
+from .base import CacheNeed, Mixer, build_part, register_part, to_compute
+
+SPLIT_KEYS = 256       # keys per split for sequences that bring one token
+MAX_SPLITS = 64
+
+
+class GQAttention(Mixer):
+    def __init__(self, spec, dtype, prefix: str = ""):
+        p = spec.params
+        self.prefix = prefix + p.get("prefix", "")
+        self.hidden = int(p["hidden_size"])
+        self.heads = int(p["num_heads"])
+        self.kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.window = int(p.get("window") or 0)
+        # 1/sqrt(head_dim) in float32, as the reference computes it (src/model/qwen3.cpp:195)
+        self.scale = float(p["scale"]) if p.get("scale") is not None else float(
+            np.float32(1.0) / np.sqrt(np.float32(self.head_dim)))
+        if self.heads % self.kv_heads:
+            raise InvalidArgument(f"{self.heads} heads are not a multiple of {self.kv_heads} kv heads")
+        self.dtype = dtype
+        self.q_norm = build_part("norm", p["q_norm"], dtype, prefix=self.prefix) if p.get("q_norm") else None
+        self.k_norm = build_part("norm", p["k_norm"], dtype, prefix=self.prefix) if p.get("k_norm") else None
+        self.position = build_part("position", p["position"], dtype, prefix=self.prefix)
+        self.q_dim, self.kv_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        self.w_qkv = self.w_o = None
+
+    # -- weights
+    def needs(self):
+        n = {self.prefix + "q_proj.weight": TensorNeed((self.q_dim, self.hidden)),
+             self.prefix + "k_proj.weight": TensorNeed((self.kv_dim, self.hidden)),
+             self.prefix + "v_proj.weight": TensorNeed((self.kv_dim, self.hidden)),
+             self.prefix + "o_proj.weight": TensorNeed((self.hidden, self.q_dim))}
+        for part in (self.q_norm, self.k_norm, self.position):
+            if part is not None:
+                n.update(part.needs())
+        return n
+
+    def bind(self, get):
+        w = [to_compute(get(self.prefix + f"{n}_proj.weight"), self.dtype) for n in "qkv"]
+        self.w_qkv = torch.cat(w, dim=0).contiguous()
+        self.w_q = self.w_qkv[:self.q_dim]
+        self.w_k = self.w_qkv[self.q_dim:self.q_dim + self.kv_dim]
+        self.w_v = self.w_qkv[self.q_dim + self.kv_dim:]
+        self.w_o = to_compute(get(self.prefix + "o_proj.weight"), self.dtype).contiguous()
+        for part in (self.q_norm, self.k_norm, self.position):
+            if part is not None:
+                part.bind(get)
+
+    def cache_need(self):
+        return CacheNeed("window" if self.window > 0 else "full", self.kv_heads, self.head_dim, self.window)
+
+    # -- one step
+    def forward(self, h, ctx, cache, state):
+        T = h.shape[0]
+        Hq, Hkv, Dh = self.heads, self.kv_heads, self.head_dim
+        g = ctx.groups[cache.group]
+        table = self.position.fused_table()
+        fused = table is not None or type(self.position).__name__ == "NoPositionEncoding"
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        q_eps = self.q_norm.eps if self.q_norm is not None else 0.0
+        k_eps = self.k_norm.eps if self.k_norm is not None else 0.0
+        fused = fused and all(n is None or hasattr(n, "weight") for n in (self.q_norm, self.k_norm))
+        if fused:
+            width = self.q_dim + (2 * self.kv_dim if cache.writes else 0)
+            qkv = ctx.ws.rows("attn.qkv", T, self.q_dim + 2 * self.kv_dim, self.dtype)[:, :width]
+            ops.gemm(h, self.w_qkv if cache.writes else self.w_q, qkv)
+            ops.qk_norm_rope_append(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, g.slots, cache.k, cache.v, Hq, Hkv,
+                                    Dh, write_kv=cache.writes)
+            q = qkv[:, :self.q_dim]
+        else:
+            # Any other norm or position encoding: separate products and the parts' own kernels.
+            q = ctx.ws.rows("attn.q", T, self.q_dim, self.dtype)
+            ops.gemm(h, self.w_q, q)
+            if self.q_norm is not None:
+                self.q_norm.rows(q.view(T * Hq, Dh), q.view(T * Hq, Dh))
+            self.position.apply(q, ctx.positions, Hq, Dh)
+            if cache.writes:
+                k = ctx.ws.rows("attn.k", T, self.kv_dim, self.dtype)
+                v = ctx.ws.rows("attn.v", T, self.kv_dim, self.dtype)
+                ops.gemm(h, self.w_k, k)
+                ops.gemm(h, self.w_v, v)
+                if self.k_norm is not None:
+                    self.k_norm.rows(k.view(T * Hkv, Dh), k.view(T * Hkv, Dh))
+                self.position.apply(k, ctx.positions, Hkv, Dh)
+                ops.kv_append(k, v, g.slots, cache.k, cache.v)
+        attn = ctx.ws.rows("attn.out", T, self.q_dim, self.dtype)
+        self.attend(q, attn, ctx, g, cache)
+        out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
+        ops.gemm(attn, self.w_o, out)
+        return out
+
+    def attend(self, q, attn, ctx, g, cache):
+        """Rows of sequences that bring several tokens come first in a step, then one row per
+        sequence that brings one token (ctx.multi_rows, ctx.single_seqs)."""
+        Hq, Hkv, Dh = self.heads, self.kv_heads, self.head_dim
+        if ctx.multi_rows > 0:
+            n = ctx.multi_rows
+            ops.attention_rows(q[:n], cache.k, cache.v, attn[:n], ctx.seq_of_row[:n], ctx.query_start, ctx.context_lens,
+                               g.block_tables, Hq, Hkv, Dh, self.scale, self.window)
+        if ctx.single_count > 0:
+            longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
+            split_keys = SPLIT_KEYS
+            while math.ceil(longest / split_keys) > MAX_SPLITS:
+                split_keys *= 2
+            max_splits = max(1, math.ceil(longest / split_keys))
+            scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
+                                  torch.float32)
+            ops.attention_split(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv,
+                                Dh, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch,
+                                self.window)
+
+
+register_part("mixer", "gqa_attention", GQAttention, replace=True)

@@ -1,0 +1,46 @@
+"""Token embedding and the output table (src/model/qwen3.cpp:75,92-100,213,255-259): x[t] = table[id],
+logits = last . W^T in float32, W = the embedding table when the model ties them."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorNeed
+from .base import Part, to_compute
+
+
+class TokenEmbedding(Part):
+    def __init__(self, spec, dtype):
+        self.name = spec["name"]
+        self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
+        self.dtype = dtype
+        self.table = None
+
+    def needs(self):
+        return {self.name: TensorNeed((self.vocab, self.hidden))}
+
+    def bind(self, get):
+        self.table = to_compute(get(self.name), self.dtype).contiguous()
+
+    def forward(self, tokens, x):
+        ops.embed(self.table, tokens, x)
+
+
+class LMHead(Part):
+    def __init__(self, spec, dtype, embedding: TokenEmbedding):
+        self.name = spec["name"]
+        self.tied = bool(spec["tied"])
+        self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
+        self.dtype = dtype
+        self.embedding = embedding
+        self.weight = None
+
+    def needs(self):
+        # A tied checkpoint may still carry a duplicate output table; it is accepted and ignored.
+        return {self.name: TensorNeed((self.vocab, self.hidden), optional=self.tied)}
+
+    def bind(self, get):
+        self.weight = self.embedding.table if self.tied else to_compute(get(self.name), self.dtype).contiguous()
+
+    def forward(self, last, logits):
+        ops.gemm(last, self.weight, logits)

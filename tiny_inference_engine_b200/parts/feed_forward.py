@@ -1,0 +1,44 @@
+"""SwiGLU feed-forward: down(silu(gate(h)) * up(h)), silu(g) = g / (1 + exp(-g))
+(src/model/qwen3.cpp:235-238, src/backend/cpu/cpu_backend.cpp:195-207). Gate and up are
+stacked into one weight so that one product reads h once."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorNeed
+from .base import FeedForward, register_part, to_compute
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, spec, dtype, prefix: str = ""):
+        p = spec.params
+        self.prefix = prefix + p.get("prefix", "")
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.dtype = dtype
+        self.w_gate_up = self.w_down = None
+
+    def needs(self):
+        return {self.prefix + "gate_proj.weight": TensorNeed((self.inter, self.hidden)),
+                self.prefix + "up_proj.weight": TensorNeed((self.inter, self.hidden)),
+                self.prefix + "down_proj.weight": TensorNeed((self.hidden, self.inter))}
+
+    def bind(self, get):
+        gate = to_compute(get(self.prefix + "gate_proj.weight"), self.dtype)
+        up = to_compute(get(self.prefix + "up_proj.weight"), self.dtype)
+        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_down = to_compute(get(self.prefix + "down_proj.weight"), self.dtype).contiguous()
+
+    def forward(self, h, ctx):
+        T = h.shape[0]
+        gu = ctx.ws.rows("ffn.gate_up", T, 2 * self.inter, self.dtype)
+        ops.gemm(h, self.w_gate_up, gu)
+        act = ctx.ws.rows("ffn.act", T, self.inter, self.dtype)
+        ops.silu_mul(gu, act)
+        out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
+        ops.gemm(act, self.w_down, out)
+        return out
+
+
+register_part("feed_forward", "swiglu", SwiGLU, replace=True)

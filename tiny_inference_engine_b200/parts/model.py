@@ -1,0 +1,99 @@
+"""A model built from a `ModelSpec`: embedding, the layers in their run order, final norm, output table."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..config.spec import ModelSpec
+from ..errors import InvalidArgument
+from ..weights.loader import TensorNeed, TensorSource, bind_check
+from .base import BLOCKS, CacheNeed, StateNeed, build_part
+from .embedding import LMHead, TokenEmbedding
+from ..errors import UnsupportedError
+
+
+@dataclass
+class LayerCache:
+    """What a run entry sees of the cache: its planes, its group, and whether it writes them."""
+    k: torch.Tensor | None
+    v: torch.Tensor | None
+    group: int
+    writes: bool
+
+
+def _build_block(layer_spec, dtype):
+    kind = layer_spec.block.kind
+    if kind not in BLOCKS:
+        raise UnsupportedError(f"no block of kind '{kind}' (registered: {', '.join(sorted(BLOCKS))})")
+    return BLOCKS[kind](layer_spec, dtype)
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise InvalidArgument(f"compute dtype must be float32 or bfloat16, got {dtype}")
+        spec.validate()
+        self.spec, self.dtype = spec, dtype
+        self.embedding = TokenEmbedding(spec.embedding, dtype)
+        self.layers = [_build_block(l, dtype) for l in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, dtype)
+        self.head = LMHead(spec.head, dtype, self.embedding)
+        self.loaded = False
+
+    # -- what the model needs of a checkpoint, of the cache and of per-request state
+    def needs(self) -> dict[str, TensorNeed]:
+        n = dict(self.embedding.needs())
+        for l in self.layers:
+            n.update(l.needs())
+        n.update(self.final_norm.needs())
+        n.update(self.head.needs())
+        return n
+
+    def cache_needs(self) -> list[CacheNeed | None]:
+        """Per run entry: the cache it owns (None if it has none or reads another entry's)."""
+        return [self.layers[e.layer].mixer.cache_need() if e.cache_of is None else None for e in self.spec.run_order]
+
+    def state_needs(self) -> list[StateNeed | None]:
+        return [self.layers[e.layer].mixer.state_need() for e in self.spec.run_order]
+
+    def load(self, source: TensorSource, device="cuda") -> "Model":
+        needs = self.needs()
+        bind_check(needs, source, what=self.spec.architecture)
+
+        def get(name: str) -> torch.Tensor:
+            return source.get(name).to(device, non_blocking=False)
+
+        self.embedding.bind(get)
+        for l in self.layers:
+            l.bind(get)
+        self.final_norm.bind(get)
+        self.head.bind(get)
+        self.loaded = True
+        return self
+
+    # -- one step over the rows of ctx; returns float32 logits [R, V] or None when no row is wanted
+    def forward(self, ctx, cache, states) -> torch.Tensor | None:
+        T, D = ctx.T, self.spec.hidden_size
+        x = ctx.ws.rows("model.x", T, D, torch.float32)
+        self.embedding.forward(ctx.tokens, x)
+        pending = None
+        for i, entry in enumerate(self.spec.run_order):
+            owner = i if entry.cache_of is None else entry.cache_of
+            view = cache.layer_cache(owner, writes=entry.cache_of is None) if cache is not None else None
+            state = states.tensor(i) if states is not None else None
+            pending = self.layers[entry.layer].forward(x, pending, ctx, view, state)
+            if ctx.layer_hook is not None:
+                ctx.layer_hook(i, x, pending)
+        if ctx.R == 0:
+            return None
+        last = ctx.logit_ws.rows("model.last", ctx.R, D, self.dtype)
+        self.final_norm.add_norm(x, pending, last, rows=ctx.logit_rows)
+        logits = ctx.logit_ws.rows("model.logits", ctx.R, self.spec.vocab_size, torch.float32)
+        self.head.forward(last, logits)
+        return logits
+
+
+def expected_tensors(spec: ModelSpec) -> dict[str, TensorNeed]:
+    """Names, shapes and roles of the checkpoint tensors of a model description (no device needed)."""
+    return Model(spec, torch.bfloat16).needs()
