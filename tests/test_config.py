@@ -1,0 +1,118 @@
+"""Configuration parsing, the architecture registry and the model description (CPU)."""
+import json
+
+import pytest
+
+import plain_qwen3 as plain
+from tiny_inference_engine_b200.config import (Architecture, ModelSpec, PartSpec, RunEntry, load_config,
+                                               parse_qwen3_config, qwen3_spec, register_architecture,
+                                               resolve_architecture)
+from tiny_inference_engine_b200.errors import InvalidArgument, LoadError, UnsupportedError
+
+
+def test_defaults_of_absent_keys():
+    c = parse_qwen3_config(plain.TINY_C)          # no num_key_value_heads, head_dim, rope_theta, tie_word_embeddings
+    assert c.num_key_value_heads == c.num_attention_heads == 3
+    assert c.head_dim == 144 // 3 and c.rope_theta == 10000.0 and c.tie_word_embeddings is False
+    assert c.q_dim == 144 and c.kv_dim == 144
+
+
+def test_every_size_comes_from_the_file():
+    c = parse_qwen3_config(plain.TINY_B)
+    assert (c.vocab_size, c.hidden_size, c.intermediate_size, c.num_hidden_layers) == (503, 96, 200, 3)
+    assert (c.num_attention_heads, c.num_key_value_heads, c.head_dim) == (8, 1, 32)
+    assert c.q_dim == 256 != c.hidden_size
+    assert c.rms_norm_eps == 1e-5 and c.rope_theta == 1e6 and c.max_position_embeddings == 1024
+
+
+@pytest.mark.parametrize("key", ["vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                 "num_attention_heads", "max_position_embeddings", "rms_norm_eps"])
+def test_required_keys(key):
+    cfg = dict(plain.TINY_A)
+    del cfg[key]
+    with pytest.raises(LoadError, match=f"config.json has no '{key}'"):
+        parse_qwen3_config(cfg)
+
+
+@pytest.mark.parametrize("patch,err,text", [
+    ({"model_type": "llama"}, UnsupportedError, "llama"),
+    ({"use_sliding_window": True}, UnsupportedError, "use_sliding_window"),
+    ({"rope_scaling": {"type": "yarn"}}, UnsupportedError, "rope_scaling"),
+    ({"attention_bias": True}, UnsupportedError, "attention_bias"),
+    ({"num_key_value_heads": 3}, LoadError, "multiple"),
+    ({"head_dim": 15}, LoadError, "even"),
+    ({"vocab_size": 0}, LoadError, "vocab_size"),
+    ({"hidden_size": -4}, LoadError, "hidden_size"),
+    ({"rms_norm_eps": 0.0}, LoadError, "rms_norm_eps"),
+    ({"rope_theta": -1.0}, LoadError, "rope_theta"),
+    ({"num_hidden_layers": 2.5}, LoadError, "num_hidden_layers"),
+])
+def test_rejections(patch, err, text):
+    with pytest.raises(err, match=text):
+        parse_qwen3_config({**plain.TINY_A, **patch})
+
+
+def test_null_rope_scaling_and_false_flags_are_fine():
+    parse_qwen3_config({**plain.TINY_A, "rope_scaling": None, "use_sliding_window": False, "attention_bias": False,
+                        "sliding_window": 4096, "max_window_layers": 2, "torch_dtype": "bfloat16"})
+
+
+def test_registry_by_architecture_then_model_type():
+    assert resolve_architecture({"architectures": ["Qwen3ForCausalLM"]}).name == "Qwen3ForCausalLM"
+    assert resolve_architecture({"model_type": "qwen3"}).name == "Qwen3ForCausalLM"
+    with pytest.raises(UnsupportedError, match="LlamaForCausalLM"):
+        resolve_architecture({"architectures": ["LlamaForCausalLM"], "model_type": "qwen3"})
+    with pytest.raises(UnsupportedError, match="gpt2"):
+        resolve_architecture({"model_type": "gpt2"})
+    with pytest.raises(LoadError, match="model_type"):
+        resolve_architecture({})
+
+
+def test_load_config_from_a_folder(tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps(plain.TINY_A))
+    arch, cfg, spec = load_config(tmp_path)
+    assert arch.name == "Qwen3ForCausalLM" and cfg.hidden_size == 64 and len(spec.layers) == 2
+    (tmp_path / "config.json").write_text("{not json")
+    with pytest.raises(LoadError, match="invalid JSON"):
+        load_config(tmp_path)
+    with pytest.raises(LoadError, match="cannot open"):
+        load_config(tmp_path / "nowhere")
+
+
+def test_spec_carries_the_constants_layer_by_layer():
+    spec = qwen3_spec(parse_qwen3_config(plain.TINY_B))
+    assert [e.layer for e in spec.run_order] == [0, 1, 2] and all(e.cache_of is None for e in spec.run_order)
+    l1 = spec.layers[1]
+    assert l1.mixer.kind == "gqa_attention" and l1.ffn.kind == "swiglu" and l1.block.kind == "prenorm"
+    assert l1.mixer["num_kv_heads"] == 1 and l1.mixer["head_dim"] == 32 and l1.mixer["window"] == 0
+    assert l1.mixer["position"].kind == "rope" and l1.mixer["position"]["theta"] == 1e6
+    assert l1.mixer["q_norm"]["eps"] == 1e-5 and l1.mixer_norm["name"] == "model.layers.1.input_layernorm.weight"
+    assert spec.head["tied"] is False and spec.final_norm["size"] == 96
+
+
+def test_run_order_is_checked():
+    spec = qwen3_spec(parse_qwen3_config(plain.TINY_A))
+
+    def with_order(order):
+        return ModelSpec(**{**spec.__dict__, "run_order": tuple(order)})
+
+    with_order([RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(1, cache_of=1)]).validate()   # twice, and a shared cache
+    with pytest.raises(InvalidArgument, match="names layer 5"):
+        with_order([RunEntry(5)]).validate()
+    with pytest.raises(InvalidArgument, match="not earlier"):
+        with_order([RunEntry(0, cache_of=0)]).validate()
+    with pytest.raises(InvalidArgument, match="none of its own"):
+        with_order([RunEntry(0), RunEntry(1, cache_of=0), RunEntry(0, cache_of=1)]).validate()
+
+
+def test_another_architecture_can_be_registered():
+    def spec_of(cfg):
+        base = qwen3_spec(parse_qwen3_config(cfg))
+        return ModelSpec(**{**base.__dict__, "architecture": "ToyForCausalLM"})
+
+    register_architecture(Architecture("ToyForCausalLM", parse_config=lambda j: j, build_spec=spec_of,
+                                       model_types=("toy",)), replace=True)
+    arch = resolve_architecture({"architectures": ["ToyForCausalLM"]})
+    assert arch.build_spec(arch.parse_config(plain.TINY_A)).architecture == "ToyForCausalLM"
+    with pytest.raises(ValueError, match="already registered"):
+        register_architecture(Architecture("ToyForCausalLM", parse_config=dict, build_spec=spec_of))

@@ -1,0 +1,150 @@
+"""Generation through the Python entry point and the scheduler, against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import assert_logits_close
+
+pytestmark = pytest.mark.gpu
+
+
+def engine_for(model_dir, dtype="float32", **kw):
+    from tiny_inference_engine_b200 import load_engine
+    return load_engine(model_dir, dtype=dtype, **kw)
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+def test_greedy_and_sampled_generation_match_the_plain_implementation(tiny_models, name):
+    from tiny_inference_engine_b200 import SamplingParams
+    cfg, page, w, d = tiny_models[name]
+    eng = engine_for(d, num_pages=64, page_size=page)
+    rng = np.random.default_rng(2)
+    for n_prompt in (1, 9, 40):
+        prompt = rng.integers(0, cfg["vocab_size"], n_prompt).tolist()
+        assert eng.generate(prompt, SamplingParams(max_tokens=8)) == plain.generate(w, cfg, prompt, 8)
+        assert eng.generate(prompt, SamplingParams(max_tokens=6, temperature=0.8, seed=7)) == \
+            plain.generate(w, cfg, prompt, 6, temperature=0.8, seed=7)
+        assert eng.generate(prompt, SamplingParams(max_tokens=6, temperature=1.3, seed=3, top_k=10, top_p=0.9)) == \
+            plain.generate(w, cfg, prompt, 6, temperature=1.3, seed=3, top_k=10, top_p=0.9)
+    assert eng.cache.num_free() == 64 and not eng.has_work()
+
+
+def test_bfloat16_generation_follows_the_plain_one_where_the_choice_is_clear(tiny_models):
+    from tiny_inference_engine_b200 import SamplingParams
+    cfg, page, w, d = tiny_models["tiny_b"]
+    eng = engine_for(d, dtype="bfloat16", num_pages=64, page_size=page)
+    prompt = np.random.default_rng(3).integers(0, cfg["vocab_size"], 20).tolist()
+    got = eng.generate(prompt, SamplingParams(max_tokens=12))
+    wq = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()}
+    tokens = list(prompt)
+    for t in got:                                   # teacher-forced: each step's choice is checked on its own
+        logits = plain.forward(wq, cfg, tokens)[-1]
+        top = np.sort(logits)[-2:]
+        if top[1] - top[0] > 0.04 * np.abs(logits).max():
+            assert t == int(np.argmax(logits))
+        tokens.append(t)
+
+
+@pytest.mark.parametrize("pages", [256, 7])
+@pytest.mark.parametrize("sampled", [False, True])
+def test_batched_requests_generate_what_each_generates_alone(tiny_models, pages, sampled):
+    """Eight mixed requests, 16 tokens per step, with plenty of pages and with so few that requests
+    are preempted and recomputed; greedy and seeded temperature sampling (the reference's
+    tests/engine/test_engine_batching.cpp:25-75)."""
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig
+    cfg, page, w, d = tiny_models["tiny_b"]
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (1, 30, 7, 12, 3, 22, 9, 16)]
+    params = [SamplingParams(max_tokens=4 + i, temperature=0.8 if sampled else 0.0, seed=100 + i) for i in range(8)]
+    alone = engine_for(d, num_pages=64, page_size=page)
+    want = [alone.generate(p, q) for p, q in zip(prompts, params)]
+    eng = engine_for(d, num_pages=pages, page_size=page, serving=ServingConfig(16, 8), policy="fcfs")
+    got = eng.generate_batch(prompts, params)
+    assert got == want
+    st = eng.stats()
+    assert (st.preemptions > 0) == (pages == 7)
+    assert eng.cache.num_free() == pages and st.steps > 0 and st.decode_tokens > 0
+
+
+def test_a_failed_step_is_rolled_back_and_the_requests_still_finish(tiny_models):
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig
+    cfg, page, w, d = tiny_models["tiny_a"]
+    prompts = [[5, 6, 7, 8, 9, 10, 11, 12, 13], [3] * 20, [200, 100]]
+    alone = engine_for(d, num_pages=64, page_size=page)
+    want = [alone.generate(p, SamplingParams(max_tokens=6)) for p in prompts]
+    eng = engine_for(d, num_pages=64, page_size=page, serving=ServingConfig(8, 4), policy="fcfs")
+    calls = {"n": 0}
+
+    def fail_third(ctx):
+        calls["n"] += 1
+        if calls["n"] == 3:
+            raise RuntimeError("injected")
+
+    eng.runner.fail_hook = fail_third
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6)) for p in prompts]
+    failures = 0
+    while eng.has_work():
+        try:
+            eng.step()
+        except RuntimeError:
+            failures += 1
+    assert failures == 1
+    assert [eng.sequence(i).tokens[eng.sequence(i).prompt_len:] for i in ids] == want
+    assert eng.cache.num_free() == 64
+
+
+def test_capacity_errors_cancel_and_callbacks(tiny_models):
+    from tiny_inference_engine_b200 import CapacityError, InvalidArgument, SamplingParams
+    from tiny_inference_engine_b200.engine import FinishReason, SeqState
+    cfg, page, w, d = tiny_models["tiny_a"]
+    eng = engine_for(d, num_pages=4, page_size=page, stop_tokens=[])
+    with pytest.raises(CapacityError, match="raise --kv-mem"):
+        eng.add_request([1] * 64)
+    with pytest.raises(CapacityError, match="context"):
+        eng.add_request([1] * 512)
+    with pytest.raises(InvalidArgument, match="outside vocabulary"):
+        eng.add_request([1, 256])
+    with pytest.raises(InvalidArgument, match="empty"):
+        eng.add_request([])
+    a = eng.add_request([1, 2, 3], SamplingParams(max_tokens=500))
+    assert eng.sequence(a).params.max_tokens == 4 * page - 3      # clamped to the pool
+    seen = []
+    eng.set_token_callback(lambda i, t: (seen.append((i, t)), eng.cancel(i) if len(seen) == 3 else None))
+    while eng.has_work():
+        eng.step()
+    assert len(seen) == 3 and eng.sequence(a).finish_reason == FinishReason.CANCELLED
+    assert eng.cache.num_free() == 4
+    eng.release(a)
+    with pytest.raises(InvalidArgument, match="no sequence"):
+        eng.sequence(a)
+    # a stop token ends a request and is part of its output
+    eng.set_token_callback(None)
+    first = eng.generate([9, 9, 9], SamplingParams(max_tokens=5))
+    eng2 = engine_for(d, num_pages=4, page_size=page, stop_tokens=[first[1]])
+    assert eng2.generate([9, 9, 9], SamplingParams(max_tokens=5)) == first[:first.index(first[1]) + 1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_the_first_tokens(tiny_models, dtype):
+    """One token from position 0 on, then 600 more one by one (the split attention kernel sees one,
+    two and three splits); all logits against the plain implementation."""
+    from tiny_inference_engine_b200 import StepEntry, StepRunner, load_model, make_cache
+    cfg, page, w, d = tiny_models["tiny_c"]
+    toks = np.random.default_rng(6).integers(0, cfg["vocab_size"], 601).tolist()
+    wq = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()} if dtype == "bfloat16" else w
+    want = plain.forward(wq, cfg, toks)
+    model = load_model(d, dtype)
+    cache, states = make_cache(model, page_size=page, num_pages=24, max_requests=2)
+    runner = StepRunner(model, cache, 64, 2, 8, states=states)
+    req = cache.new_request()
+    got = []
+    for t, tok in enumerate(toks):
+        assert cache.reserve(req, t + 1)
+        got.append(runner.run([StepEntry(req, [tok], t, [0])]))
+        if t % 50 == 0:
+            got[-1] = got[-1].clone()
+        got[-1] = got[-1].float().cpu().numpy()
+    got = np.concatenate(got)
+    assert_logits_close(got[:3], want[:3], dtype, "the first tokens")
+    assert_logits_close(got, want, dtype, "600 decoded tokens")

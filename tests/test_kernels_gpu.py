@@ -1,0 +1,310 @@
+"""Each CUDA kernel alone against the plain implementation's function for the same op, at sizes the
+tiny models do not use: widths and vocabularies that are no power of two, head sizes in steps
+of 16, odd numbers of heads and groups, scattered pages."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 1.2e-2}   # one kernel: a few float32 roundings, or one bfloat16 rounding of the output
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(dtype)
+
+
+def host(t):
+    return t.float().cpu().numpy()
+
+
+def as_stored(a, dtype):
+    """What the kernel sees: the values after rounding to the storage dtype."""
+    return plain.round_bf16(a.astype(np.float32)) if dtype == "bfloat16" else a.astype(np.float32)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tiny_inference_engine_b200 import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(ops, dtype):
+    rng = np.random.default_rng(0)
+    table = as_stored(rng.standard_normal((311, 72)), dtype)
+    ids = rng.integers(0, 311, 37)
+    out = torch.empty(37, 72, device="cuda")
+    ops.embed(dev(table, DT[dtype]), dev(ids, torch.int32), out)
+    assert np.array_equal(host(out), plain.embed(table, ids).astype(np.float32))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dim", [72, 1000, 5120])
+def test_add_rmsnorm(ops, dtype, dim):
+    rng = np.random.default_rng(dim)
+    x = rng.standard_normal((9, dim)).astype(np.float32) * 3
+    delta = as_stored(rng.standard_normal((9, dim)), dtype)
+    w = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    xd, out = dev(x), torch.empty(9, dim, device="cuda", dtype=DT[dtype])
+    ops.add_rmsnorm(xd, dev(delta, DT[dtype]), dev(w), 1e-5, out)
+    want_x = x.astype(np.float64) + delta
+    assert np.abs(host(xd) - want_x).max() < 1e-6 * np.abs(want_x).max()        # the residual sum is float32
+    assert rel_err(host(out), plain.rms_norm(want_x, w, 1e-5)) < TOL[dtype]
+    # without a delta x is untouched; with rows only those rows come out and x is not written
+    x2 = dev(x)
+    ops.add_rmsnorm(x2, None, dev(w), 1e-5, out)
+    assert np.array_equal(host(x2), x) and rel_err(host(out), plain.rms_norm(x, w, 1e-5)) < TOL[dtype]
+    rows = np.array([7, 0, 7, 3])
+    out4 = torch.empty(4, dim, device="cuda", dtype=DT[dtype])
+    x3 = dev(x)
+    ops.add_rmsnorm(x3, dev(delta, DT[dtype]), dev(w), 1e-5, out4, rows=dev(rows, torch.int32))
+    assert np.array_equal(host(x3), x) and rel_err(host(out4), plain.rms_norm(want_x[rows], w, 1e-5)) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rmsnorm_rows_on_a_strided_view(ops, dtype):
+    rng = np.random.default_rng(1)
+    x = as_stored(rng.standard_normal((20, 200)), dtype)
+    w = (1 + 0.1 * rng.standard_normal(48)).astype(np.float32)
+    xd = dev(x, DT[dtype])
+    view = xd[:, 16:64]
+    ops.rmsnorm_rows(view, dev(w), 3e-6, view)
+    got = host(xd)
+    assert rel_err(got[:, 16:64], plain.rms_norm(x[:, 16:64], w, 3e-6)) < TOL[dtype]
+    assert np.array_equal(got[:, :16], x[:, :16]) and np.array_equal(got[:, 64:], x[:, 64:])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul(ops, dtype):
+    rng = np.random.default_rng(2)
+    gu = as_stored(rng.standard_normal((11, 2 * 203)) * 4, dtype)
+    out = torch.empty(11, 203, device="cuda", dtype=DT[dtype])
+    ops.silu_mul(dev(gu, DT[dtype]), out)
+    assert rel_err(host(out), plain.swiglu(gu[:, :203], gu[:, 203:])) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,head_dim,theta", [(3, 48, 1e4), (5, 16, 1e6), (2, 128, 5e5)])
+def test_rope(ops, dtype, heads, head_dim, theta):
+    rng = np.random.default_rng(3)
+    x = as_stored(rng.standard_normal((13, heads * head_dim)), dtype)
+    pos = np.array([0, 1, 2, 3, 17, 100, 1000, 4095, 40000, 5, 6, 7, 8])
+    xd = dev(x, DT[dtype])
+    ops.rope(xd, dev(pos, torch.int32), dev(plain.rope_inv_freq(theta, head_dim)), heads, head_dim)
+    assert rel_err(host(xd), plain.rope_neox(x, pos, heads, head_dim, theta)) < TOL[dtype]
+    assert np.array_equal(host(xd)[0], x[0])     # position 0 is the identity
+
+
+def paged_cache(rng, dtype, n_tokens_per_seq, kv_heads, head_dim, page, n_pages):
+    """Keys and values of several sequences scattered over shuffled pages."""
+    pages = rng.permutation(n_pages)
+    kc = np.zeros((n_pages, kv_heads, page, head_dim), dtype=np.float32)
+    vc = np.zeros_like(kc)
+    tables, ks, vs, used = [], [], [], 0
+    for n in n_tokens_per_seq:
+        nb = -(-n // page)
+        tab = pages[used:used + nb]
+        used += nb
+        k = as_stored(rng.standard_normal((n, kv_heads, head_dim)), dtype)
+        v = as_stored(rng.standard_normal((n, kv_heads, head_dim)), dtype)
+        for j in range(n):
+            kc[tab[j // page], :, j % page] = k[j]
+            vc[tab[j // page], :, j % page] = v[j]
+        tables.append(tab), ks.append(k), vs.append(v)
+    mb = max(len(t) for t in tables) + 3
+    bt = np.zeros((len(tables), mb), dtype=np.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = t
+    return kc, vc, bt, ks, vs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_kv_append_and_fused_norm_rope_append(ops, dtype):
+    rng = np.random.default_rng(4)
+    Hq, Hkv, Dh, page, T = 6, 3, 48, 8, 21
+    qkv = as_stored(rng.standard_normal((T, (Hq + 2 * Hkv) * Dh)), dtype)
+    qw, kw = (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32), (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32)
+    pos = rng.integers(0, 3000, T)
+    slots = rng.permutation(12 * page)[:T]
+    slots[5] = -1                                  # a padding row writes nothing
+    kc = torch.zeros(12, Hkv, page, Dh, device="cuda", dtype=DT[dtype])
+    vc = torch.zeros_like(kc)
+    inv = plain.rope_inv_freq(1e6, Dh)
+    qd = dev(qkv, DT[dtype])
+    ops.qk_norm_rope_append(qd, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), dev(slots, torch.int32),
+                            kc, vc, Hq, Hkv, Dh)
+    q, k, v = qkv[:, :Hq * Dh], qkv[:, Hq * Dh:(Hq + Hkv) * Dh], qkv[:, (Hq + Hkv) * Dh:]
+    want_q = plain.rope_neox(plain.rms_norm(q.reshape(T * Hq, Dh), qw, 1e-6).reshape(T, -1), pos, Hq, Dh, 1e6)
+    want_k = plain.rope_neox(plain.rms_norm(k.reshape(T * Hkv, Dh), kw, 1e-5).reshape(T, -1), pos, Hkv, Dh, 1e6)
+    assert rel_err(host(qd)[:, :Hq * Dh], want_q) < TOL[dtype]
+    got_k, got_v = host(kc), host(vc)
+    for t in range(T):
+        if slots[t] < 0:
+            continue
+        p, o = slots[t] // page, slots[t] % page
+        assert rel_err(got_k[p, :, o].reshape(1, -1), want_k[t].reshape(1, -1)) < TOL[dtype]
+        assert np.array_equal(got_v[p, :, o].reshape(-1), v[t])
+    written = {(s // page, s % page) for s in slots if s >= 0}
+    for p in range(12):
+        for o in range(page):
+            if (p, o) not in written:
+                assert not got_k[p, :, o].any() and not got_v[p, :, o].any()
+    # the unfused kernel writes the same places
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    ops.kv_append(dev(want_k, DT[dtype]), dev(v, DT[dtype]), dev(slots, torch.int32), kc2, vc2)
+    assert np.array_equal(host(vc2), got_v)
+    # without norm weights and without rotation the fused kernel only copies
+    q2 = dev(qkv, DT[dtype])
+    ops.qk_norm_rope_append(q2, None, None, 0, 0, None, dev(pos, torch.int32), dev(slots, torch.int32), kc2, vc2, Hq, Hkv, Dh)
+    assert np.array_equal(host(q2), qkv)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 503, 96), (3, 72, 200), (8, 1000, 520), (13, 311, 144), (70, 130, 75), (200, 96, 1000)])
+def test_gemm_simt(ops, dtype, M, N, K):
+    rng = np.random.default_rng(M * N)
+    a, w = as_stored(rng.standard_normal((M, K)), dtype), as_stored(rng.standard_normal((N, K)), dtype)
+    out = torch.empty(M, N, device="cuda", dtype=DT[dtype])
+    ops.gemm_simt(dev(a, DT[dtype]), dev(w, DT[dtype]), out)
+    assert rel_err(host(out), plain.linear(a, w)) < TOL[dtype]
+    if dtype == "bfloat16":                         # logits come out in float32
+        out32 = torch.empty(M, N, device="cuda")
+        ops.gemm_simt(dev(a, DT[dtype]), dev(w, DT[dtype]), out32)
+        assert rel_err(host(out32), plain.linear(a, w)) < 2e-5
+
+
+def dense_reference(q, k, v, Hq, Hkv, Dh, n_new, window=0):
+    """The last n_new rows of causal attention over all of k, v."""
+    n = k.shape[0]
+    qfull = np.zeros((n, Hq * Dh))
+    qfull[n - n_new:] = q
+    return plain.causal_attention(qfull, k.reshape(n, -1), v.reshape(n, -1), Hq, Hkv, Dh, window)[n - n_new:]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(4, 2, 16, 16, 0), (8, 1, 32, 8, 0), (3, 3, 48, 32, 0), (6, 2, 128, 16, 0),
+                                                  (5, 5, 80, 4, 0), (4, 1, 64, 16, 37)])
+def test_paged_attention_rows_and_split(ops, dtype, Hq, Hkv, Dh, page, window):
+    """Mixed batch: two sequences bring portions over a cached prefix, three bring one token;
+    pages are scattered. Rows kernel for the first, split kernel for the others."""
+    rng = np.random.default_rng(Hq * Dh)
+    ctx = [45, 300, 1, 33, 700]          # tokens in the cache after the step
+    new = [45, 17, 1, 1, 1]              # of which this step brings
+    kc, vc, bt, ks, vs = paged_cache(rng, dtype, ctx, Hkv, Dh, page, 120 * 16 // page)
+    T = sum(new)
+    q = as_stored(rng.standard_normal((T, Hq * Dh)), dtype)
+    qs = np.concatenate([[0], np.cumsum(new)])
+    scale = 1.0 / np.sqrt(Dh)
+    want = np.concatenate([dense_reference(q[qs[i]:qs[i + 1]], ks[i], vs[i], Hq, Hkv, Dh, new[i], window) for i in range(5)])
+    seq_of_row = np.repeat(np.arange(5), new)
+    out = torch.zeros(T, Hq * Dh, device="cuda", dtype=DT[dtype])
+    args = (dev(kc, DT[dtype]), dev(vc, DT[dtype]), out)
+    meta = (dev(qs, torch.int32), dev(np.array(ctx), torch.int32), dev(bt, torch.int32))
+    ops.attention_rows(dev(q, DT[dtype]), *args, dev(seq_of_row, torch.int32), *meta, Hq, Hkv, Dh, scale, window)
+    assert rel_err(host(out), want) < TOL[dtype]
+    # the same single-token sequences through the split kernel, with splits of 64 keys
+    out2 = torch.zeros_like(out)
+    n_multi = new[0] + new[1]
+    scratch = torch.empty(ops.attention_split_scratch_floats(3, Hq, Dh, 11), device="cuda")
+    ops.attention_split(dev(q, DT[dtype]), *args[:2], out2, *meta, Hq, Hkv, Dh, scale, dev(np.array([2, 3, 4]), torch.int32),
+                        3, 64, 11, scratch, window)
+    assert rel_err(host(out2)[n_multi:], want[n_multi:]) < TOL[dtype]
+    assert not host(out2)[:n_multi].any()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 15, 16, 31, 32, 255, 256, 257, 511, 512, 1022, 1023])
+def test_one_far_key_among_a_thousand_is_found(ops, dtype, far):
+    """The query matches exactly one key, at a page's edge, a chunk's edge, a split's edge, the
+    first key, the last: the output must be that key's value row. Random data would hide a key
+    that is skipped or read from the wrong page: it would move the result by a thousandth."""
+    rng = np.random.default_rng(far)
+    Hq, Hkv, Dh, page, n = 4, 2, 32, 16, 1024
+    kc, vc, bt, ks, vs = paged_cache(rng, dtype, [n], Hkv, Dh, page, 80)
+    q = np.zeros((1, Hq * Dh), dtype=np.float32)
+    for h in range(Hq):
+        q[0, h * Dh:(h + 1) * Dh] = 8.0 * ks[0][far, h // 2] * np.sqrt(Dh)   # score ~ 8 * |k|^2 ~ 256 above the rest
+    q = as_stored(q, dtype)
+    meta = (dev(np.array([0, 1]), torch.int32), dev(np.array([n]), torch.int32), dev(bt, torch.int32))
+    one_hot = np.concatenate([vs[0][far, h // 2] for h in range(Hq)])[None]
+    want = dense_reference(q, ks[0], vs[0], Hq, Hkv, Dh, 1)
+    assert np.abs(want - one_hot).max() < 1e-3      # the far key really holds all the weight
+    for split in (False, True):
+        out = torch.zeros(1, Hq * Dh, device="cuda", dtype=DT[dtype])
+        if split:
+            scratch = torch.empty(ops.attention_split_scratch_floats(1, Hq, Dh, 4), device="cuda")
+            ops.attention_split(dev(q, DT[dtype]), dev(kc, DT[dtype]), dev(vc, DT[dtype]), out, *meta, Hq, Hkv, Dh,
+                                1 / np.sqrt(Dh), dev(np.array([0]), torch.int32), 1, 256, 4, scratch)
+        else:
+            ops.attention_rows(dev(q, DT[dtype]), dev(kc, DT[dtype]), dev(vc, DT[dtype]), out,
+                               dev(np.array([0]), torch.int32), *meta, Hq, Hkv, Dh, 1 / np.sqrt(Dh))
+        assert np.abs(host(out) - want).max() < 1e-2, f"split={split}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_edge(ops, dtype):
+    """With a window of 40 the key at position pos-39 counts and the one at pos-40 does not."""
+    rng = np.random.default_rng(9)
+    Hq, Hkv, Dh, page, n, window = 2, 1, 32, 8, 200, 40
+    kc, vc, bt, ks, vs = paged_cache(rng, dtype, [n], Hkv, Dh, page, 40)
+    meta = (dev(np.array([0, 1]), torch.int32), dev(np.array([n]), torch.int32), dev(bt, torch.int32))
+    for target, inside in ((n - 1 - 39, True), (n - 1 - 40, False)):
+        q = as_stored(np.tile(8.0 * ks[0][target, 0] * np.sqrt(Dh), Hq)[None], dtype)
+        out = torch.zeros(1, Hq * Dh, device="cuda", dtype=DT[dtype])
+        ops.attention_rows(dev(q, DT[dtype]), dev(kc, DT[dtype]), dev(vc, DT[dtype]), out, dev(np.array([0]), torch.int32),
+                           *meta, Hq, Hkv, Dh, 1 / np.sqrt(Dh), window)
+        hit = np.abs(host(out)[0, :Dh] - vs[0][target, 0]).max() < 1e-2
+        assert hit == inside
+
+
+def test_sampling_kernel_greedy_and_temperature(ops):
+    rng = np.random.default_rng(5)
+    R, V = 7, 1531
+    z = (rng.standard_normal((R, V)) * 2).astype(np.float32)
+    z[2, 100] = z[2, 900] = z[2].max() + 1          # a tie goes to the lowest id
+    z[3, 5] = np.inf
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(dev(z), out)
+    assert out.tolist() == [plain.sample(z[r]) for r in range(R)] and out[2].item() == 100
+    temps = np.array([0.8, 0.0, 1.0, 0.7, 1e-45, 2.5, 0.3], dtype=np.float32)
+    with np.errstate(divide="ignore", over="ignore"):
+        inv = np.where(temps > 0, np.float32(1) / temps, 0).astype(np.float32)
+    inv[~np.isfinite(inv)] = 0
+    seeds = np.array([7, 1, 2 ** 63 + 11, 4, 5, 6, 2 ** 40], dtype=np.uint64)
+    for counter in (0, 1, 2, 1000, 2 ** 33):
+        ctr = np.full(R, counter, dtype=np.int64)
+        ops.sample(dev(z), out, dev(inv), torch.from_numpy(seeds.view(np.int64)).cuda(), dev(ctr, torch.int64))
+        want = [plain.sample(z[r], float(temps[r]), u=plain.uniform_for(int(seeds[r]), counter)) for r in range(R)]
+        assert out.tolist() == want
+
+
+def test_sampling_kernel_frequencies(ops):
+    z = np.tile(np.array([[0.0, 1.0, 2.0, -30.0, 0.5]], dtype=np.float32), (2000, 1))
+    out = torch.empty(2000, dtype=torch.int32, device="cuda")
+    inv = np.full(2000, 1 / 0.8, dtype=np.float32)
+    ops.sample(dev(z), out, dev(inv), dev(np.full(2000, 3), torch.int64), dev(np.arange(2000), torch.int64))
+    p = np.exp(z[0] / 0.8 - (z[0] / 0.8).max())
+    p /= p.sum()
+    assert np.abs(np.bincount(out.cpu().numpy(), minlength=5) / 2000 - p).max() < 0.03
+
+
+def test_refusals_are_clear(ops):
+    from tiny_inference_engine_b200.errors import InvalidArgument
+    q = torch.zeros(1, 2 * 20, device="cuda")
+    kc = torch.zeros(4, 1, 8, 20, device="cuda")
+    i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    with pytest.raises(InvalidArgument, match="head_dim 20 must be a multiple of 8"):
+        ops.attention_rows(q, kc, kc.clone(), torch.zeros_like(q), i32(0), i32(0, 1), i32(1), i32(0, 0).view(1, 2), 2, 1, 20, 1.0)
+    with pytest.raises(InvalidArgument, match="not a multiple"):
+        ops.attention_rows(torch.zeros(1, 48, device="cuda"), torch.zeros(4, 2, 8, 16, device="cuda"),
+                           torch.zeros(4, 2, 8, 16, device="cuda"), torch.zeros(1, 48, device="cuda"), i32(0), i32(0, 1),
+                           i32(1), i32(0, 0).view(1, 2), 3, 2, 16, 1.0)
+    with pytest.raises(InvalidArgument, match="CUDA tensors"):
+        ops.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
+    with pytest.raises(InvalidArgument, match="shapes"):
+        ops.gemm_simt(torch.zeros(2, 8, device="cuda"), torch.zeros(4, 9, device="cuda"), torch.zeros(2, 4, device="cuda"))

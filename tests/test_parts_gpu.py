@@ -1,0 +1,313 @@
+"""Each part of a layer alone against the plain implementation, and parts put together in other
+ways than Qwen3 does: a layer named twice, a layer that reads another layer's cache, a window,
+a toy mixer with state of its own that the framework has never seen."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import TOL, assert_logits_close, rel_err, sharp_weights
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(dtype)
+
+
+class DictSource:
+    """A TensorSource over numpy arrays."""
+
+    def __init__(self, tensors):
+        self.t = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in tensors.items()}
+
+    def shapes(self):
+        return {k: (tuple(v.shape), v.dtype) for k, v in self.t.items()}
+
+    def get(self, name):
+        return self.t[name]
+
+
+def build(spec, weights, dtype, page=8, pages=64, max_tokens=256, max_seqs=8):
+    from tiny_inference_engine_b200 import StepRunner, make_cache
+    from tiny_inference_engine_b200.parts import Model
+    model = Model(spec, DT[dtype]).load(DictSource(weights))
+    cache, states = make_cache(model, page_size=page, num_pages=pages, max_requests=max_seqs)
+    return model, cache, StepRunner(model, cache, max_tokens, max_seqs, max_tokens, states=states)
+
+
+def run_whole(runner, cache, tokens, cuts=None):
+    from tiny_inference_engine_b200 import StepEntry
+    req = cache.new_request()
+    out, pos = [], 0
+    for n in (cuts or [len(tokens)]):
+        assert cache.reserve(req, pos + n)
+        out.append(runner.run([StepEntry(req, tokens[pos:pos + n], pos, list(range(n)))]).float().cpu().numpy())
+        pos += n
+        cache.advance_window(req, pos)
+    cache.release(req)
+    return np.concatenate(out)
+
+
+def qwen_spec(cfg):
+    from tiny_inference_engine_b200.config import parse_qwen3_config, qwen3_spec
+    return qwen3_spec(parse_qwen3_config(cfg))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_alone(dtype):
+    """The mixer of layer 1 of tiny-B on random rows, whole and cut, against the plain attention block."""
+    from tiny_inference_engine_b200 import StepEntry
+    from tiny_inference_engine_b200.parts import build_part
+    cfg = plain.normalise_config(plain.TINY_B)
+    w = sharp_weights(cfg, 4)
+    if dtype == "bfloat16":
+        w = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()}
+    spec = qwen_spec(cfg)
+    model, cache, runner = build(spec, w, dtype)
+    mixer = model.layers[1].mixer
+    rng = np.random.default_rng(0)
+    T = 50
+    h = rng.standard_normal((T, cfg["hidden_size"])).astype(np.float32)
+    if dtype == "bfloat16":
+        h = plain.round_bf16(h)
+    want = plain.attention_block(h, w, "model.layers.1.", cfg, np.arange(T))
+    for cuts in ([T], [9, 2, 25, 1, 1, 12]):
+        req = cache.new_request()
+        got, pos = [], 0
+        for n in cuts:
+            assert cache.reserve(req, pos + n)
+            ctx, _ = runner.prepare([StepEntry(req, [0] * n, pos, [])])
+            out = mixer.forward(dev(h[pos:pos + n], DT[dtype]), ctx, cache.layer_cache(1, writes=True), None)
+            got.append(out.float().cpu().numpy())
+            pos += n
+        cache.release(req)
+        assert rel_err(np.concatenate(got), want) < TOL[dtype] * (1 if dtype == "float32" else 0.6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_norm_and_block_alone(dtype):
+    from tiny_inference_engine_b200 import StepEntry
+    cfg = plain.normalise_config(plain.TINY_C)
+    w = plain.random_weights(cfg, 2, std=0.2)
+    if dtype == "bfloat16":
+        w = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()}
+    model, cache, runner = build(qwen_spec(cfg), w, dtype)
+    rng = np.random.default_rng(1)
+    T, D = 23, cfg["hidden_size"]
+    h = rng.standard_normal((T, D)).astype(np.float32)
+    h = plain.round_bf16(h) if dtype == "bfloat16" else h
+    req = cache.new_request()
+    cache.reserve(req, T)
+    ctx, _ = runner.prepare([StepEntry(req, [0] * T, 0, [])])
+    block = model.layers[0]
+    got = block.ffn.forward(dev(h, DT[dtype]), ctx).float().cpu().numpy()
+    assert rel_err(got, plain.mlp_block(h, w, "model.layers.0.")) < TOL[dtype]
+    # the norm part: x += delta, h = norm(x)
+    x = rng.standard_normal((T, D)).astype(np.float32)
+    xd, out = dev(x), torch.empty(T, D, device="cuda", dtype=DT[dtype])
+    block.mixer_norm.add_norm(xd, dev(h, DT[dtype]), out)
+    want = plain.rms_norm(x.astype(np.float64) + h, w["model.layers.0.input_layernorm.weight"], cfg["rms_norm_eps"])
+    assert rel_err(out.float().cpu().numpy(), want) < TOL[dtype]
+    # the whole block: the residual stream after it is x + attn + mlp
+    xd = dev(x)
+    pending = block.forward(xd, None, ctx, cache.layer_cache(0, writes=True), None)
+    torch.cuda.synchronize()
+    got_x = xd.cpu().numpy().astype(np.float64) + pending.float().cpu().numpy()
+    want_x = plain.decoder_layer(x.astype(np.float64), w, 0, cfg, np.arange(T))
+    assert rel_err(got_x, want_x) < TOL[dtype]
+    cache.release(req)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_position_encoding_part_and_the_unfused_path(dtype):
+    """A position encoding the fused kernel does not know (no table) takes the separate kernels; same numbers."""
+    from tiny_inference_engine_b200.config import LayerSpec, ModelSpec, PartSpec
+    from tiny_inference_engine_b200.parts import RotaryEncoding, register_part
+
+    class OpaqueRope(RotaryEncoding):
+        def fused_table(self):
+            return None
+
+        def apply(self, x, positions, heads, head_dim):
+            from tiny_inference_engine_b200 import ops
+            ops.rope(x, positions, RotaryEncoding.fused_table(self), heads, head_dim)
+
+    register_part("position", "opaque_rope", OpaqueRope, replace=True)
+    cfg = plain.normalise_config(plain.TINY_A)
+    w = sharp_weights(cfg, 3)
+    base = qwen_spec(cfg)
+    layers = []
+    for l in base.layers:
+        params = dict(l.mixer.params)
+        params["position"] = PartSpec("opaque_rope", dict(params["position"].params))
+        layers.append(LayerSpec(l.prefix, l.block, PartSpec("gqa_attention", params), l.mixer_norm, l.ffn, l.ffn_norm))
+    spec = ModelSpec(**{**base.__dict__, "layers": tuple(layers)})
+    toks = np.random.default_rng(2).integers(0, cfg["vocab_size"], 70).tolist()
+    wq = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()} if dtype == "bfloat16" else w
+    want = plain.forward(wq, cfg, toks)
+    model, cache, runner = build(spec, w, dtype, page=16)
+    assert_logits_close(run_whole(runner, cache, toks, [33, 2, 35]), want, dtype, "unfused position encoding")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_run_order_names_a_layer_twice_and_shares_a_cache(dtype):
+    """Run order [0, 1, 0, 1*] where 1* reads the cache that the first run of layer 1 wrote. The
+    plain side recomputes it with whole sequences."""
+    from tiny_inference_engine_b200.config import ModelSpec, RunEntry
+    cfg = plain.normalise_config(plain.TINY_A)
+    w = sharp_weights(cfg, 5)
+    wq = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()} if dtype == "bfloat16" else w
+    base = qwen_spec(cfg)
+    spec = ModelSpec(**{**base.__dict__, "run_order": (RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(1, cache_of=1))})
+    toks = np.random.default_rng(3).integers(0, cfg["vocab_size"], 60).tolist()
+
+    # plain: layers 0, 1, 0 as usual; the fourth entry attends with its own q over layer 1's first-run k, v
+    T = len(toks)
+    pos = np.arange(T)
+    x = plain.embed(wq["model.embed_tokens.weight"], toks)
+    x = plain.decoder_layer(x, wq, 0, cfg, pos)
+    p = "model.layers.1."
+    h1 = plain.rms_norm(x, wq[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+    Hq, Hkv, Dh, eps, th = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"], cfg["rope_theta"]
+    k1 = plain.rope_neox(plain.rms_norm(plain.linear(h1, wq[p + "self_attn.k_proj.weight"]).reshape(T * Hkv, Dh),
+                                        wq[p + "self_attn.k_norm.weight"], eps).reshape(T, -1), pos, Hkv, Dh, th)
+    v1 = plain.linear(h1, wq[p + "self_attn.v_proj.weight"])
+    x = plain.decoder_layer(x, wq, 1, cfg, pos)
+    x = plain.decoder_layer(x, wq, 0, cfg, pos)
+    h = plain.rms_norm(x, wq[p + "input_layernorm.weight"], eps)
+    q = plain.rope_neox(plain.rms_norm(plain.linear(h, wq[p + "self_attn.q_proj.weight"]).reshape(T * Hq, Dh),
+                                       wq[p + "self_attn.q_norm.weight"], eps).reshape(T, -1), pos, Hq, Dh, th)
+    x = x + plain.linear(plain.causal_attention(q, k1, v1, Hq, Hkv, Dh), wq[p + "self_attn.o_proj.weight"])
+    x = x + plain.mlp_block(plain.rms_norm(x, wq[p + "post_attention_layernorm.weight"], eps), wq, p)
+    want = plain.linear(plain.rms_norm(x, wq["model.norm.weight"], eps), wq["model.embed_tokens.weight"])
+
+    model, cache, runner = build(spec, w, dtype, page=16)
+    assert len(cache.groups) == 1 and cache.groups[0].entries == (0, 1, 2)      # three planes, the fourth entry has none
+    assert_logits_close(run_whole(runner, cache, toks, [31, 1, 1, 27]), want, dtype, "run order with a shared cache")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_different_mixers_one_windowed(dtype):
+    """Layer 0 keeps all keys, layer 1 a window of 24: two cache groups, pages of the window group
+    come back while the request is still running, and the logits match the plain windowed attention."""
+    from tiny_inference_engine_b200.config import LayerSpec, ModelSpec, PartSpec
+    cfg = plain.normalise_config(plain.TINY_A)
+    w = sharp_weights(cfg, 6)
+    wq = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()} if dtype == "bfloat16" else w
+    base = qwen_spec(cfg)
+    l1 = base.layers[1]
+    windowed = LayerSpec(l1.prefix, l1.block, PartSpec("gqa_attention", {**l1.mixer.params, "window": 24}), l1.mixer_norm,
+                         l1.ffn, l1.ffn_norm)
+    spec = ModelSpec(**{**base.__dict__, "layers": (base.layers[0], windowed)})
+    toks = np.random.default_rng(4).integers(0, cfg["vocab_size"], 120).tolist()
+    T, pos = len(toks), np.arange(len(toks))
+    x = plain.embed(wq["model.embed_tokens.weight"], toks)
+    x = plain.decoder_layer(x, wq, 0, cfg, pos)
+    p = "model.layers.1."
+    x = x + plain.attention_block(plain.rms_norm(x, wq[p + "input_layernorm.weight"], cfg["rms_norm_eps"]), wq, p, cfg, pos,
+                                  window=24)
+    x = x + plain.mlp_block(plain.rms_norm(x, wq[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]), wq, p)
+    want = plain.linear(plain.rms_norm(x, wq["model.norm.weight"], cfg["rms_norm_eps"]), wq["model.embed_tokens.weight"])
+
+    model, cache, runner = build(spec, w, dtype, page=8, pages=16)
+    assert [g.kind for g in cache.groups] == ["full", "window"]
+    from tiny_inference_engine_b200 import StepEntry
+    req = cache.new_request()
+    got, at = [], 0
+    for n in [40, 3, 1, 1, 30, 2, 43]:
+        assert cache.reserve(req, at + n)
+        got.append(runner.run([StepEntry(req, toks[at:at + n], at, list(range(n)))]).float().cpu().numpy())
+        at += n
+        cache.advance_window(req, at)
+    assert cache.num_free(0) == 16 - 15 and cache.num_free(1) >= 16 - 4          # the window group holds at most 4 pages
+    cache.release(req)
+    assert_logits_close(np.concatenate(got), want, dtype, "windowed layer")
+
+
+def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
+    """A mixer the framework has never seen: a running mean of the rows of a request,
+    s_t = s_{t-1} + h_t, out_t = (s_t / (t+1)) W. Its state lives in the engine's state slots; it is
+    registered from here, built by the same Model and stepped by the same step function, cut
+    anywhere and beside other requests."""
+    from tiny_inference_engine_b200 import StepEntry
+    from tiny_inference_engine_b200.config import LayerSpec, ModelSpec, PartSpec
+    from tiny_inference_engine_b200.parts import Mixer, StateNeed, register_part
+    from tiny_inference_engine_b200.weights import TensorNeed
+
+    class RunningMean(Mixer):
+        def __init__(self, spec, dtype, prefix=""):
+            self.name, self.d, self.dtype = spec["name"], spec["hidden_size"], dtype
+
+        def needs(self):
+            return {self.name: TensorNeed((self.d, self.d))}
+
+        def bind(self, get):
+            self.w = get(self.name).float()
+
+        def state_need(self):
+            return StateNeed((self.d,), torch.float32)
+
+        def forward(self, h, ctx, cache, state):
+            out = torch.empty_like(h)
+            qs = ctx.host.query_start
+            for s in range(ctx.S):                 # a toy: plain torch, one request at a time
+                slot = int(ctx.host.state_slots[s])
+                rows = h[qs[s]:qs[s + 1]].float()
+                sums = state[slot] + torch.cumsum(rows, 0)
+                state[slot] = sums[-1]
+                counts = torch.arange(ctx.host.starts[s] + 1, ctx.host.starts[s] + 1 + rows.shape[0], device=h.device)
+                out[qs[s]:qs[s + 1]] = ((sums / counts[:, None]) @ self.w.T).to(h.dtype)
+            return out
+
+    register_part("mixer", "running_mean", RunningMean, replace=True)
+    cfg = plain.normalise_config(plain.TINY_A)
+    w = plain.random_weights(cfg, 7, std=0.1)
+    D = cfg["hidden_size"]
+    w["model.layers.1.toy.weight"] = (np.random.default_rng(0).standard_normal((D, D)) * 0.1).astype(np.float32)
+    for k in [k for k in w if k.startswith("model.layers.1.self_attn")]:
+        del w[k]
+    base = qwen_spec(cfg)
+    l1 = base.layers[1]
+    toy = LayerSpec(l1.prefix, l1.block, PartSpec("running_mean", {"name": "model.layers.1.toy.weight", "hidden_size": D}),
+                    l1.mixer_norm, l1.ffn, l1.ffn_norm)
+    spec = ModelSpec(**{**base.__dict__, "layers": (base.layers[0], toy)})
+
+    def plain_forward(toks):
+        T, pos = len(toks), np.arange(len(toks))
+        x = plain.embed(w["model.embed_tokens.weight"], toks)
+        x = plain.decoder_layer(x, w, 0, cfg, pos)
+        p = "model.layers.1."
+        h = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        x = x + (np.cumsum(h, 0) / (pos + 1)[:, None]) @ w[p + "toy.weight"].astype(np.float64).T
+        x = x + plain.mlp_block(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]), w, p)
+        return plain.linear(plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), w["model.embed_tokens.weight"])
+
+    model, cache, runner = build(spec, w, "float32", page=8, pages=32)
+    assert model.cache_needs()[1] is None and model.state_needs()[1].shape == (D,)
+    assert len(cache.groups) == 1 and cache.groups[0].entries == (0,)
+    rng = np.random.default_rng(8)
+    a, b = rng.integers(0, 256, 40).tolist(), rng.integers(0, 256, 25).tolist()
+    ra, rb = cache.new_request(), cache.new_request()
+    assert ra.state_slot != rb.state_slot
+    got_a, got_b, pa, pb = [], [], 0, 0
+    for na, nb in [(7, 0), (2, 11), (1, 1), (20, 13), (10, 0)]:
+        entries = []
+        if na:
+            cache.reserve(ra, pa + na)
+            entries.append(StepEntry(ra, a[pa:pa + na], pa, list(range(na))))
+        if nb:
+            cache.reserve(rb, pb + nb)
+            entries.append(StepEntry(rb, b[pb:pb + nb], pb, list(range(nb))))
+        out = runner.run(entries).float().cpu().numpy()
+        got_a.append(out[:na]), got_b.append(out[na:])
+        pa, pb = pa + na, pb + nb
+    assert_logits_close(np.concatenate(got_a), plain_forward(a), "float32", "toy mixer, request a")
+    assert_logits_close(np.concatenate(got_b), plain_forward(b), "float32", "toy mixer, request b")
+    # a slot handed out again starts from zero
+    cache.release(ra)
+    rc = cache.new_request()
+    cache.reserve(rc, 40)
+    out = runner.run([StepEntry(rc, a, 0, list(range(40)))]).float().cpu().numpy()
+    assert_logits_close(out, plain_forward(a), "float32", "toy mixer, slot used again")
