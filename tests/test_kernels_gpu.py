@@ -308,3 +308,51 @@ def test_refusals_are_clear(ops):
         ops.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
     with pytest.raises(InvalidArgument, match="shapes"):
         ops.gemm_simt(torch.zeros(2, 8, device="cuda"), torch.zeros(4, 9, device="cuda"), torch.zeros(2, 4, device="cuda"))
+
+
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("M,N,K", [(1, 503, 96), (3, 311, 144), (8, 1000, 520), (16, 72, 200), (33, 300, 64), (77, 130, 1000),
+                                   (128, 256, 512), (200, 96, 72), (300, 503, 96), (700, 311, 136)])
+def test_gemm_tensor_cores(ops, out_dtype, M, N, K):
+    """tcgen05 product with the tiling the engine would pick, at sizes that end inside a tile in
+    every direction (rows, columns, k)."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(M + N + K)
+    a, w = as_stored(rng.standard_normal((M, K)), "bfloat16"), as_stored(rng.standard_normal((N, K)), "bfloat16")
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=DT[out_dtype])
+    ops.gemm(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(out), plain.linear(a, w)) < (TOL["bfloat16"] if out_dtype == "bfloat16" else 2e-5)
+
+
+@pytest.mark.parametrize("transposed,bn,splits", [(0, 16, 1), (0, 64, 1), (0, 256, 1), (1, 128, 1), (1, 256, 1), (1, 128, 3),
+                                                  (1, 256, 5), (0, 128, 2)])
+def test_gemm_tensor_cores_every_tiling(ops, transposed, bn, splits):
+    """Every tile width, both orientations, with and without splits of k, into a strided output."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(bn + splits)
+    M, N, K = 77, 300, 520
+    a, w = as_stored(rng.standard_normal((M, K)), "bfloat16"), as_stored(rng.standard_normal((N, K)), "bfloat16")
+    wide = torch.full((M, N + 40), 7.0, device="cuda", dtype=torch.float32)
+    out = wide[:, 8:8 + N]
+    gemm_select.gemm_tc(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out, transposed=transposed, bn=bn, splits=splits)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(out), plain.linear(a, w)) < 2e-5
+    assert (wide[:, :8] == 7).all() and (wide[:, 8 + N:] == 7).all()      # nothing is written beside the output
+
+
+def test_gemm_falls_back_when_tma_cannot_address_the_operands(ops):
+    """K = 75 is no multiple of 8: the CUDA-core kernel serves it, same numbers."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(0)
+    a, w = as_stored(rng.standard_normal((40, 75)), "bfloat16"), as_stored(rng.standard_normal((90, 75)), "bfloat16")
+    ad, wd = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    out = torch.empty(40, 90, device="cuda", dtype=torch.bfloat16)
+    assert not gemm_select.tc_takes(ad, wd, out)
+    ops.gemm(ad, wd, out)
+    assert rel_err(host(out), plain.linear(a, w)) < TOL["bfloat16"]
+    from tiny_inference_engine_b200.errors import InvalidArgument
+    with pytest.raises(InvalidArgument, match="multiples of 8"):
+        gemm_select.gemm_tc(ad, wd, out)

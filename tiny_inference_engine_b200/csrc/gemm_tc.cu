@@ -1,0 +1,437 @@
+// bfloat16 matrix products on the 5th-generation tensor cores (tcgen05), operands staged by TMA,
+// accumulators in tensor memory:  out[M, N] = a[M, K] . w[N, K]^T, float accumulation.
+//
+// One CTA computes a 128 x BN tile of  P[i, j] = sum_k X[i, k] Y[j, k]  where X (the
+// "row operand", 128 rows per tile) and Y (the "column operand", BN rows per tile, BN in
+// {16, 32, 64, 128, 256}) are both k-contiguous, which is how activations [T, K] and
+// checkpoint weights [out, in] are stored (the reference's matmul contract,
+// src/backend/backend.h:44-50: y = x . W^T). Two ways to map a product onto it:
+//   plain       X = activations, Y = weights : prompt portions (many tokens).
+//   transposed  X = weights, Y = activations : few tokens (decode). The 128-row side of the
+//               MMA is filled by weight rows, the tokens are the narrow BN side, so no
+//               tensor-core work is wasted on padding and every weight byte streams through
+//               shared memory exactly once. The epilogue writes P transposed.
+// With `splits` > 1 the k range is cut into equal parts along gridDim.z; each part writes
+// float partial sums to scratch memory and a second kernel adds them in split order
+// (deterministic; no atomics).
+//
+// Roles inside a CTA of 192 threads: warps 0-3 read the accumulator out of tensor memory
+// (warp w owns lanes 32w..32w+31) and store it, warp 4 issues the TMA loads, warp 5 issues
+// the MMAs. A ring of STAGES shared-memory stages is handed back and forth with mbarriers:
+// full[s] (TMA bytes landed) and empty[s] (the MMAs that read stage s retired, signalled by
+// tcgen05.commit). Every wait is bounded: when it runs out the kernel records where in a
+// status word, stops waiting, frees its tensor memory and returns; the host reads the word.
+// No TMA multicast is used anywhere.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace tie {
+
+constexpr int kBM = 128;          // rows of the row operand per tile = MMA M
+constexpr int kBK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;        // k per tcgen05.mma for 16-bit inputs
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitCycles = 4000000000ull;  // about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false (and records `where`) when the barrier did not flip in time or
+// another role of this CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag != 0) return false;
+    if (clock64() - start > kWaitCycles) {
+      *abort_flag = 1;
+      *reinterpret_cast<volatile int*>(status) = where;
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a k-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);        // start address, 16-byte units
+  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset: unused with swizzle
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                      // version
+  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: float accumulator, bfloat16 A and B, both k-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+template <int BN> struct TcConfig {
+  static constexpr int kStageA = kBM * kBK * 2;
+  static constexpr int kStageB = BN * kBK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  // As many stages as fit beside the barriers in the 227 KB a CTA may use, at most 8.
+  static constexpr int kStages = (200 * 1024 / kStage) > 8 ? 8 : (200 * 1024 / kStage);
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr size_t kSmem = static_cast<size_t>(kStages) * kStage + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+// out_mode: 0 = OutT out[i * ldo + j] (plain), 1 = OutT out[j * ldo + i] (transposed),
+// and with partial != nullptr the same two layouts in float at partial + z * part_stride.
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, OutT* __restrict__ out,
+               float* __restrict__ partial, long long part_stride, long long ldp, int rows_x, int rows_y, int k_blocks,
+               int k_blocks_per_split, long long ldo, int transposed, int* status) {
+  using C = TcConfig<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStage);
+  uint64_t* empty = full + C::kStages;
+  uint64_t* acc_full = empty + C::kStages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i0 = blockIdx.x * kBM;   // first row of the row operand
+  const int j0 = blockIdx.y * BN;    // first row of the column operand
+  const int kb_begin = blockIdx.z * k_blocks_per_split;
+  const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 4) {  // this warp owns the tensor memory: it allocates here and frees at the end
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_holder;
+
+  if (warp == 4) {
+    // ---- TMA producer
+    if (lane == 0) {
+      int it = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+        const int s = it % C::kStages;
+        const uint32_t parity = ((it / C::kStages) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
+        if (!mbar_wait(empty + s, parity, abort_flag, status, 1)) break;
+        uint8_t* sa = smem + s * C::kStage;
+        mbar_expect_tx(full + s, C::kStage);
+        tma_load_2d(sa, &map_x, kb * kBK, i0, full + s);
+        tma_load_2d(sa + C::kStageA, &map_y, kb * kBK, j0, full + s);
+      }
+    }
+  } else if (warp == 5) {
+    // ---- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      int it = 0;
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+        const int s = it % C::kStages;
+        if (!mbar_wait(full + s, (it / C::kStages) & 1, abort_flag, status, 2)) {
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + s * C::kStage);
+        const uint32_t b_addr = a_addr + C::kStageA;
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          umma_bf16(tmem_acc, smem_desc_sw128(a_addr + k * kUmmaK * 2), smem_desc_sw128(b_addr + k * kUmmaK * 2), idesc,
+                    (it > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty + s);   // arrives once the MMAs above have read the stage
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // ---- epilogue: warp w reads lanes 32w..32w+31, 16 columns at a time
+    const bool have = kb_end > kb_begin;
+    bool ok = true;
+    if (have) ok = mbar_wait(acc_full, 0, abort_flag, status, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int i = i0 + warp * 32 + lane;
+    float* part = partial ? partial + static_cast<long long>(blockIdx.z) * part_stride : nullptr;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (j0 + c0 >= rows_y) break;   // uniform over the warp
+        uint32_t r[16];
+        if (have) {
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) r[e] = 0u;
+        }
+        if (i < rows_x) {
+          if (transposed) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int j = j0 + c0 + e;
+              if (j < rows_y) {
+                if (part) part[static_cast<long long>(j) * ldp + i] = __uint_as_float(r[e]);
+                else st(out + static_cast<long long>(j) * ldo + i, __uint_as_float(r[e]));
+              }
+            }
+          } else {
+            const long long at = static_cast<long long>(i) * ldo + j0 + c0;
+            const int n = min(16, rows_y - (j0 + c0));
+            if (part) {
+              const long long pat = static_cast<long long>(i) * ldp + j0 + c0;
+              if (n == 16 && (pat & 3) == 0) {
+#pragma unroll
+                for (int e = 0; e < 16; e += 4)
+                  *reinterpret_cast<uint4*>(part + pat + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+              } else {
+                for (int e = 0; e < n; ++e) part[pat + e] = __uint_as_float(r[e]);
+              }
+            } else if (n == 16 && ((at * sizeof(OutT)) & 15) == 0) {
+              if constexpr (sizeof(OutT) == 2) {
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+                  w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(out + at) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(out + at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 16; e += 4)
+                  *reinterpret_cast<uint4*>(out + at + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+              }
+            } else {
+              for (int e = 0; e < n; ++e) st(out + at + e, __uint_as_float(r[e]));
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag != 0) {  // a wait ran out: give copies that are still in flight time to land before the CTA goes away
+    const unsigned long long t0 = clock64();
+    while (clock64() - t0 < 4000000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// out[m, n] = sum over splits of partial[z][m, n], in split order, converted to OutT.
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, long long part_stride, int splits,
+                                     OutT* __restrict__ out, long long ldo, int N, long long total) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  float acc = partial[idx];
+  for (int z = 1; z < splits; ++z) acc += partial[static_cast<long long>(z) * part_stride + idx];
+  st(out + (idx / N) * ldo + idx % N, acc);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// [rows, K] bfloat16, row stride ld elements; box = 64 k x box_rows rows, 128-byte swizzle, zeros outside.
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int* g_status_host = nullptr;   // pinned, mapped: the kernels write it, the host reads it without a copy
+static int* g_status_dev = nullptr;
+
+static bool ensure_status() {
+  if (g_status_host != nullptr) return true;
+  if (cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), sizeof(int), cudaHostAllocMapped) != cudaSuccess) return false;
+  *g_status_host = 0;
+  return cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0) == cudaSuccess;
+}
+
+template <int BN, typename OutT>
+static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, long long part_stride,
+                     long long ldp, int rows_x, int rows_y, int K, long long ldo, int transposed, int splits, cudaStream_t s) {
+  using C = TcConfig<BN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(C::kSmem)) != cudaSuccess) {
+      set_error("gemm_tc: cannot reserve %zu bytes of shared memory", C::kSmem);
+      return kCudaError;
+    }
+    configured = true;
+  }
+  const int k_blocks = ceil_div(K, kBK);
+  const int per_split = ceil_div(k_blocks, splits);
+  const dim3 grid(ceil_div(rows_x, kBM), ceil_div(rows_y, BN), ceil_div(k_blocks, per_split));
+  gemm_tc_kernel<BN, OutT><<<grid, kThreads, C::kSmem, s>>>(mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
+                                                            rows_x, rows_y, k_blocks, per_split, ldo, transposed,
+                                                            g_status_dev);
+  return kOk;
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+// out[M, N] (OutT = bfloat16 or float, row stride ldo) = a[M, K] . w[N, K]^T, a and w bfloat16.
+// transposed != 0 puts the weights on the 128-row side (few tokens). splits > 1 needs
+// `scratch` with splits * M * ldo floats... see tie_gemm_tc_scratch_floats. Returns kBadArgument
+// with a message for sizes it does not take (K or a row stride not a multiple of 8, unaligned
+// pointers): the caller then uses the CUDA-core kernel.
+TIE_API long long tie_gemm_tc_scratch_floats(int M, int N, int splits) {
+  return splits > 1 ? static_cast<long long>(splits) * M * N : 0;
+}
+
+TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, int M, int N, int K, long long lda,
+                        long long ldw, long long ldo, int transposed, int bn, int splits, float* scratch,
+                        cudaStream_t s) {
+  TIE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+  TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: K=%d and the row strides must be multiples of 8", K);
+  TIE_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
+              "gemm_tc: operands must be 16-byte aligned");
+  TIE_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm_tc: tile width %d", bn);
+  TIE_REQUIRE(splits >= 1 && (splits == 1 || scratch != nullptr), "gemm_tc: splits=%d needs scratch memory", splits);
+  TIE_REQUIRE(out_dtype == TIE_BF16 || out_dtype == TIE_F32, "gemm_tc: output dtype code %d", out_dtype);
+  TIE_REQUIRE(ensure_status(), "gemm_tc: cannot allocate the status word");
+  // row operand X (128 per tile) and column operand Y (bn per tile)
+  const void* x = transposed ? w : a;
+  const void* y = transposed ? a : w;
+  const int rows_x = transposed ? N : M, rows_y = transposed ? M : N;
+  const long long ldx = transposed ? ldw : lda, ldy = transposed ? lda : ldw;
+  CUtensorMap mx, my;
+  TIE_REQUIRE(make_map(&mx, x, rows_x, K, ldx, kBM) && make_map(&my, y, rows_y, K, ldy, bn),
+              "gemm_tc: cuTensorMapEncodeTiled failed (rows %d/%d, K %d)", rows_x, rows_y, K);
+  float* partial = splits > 1 ? scratch : nullptr;
+  const long long part_stride = static_cast<long long>(M) * N;
+  const long long ldp = N;
+  int st = kOk;
+#define TIE_TC_CASE(B)                                                                                                \
+  case B:                                                                                                             \
+    st = out_dtype == TIE_BF16                                                                                        \
+             ? launch_tc<B, __nv_bfloat16>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, splits, s) \
+             : launch_tc<B, float>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, splits, s);  \
+    break;
+  switch (bn) {
+    TIE_TC_CASE(16)
+    TIE_TC_CASE(32)
+    TIE_TC_CASE(64)
+    TIE_TC_CASE(128)
+    TIE_TC_CASE(256)
+  }
+#undef TIE_TC_CASE
+  if (st != kOk) return st;
+  if (splits > 1) {
+    const int k_blocks = ceil_div(K, kBK);
+    const int real_splits = ceil_div(k_blocks, ceil_div(k_blocks, splits));
+    const long long total = part_stride;
+    if (out_dtype == TIE_BF16) {
+      splitk_reduce_kernel<__nv_bfloat16><<<ceil_div(total, 256), 256, 0, s>>>(
+          partial, part_stride, real_splits, static_cast<__nv_bfloat16*>(out), ldo, N, total);
+    } else {
+      splitk_reduce_kernel<float><<<ceil_div(total, 256), 256, 0, s>>>(partial, part_stride, real_splits,
+                                                                      static_cast<float*>(out), ldo, N, total);
+    }
+  }
+  TIE_RETURN_LAUNCH("gemm_tc");
+}
+
+// 0 when no kernel gave up waiting since the last call; else where the first one did
+// (1 = the TMA producer on a free stage, 2 = the MMA issuer on landed bytes, 3 = the epilogue
+// on the accumulator). Reading clears it. Call after the stream has been synchronized.
+TIE_API int tie_gemm_tc_status() {
+  if (g_status_host == nullptr) return 0;
+  const int v = *reinterpret_cast<volatile int*>(g_status_host);
+  *g_status_host = 0;
+  return v;
+}

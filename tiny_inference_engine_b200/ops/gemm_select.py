@@ -1,12 +1,92 @@
-"""Which matrix-product kernel runs for which operands."""
+"""Which matrix-product kernel runs for which operands, and with which tiling.
+
+float32 always runs on the CUDA cores: the 32-bit path has no reduced-precision matrix mode.
+bfloat16 runs on the tensor cores (tcgen05) whenever TMA can address the operands (K and the
+row strides multiples of 8 elements, 16-byte aligned bases), else on the CUDA cores.
+"""
 from __future__ import annotations
+
+import math
 
 import torch
 
-from . import gemm_simt
+from ..errors import TieError
+from .library import call as _call, library as _library
+
+NUM_SMS = 148
+_scratch: dict = {}
+
+
+def tc_takes(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    K = a.shape[1]
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
+    """(transposed, tile width, splits) for out[M, N] = a[M, K] w[N, K]^T.
+
+    Up to 256 tokens the weights take the 128-row side of the MMA and the tokens the narrow side
+    (width = the smallest of 16, 32, 64, 128, 256 that holds them): the product is bound by
+    streaming the weights, and k is cut into splits so that about two CTAs per SM pull bytes,
+    as long as the float partial sums stay a few percent of the weight bytes. More tokens:
+    128-token row tiles against 256-wide weight tiles."""
+    k_blocks = math.ceil(K / 64)
+    if M <= 256:
+        bn = next(b for b in (16, 32, 64, 128, 256) if b >= M)
+        tiles = math.ceil(N / 128)
+        splits = 1
+        if tiles < 2 * NUM_SMS:
+            want = max(1, round(2 * NUM_SMS / tiles))
+            cap_traffic = max(1, K // (80 * M))            # partial sums (write + read) under 5 % of the weight bytes
+            cap_depth = max(1, k_blocks // 4)              # at least 4 k-blocks per split
+            splits = max(1, min(want, cap_traffic, cap_depth))
+        return 1, bn, splits
+    bn = next((b for b in (16, 32, 64, 128, 256) if b >= N), 256)
+    return 0, bn, 1
+
+
+def _scratch_for(numel: int, device) -> torch.Tensor:
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < numel:
+        buf = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None, bn=None, splits=None, scratch=None) -> None:
+    """The tensor-core product; the tiling can be forced (tests)."""
+    from . import _need, _stream, dtype_code
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm: last axes must be contiguous")
+    _need(tc_takes(a, w, out), "gemm_tc: operands must be bfloat16 with K and row strides multiples of 8, 16-byte aligned")
+    t, b, s = plan(M, N, K)
+    transposed = t if transposed is None else int(transposed)
+    bn = b if bn is None else bn
+    splits = s if splits is None else splits
+    if splits > 1 and scratch is None:
+        scratch = _scratch_for(splits * M * N, a.device)
+    _call("tie_gemm_tc", dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
+                 w.stride(0), out.stride(0), transposed, bn, splits, scratch.data_ptr() if splits > 1 else 0, _stream())
+
+
+def check_status() -> None:
+    """After a synchronize: raises if a tensor-core kernel gave up a bounded wait."""
+    code = _library().tie_gemm_tc_status()
+    if code:
+        where = {1: "the TMA producer waiting for a free stage", 2: "the MMA issuer waiting for operands",
+                 3: "the epilogue waiting for the accumulator"}.get(code, f"code {code}")
+        raise TieError(f"a tensor-core matrix product gave up after its wait limit ({where}); its output is invalid")
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """float32 always runs on the CUDA cores (true 32-bit). bfloat16 runs on the tensor cores
-    when the kernel takes the sizes, else on the CUDA cores."""
-    gemm_simt(a, w, out)
+    from . import gemm_simt
+    if a.shape[0] == 0:
+        return
+    if tc_takes(a, w, out):
+        gemm_tc(a, w, out)
+    else:
+        gemm_simt(a, w, out)

@@ -27,6 +27,7 @@ _SIGNATURES = {
     "tie_attention_rows": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_split": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_sample": [P, L, I, I, P, P, P, P, P],
+    "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
 }
 
 
@@ -54,6 +55,8 @@ def library() -> ctypes.CDLL:
         lib.tie_last_error.restype = ctypes.c_char_p
         lib.tie_last_error.argtypes = []
         lib.tie_compiled_arch.restype = c_int
+        lib.tie_gemm_tc_status.restype = c_int
+        lib.tie_gemm_tc_status.argtypes = []
         for name, args in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = args
