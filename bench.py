@@ -1,0 +1,296 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, Qwen3-8B shape, random bfloat16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout. `value` is decoded tokens per second at batch 8 with the timed steps
+ending at the benchmark context (device time, CUDA events around K decode steps through the
+step function); `e2e` is the same through the Python entry point (Engine.step: host token
+ids in, sampled ids out, every step). `prefill` is one 2,048-token prompt in one step;
+`roofline` is the bytes a decode step has to read (every weight it uses once, and the cache
+of the live requests) over its time, against the measured copy bandwidth; `points` holds
+decode at batch 1 and 64. Weights are 16 GB and the caches gigabytes, far more than the
+126 MB L2, so no flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# BASELINE.json configs[2]: the Qwen3-8B shape.
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 151936, "hidden_size": 4096,
+    "intermediate_size": 12288, "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": False,
+}
+FULL_LAYERS = 36
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"]))}, "measured"
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([f.strip() for f in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def weight_bytes_per_decode_step(cfg, layers):
+    D, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (q + 2 * kv) * D + D * q + 2 * I * D + D * I
+    return 2 * (layers * per_layer + V * D)      # bfloat16; the embedding table is read one row per token
+
+
+def kv_bytes_per_token(cfg, layers):
+    return 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg, layers, T):
+    D, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (q + 2 * kv) * D + D * q + 2 * I * D + D * I
+    gemm = 2 * T * layers * per_layer + 2 * V * D            # one logits row
+    attn = layers * 2 * 2 * cfg["num_attention_heads"] * cfg["head_dim"] * T * (T + 1) // 2   # causal QK^T and PV
+    return gemm + attn
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096, help="context length at which the timed decode steps end")
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported in config)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--profile", choices=["decode", "prefill"], help="run two steps of one kind, kernel by kernel, between "
+                    "cudaProfilerStart/Stop (for ncu --profile-from-start off) and print no bench line")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a C++/Objective-C++ CMake project with a "
+                          "Metal GPU backend (Apple only); pip cannot install it (no setup.py or pyproject.toml) and it has no CUDA path"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this engine is single-GPU by design (asked for --gpus {args.gpus})")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+    from tiny_inference_engine_b200 import (Engine, SamplingParams, Scheduler, SchedulerConfig, ServingConfig, StepEntry,
+                                            StepRunner, load_model, make_cache)
+    from tiny_inference_engine_b200.ops import library as kernel_library
+
+    pk, pk_src = peaks()
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    K, W, B, CTX = args.steps, args.warmup, args.batch, args.context
+    rng = np.random.default_rng(0)
+    clocks = ClockSampler()
+
+    with tempfile.TemporaryDirectory() as d:
+        (Path(d) / "config.json").write_text(json.dumps(cfg))
+        t0 = time.time()
+        model = load_model(d, "bfloat16", random_weights=True, seed=0)
+        torch.cuda.synchronize()
+        print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+
+    V = cfg["vocab_size"]
+    max_batch = B if args.no_points else max(B, 64)
+    pages_per_seq = (CTX + PAGE - 1) // PAGE + 1
+    cache, states = make_cache(model, page_size=PAGE, num_pages=max_batch * pages_per_seq + 8, max_requests=max_batch * 2)
+    chunk = max(args.prefill_tokens, 2048)
+    runner = StepRunner(model, cache, max_tokens=chunk, max_seqs=max_batch, max_logit_rows=max_batch, states=states,
+                        use_graphs=args.profile is None)
+
+    def fill(batch, length):
+        """`batch` requests with `length` random tokens each in the cache, by real prefill in portions."""
+        reqs = []
+        for _ in range(batch):
+            req = cache.new_request()
+            assert cache.reserve(req, CTX)
+            toks = rng.integers(0, V, length)
+            for at in range(0, length, chunk):
+                runner.run([StepEntry(req, toks[at:at + chunk], at, [])])
+            reqs.append(req)
+        torch.cuda.synchronize()
+        runner.check()
+        return reqs
+
+    def decode_device(batch, steps, warmup):
+        """Device time of `steps` decode steps of `batch` requests whose context ends at CTX."""
+        start = CTX - steps - warmup
+        reqs = fill(batch, start)
+        toks = rng.integers(0, V, (steps + warmup, batch))
+        greedy = [(SamplingParams(), 0)] * batch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = replays0 = 0
+        for i in range(steps + warmup):
+            if i == warmup:
+                torch.cuda.synchronize()
+                launches0, replays0 = kernel_library.launch_count(), runner.graph_replays
+                e0.record()
+            runner.run([StepEntry(r, [int(toks[i, j])], start + i, [0]) for j, r in enumerate(reqs)], greedy)
+        e1.record()
+        torch.cuda.synchronize()
+        runner.check()
+        ms = e0.elapsed_time(e1)
+        per_graph = max(runner.kernels_in_graph.values(), default=0)
+        launches = (kernel_library.launch_count() - launches0) + (runner.graph_replays - replays0) * per_graph
+        for r in reqs:
+            cache.release(r)
+        return ms / steps, launches
+
+    if args.profile is not None:
+        greedy = [(SamplingParams(), 0)] * B
+        if args.profile == "decode":
+            reqs = fill(B, CTX - 4)
+            steps = [[StepEntry(r, [int(rng.integers(0, V))], CTX - 4 + i, [0]) for r in reqs] for i in range(3)]
+        else:
+            reqs = [cache.new_request() for _ in range(3)]
+            for r in reqs:
+                cache.reserve(r, args.prefill_tokens)
+            steps = [[StepEntry(r, rng.integers(0, V, args.prefill_tokens), 0, [args.prefill_tokens - 1])] for r in reqs]
+        runner.run(steps[0], greedy if args.profile == "decode" else None)      # warm-up, not profiled
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for st in steps[1:]:
+            runner.run(st, greedy if args.profile == "decode" else None)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        runner.check()
+        print(f"[bench] profiled two {args.profile} steps (batch {B}, context {CTX}, {args.layers} layers)", file=sys.stderr)
+        return 0
+
+    clocks.start()
+    ms_step, launches = decode_device(B, K, W)
+    value = B / (ms_step / 1e3)
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            ms_b, _ = decode_device(b, max(16, K // 4), W)
+            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+
+    # prefill: one prompt, one step, the logits of its last token
+    T = args.prefill_tokens
+    pre_ms = []
+    for i in range(4):
+        req = cache.new_request()
+        cache.reserve(req, T)
+        toks = rng.integers(0, V, T)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.run([StepEntry(req, toks, 0, [T - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms.append(e0.elapsed_time(e1))
+        cache.release(req)
+    runner.check()
+    pre = min(pre_ms[1:])
+    flops = prefill_flops(cfg, args.layers, T)
+
+    # end to end through the Python entry point: host token ids in, sampled ids out, every step
+    serving = ServingConfig(max_tokens_per_step=chunk, max_seqs=B)
+    engine = Engine(model, cache, Scheduler(cache, SchedulerConfig(serving=serving, policy="fcfs")), serving, states=states,
+                    runner=runner)
+    start = CTX - K - W - 1
+    for _ in range(B):
+        engine.add_request(rng.integers(0, V, start).tolist(), SamplingParams(max_tokens=K + W + 1))
+    while any(s.num_pending > 1 for s in engine.sequences.values()):
+        engine.step()                       # prompts (not timed)
+    for _ in range(W):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    steps_before = engine.stats().decode_tokens
+    for _ in range(K - 1):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e_tokens = engine.stats().decode_tokens - steps_before
+    sb = B
+    mb = 16
+    while mb < pages_per_seq:
+        mb *= 2
+    h2d = 4 * (3 * sb + (sb + 1) + 4 * sb + 5 * sb + sb + sb * mb + 64)
+    while engine.has_work():
+        engine.step()
+    clk = clocks.stop()
+
+    step_bytes = weight_bytes_per_decode_step(cfg, args.layers) + B * (CTX - K / 2) * kv_bytes_per_token(cfg, args.layers)
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, 1 B200)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
+        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_model": FULL_LAYERS, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": V, "global_batch": B, "seq_len": CTX,
+                   "context_during_timed_steps": f"{CTX - K}..{CTX}", "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (16 GB of weights per step)", "peaks": pk_src},
+        "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": int(launches),
+        "prefill": {"value": round(T / (pre / 1e3), 1), "tokens": T, "ms": round(pre, 3),
+                    "frac": round(flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clk,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

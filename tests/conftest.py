@@ -18,7 +18,8 @@ import plain_qwen3 as plain  # noqa: E402
 # (1.6e-3 to 4.4e-3, see tests/test_plain.py::test_bfloat16_noise_is_small).
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
 
-CONFIGS = {"tiny_a": (plain.TINY_A, 16), "tiny_b": (plain.TINY_B, 8), "tiny_c": (plain.TINY_C, 32)}
+CONFIGS = {"tiny_a": (plain.TINY_A, 16), "tiny_b": (plain.TINY_B, 8), "tiny_c": (plain.TINY_C, 32),
+           "tiny_d": (plain.TINY_D, 16)}
 
 
 def pytest_configure(config):
@@ -37,7 +38,7 @@ def sharp_weights(cfg, seed):
 
 @pytest.fixture(scope="session")
 def tiny_models(tmp_path_factory):
-    """name -> (config, page size, float32 weights, model folder) for the three tiny configurations."""
+    """name -> (config, page size, float32 weights, model folder) for the tiny configurations."""
     out = {}
     for i, (name, (cfg, page)) in enumerate(CONFIGS.items()):
         w = sharp_weights(cfg, i)

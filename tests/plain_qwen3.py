@@ -352,3 +352,12 @@ TINY_C = {
     "num_attention_heads": 3,
     "max_position_embeddings": 640, "rms_norm_eps": 3e-6,
 }
+# A fourth one whose head size (64) is one the tensor-core attention kernels take, so that the
+# bfloat16 runs of the tests go through them; a group of 3 query heads per kv head.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "vocab_size": 389, "hidden_size": 136, "intermediate_size": 264, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64,
+    "max_position_embeddings": 2048, "rms_norm_eps": 1e-6, "rope_theta": 500000.0,
+    "tie_word_embeddings": False,
+}

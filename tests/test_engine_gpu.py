@@ -14,7 +14,7 @@ def engine_for(model_dir, dtype="float32", **kw):
     return load_engine(model_dir, dtype=dtype, **kw)
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_greedy_and_sampled_generation_match_the_plain_implementation(tiny_models, name):
     from tiny_inference_engine_b200 import SamplingParams
     cfg, page, w, d = tiny_models[name]
@@ -130,12 +130,12 @@ def test_long_decoding_and_the_first_tokens(tiny_models, dtype):
     """One token from position 0 on, then 600 more one by one (the split attention kernel sees one,
     two and three splits); all logits against the plain implementation."""
     from tiny_inference_engine_b200 import StepEntry, StepRunner, load_model, make_cache
-    cfg, page, w, d = tiny_models["tiny_c"]
+    cfg, page, w, d = tiny_models["tiny_d" if dtype == "bfloat16" else "tiny_c"]   # bfloat16: the tensor-core kernels
     toks = np.random.default_rng(6).integers(0, cfg["vocab_size"], 601).tolist()
     wq = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()} if dtype == "bfloat16" else w
     want = plain.forward(wq, cfg, toks)
     model = load_model(d, dtype)
-    cache, states = make_cache(model, page_size=page, num_pages=24, max_requests=2)
+    cache, states = make_cache(model, page_size=page, num_pages=40, max_requests=2)
     runner = StepRunner(model, cache, 64, 2, 8, states=states)
     req = cache.new_request()
     got = []

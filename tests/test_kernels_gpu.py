@@ -356,3 +356,68 @@ def test_gemm_falls_back_when_tma_cannot_address_the_operands(ops):
     from tiny_inference_engine_b200.errors import InvalidArgument
     with pytest.raises(InvalidArgument, match="multiples of 8"):
         gemm_select.gemm_tc(ad, wd, out)
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(8, 2, 128, 16, 0), (6, 2, 64, 16, 0), (4, 4, 64, 8, 0), (16, 1, 128, 32, 0),
+                                                  (3, 1, 256, 16, 0), (8, 2, 128, 16, 100), (5, 5, 64, 4, 37), (32, 2, 64, 64, 0)])
+def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window):
+    """The mma kernels on a mixed batch with scattered pages: three sequences bring portions over a
+    cached prefix (one of them its whole prompt, one a portion that is no multiple of anything),
+    three bring one token with one, two and twelve splits."""
+    rng = np.random.default_rng(Hq * Dh + page)
+    ctx = [45, 300, 130, 1, 70, 700]
+    new = [45, 17, 129, 1, 1, 1]
+    kc, vc, bt, ks, vs = paged_cache(rng, "bfloat16", ctx, Hkv, Dh, page, 128 * 16 // page)
+    T = sum(new)
+    stride = Hq * Dh + 2 * Hkv * Dh                     # q as the engine holds it: the first columns of the qkv rows
+    qkv = as_stored(rng.standard_normal((T, stride)), "bfloat16")
+    q = qkv[:, :Hq * Dh]
+    qs = np.concatenate([[0], np.cumsum(new)])
+    scale = 1.0 / np.sqrt(Dh)
+    want = np.concatenate([dense_reference(q[qs[i]:qs[i + 1]], ks[i], vs[i], Hq, Hkv, Dh, new[i], window) for i in range(6)])
+    qd = dev(qkv, torch.bfloat16)[:, :Hq * Dh]
+    assert ops.attention_tc_takes(qd, Hq, Hkv, Dh)
+    out = torch.full((T, Hq * Dh), float("nan"), device="cuda", dtype=torch.bfloat16)
+    meta = (dev(qs, torch.int32), dev(np.array(ctx), torch.int32), dev(bt, torch.int32))
+    n_multi = new[0] + new[1] + new[2]
+    ops.attention_prompt_tc(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, 3, 129, Hq, Hkv, Dh, scale, window)
+    assert rel_err(host(out)[:n_multi], want[:n_multi]) < TOL["bfloat16"]
+    assert torch.isnan(out[n_multi:].float()).all()          # rows of other sequences are not touched
+    scratch = torch.empty(ops.attention_split_scratch_floats(3, Hq, Dh, 12), device="cuda")
+    ops.attention_decode_tc(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, Hq, Hkv, Dh, scale,
+                            dev(np.array([3, 4, 5]), torch.int32), 3, 64, 12, scratch, window)
+    assert rel_err(host(out), want) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 65, 255, 256, 511, 512, 1022, 1023])
+def test_tensor_core_attention_finds_one_far_key(ops, far):
+    """As test_one_far_key_among_a_thousand_is_found, for the mma kernels: edges of pages (16),
+    of a warp's 16 keys, of 64-key tiles, of 256-key splits, the first and the last key."""
+    rng = np.random.default_rng(far)
+    Hq, Hkv, Dh, page, n = 8, 2, 64, 16, 1024
+    kc, vc, bt, ks, vs = paged_cache(rng, "bfloat16", [n, n], Hkv, Dh, page, 140)
+    for n_new in (1, 40):                                  # decode kernel, then the prompt kernel (last 40 rows)
+        q = np.zeros((n_new, Hq * Dh), dtype=np.float32)
+        for h in range(Hq):
+            q[-1, h * Dh:(h + 1) * Dh] = 8.0 * ks[0][far, h // 4] * np.sqrt(Dh)
+        q = as_stored(q, "bfloat16")
+        want = dense_reference(q, ks[0], vs[0], Hq, Hkv, Dh, n_new)
+        one_hot = np.concatenate([vs[0][far, h // 4] for h in range(Hq)])
+        if far <= n - n_new or n_new == 1:
+            assert np.abs(want[-1] - one_hot).max() < 2e-3
+        meta = (dev(np.array([0, n_new]), torch.int32), dev(np.array([n]), torch.int32), dev(bt[:1], torch.int32))
+        out = torch.zeros(n_new, Hq * Dh, device="cuda", dtype=torch.bfloat16)
+        args = (dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out)
+        if n_new == 1:
+            scratch = torch.empty(ops.attention_split_scratch_floats(1, Hq, Dh, 4), device="cuda")
+            ops.attention_decode_tc(*args, *meta, Hq, Hkv, Dh, 1 / np.sqrt(Dh), dev(np.array([0]), torch.int32), 1, 256, 4, scratch)
+        else:
+            ops.attention_prompt_tc(*args, *meta, 1, n_new, Hq, Hkv, Dh, 1 / np.sqrt(Dh))
+        assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, f"n_new={n_new}"
+
+
+def test_tensor_core_attention_refuses_other_sizes(ops):
+    q = torch.zeros(4, 2 * 48, device="cuda", dtype=torch.bfloat16)
+    assert not ops.attention_tc_takes(q, 2, 1, 48)
+    assert not ops.attention_tc_takes(torch.zeros(4, 34 * 64, device="cuda", dtype=torch.bfloat16), 34, 2, 64)
+    assert not ops.attention_tc_takes(torch.zeros(4, 128, device="cuda"), 2, 1, 64)

@@ -78,7 +78,7 @@ def test_attention_part_alone(dtype):
         got, pos = [], 0
         for n in cuts:
             assert cache.reserve(req, pos + n)
-            ctx, _ = runner.prepare([StepEntry(req, [0] * n, pos, [])])
+            ctx = runner.prepare([StepEntry(req, [0] * n, pos, [])])
             out = mixer.forward(dev(h[pos:pos + n], DT[dtype]), ctx, cache.layer_cache(1, writes=True), None)
             got.append(out.float().cpu().numpy())
             pos += n
@@ -100,7 +100,7 @@ def test_feed_forward_norm_and_block_alone(dtype):
     h = plain.round_bf16(h) if dtype == "bfloat16" else h
     req = cache.new_request()
     cache.reserve(req, T)
-    ctx, _ = runner.prepare([StepEntry(req, [0] * T, 0, [])])
+    ctx = runner.prepare([StepEntry(req, [0] * T, 0, [])])
     block = model.layers[0]
     got = block.ffn.forward(dev(h, DT[dtype]), ctx).float().cpu().numpy()
     assert rel_err(got, plain.mlp_block(h, w, "model.layers.0.")) < TOL[dtype]

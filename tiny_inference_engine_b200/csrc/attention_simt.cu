@@ -174,6 +174,11 @@ __global__ void attention_merge_kernel(AttnArgs a, const int* __restrict__ seq_l
   const int s = seq_list[li];
   const int t = a.query_start[s];
   const int pos = a.context_lens[s] - 1;
+  T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.head_dim;
+  if (pos < 0) {  // a padding sequence: no keys, zeros
+    for (int d = lane; d < a.head_dim; d += 32) st(o + d, 0.0f);
+    return;
+  }
   const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   const int splits = (pos - lo0) / split_keys + 1;
   const float* src = scratch + (static_cast<long long>(li) * a.q_heads + h) * max_splits * (a.head_dim + 2);
@@ -184,7 +189,6 @@ __global__ void attention_merge_kernel(AttnArgs a, const int* __restrict__ seq_l
     const float* p = src + i * (a.head_dim + 2);
     l += p[a.head_dim + 1] * expf(p[a.head_dim] - m);
   }
-  T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.head_dim;
   for (int d = lane; d < a.head_dim; d += 32) {
     float acc = 0.0f;
     for (int i = 0; i < splits; ++i) {
@@ -273,4 +277,30 @@ TIE_API int tie_attention_split(int dtype, const void* q, long long q_stride, co
     return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
   set_error("attention: unknown dtype code %d", dtype);
   return kBadArgument;
+}
+
+// Combines the (acc, max, sum) that a split kernel (this file's or the tensor-core one) left in
+// scratch [n_list, q_heads, max_splits, head_dim + 2] into out rows, in split order.
+TIE_API int tie_attention_merge(int dtype, void* out, const int* query_start, const int* context_lens, int q_heads,
+                                int head_dim, int window, const int* seq_list, int n_list, int split_keys, int max_splits,
+                                const float* scratch, cudaStream_t s) {
+  TIE_REQUIRE(q_heads > 0 && head_dim > 0 && split_keys > 0 && max_splits > 0, "attention merge: bad geometry");
+  if (n_list == 0) return kOk;
+  AttnArgs a{};
+  a.out = out;
+  a.query_start = query_start;
+  a.context_lens = context_lens;
+  a.q_heads = q_heads;
+  a.head_dim = head_dim;
+  a.window = window;
+  const long long items = static_cast<long long>(n_list) * q_heads;
+  if (dtype == TIE_F32) {
+    attention_merge_kernel<float><<<ceil_div(items, 4), 128, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
+  } else if (dtype == TIE_BF16) {
+    attention_merge_kernel<__nv_bfloat16><<<ceil_div(items, 4), 128, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
+  } else {
+    set_error("attention merge: unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("attention_merge");
 }

@@ -16,7 +16,6 @@ from ..cache.manager import CacheManager, blocks_for
 from ..cache.state_slots import StateSlots
 from ..errors import CapacityError, InvalidArgument
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler
 from .scheduler import ScheduledBatch, Scheduler, SchedulerConfig, ServingConfig
 from .sequence import FinishReason, SeqState, Sequence
 from .step import StepEntry, StepRunner
@@ -46,7 +45,6 @@ class Engine:
             raise InvalidArgument(f"serving config ({serving.max_tokens_per_step} tokens, {serving.max_seqs} sequences "
                                   f"per step) exceeds the step function's limits ({self.runner.max_tokens} tokens, "
                                   f"{self.runner.max_seqs} sequences, {self.runner.max_logit_rows} logit rows)")
-        self.sampler = Sampler(serving.max_seqs)
         self.sequences: dict[int, Sequence] = {}
         self._next_id = 0
         self._stepping = False
@@ -146,11 +144,9 @@ class Engine:
                 else:
                     prefill += n
             t0 = time.perf_counter()
-            logits = self.runner.run(entries)
-            if sampled:
-                tokens = self.sampler.sample(logits, [s.params for s in sampled], [s.num_generated for s in sampled])
-            else:
-                tokens = []
+            sampling = [(s.params, s.num_generated) for s in sampled]
+            logits, ids = self.runner.run(entries, sampling)
+            tokens = self.runner.tokens_of(logits, ids, sampling)
             self._stats.step_seconds += time.perf_counter() - t0
             self._stats.steps += 1
             self._stats.seqs_scheduled += len(batch.seqs)

@@ -2,28 +2,37 @@
 
 A step takes portions of prompts beside single decoded tokens, cut anywhere, runs only the
 tokens it is given as one flat unpadded batch, appends their keys and values to the pages
-the requests hold, and returns float32 logits at the wanted places only. It is the one way
-into the model: generation, the scheduler's batches and trace replay all come through here.
+the requests hold, and returns float32 logits at the wanted places only (and, when asked,
+the token sampled from each of those rows). It is the one way into the model: generation,
+the scheduler's batches and trace replay all come through here.
 
 The flat batch is the reference's BatchInput (src/model/qwen3.h:24-32, built in
 src/engine/engine.cpp:114-135): tokens, positions and slots per row, query_start and
 context_lens (length AFTER the step) per sequence, zero-padded block tables, logit rows.
 Here rows are ordered so that sequences bringing several tokens come first and sequences
-bringing one token last (the attention kernels differ), all index arrays travel in one
-pinned buffer and one copy, and block-table rows are as long as this step's longest
-sequence needs, not as long as the longest a model could have.
+bringing one token last (the attention kernels differ), all index arrays and sampling
+parameters travel in one pinned buffer and one copy, and block-table rows are as long as
+this step's longest sequence needs, not as long as the longest a model could have.
+
+Steps in which every sequence brings one token (decoding) are launch-bound when issued
+kernel by kernel, so they are captured once per (batch bucket, table-length bucket) as a
+CUDA graph over fixed buffers and replayed; sequences that pad a bucket have no keys and
+write nothing.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Sequence
 
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager, RequestCache, blocks_for
 from ..errors import CapacityError, InvalidArgument
+from ..ops import gemm_select
 from ..ops.library import check_device
+from ..sampling.params import SamplingParams
 from .workspace import Workspace
 
 
@@ -44,6 +53,15 @@ class GroupStep:
 
 
 @dataclass
+class HostStep:
+    """Host copies for parts that decide on the host (and for toy parts in tests)."""
+    query_start: np.ndarray
+    context_lens: np.ndarray
+    starts: np.ndarray            # position of each sequence's first token in this step
+    state_slots: np.ndarray
+
+
+@dataclass
 class StepContext:
     """Everything a part may read about the step. Device tensors are int32."""
     T: int
@@ -59,40 +77,44 @@ class StepContext:
     single_seqs: torch.Tensor        # [single_count] sequences that bring one token
     groups: list[GroupStep]
     multi_rows: int                  # rows [0, multi_rows) belong to sequences that bring several tokens
+    multi_seqs: int                  # sequences [0, multi_seqs) are those
+    multi_max_queries: int           # the most tokens one of them brings
     single_count: int
     single_max_context: int
     max_context: int
     max_seqs: int
     ws: Workspace                    # buffers of max_tokens rows
     logit_ws: Workspace              # buffers of max_logit_rows rows (final norm, logits)
-    host: "HostStep"
+    host: HostStep
     layer_hook: Callable | None = None
-
-
-@dataclass
-class HostStep:
-    """Host copies for parts that decide on the host (and for toy parts in tests)."""
-    query_start: np.ndarray
-    context_lens: np.ndarray
-    starts: np.ndarray            # position of each sequence's first token in this step
-    state_slots: np.ndarray
+    # sampling parameters per logit row (None when the step does not sample)
+    inv_temperature: torch.Tensor | None = None
+    seeds: torch.Tensor | None = None
+    counters: torch.Tensor | None = None
 
 
 def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
 
+def _bucket(n: int, limit: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return min(b, limit) if n <= limit else n
+
+
 class StepRunner:
-    """Owns the workspace and the pinned staging buffer; `run(entries)` is the step function."""
+    """Owns the workspace, the staging buffers and the decode graphs; `run(entries)` is the step function."""
 
     def __init__(self, model, cache: CacheManager, max_tokens: int, max_seqs: int, max_logit_rows: int | None = None,
-                 states=None, device="cuda"):
+                 states=None, device="cuda", use_graphs: bool = True):
         check_device()
         if max_tokens <= 0 or max_seqs <= 0:
             raise InvalidArgument("step limits must be positive")
         self.model, self.cache, self.states = model, cache, states
-        self.max_tokens, self.max_seqs = max_tokens, max_seqs
-        self.max_logit_rows = max_logit_rows if max_logit_rows is not None else max_seqs
+        self.max_tokens, self.max_seqs = max_tokens, max(1, min(max_seqs, max_tokens))
+        self.max_logit_rows = max_logit_rows if max_logit_rows is not None else self.max_seqs
         self.device = device
         self.ws = Workspace(max_tokens, device)
         self.logit_ws = Workspace(self.max_logit_rows, device)
@@ -100,48 +122,143 @@ class StepRunner:
         self.max_positions = model.spec.max_positions
         self._staging_bufs = [None, None]   # two pinned buffers, used in turn, each with the event of its last copy
         self._staging_turn = 0
-        self._dev = None
+        # The device copy of the index arrays never moves: captured graphs read it at fixed offsets.
+        G = len(cache.groups)
+        mb = _round_up(blocks_for(self.max_positions, cache.page_size), 4)
+        words = 4 * max_tokens + 6 * self.max_seqs + 6 * self.max_logit_rows + G * (max_tokens + self.max_seqs * mb) + 64 * (8 + 2 * G)
+        self._dev = torch.zeros(words, dtype=torch.int32, device=device)
+        self._ids = torch.zeros(self.max_logit_rows, dtype=torch.int32, device=device)
+        self._ids_host = torch.zeros(self.max_logit_rows, dtype=torch.int32, pin_memory=True)
         self.layer_hook = None
         self.fail_hook = None     # tests: called after the batch is built, may raise
+        # Per-request state is updated by plain torch code in toy mixers: no graphs then.
+        self.use_graphs = use_graphs and (states is None or states.bytes_per_slot == 0)
+        self._graphs: dict[tuple, tuple] = {}
+        self.graph_replays = 0
+        self.kernels_in_graph: dict[tuple, int] = {}
 
+    # -- staging
     def _staging(self, n: int):
-        """A pinned host buffer that no copy in flight still reads, and the device buffer it goes to."""
+        """A pinned host buffer that no copy in flight still reads."""
         self._staging_turn ^= 1
         slot = self._staging_bufs[self._staging_turn]
         if slot is None or slot[0].numel() < n:
             if slot is not None:
                 slot[2].synchronize()
-            size = max(n, 1 << 14)
-            host = torch.empty(size, dtype=torch.int32, pin_memory=True)
+            host = torch.empty(max(n, 1 << 14), dtype=torch.int32, pin_memory=True)
             slot = [host, host.numpy(), torch.cuda.Event()]
             self._staging_bufs[self._staging_turn] = slot
         else:
             slot[2].synchronize()
-        if self._dev is None or self._dev.numel() < n:
-            self._dev = torch.empty(max(n, 1 << 14), dtype=torch.int32, device=self.device)
+        if self._dev.numel() < n:
+            raise CapacityError(f"step needs {n} index words; the step function was sized for {self._dev.numel()}")
         return slot
 
-    def run(self, entries: Sequence[StepEntry], return_context: bool = False):
-        """Runs one step. Returns float32 logits [R, V] on the device in the order of the entries
-        and of their `want` (None when nothing is wanted)."""
-        ctx, order = self.prepare(entries)
+    # -- the step function
+    def run(self, entries: Sequence[StepEntry], sampling: Sequence[tuple[SamplingParams, int]] | None = None):
+        """Runs one step. Returns float32 logits [R, V] on the device in the order of the entries and
+        of their `want` (None when nothing is wanted). With `sampling` (one (parameters, index of
+        the generated token) per wanted row) returns (logits, ids): ids is an int32 device tensor
+        [R] picked by the sampling kernel (greedy or temperature); rows whose parameters ask for
+        top-k or top-p are to be sampled from the logits by the caller."""
+        graph_key = self._graph_key(entries, sampling)
+        if graph_key is not None:
+            return self._run_graph(entries, sampling, graph_key)
+        ctx = self.prepare(entries, sampling)
         logits = self.model.forward(ctx, self.cache, self.states)
-        return (logits, ctx) if return_context else logits
+        if sampling is None:
+            return logits
+        return logits, self._sample(ctx, logits)
 
-    def prepare(self, entries: Sequence[StepEntry]):
+    def _sample(self, ctx: StepContext, logits):
+        if logits is None:
+            return None
+        ops.sample(logits, self._ids, ctx.inv_temperature, ctx.seeds, ctx.counters)
+        return self._ids[:ctx.R]
+
+    def tokens_of(self, logits, ids, sampling) -> list[int]:
+        """Brings the sampled ids to the host (one copy, one synchronize) and samples rows that need
+        the host filter (top-k, top-p) from their logits. Checks the kernels' status words."""
+        from ..sampling.sampler import sample_host
+        R = len(sampling)
+        if R == 0:
+            return []
+        self._ids_host[:R].copy_(ids[:R], non_blocking=True)
+        host_rows = [r for r, (p, _) in enumerate(sampling) if not p.on_device]
+        host_logits = logits[host_rows].cpu().numpy() if host_rows else None
+        torch.cuda.current_stream().synchronize()
+        gemm_select.check_status()
+        out = self._ids_host[:R].tolist()
+        for j, r in enumerate(host_rows):
+            out[r] = sample_host(host_logits[j], sampling[r][0], sampling[r][1])
+        return out
+
+    def check(self) -> None:
+        """After a synchronize: raises if a kernel of an earlier step gave up a bounded wait."""
+        gemm_select.check_status()
+
+    # -- decode graphs
+    def _graph_key(self, entries, sampling):
+        if not self.use_graphs or self.layer_hook is not None or self.fail_hook is not None:
+            return None
         S = len(entries)
-        if not 1 <= S <= self.max_seqs:
-            raise CapacityError(f"step has {S} sequences; the step function allows 1 to {self.max_seqs}")
+        if S > self.max_seqs or any(len(e.tokens) != 1 for e in entries):
+            return None
+        if any(len(e.want) != 1 for e in entries) or S > self.max_logit_rows:
+            return None
+        if sampling is not None and len(sampling) != S:
+            return None
+        page = self.cache.page_size
+        need = max(blocks_for(e.start + 1, page) for e in entries)
+        sb = _bucket(S, self.max_seqs)
+        if sb > self.max_logit_rows or sb > self.max_tokens:
+            return None
+        mb = max(16, _bucket(need, 1 << 30))
+        return (sb, mb, sampling is not None)
+
+    def _run_graph(self, entries, sampling, key):
+        sb, mb, sampled = key
+        ctx = self.prepare(entries, sampling, pad_seqs=sb, table_len=mb)
+        if key not in self._graphs:
+            # one eager run allocates every buffer and loads every kernel, then the capture
+            logits = self.model.forward(ctx, self.cache, self.states)
+            if sampled:
+                self._sample(ctx, logits)
+            torch.cuda.synchronize()
+            before = ops.library.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.cache, self.states)
+                if sampled:
+                    self._sample(ctx, logits)
+            self.kernels_in_graph[key] = ops.library.launch_count() - before
+            self._graphs[key] = (graph, logits)
+        graph, logits = self._graphs[key]
+        graph.replay()
+        self.graph_replays += 1
+        S = len(entries)
+        if sampling is None:
+            return logits[:S]
+        return logits[:S], self._ids[:S]
+
+    # -- building the flat batch
+    def prepare(self, entries: Sequence[StepEntry], sampling=None, pad_seqs: int | None = None,
+                table_len: int | None = None) -> StepContext:
+        S_real = len(entries)
+        if not 1 <= S_real <= self.max_seqs:
+            raise CapacityError(f"step has {S_real} sequences; the step function allows 1 to {self.max_seqs}")
         page = self.cache.page_size
         counts = [len(e.tokens) for e in entries]
-        T = sum(counts)
+        T_real = sum(counts)
         if min(counts) < 1:
             raise InvalidArgument("a step entry brings no token")
-        if T > self.max_tokens:
-            raise CapacityError(f"step has {T} tokens; the step function allows 1 to {self.max_tokens}")
-        R = sum(len(e.want) for e in entries)
-        if R > self.max_logit_rows:
-            raise CapacityError(f"step requests {R} logit rows; the step function allows 0 to {self.max_logit_rows}")
+        if T_real > self.max_tokens:
+            raise CapacityError(f"step has {T_real} tokens; the step function allows 1 to {self.max_tokens}")
+        R_real = sum(len(e.want) for e in entries)
+        if R_real > self.max_logit_rows:
+            raise CapacityError(f"step requests {R_real} logit rows; the step function allows 0 to {self.max_logit_rows}")
+        if sampling is not None and len(sampling) != R_real:
+            raise InvalidArgument(f"{len(sampling)} sampling entries for {R_real} wanted rows")
         seen = set()
         for e in entries:
             if id(e.cache) in seen:
@@ -157,22 +274,25 @@ class StepRunner:
                     raise InvalidArgument(f"a request has {len(t)} pages reserved; {end} tokens need "
                                           f"{blocks_for(end, page)}")
         # Sequences that bring several tokens first, then those that bring one (stable).
-        order = sorted(range(S), key=lambda i: counts[i] == 1)
+        order = sorted(range(S_real), key=lambda i: counts[i] == 1)
         n_multi = sum(1 for c in counts if c > 1)
         multi_rows = sum(c for c in counts if c > 1)
         max_ctx = max(e.start + c for e, c in zip(entries, counts))
-        MB = _round_up(blocks_for(max_ctx, page), 4)
+        pad = (pad_seqs or S_real) - S_real          # padding sequences: one row each, no keys, no slot
+        S, T, R = S_real + pad, T_real + pad, R_real + pad
+        MB = table_len if table_len is not None else _round_up(blocks_for(max_ctx, page), 4)
         G = len(self.cache.groups)
 
-        # layout of the staging buffer (int32 words)
+        # layout of the staging buffer (int32 words); 64-bit sections are 8-byte aligned because every section is 16-byte aligned
         sizes = [("tokens", T), ("positions", T), ("seq_of_row", T), ("query_start", S + 1), ("context_lens", S),
-                 ("logit_rows", max(R, 1)), ("state_slots", S), ("single_seqs", max(S, 1))]
+                 ("logit_rows", max(R, 1)), ("state_slots", S), ("single_seqs", max(S, 1)),
+                 ("inv_t", max(R, 1)), ("seeds", 2 * max(R, 1)), ("counters", 2 * max(R, 1))]
         for g in range(G):
             sizes += [(f"slots{g}", T), (f"tables{g}", S * MB)]
         offs, total = {}, 0
         for name, n in sizes:
             offs[name] = (total, n)
-            total += _round_up(n, 4)  # 16-byte aligned sections
+            total += _round_up(n, 4)
         slot = self._staging(total)
         host, dev = slot[1], self._dev
 
@@ -183,10 +303,10 @@ class StepRunner:
         tokens, positions, seq_of_row = sec("tokens"), sec("positions"), sec("seq_of_row")
         query_start, context_lens = sec("query_start"), sec("context_lens")
         state_slots = sec("state_slots")
-        row_of = {}  # (original entry index) -> first row
+        row_of = {}
         row = 0
         query_start[0] = 0
-        starts = np.empty(S, dtype=np.int64)
+        starts = np.zeros(S, dtype=np.int64)
         tables = [sec(f"tables{g}").reshape(S, MB) for g in range(G)]
         for g in range(G):
             tables[g][:] = 0
@@ -210,6 +330,13 @@ class StepRunner:
                 tables[g][s, :k] = np.maximum(t.ids[:k], 0)  # pages below a window are never read
             row += n
             query_start[s + 1] = row
+        for s in range(S_real, S):                  # padding
+            tokens[row], positions[row], seq_of_row[row] = 0, 0, s
+            context_lens[s], state_slots[s] = 0, -1
+            for g in range(G):
+                sec(f"slots{g}")[row] = -1
+            row += 1
+            query_start[s + 1] = row
         logit_rows = sec("logit_rows")
         r = 0
         for i, e in enumerate(entries):
@@ -218,10 +345,22 @@ class StepRunner:
                     raise InvalidArgument(f"wanted place {wpos} outside the {counts[i]} tokens of its entry")
                 logit_rows[r] = row_of[i] + wpos
                 r += 1
+        for s in range(S_real, S):
+            logit_rows[r] = T_real + (s - S_real)
+            r += 1
         single = sec("single_seqs")
         n_single = S - n_multi
         single[:n_single] = np.arange(n_multi, S)
-        single_max_ctx = int(context_lens[n_multi:S].max()) if n_single else 0
+        if table_len is not None:
+            single_max_ctx = MB * page               # a captured graph must hold for every context of its bucket
+        else:
+            single_max_ctx = int(context_lens[n_multi:S].max()) if n_single else 0
+        if sampling is not None:
+            inv_t = sec("inv_t").view(np.float32)
+            seeds, counters = sec("seeds").view(np.uint64), sec("counters").view(np.int64)
+            inv_t[:], seeds[:], counters[:] = 0.0, 0, 0
+            for r, (p, index) in enumerate(sampling):
+                inv_t[r], seeds[r], counters[r] = p.inv_temperature(), p.seed, index
 
         dev[:total].copy_(slot[0][:total], non_blocking=True)
         slot[2].record()
@@ -236,9 +375,14 @@ class StepRunner:
                           seq_of_row=dsec("seq_of_row"), query_start=dsec("query_start"),
                           context_lens=dsec("context_lens"), logit_rows=dsec("logit_rows", R),
                           state_slots=dsec("state_slots"), single_seqs=dsec("single_seqs"), groups=groups,
-                          multi_rows=multi_rows, single_count=n_single, single_max_context=single_max_ctx,
+                          multi_rows=multi_rows, multi_seqs=n_multi,
+                          multi_max_queries=max((c for c in counts if c > 1), default=0), single_count=n_single, single_max_context=single_max_ctx,
                           max_context=max_ctx, max_seqs=self.max_seqs, ws=self.ws, logit_ws=self.logit_ws, host=hs,
                           layer_hook=self.layer_hook)
+        if sampling is not None:
+            ctx.inv_temperature = dsec("inv_t", R).view(torch.float32)
+            ctx.seeds = dsec("seeds", 2 * R).view(torch.int64)
+            ctx.counters = dsec("counters", 2 * R).view(torch.int64)
         if self.fail_hook is not None:
             self.fail_hook(ctx)
-        return ctx, order
+        return ctx

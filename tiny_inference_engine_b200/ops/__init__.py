@@ -7,7 +7,8 @@ from __future__ import annotations
 import torch
 
 from ..errors import InvalidArgument
-from .library import call, check_device, library
+from . import library
+from .library import call, check_device
 
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
@@ -204,6 +205,41 @@ def attention_split(q, k_cache, v_cache, out, query_start, context_lens, block_t
          out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
          S, q_heads, kv_heads, head_dim, k_cache.shape[2], int(window), float(scale), seq_list.data_ptr(), n_list,
          split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
+def attention_tc_takes(q: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether the tensor-core attention kernels take these operands (else the CUDA-core ones do)."""
+    return (q.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and q_heads // kv_heads <= 16 and
+            q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attention_prompt_tc(q, k_cache, v_cache, out, query_start, context_lens, block_tables, n_seqs: int, max_queries: int,
+                        q_heads, kv_heads, head_dim, scale: float, window: int = 0) -> None:
+    """Tensor-core attention of the first n_seqs sequences of the step (each brings several tokens;
+    their rows come first); max_queries is the most tokens one of them brings."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables)
+    _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    call("tie_attention_prompt_tc", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+         query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs,
+         max_queries, q_heads, kv_heads, head_dim, k_cache.shape[2], int(window), float(scale), _stream())
+
+
+def attention_decode_tc(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim,
+                        scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch,
+                        window: int = 0) -> None:
+    """Tensor-core attention of sequences that bring one token each: split kernel, then the merge."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch)
+    _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
+    _need(scratch.dtype == torch.float32 and
+          scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, head_dim, max_splits),
+          "attention: scratch too small")
+    call("tie_attention_decode_tc", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+         query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads,
+         head_dim, k_cache.shape[2], int(window), float(scale), seq_list.data_ptr(), n_list, split_keys, max_splits,
+         scratch.data_ptr(), _stream())
+    call("tie_attention_merge", dtype_code(out), out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), q_heads,
+         head_dim, int(window), seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None) -> None:

@@ -28,6 +28,9 @@ _SIGNATURES = {
     "tie_attention_split": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_sample": [P, L, I, I, P, P, P, P, P],
     "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
+    "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "tie_attention_decode_tc": [P, L, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
+    "tie_attention_merge": [I, P, P, P, I, I, I, P, I, I, I, P, P],
 }
 
 
@@ -84,8 +87,18 @@ def check_device() -> None:
         raise KernelLibraryError(f"the kernels are compiled for sm_100a, this GPU is sm_{major}{minor}")
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """How many launcher calls this process has made (each launches one to three kernels of this library)."""
+    return _LAUNCHES
+
+
 def call(name: str, *args) -> None:
+    global _LAUNCHES
     lib = library()
+    _LAUNCHES += 1
     status = getattr(lib, name)(*args)
     if status != 0:
         from ..errors import InvalidArgument, TieError

@@ -114,12 +114,18 @@ class GQAttention(Mixer):
 
     def attend(self, q, attn, ctx, g, cache):
         """Rows of sequences that bring several tokens come first in a step, then one row per
-        sequence that brings one token (ctx.multi_rows, ctx.single_seqs)."""
+        sequence that brings one token (ctx.multi_rows, ctx.single_seqs). bfloat16 with a head
+        size the tensor-core kernels take runs there, everything else on the CUDA cores."""
         Hq, Hkv, Dh = self.heads, self.kv_heads, self.head_dim
+        tc = ops.attention_tc_takes(q, Hq, Hkv, Dh)
         if ctx.multi_rows > 0:
             n = ctx.multi_rows
-            ops.attention_rows(q[:n], cache.k, cache.v, attn[:n], ctx.seq_of_row[:n], ctx.query_start, ctx.context_lens,
-                               g.block_tables, Hq, Hkv, Dh, self.scale, self.window)
+            if tc:
+                ops.attention_prompt_tc(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables,
+                                        ctx.multi_seqs, ctx.multi_max_queries, Hq, Hkv, Dh, self.scale, self.window)
+            else:
+                ops.attention_rows(q[:n], cache.k, cache.v, attn[:n], ctx.seq_of_row[:n], ctx.query_start,
+                                   ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale, self.window)
         if ctx.single_count > 0:
             longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
             split_keys = SPLIT_KEYS
@@ -128,9 +134,9 @@ class GQAttention(Mixer):
             max_splits = max(1, math.ceil(longest / split_keys))
             scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
                                   torch.float32)
-            ops.attention_split(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv,
-                                Dh, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch,
-                                self.window)
+            fn = ops.attention_decode_tc if tc else ops.attention_split
+            fn(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale,
+               ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, self.window)
 
 
 register_part("mixer", "gqa_attention", GQAttention, replace=True)

@@ -1,4 +1,5 @@
-"""Sampling: the device kernel for greedy and temperature, and the host path with top-k and top-p.
+"""Sampling on the host, with top-k and top-p. (Greedy and plain temperature sampling run in the
+sampling kernel inside the step: engine/step.py.)
 
 The host path restates the reference's sampler (src/sampling/sampler.cpp:18-81): NaN or empty
 logits and all -inf are errors, a +inf logit is certain, greedy is the first maximum,
@@ -9,9 +10,7 @@ with a uniform draw in [0, total).
 from __future__ import annotations
 
 import numpy as np
-import torch
 
-from .. import ops
 from ..errors import InvalidArgument
 from .params import SamplingParams
 from .philox import uniform
@@ -50,47 +49,3 @@ def sample_host(logits: np.ndarray, params: SamplingParams, index: int) -> int:
     cum = np.cumsum(weights)
     pick = min(int(np.searchsorted(cum, r, side="right")), weights.size - 1)
     return int(order[pick]) if order is not None else pick
-
-
-class Sampler:
-    """Samples one token for each row of a step's logits; rows of requests with top-k or top-p
-    come back to the host, the others are picked by the kernel and only their ids come back."""
-
-    def __init__(self, max_rows: int, device="cuda"):
-        self.max_rows = max_rows
-        self._ids = torch.empty(max_rows, dtype=torch.int32, device=device)
-        self._ids_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
-        self._inv_t = torch.empty(max_rows, dtype=torch.float32, pin_memory=True)
-        self._seeds = torch.empty(max_rows, dtype=torch.int64, pin_memory=True)
-        self._counters = torch.empty(max_rows, dtype=torch.int64, pin_memory=True)
-        self._inv_t_d = torch.empty(max_rows, dtype=torch.float32, device=device)
-        self._seeds_d = torch.empty(max_rows, dtype=torch.int64, device=device)
-        self._counters_d = torch.empty(max_rows, dtype=torch.int64, device=device)
-
-    def sample(self, logits: torch.Tensor, params: list[SamplingParams], indices: list[int]) -> list[int]:
-        """logits [R, V] float32 on the device; params[r] and indices[r] (how many tokens request r
-        has generated so far) per row."""
-        R = logits.shape[0]
-        if R == 0:
-            return []
-        greedy_only = all(p.temperature == 0.0 for p in params)
-        inv_np, seeds_np, ctr_np = self._inv_t.numpy(), self._seeds.numpy(), self._counters.numpy()
-        if greedy_only:
-            ops.sample(logits, self._ids)
-        else:
-            for r, (p, i) in enumerate(zip(params, indices)):
-                inv_np[r] = p.inv_temperature()
-                seeds_np[r] = np.array(p.seed, dtype=np.uint64).view(np.int64)
-                ctr_np[r] = i
-            self._inv_t_d[:R].copy_(self._inv_t[:R], non_blocking=True)
-            self._seeds_d[:R].copy_(self._seeds[:R], non_blocking=True)
-            self._counters_d[:R].copy_(self._counters[:R], non_blocking=True)
-            ops.sample(logits, self._ids, self._inv_t_d, self._seeds_d, self._counters_d)
-        self._ids_host[:R].copy_(self._ids[:R], non_blocking=True)
-        host_rows = [r for r, p in enumerate(params) if not p.on_device]
-        host_logits = logits[host_rows].cpu().numpy() if host_rows else None   # synchronizes
-        torch.cuda.current_stream().synchronize()
-        out = self._ids_host[:R].tolist()
-        for j, r in enumerate(host_rows):
-            out[r] = sample_host(host_logits[j], params[r], indices[r])
-        return out
