@@ -304,3 +304,52 @@ TIE_API int tie_attention_merge(int dtype, void* out, const int* query_start, co
   }
   TIE_RETURN_LAUNCH("attention_merge");
 }
+
+// ---------------------------------------------------------------------------------------------
+// The variant of tie_attention_split that allocates nothing (see attention_noalloc.h).
+#include "attention_noalloc.h"
+
+namespace tie {
+// Partial results of the splits. In host code this name is only a handle for
+// cudaGetSymbolAddress; the address a kernel can use is looked up once per device below.
+static __device__ __align__(256) float g_noalloc_scratch[TIE_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_noalloc_ptr[kMaxDevices] = {};   // device address of the array on each device, once known
+}  // namespace tie
+
+TIE_API int tie_attention_split_noalloc(int dtype, const void* q, long long q_stride, const void* k_cache,
+                                        const void* v_cache, void* out, const int* query_start, const int* context_lens,
+                                        const int* block_tables, int max_blocks, int seqs, int q_heads, int kv_heads,
+                                        int head_dim, int page_size, int window, float scale, const int* seq_list,
+                                        int n_list, int split_keys, int max_splits, cudaStream_t s) {
+  const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
+                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
+  if (const int st = check_attn(a)) return st;
+  TIE_REQUIRE(n_list >= 0 && split_keys > 0 && max_splits > 0, "attention split (no alloc): bad split geometry");
+  const long long need = static_cast<long long>(n_list) * q_heads * max_splits * (head_dim + 2);
+  TIE_REQUIRE(need <= TIE_NOALLOC_SCRATCH_FLOATS,
+              "attention split (no alloc): %d sequences x %d heads x %d splits x (%d + 2) = %lld floats of partial results "
+              "exceed the built-in %d; use fewer splits or tie_attention_split with your own scratch",
+              n_list, q_heads, max_splits, head_dim, need, TIE_NOALLOC_SCRATCH_FLOATS);
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    set_error("attention split (no alloc): cannot use device %d (at most %d devices)", device, kMaxDevices);
+    return kCudaError;
+  }
+  if (g_noalloc_ptr[device] == nullptr) {   // set-up, once per device, with that device current
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("attention split (no alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return kCudaError;
+    }
+    g_noalloc_ptr[device] = p;
+  }
+  float* scratch = g_noalloc_ptr[device];
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  if (dtype == TIE_BF16)
+    return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  set_error("attention: unknown dtype code %d", dtype);
+  return kBadArgument;
+}
