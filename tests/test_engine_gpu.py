@@ -148,3 +148,20 @@ def test_long_decoding_and_the_first_tokens(tiny_models, dtype):
     got = np.concatenate(got)
     assert_logits_close(got[:3], want[:3], dtype, "the first tokens")
     assert_logits_close(got, want, dtype, "600 decoded tokens")
+
+
+def test_command_line_generates_the_plain_tokens(tiny_models):
+    import subprocess
+    import sys
+    from conftest import ROOT
+    cfg, page, w, d = tiny_models["tiny_a"]
+    prompt = [7, 200, 13, 99, 5]
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "tie"), "generate", "-m", str(d), "-p", " ".join(map(str, prompt)),
+                        "--dtype", "float32", "--temp", "0", "--top-k", "0", "--top-p", "1", "--max-tokens", "6", "--kv-mem", "1M"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert [int(t) for t in r.stdout.split()] == plain.generate(w, cfg, prompt, 6)
+    assert "[tie] cuda | load" in r.stderr and "6 tok generated" in r.stderr
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "tie"), "generate", "-m", str(d), "-p", "1 2 999"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 1 and "outside vocabulary" in r.stderr
