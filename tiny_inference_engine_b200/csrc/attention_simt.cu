@@ -162,40 +162,50 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   }
 }
 
-// Merge of the splits of one (sequence, head), in split order: one warp each.
+// Merge of the splits of one (sequence, head), in split order: one block each. The weights
+// exp(m_i - m) of the splits are computed once into shared memory, then every thread sums its
+// dims over the splits.
+constexpr int kMergeThreads = 128;
+constexpr int kMergeMaxSplits = 256;
+
 template <typename T>
-__global__ void attention_merge_kernel(AttnArgs a, const int* __restrict__ seq_list, int n_list, int split_keys,
-                                       int max_splits, const float* __restrict__ scratch) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
-  if (item >= static_cast<long long>(n_list) * a.q_heads) return;
-  const int li = static_cast<int>(item / a.q_heads);
-  const int h = static_cast<int>(item % a.q_heads);
+__global__ void __launch_bounds__(kMergeThreads) attention_merge_kernel(AttnArgs a, const int* __restrict__ seq_list,
+                                                                        int n_list, int split_keys, int max_splits,
+                                                                        const float* __restrict__ scratch) {
+  __shared__ float weight[kMergeMaxSplits];
+  __shared__ float inv_l;
+  const int item = blockIdx.x;
+  const int li = item / a.q_heads, h = item % a.q_heads;
   const int s = seq_list[li];
   const int t = a.query_start[s];
   const int pos = a.context_lens[s] - 1;
   T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.head_dim;
   if (pos < 0) {  // a padding sequence: no keys, zeros
-    for (int d = lane; d < a.head_dim; d += 32) st(o + d, 0.0f);
+    for (int d = threadIdx.x; d < a.head_dim; d += kMergeThreads) st(o + d, 0.0f);
     return;
   }
   const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   const int splits = (pos - lo0) / split_keys + 1;
-  const float* src = scratch + (static_cast<long long>(li) * a.q_heads + h) * max_splits * (a.head_dim + 2);
-  float m = -INFINITY;
-  for (int i = 0; i < splits; ++i) m = fmaxf(m, src[i * (a.head_dim + 2) + a.head_dim]);
-  float l = 0.0f;
-  for (int i = 0; i < splits; ++i) {
-    const float* p = src + i * (a.head_dim + 2);
-    l += p[a.head_dim + 1] * expf(p[a.head_dim] - m);
-  }
-  for (int d = lane; d < a.head_dim; d += 32) {
-    float acc = 0.0f;
-    for (int i = 0; i < splits; ++i) {
-      const float* p = src + i * (a.head_dim + 2);
-      acc = fmaf(p[d], expf(p[a.head_dim] - m), acc);
+  const int stride = a.head_dim + 2;
+  const float* src = scratch + (static_cast<long long>(li) * a.q_heads + h) * max_splits * stride;
+  if (threadIdx.x < 32) {
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < splits; i += 32) m = fmaxf(m, src[i * stride + a.head_dim]);
+    m = warp_max(m);
+    float l = 0.0f;
+    for (int i = threadIdx.x; i < splits; i += 32) {
+      const float w = expf(src[i * stride + a.head_dim] - m);
+      weight[i] = w;
+      l += src[i * stride + a.head_dim + 1] * w;   // summed below in a fixed lane order
     }
-    st(o + d, l > 0.0f ? acc / l : 0.0f);
+    l = warp_sum(l);
+    if (threadIdx.x == 0) inv_l = l > 0.0f ? 1.0f / l : 0.0f;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < a.head_dim; d += kMergeThreads) {
+    float acc = 0.0f;
+    for (int i = 0; i < splits; ++i) acc = fmaf(src[i * stride + d], weight[i], acc);
+    st(o + d, acc * inv_l);
   }
 }
 
@@ -216,8 +226,8 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
       if (items > 0) {                                                                                           \
         attention_split_kernel<T, D><<<dim3(ceil_div(items, warps), max_splits), warps * 32, smem, s>>>(          \
             a, seq_list, n_list, split_keys, max_splits, scratch);                                               \
-        attention_merge_kernel<T><<<ceil_div(items, warps), warps * 32, 0, s>>>(a, seq_list, n_list, split_keys, \
-                                                                                 max_splits, scratch);           \
+        attention_merge_kernel<T><<<static_cast<int>(items), kMergeThreads, 0, s>>>(a, seq_list, n_list, split_keys, \
+                                                                                    max_splits, scratch);         \
       }                                                                                                          \
     }                                                                                                            \
   } while (0)
@@ -271,7 +281,8 @@ TIE_API int tie_attention_split(int dtype, const void* q, long long q_stride, co
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
                    0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
   if (const int st = check_attn(a)) return st;
-  TIE_REQUIRE(split_keys > 0 && max_splits > 0 && scratch != nullptr, "attention split: bad split geometry");
+  TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
+              "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);
   if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
   if (dtype == TIE_BF16)
     return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
@@ -284,7 +295,8 @@ TIE_API int tie_attention_split(int dtype, const void* q, long long q_stride, co
 TIE_API int tie_attention_merge(int dtype, void* out, const int* query_start, const int* context_lens, int q_heads,
                                 int head_dim, int window, const int* seq_list, int n_list, int split_keys, int max_splits,
                                 const float* scratch, cudaStream_t s) {
-  TIE_REQUIRE(q_heads > 0 && head_dim > 0 && split_keys > 0 && max_splits > 0, "attention merge: bad geometry");
+  TIE_REQUIRE(q_heads > 0 && head_dim > 0 && split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits,
+              "attention merge: bad geometry (at most %d splits)", kMergeMaxSplits);
   if (n_list == 0) return kOk;
   AttnArgs a{};
   a.out = out;
@@ -295,9 +307,9 @@ TIE_API int tie_attention_merge(int dtype, void* out, const int* query_start, co
   a.window = window;
   const long long items = static_cast<long long>(n_list) * q_heads;
   if (dtype == TIE_F32) {
-    attention_merge_kernel<float><<<ceil_div(items, 4), 128, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
+    attention_merge_kernel<float><<<static_cast<int>(items), kMergeThreads, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
   } else if (dtype == TIE_BF16) {
-    attention_merge_kernel<__nv_bfloat16><<<ceil_div(items, 4), 128, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
+    attention_merge_kernel<__nv_bfloat16><<<static_cast<int>(items), kMergeThreads, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
   } else {
     set_error("attention merge: unknown dtype code %d", dtype);
     return kBadArgument;
@@ -326,7 +338,8 @@ TIE_API int tie_attention_split_noalloc(int dtype, const void* q, long long q_st
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
                    0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
   if (const int st = check_attn(a)) return st;
-  TIE_REQUIRE(n_list >= 0 && split_keys > 0 && max_splits > 0, "attention split (no alloc): bad split geometry");
+  TIE_REQUIRE(n_list >= 0 && split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits,
+              "attention split (no alloc): bad split geometry (at most %d splits)", kMergeMaxSplits);
   const long long need = static_cast<long long>(n_list) * q_heads * max_splits * (head_dim + 2);
   TIE_REQUIRE(need <= TIE_NOALLOC_SCRATCH_FLOATS,
               "attention split (no alloc): %d sequences x %d heads x %d splits x (%d + 2) = %lld floats of partial results "

@@ -73,22 +73,31 @@ template <int DH> __device__ __forceinline__ uint32_t swz(int r, int c) {
 }
 
 // Copies keys [key0, key0 + 64) of one kv head (rows of DH elements) from their pages into a
-// swizzled tile; keys outside [lo, hi] are zero-filled and their pages never touched.
+// swizzled K tile and the V tile behind it; keys outside [lo, hi] are zero-filled and their
+// pages never touched. A thread always handles the same 16-byte column of the rows it copies,
+// and the page of a key is looked up once for both planes.
 template <int DH>
-__device__ __forceinline__ void load_kv_tile(uint32_t dst, const __nv_bfloat16* __restrict__ plane,
-                                             const int* __restrict__ table, int kvh, int kv_heads, int page_size, int key0,
-                                             int lo, int hi) {
-  constexpr int CPR = DH / 8;   // chunks per row
-  for (int id = threadIdx.x; id < kKeysPerTile * CPR; id += kAttnThreads) {
-    const int r = id / CPR, c = id % CPR;
+__device__ __forceinline__ void load_kv_tiles(uint32_t k_dst, uint32_t v_dst, const __nv_bfloat16* __restrict__ k_plane,
+                                              const __nv_bfloat16* __restrict__ v_plane, const int* __restrict__ table,
+                                              int kvh, int kv_heads, int page_size, int key0, int lo, int hi) {
+  constexpr int CPR = DH / 8;                       // 16-byte chunks per row
+  constexpr int RPP = kAttnThreads / CPR;           // rows covered by one pass of the block
+  static_assert(kAttnThreads % CPR == 0 && kKeysPerTile % RPP == 0, "tile does not divide among the threads");
+  const int c = threadIdx.x % CPR;
+  const int r0 = threadIdx.x / CPR;
+#pragma unroll
+  for (int p = 0; p < kKeysPerTile / RPP; ++p) {
+    const int r = r0 + p * RPP;
     const int key = key0 + r;
     const bool valid = key >= lo && key <= hi;
-    const __nv_bfloat16* src = plane;
+    long long off = 0;
     if (valid) {
       const int page = table[key / page_size];
-      src = plane + (static_cast<long long>(page * kv_heads + kvh) * page_size + key % page_size) * DH + c * 8;
+      off = (static_cast<long long>(page * kv_heads + kvh) * page_size + key % page_size) * DH + c * 8;
     }
-    cp_async16(dst + swz<DH>(r, c), src, valid ? 16 : 0);
+    const uint32_t sw = swz<DH>(r, c);
+    cp_async16(k_dst + sw, k_plane + off, valid ? 16 : 0);
+    cp_async16(v_dst + sw, v_plane + off, valid ? 16 : 0);
   }
 }
 
@@ -207,8 +216,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_prompt_tc_kernel(AttnTcArgs
   for (int st = 0; st < STAGES - 1; ++st) {
     if (st < n_tiles) {
       const int key0 = (kt_first + st) * kKeysPerTile;
-      load_kv_tile<DH>(kv_base + st * 2 * TILE_BYTES, a.k_cache, table, kvh, a.kv_heads, a.page_size, key0, lo_cta, hi_cta);
-      load_kv_tile<DH>(kv_base + st * 2 * TILE_BYTES + TILE_BYTES, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo_cta, hi_cta);
+      load_kv_tiles<DH>(kv_base + st * 2 * TILE_BYTES, kv_base + st * 2 * TILE_BYTES + TILE_BYTES, a.k_cache, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo_cta, hi_cta);
     }
     cp_async_commit();
   }
@@ -241,8 +249,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_prompt_tc_kernel(AttnTcArgs
     if (nxt < n_tiles) {
       const int key0 = (kt_first + nxt) * kKeysPerTile;
       const uint32_t dst = kv_base + (nxt % STAGES) * 2 * TILE_BYTES;
-      load_kv_tile<DH>(dst, a.k_cache, table, kvh, a.kv_heads, a.page_size, key0, lo_cta, hi_cta);
-      load_kv_tile<DH>(dst + TILE_BYTES, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo_cta, hi_cta);
+      load_kv_tiles<DH>(dst, dst + TILE_BYTES, a.k_cache, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo_cta, hi_cta);
     }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
@@ -320,8 +327,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_tc_kernel(AttnTcArgs
   for (int st = 0; st < STAGES - 1; ++st) {
     if (st < n_tiles) {
       const int key0 = (kt_first + st) * kKeysPerTile;
-      load_kv_tile<DH>(kv_base + st * 2 * TILE_BYTES, a.k_cache, table, kvh, a.kv_heads, a.page_size, key0, lo, hi);
-      load_kv_tile<DH>(kv_base + st * 2 * TILE_BYTES + TILE_BYTES, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo, hi);
+      load_kv_tiles<DH>(kv_base + st * 2 * TILE_BYTES, kv_base + st * 2 * TILE_BYTES + TILE_BYTES, a.k_cache, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo, hi);
     }
     cp_async_commit();
   }
@@ -342,8 +348,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_tc_kernel(AttnTcArgs
     if (nxt < n_tiles) {
       const int key0 = (kt_first + nxt) * kKeysPerTile;
       const uint32_t dst = kv_base + (nxt % STAGES) * 2 * TILE_BYTES;
-      load_kv_tile<DH>(dst, a.k_cache, table, kvh, a.kv_heads, a.page_size, key0, lo, hi);
-      load_kv_tile<DH>(dst + TILE_BYTES, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo, hi);
+      load_kv_tiles<DH>(dst, dst + TILE_BYTES, a.k_cache, a.v_cache, table, kvh, a.kv_heads, a.page_size, key0, lo, hi);
     }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();

@@ -29,9 +29,11 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 //   out[t] = (x[t] * inv) * w,  inv = 1 / sqrt(mean(x[t]^2) + eps)
 // With `rows` non-null, row t of the output comes from row rows[t] of x and delta, and x is
 // not written back (the rows that reach the final norm are the last use of x).
-template <typename T>
+template <typename T, int VPT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
                                    const float* __restrict__ w, float eps, T* __restrict__ out, int dim) {
+  // VPT > 0: every thread keeps its VPT elements (index threadIdx.x + i * blockDim.x) in registers
+  // between the sum and the scaling; VPT == 0: rows longer than that are read twice.
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[t] : t) * dim;
@@ -40,18 +42,40 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   T* o = out + static_cast<size_t>(t) * dim;
   const bool write_back = dr != nullptr && rows == nullptr;
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    float v = xr[i];
-    if (dr) v += ld(dr + i);
-    if (write_back) xr[i] = v;
-    ss += v * v;
-  }
-  ss = block_sum(ss, scratch);
-  const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    float v = xr[i];
-    if (dr && !write_back) v += ld(dr + i);
-    st(o + i, (v * inv) * w[i]);
+  if constexpr (VPT > 0) {
+    float v[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int k = threadIdx.x + i * blockDim.x;
+      v[i] = 0.0f;
+      if (k < dim) {
+        v[i] = xr[k];
+        if (dr) v[i] += ld(dr + k);
+        if (write_back) xr[k] = v[i];
+        ss += v[i] * v[i];
+      }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int k = threadIdx.x + i * blockDim.x;
+      if (k < dim) st(o + k, (v[i] * inv) * w[k]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      float v = xr[i];
+      if (dr) v += ld(dr + i);
+      if (write_back) xr[i] = v;
+      ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      float v = xr[i];
+      if (dr && !write_back) v += ld(dr + i);
+      st(o + i, (v * inv) * w[i]);
+    }
   }
 }
 
@@ -206,8 +230,12 @@ template <typename T>
 int launch_add_rmsnorm(float* x, const void* delta, const int* rows, const float* w, float eps, void* out, int n,
                        int dim, cudaStream_t s) {
   if (n == 0) return kOk;
-  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
-  add_rmsnorm_kernel<T><<<n, threads, 0, s>>>(x, static_cast<const T*>(delta), rows, w, eps, static_cast<T*>(out), dim);
+  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
+  const T* d = static_cast<const T*>(delta);
+  T* o = static_cast<T*>(out);
+  if (dim <= 4 * threads) add_rmsnorm_kernel<T, 4><<<n, threads, 0, s>>>(x, d, rows, w, eps, o, dim);
+  else if (dim <= 16 * threads) add_rmsnorm_kernel<T, 16><<<n, threads, 0, s>>>(x, d, rows, w, eps, o, dim);
+  else add_rmsnorm_kernel<T, 0><<<n, threads, 0, s>>>(x, d, rows, w, eps, o, dim);
   TIE_RETURN_LAUNCH("add_rmsnorm");
 }
 

@@ -29,18 +29,20 @@ def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
 
     Up to 256 tokens the weights take the 128-row side of the MMA and the tokens the narrow side
     (width = the smallest of 16, 32, 64, 128, 256 that holds them): the product is bound by
-    streaming the weights, and k is cut into splits so that about two CTAs per SM pull bytes,
-    as long as the float partial sums stay a few percent of the weight bytes. More tokens:
-    128-token row tiles against 256-wide weight tiles."""
+    streaming the weights, and k is cut into splits so that every SM has a CTA pulling bytes.
+    More tokens: 128-token row tiles against 256-wide weight tiles."""
     k_blocks = math.ceil(K / 64)
     if M <= 256:
         bn = next(b for b in (16, 32, 64, 128, 256) if b >= M)
         tiles = math.ceil(N / 128)
         splits = 1
-        if tiles < 2 * NUM_SMS:
-            want = max(1, round(2 * NUM_SMS / tiles))
-            cap_traffic = max(1, K // (80 * M))            # partial sums (write + read) under 5 % of the weight bytes
-            cap_depth = max(1, k_blocks // 4)              # at least 4 k-blocks per split
+        if tiles < NUM_SMS:
+            # One CTA fits on an SM: as many splits as keep all CTAs resident at once (a second
+            # wave costs more than it gains), while the float partial sums (written and read
+            # once) stay under a tenth of the weight bytes and a split keeps 4 k-blocks.
+            want = NUM_SMS // tiles
+            cap_traffic = max(1, K // (40 * M))
+            cap_depth = max(1, k_blocks // 4)
             splits = max(1, min(want, cap_traffic, cap_depth))
         return 1, bn, splits
     bn = next((b for b in (16, 32, 64, 128, 256) if b >= N), 256)
