@@ -361,3 +361,12 @@ TINY_D = {
     "max_position_embeddings": 2048, "rms_norm_eps": 1e-6, "rope_theta": 500000.0,
     "tie_word_embeddings": False,
 }
+# A fifth one wide enough (hidden 1024, head size 128) that decode-sized matrix products are cut
+# along k and hand their partial sums to the kernels behind them, as they do at real sizes.
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "vocab_size": 300, "hidden_size": 1024, "intermediate_size": 1536, "num_hidden_layers": 1,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": True,
+}

@@ -14,7 +14,7 @@ def engine_for(model_dir, dtype="float32", **kw):
     return load_engine(model_dir, dtype=dtype, **kw)
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
 def test_greedy_and_sampled_generation_match_the_plain_implementation(tiny_models, name):
     from tiny_inference_engine_b200 import SamplingParams
     cfg, page, w, d = tiny_models[name]

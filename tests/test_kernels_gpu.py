@@ -421,3 +421,66 @@ def test_tensor_core_attention_refuses_other_sizes(ops):
     assert not ops.attention_tc_takes(q, 2, 1, 48)
     assert not ops.attention_tc_takes(torch.zeros(4, 34 * 64, device="cuda", dtype=torch.bfloat16), 34, 2, 64)
     assert not ops.attention_tc_takes(torch.zeros(4, 128, device="cuda"), 2, 1, 64)
+
+
+def test_split_products_hand_partial_sums_to_their_consumers(ops):
+    """A decode-sized product whose k range is cut leaves float partial sums; the add+norm kernel and
+    the q/k norm + RoPE + append kernel add them up themselves. Same numbers as the unsplit way."""
+    rng = np.random.default_rng(3)
+    M, D, K = 5, 1024, 2048
+    a, w = as_stored(rng.standard_normal((M, K)), "bfloat16"), as_stored(rng.standard_normal((D, K)) * 0.05, "bfloat16")
+    bufs = {}
+    got = ops.gemm(dev(a, torch.bfloat16), dev(w, torch.bfloat16), torch.empty(M, D, device="cuda", dtype=torch.bfloat16),
+                   partial_scratch=lambda n: bufs.setdefault("p", torch.empty(n, device="cuda")))
+    assert isinstance(got, ops.SplitSum) and got.splits > 1 and (got.M, got.N) == (M, D)
+    prod = plain.linear(a, w)
+    whole = got.materialize(torch.empty(M, D, device="cuda"))
+    assert rel_err(host(whole), prod) < 2e-5
+    # residual add + norm straight from the partial sums
+    x = rng.standard_normal((M, D)).astype(np.float32)
+    wn = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    xd, out = dev(x), torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
+    ops.add_rmsnorm(xd, got, dev(wn), 1e-6, out)
+    assert np.abs(host(xd) - (x + prod)).max() < 1e-4 * np.abs(prod).max()
+    assert rel_err(host(out), plain.rms_norm(x + prod, wn, 1e-6)) < TOL["bfloat16"]
+    rows = np.array([4, 1])
+    out2, x2 = torch.empty(2, D, device="cuda", dtype=torch.bfloat16), dev(x)
+    ops.add_rmsnorm(x2, got, dev(wn), 1e-6, out2, rows=dev(rows, torch.int32))
+    assert np.array_equal(host(x2), x) and rel_err(host(out2), plain.rms_norm((x + prod)[rows], wn, 1e-6)) < TOL["bfloat16"]
+    # q/k norm + RoPE + append from the partial sums of a q,k,v product
+    Hq, Hkv, Dh, page = 4, 2, 128, 16
+    width = (Hq + 2 * Hkv) * Dh
+    wq = as_stored(rng.standard_normal((width, K)) * 0.05, "bfloat16")
+    qkv = torch.zeros(M, width, device="cuda", dtype=torch.bfloat16)
+    ps = ops.gemm(dev(a, torch.bfloat16), dev(wq, torch.bfloat16), qkv,
+                  partial_scratch=lambda n: bufs.setdefault("q", torch.empty(n, device="cuda")))
+    assert isinstance(ps, ops.SplitSum)
+    full = plain.linear(a, wq)
+    qw, kw = (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32), (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32)
+    pos, slots = np.array([0, 5, 77, 1000, 3]), np.array([3, 17, 40, -1, 8])
+    kc, vc = torch.zeros(4, Hkv, page, Dh, device="cuda", dtype=torch.bfloat16), torch.zeros(4, Hkv, page, Dh, device="cuda", dtype=torch.bfloat16)
+    ops.qk_norm_rope_append(qkv, dev(qw), dev(kw), 1e-6, 1e-6, dev(plain.rope_inv_freq(1e6, Dh)), dev(pos, torch.int32),
+                            dev(slots, torch.int32), kc, vc, Hq, Hkv, Dh, partial=ps)
+    q, k, v = full[:, :Hq * Dh], full[:, Hq * Dh:(Hq + Hkv) * Dh], full[:, (Hq + Hkv) * Dh:]
+    want_q = plain.rope_neox(plain.rms_norm(q.reshape(M * Hq, Dh), qw, 1e-6).reshape(M, -1), pos, Hq, Dh, 1e6)
+    want_k = plain.rope_neox(plain.rms_norm(k.reshape(M * Hkv, Dh), kw, 1e-6).reshape(M, -1), pos, Hkv, Dh, 1e6)
+    assert rel_err(host(qkv)[:, :Hq * Dh], want_q) < TOL["bfloat16"]
+    for t in range(M):
+        if slots[t] >= 0:
+            p, o = slots[t] // page, slots[t] % page
+            assert rel_err(host(kc)[p, :, o].reshape(1, -1), want_k[t].reshape(1, -1)) < TOL["bfloat16"]
+            assert rel_err(host(vc)[p, :, o].reshape(1, -1), v[t].reshape(1, -1)) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("M", [1, 7, 64, 200, 300, 700])
+@pytest.mark.parametrize("I,K", [(16, 64), (48, 72), (208, 136), (1536, 1024)])
+def test_gemm_with_silu_epilogue(ops, M, I, K):
+    """silu(a gate^T) * (a up^T) in the product's epilogue, both tilings, widths that end inside a tile."""
+    rng = np.random.default_rng(M + I)
+    a = as_stored(rng.standard_normal((M, K)), "bfloat16")
+    gate, up = as_stored(rng.standard_normal((I, K)) * 0.2, "bfloat16"), as_stored(rng.standard_normal((I, K)) * 0.2, "bfloat16")
+    w = ops.interleave_gate_up(dev(gate, torch.bfloat16), dev(up, torch.bfloat16))
+    assert np.array_equal(host(w)[:16], gate[:16]) and np.array_equal(host(w)[16:32], up[:16])
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_silu(dev(a, torch.bfloat16), w, out)
+    assert rel_err(host(out), plain.swiglu(plain.linear(a, gate), plain.linear(a, up))) < TOL["bfloat16"]

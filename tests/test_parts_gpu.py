@@ -16,6 +16,14 @@ def dev(a, dtype=torch.float32):
     return torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(dtype)
 
 
+def to_host(result, dtype):
+    """What a part returned (a tensor, or the partial sums of a split product) as a float numpy array."""
+    from tiny_inference_engine_b200 import ops
+    if isinstance(result, ops.SplitSum):
+        result = result.materialize(torch.empty(result.M, result.N, device="cuda", dtype=DT[dtype]))
+    return result.float().cpu().numpy()
+
+
 class DictSource:
     """A TensorSource over numpy arrays."""
 
@@ -80,7 +88,7 @@ def test_attention_part_alone(dtype):
             assert cache.reserve(req, pos + n)
             ctx = runner.prepare([StepEntry(req, [0] * n, pos, [])])
             out = mixer.forward(dev(h[pos:pos + n], DT[dtype]), ctx, cache.layer_cache(1, writes=True), None)
-            got.append(out.float().cpu().numpy())
+            got.append(to_host(out, dtype))
             pos += n
         cache.release(req)
         assert rel_err(np.concatenate(got), want) < TOL[dtype] * (1 if dtype == "float32" else 0.6)
@@ -102,7 +110,7 @@ def test_feed_forward_norm_and_block_alone(dtype):
     cache.reserve(req, T)
     ctx = runner.prepare([StepEntry(req, [0] * T, 0, [])])
     block = model.layers[0]
-    got = block.ffn.forward(dev(h, DT[dtype]), ctx).float().cpu().numpy()
+    got = to_host(block.ffn.forward(dev(h, DT[dtype]), ctx), dtype)
     assert rel_err(got, plain.mlp_block(h, w, "model.layers.0.")) < TOL[dtype]
     # the norm part: x += delta, h = norm(x)
     x = rng.standard_normal((T, D)).astype(np.float32)
@@ -114,7 +122,7 @@ def test_feed_forward_norm_and_block_alone(dtype):
     xd = dev(x)
     pending = block.forward(xd, None, ctx, cache.layer_cache(0, writes=True), None)
     torch.cuda.synchronize()
-    got_x = xd.cpu().numpy().astype(np.float64) + pending.float().cpu().numpy()
+    got_x = xd.cpu().numpy().astype(np.float64) + to_host(pending, dtype)
     want_x = plain.decoder_layer(x.astype(np.float64), w, 0, cfg, np.arange(T))
     assert rel_err(got_x, want_x) < TOL[dtype]
     cache.release(req)

@@ -90,6 +90,7 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
 
 template <typename T, int DPL>
 __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
+  pdl_sync();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
@@ -125,6 +126,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
 template <typename T, int DPL>
 __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const int* __restrict__ seq_list, int n_list,
                                                               int split_keys, int max_splits, float* __restrict__ scratch) {
+  pdl_sync();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.y;
@@ -172,6 +174,7 @@ template <typename T>
 __global__ void __launch_bounds__(kMergeThreads) attention_merge_kernel(AttnArgs a, const int* __restrict__ seq_list,
                                                                         int n_list, int split_keys, int max_splits,
                                                                         const float* __restrict__ scratch) {
+  pdl_sync();
   __shared__ float weight[kMergeMaxSplits];
   __shared__ float inv_l;
   const int item = blockIdx.x;
@@ -220,13 +223,13 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
   do {                                                                                                           \
     if (rows_kernel) {                                                                                           \
       const long long items = static_cast<long long>(a.rows) * a.q_heads;                                        \
-      if (items > 0) attention_rows_kernel<T, D><<<ceil_div(items, warps), warps * 32, smem, s>>>(a);            \
+      if (items > 0) TIE_LAUNCH((attention_rows_kernel<T, D>), ceil_div(items, warps), warps * 32, smem, s, a);            \
     } else {                                                                                                     \
       const long long items = static_cast<long long>(n_list) * a.q_heads;                                        \
       if (items > 0) {                                                                                           \
-        attention_split_kernel<T, D><<<dim3(ceil_div(items, warps), max_splits), warps * 32, smem, s>>>(          \
+        TIE_LAUNCH((attention_split_kernel<T, D>), dim3(ceil_div(items, warps), max_splits), warps * 32, smem, s,           \
             a, seq_list, n_list, split_keys, max_splits, scratch);                                               \
-        attention_merge_kernel<T><<<static_cast<int>(items), kMergeThreads, 0, s>>>(a, seq_list, n_list, split_keys, \
+        TIE_LAUNCH((attention_merge_kernel<T>), static_cast<int>(items), kMergeThreads, 0, s, a, seq_list, n_list, split_keys, \
                                                                                     max_splits, scratch);         \
       }                                                                                                          \
     }                                                                                                            \
@@ -307,9 +310,9 @@ TIE_API int tie_attention_merge(int dtype, void* out, const int* query_start, co
   a.window = window;
   const long long items = static_cast<long long>(n_list) * q_heads;
   if (dtype == TIE_F32) {
-    attention_merge_kernel<float><<<static_cast<int>(items), kMergeThreads, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
+    TIE_LAUNCH((attention_merge_kernel<float>), static_cast<int>(items), kMergeThreads, 0, s, a, seq_list, n_list, split_keys, max_splits, scratch);
   } else if (dtype == TIE_BF16) {
-    attention_merge_kernel<__nv_bfloat16><<<static_cast<int>(items), kMergeThreads, 0, s>>>(a, seq_list, n_list, split_keys, max_splits, scratch);
+    TIE_LAUNCH((attention_merge_kernel<__nv_bfloat16>), static_cast<int>(items), kMergeThreads, 0, s, a, seq_list, n_list, split_keys, max_splits, scratch);
   } else {
     set_error("attention merge: unknown dtype code %d", dtype);
     return kBadArgument;

@@ -179,6 +179,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
 // Prompt portions. grid = (row tiles of 64, kv heads, sequences with several tokens).
 template <int DH, int STAGES>
 __global__ void __launch_bounds__(kAttnThreads) attn_prompt_tc_kernel(AttnTcArgs a) {
+  pdl_sync();
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int TILE_BYTES = kKeysPerTile * DH * 2;
   const uint32_t q_tile = smem_addr(smem);                       // 64 rows x DH
@@ -295,6 +296,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_prompt_tc_kernel(AttnTcArgs
 // Sequences that bring one token. grid = (sequences of seq_list, kv heads, splits).
 template <int DH, int STAGES>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_tc_kernel(AttnTcArgs a, int n_list) {
+  pdl_sync();
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int TILE_BYTES = kKeysPerTile * DH * 2;
   const uint32_t q_tile = smem_addr(smem);                       // 16 rows x DH
@@ -430,7 +432,7 @@ static int launch_prompt(const AttnTcArgs& a, int n_seqs, int max_rows, cudaStre
     }
     configured = true;
   }
-  attn_prompt_tc_kernel<DH, STAGES><<<dim3(ceil_div(max_rows, 64), a.kv_heads, n_seqs), kAttnThreads, smem, s>>>(a);
+  TIE_LAUNCH((attn_prompt_tc_kernel<DH, STAGES>), dim3(ceil_div(max_rows, 64), a.kv_heads, n_seqs), kAttnThreads, smem, s, a);
   return kOk;
 }
 
@@ -448,7 +450,7 @@ static int launch_decode(const AttnTcArgs& a, int n_list, cudaStream_t s) {
     }
     configured = true;
   }
-  attn_decode_tc_kernel<DH, STAGES><<<dim3(n_list, a.kv_heads, a.max_splits), kAttnThreads, smem, s>>>(a, n_list);
+  TIE_LAUNCH((attn_decode_tc_kernel<DH, STAGES>), dim3(n_list, a.kv_heads, a.max_splits), kAttnThreads, smem, s, a, n_list);
   return kOk;
 }
 

@@ -96,7 +96,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
 
+// Programmatic dependent launch. Every kernel of this library starts with pdl_sync(): it waits
+// until the kernels before it in the stream have completed and their writes are visible,
+// then lets the kernel after it be scheduled. So the next kernel's blocks are already resident
+// (launch latency, block scheduling and whatever they do before their own pdl_sync() are hidden
+// behind this kernel) and start the moment this one is done. Nothing may touch global memory
+// before pdl_sync().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() {
+  pdl_wait();
+  pdl_launch_dependents();
+}
+
+bool pdl_enabled();   // false when the environment sets TIE_NO_PDL=1
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in cudaGetLastError()
+}
+
 }  // namespace tie
+
+#define TIE_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  tie::launch_kernel(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__)
 
 #define TIE_API extern "C" __attribute__((visibility("default")))
 

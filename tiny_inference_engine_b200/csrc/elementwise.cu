@@ -15,6 +15,7 @@ namespace tie {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                              int dim, int vocab) {
+  pdl_sync();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; never read outside the table
@@ -29,9 +30,13 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 //   out[t] = (x[t] * inv) * w,  inv = 1 / sqrt(mean(x[t]^2) + eps)
 // With `rows` non-null, row t of the output comes from row rows[t] of x and delta, and x is
 // not written back (the rows that reach the final norm are the last use of x).
+// The delta may also come as float partial sums of a split matrix product: part[z][row][dim],
+// z < splits, part_stride floats apart; they are added in split order.
 template <typename T, int VPT>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ part,
+                                   long long part_stride, int splits, const int* __restrict__ rows,
                                    const float* __restrict__ w, float eps, T* __restrict__ out, int dim) {
+  pdl_sync();
   // VPT > 0: every thread keeps its VPT elements (index threadIdx.x + i * blockDim.x) in registers
   // between the sum and the scaling; VPT == 0: rows longer than that are read twice.
   __shared__ float scratch[33];
@@ -39,8 +44,16 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   const size_t src = static_cast<size_t>(rows ? rows[t] : t) * dim;
   float* xr = x + src;
   const T* dr = delta ? delta + src : nullptr;
+  const float* pr = part ? part + src : nullptr;
   T* o = out + static_cast<size_t>(t) * dim;
-  const bool write_back = dr != nullptr && rows == nullptr;
+  const bool has_delta = dr != nullptr || pr != nullptr;
+  const bool write_back = has_delta && rows == nullptr;
+  auto delta_at = [&](int k) -> float {
+    if (dr) return ld(dr + k);
+    float acc = pr[k];
+    for (int z = 1; z < splits; ++z) acc += pr[static_cast<long long>(z) * part_stride + k];
+    return acc;
+  };
   float ss = 0.0f;
   if constexpr (VPT > 0) {
     float v[VPT];
@@ -50,7 +63,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
       v[i] = 0.0f;
       if (k < dim) {
         v[i] = xr[k];
-        if (dr) v[i] += ld(dr + k);
+        if (has_delta) v[i] += delta_at(k);
         if (write_back) xr[k] = v[i];
         ss += v[i] * v[i];
       }
@@ -65,7 +78,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   } else {
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
       float v = xr[i];
-      if (dr) v += ld(dr + i);
+      if (has_delta) v += delta_at(i);
       if (write_back) xr[i] = v;
       ss += v * v;
     }
@@ -73,7 +86,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
       float v = xr[i];
-      if (dr && !write_back) v += ld(dr + i);
+      if (has_delta && !write_back) v += delta_at(i);
       st(o + i, (v * inv) * w[i]);
     }
   }
@@ -85,6 +98,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 template <typename T>
 __global__ void rmsnorm_rows_kernel(const T* __restrict__ x, long long row_stride, const float* __restrict__ w,
                                     float eps, T* __restrict__ out, long long out_stride, int size, long long n) {
+  pdl_sync();
   const long long r = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= n) return;
   const int lane = threadIdx.x & 31;
@@ -104,6 +118,7 @@ __global__ void rmsnorm_rows_kernel(const T* __restrict__ x, long long row_strid
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(g) = g / (1 + exp(-g)).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, long long total) {
+  pdl_sync();
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long t = idx / inter;
@@ -119,6 +134,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 template <typename T>
 __global__ void rope_kernel(T* __restrict__ x, long long row_stride, const int* __restrict__ positions,
                             const float* __restrict__ inv_freq, int heads, int head_dim, int rot, long long total) {
+  pdl_sync();
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int half = rot / 2;
@@ -140,6 +156,7 @@ template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ v, long long k_stride,
                                  long long v_stride, const int* __restrict__ slots, T* __restrict__ k_cache,
                                  T* __restrict__ v_cache, int kv_heads, int head_dim, int page_size, long long total) {
+  pdl_sync();
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int d = static_cast<int>(idx % head_dim);
@@ -160,13 +177,18 @@ __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ 
 //   v heads: copied to the value plane at the token's slot.
 // qkv is [T, (Hq + 2 Hkv) * Dh] with q first, then k, then v. With write_kv == 0 only the q
 // heads are processed (a layer that reads another layer's cache). inv_freq null = no rotation.
+// With `part` non-null the q, k, v values are read as the sum of `splits` float partial sums
+// part[z][t][width] (the split product that made them) instead of from qkv; q still goes to qkv.
 template <typename T>
-__global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ qw,
+__global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ part,
+                                           long long part_stride, int splits, long long part_ld,
+                                           const float* __restrict__ qw,
                                            const float* __restrict__ kw, float q_eps, float k_eps,
                                            const float* __restrict__ inv_freq, int rot,
                                            const int* __restrict__ positions, const int* __restrict__ slots,
                                            T* __restrict__ k_cache, T* __restrict__ v_cache, int q_heads, int kv_heads,
                                            int head_dim, int page_size, int heads_per_token, long long total) {
+  pdl_sync();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
@@ -174,6 +196,13 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
   const long long t = item / heads_per_token;
   const int head = static_cast<int>(item - t * heads_per_token);
   T* src = qkv + t * row_stride + static_cast<long long>(head) * head_dim;
+  const float* psrc = part ? part + t * part_ld + static_cast<long long>(head) * head_dim : nullptr;
+  auto value = [&](int i) -> float {
+    if (!psrc) return ld(src + i);
+    float acc = psrc[i];
+    for (int z = 1; z < splits; ++z) acc += psrc[static_cast<long long>(z) * part_stride + i];
+    return acc;
+  };
   float* buf = smem + warp * head_dim;
 
   const bool is_q = head < q_heads;
@@ -186,7 +215,11 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
     const long long page = slot / page_size, off = slot % page_size;
     dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + h) * page_size + off) * head_dim;
     if (!is_k) {  // values are stored as they are
-      for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+      if (psrc) {
+        for (int i = lane; i < head_dim; i += 32) st(dst + i, value(i));
+      } else {
+        for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+      }
       return;
     }
   }
@@ -194,7 +227,7 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
   const float* w = is_q ? qw : kw;
   float ss = 0.0f;
   for (int i = lane; i < head_dim; i += 32) {
-    const float v = ld(src + i);
+    const float v = value(i);
     buf[i] = v;
     ss += v * v;
   }
@@ -222,20 +255,20 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
 template <typename T>
 int launch_embed(const void* table, const int* ids, float* x, int tokens, int dim, int vocab, cudaStream_t s) {
   if (tokens == 0) return kOk;
-  embed_kernel<T><<<tokens, dim >= 1024 ? 256 : 128, 0, s>>>(static_cast<const T*>(table), ids, x, dim, vocab);
+  TIE_LAUNCH((embed_kernel<T>), tokens, dim >= 1024 ? 256 : 128, 0, s, static_cast<const T*>(table), ids, x, dim, vocab);
   TIE_RETURN_LAUNCH("embed");
 }
 
 template <typename T>
-int launch_add_rmsnorm(float* x, const void* delta, const int* rows, const float* w, float eps, void* out, int n,
-                       int dim, cudaStream_t s) {
+int launch_add_rmsnorm(float* x, const void* delta, const float* part, long long part_stride, int splits,
+                       const int* rows, const float* w, float eps, void* out, int n, int dim, cudaStream_t s) {
   if (n == 0) return kOk;
   const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
   const T* d = static_cast<const T*>(delta);
   T* o = static_cast<T*>(out);
-  if (dim <= 4 * threads) add_rmsnorm_kernel<T, 4><<<n, threads, 0, s>>>(x, d, rows, w, eps, o, dim);
-  else if (dim <= 16 * threads) add_rmsnorm_kernel<T, 16><<<n, threads, 0, s>>>(x, d, rows, w, eps, o, dim);
-  else add_rmsnorm_kernel<T, 0><<<n, threads, 0, s>>>(x, d, rows, w, eps, o, dim);
+  if (dim <= 4 * threads) TIE_LAUNCH((add_rmsnorm_kernel<T, 4>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
+  else if (dim <= 16 * threads) TIE_LAUNCH((add_rmsnorm_kernel<T, 16>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
+  else TIE_LAUNCH((add_rmsnorm_kernel<T, 0>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
   TIE_RETURN_LAUNCH("add_rmsnorm");
 }
 
@@ -243,7 +276,7 @@ template <typename T>
 int launch_rmsnorm_rows(const void* x, long long xs, const float* w, float eps, void* out, long long os, int size,
                         long long n, cudaStream_t s) {
   if (n == 0) return kOk;
-  rmsnorm_rows_kernel<T><<<ceil_div(n, 4), 128, 0, s>>>(static_cast<const T*>(x), xs, w, eps, static_cast<T*>(out), os,
+  TIE_LAUNCH((rmsnorm_rows_kernel<T>), ceil_div(n, 4), 128, 0, s, static_cast<const T*>(x), xs, w, eps, static_cast<T*>(out), os,
                                                          size, n);
   TIE_RETURN_LAUNCH("rmsnorm_rows");
 }
@@ -252,7 +285,7 @@ template <typename T>
 int launch_silu_mul(const void* gu, void* out, int tokens, int inter, cudaStream_t s) {
   const long long total = static_cast<long long>(tokens) * inter;
   if (total == 0) return kOk;
-  silu_mul_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(static_cast<const T*>(gu), static_cast<T*>(out), inter, total);
+  TIE_LAUNCH((silu_mul_kernel<T>), ceil_div(total, 256), 256, 0, s, static_cast<const T*>(gu), static_cast<T*>(out), inter, total);
   TIE_RETURN_LAUNCH("silu_mul");
 }
 
@@ -261,7 +294,7 @@ int launch_rope(void* x, long long stride, const int* pos, const float* inv_freq
                 int rot, cudaStream_t s) {
   const long long total = static_cast<long long>(tokens) * heads * (rot / 2);
   if (total == 0) return kOk;
-  rope_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(static_cast<T*>(x), stride, pos, inv_freq, heads, head_dim, rot,
+  TIE_LAUNCH((rope_kernel<T>), ceil_div(total, 256), 256, 0, s, static_cast<T*>(x), stride, pos, inv_freq, heads, head_dim, rot,
                                                       total);
   TIE_RETURN_LAUNCH("rope");
 }
@@ -271,14 +304,15 @@ int launch_kv_append(const void* k, const void* v, long long ks, long long vs, c
                      int tokens, int kv_heads, int head_dim, int page_size, cudaStream_t s) {
   const long long total = static_cast<long long>(tokens) * kv_heads * head_dim;
   if (total == 0) return kOk;
-  kv_append_kernel<T><<<ceil_div(total, 256), 256, 0, s>>>(static_cast<const T*>(k), static_cast<const T*>(v), ks, vs,
+  TIE_LAUNCH((kv_append_kernel<T>), ceil_div(total, 256), 256, 0, s, static_cast<const T*>(k), static_cast<const T*>(v), ks, vs,
                                                            slots, static_cast<T*>(kc), static_cast<T*>(vc), kv_heads,
                                                            head_dim, page_size, total);
   TIE_RETURN_LAUNCH("kv_append");
 }
 
 template <typename T>
-int launch_qk_norm_rope_append(void* qkv, long long stride, const float* qw, const float* kw, float q_eps, float k_eps,
+int launch_qk_norm_rope_append(void* qkv, long long stride, const float* part, long long part_stride, int splits,
+                               long long part_ld, const float* qw, const float* kw, float q_eps, float k_eps,
                                const float* inv_freq, int rot, const int* pos, const int* slots, void* kc, void* vc,
                                int tokens, int q_heads, int kv_heads, int head_dim, int page_size, int write_kv,
                                cudaStream_t s) {
@@ -287,8 +321,9 @@ int launch_qk_norm_rope_append(void* qkv, long long stride, const float* qw, con
   if (total == 0) return kOk;
   const int warps = 4;
   const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
-  qk_norm_rope_append_kernel<T><<<ceil_div(total, warps), warps * 32, smem, s>>>(
-      static_cast<T*>(qkv), stride, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots, static_cast<T*>(kc),
+  TIE_LAUNCH((qk_norm_rope_append_kernel<T>), ceil_div(total, warps), warps * 32, smem, s, 
+      static_cast<T*>(qkv), stride, part, part_stride, splits, part_ld, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots,
+      static_cast<T*>(kc),
       static_cast<T*>(vc), q_heads, kv_heads, head_dim, page_size, heads_per_token, total);
   TIE_RETURN_LAUNCH("qk_norm_rope_append");
 }
@@ -312,12 +347,15 @@ TIE_API int tie_embed(int dtype, const void* table, const int* ids, float* x, in
                launch_embed<__nv_bfloat16>(table, ids, x, tokens, dim, vocab, s));
 }
 
-// rows may be null (row t of out from row t of x); delta may be null (no add).
-TIE_API int tie_add_rmsnorm(int dtype, float* x, const void* delta, const int* rows, const float* w, float eps,
-                            void* out, int n, int dim, cudaStream_t s) {
+// rows may be null (row t of out from row t of x); delta may be null (no add), or given as
+// `splits` float partial sums at part (then delta must be null).
+TIE_API int tie_add_rmsnorm(int dtype, float* x, const void* delta, const float* part, long long part_stride,
+                            int splits, const int* rows, const float* w, float eps, void* out, int n, int dim,
+                            cudaStream_t s) {
   TIE_REQUIRE(n >= 0 && dim > 0, "add_rmsnorm: bad sizes n=%d dim=%d", n, dim);
-  TIE_DISPATCH(dtype, launch_add_rmsnorm<float>(x, delta, rows, w, eps, out, n, dim, s),
-               launch_add_rmsnorm<__nv_bfloat16>(x, delta, rows, w, eps, out, n, dim, s));
+  TIE_REQUIRE(part == nullptr || (delta == nullptr && splits >= 1), "add_rmsnorm: give a delta or partial sums, not both");
+  TIE_DISPATCH(dtype, launch_add_rmsnorm<float>(x, delta, part, part_stride, splits, rows, w, eps, out, n, dim, s),
+               launch_add_rmsnorm<__nv_bfloat16>(x, delta, part, part_stride, splits, rows, w, eps, out, n, dim, s));
 }
 
 TIE_API int tie_rmsnorm_rows(int dtype, const void* x, long long x_stride, const float* w, float eps, void* out,
@@ -351,7 +389,8 @@ TIE_API int tie_kv_append(int dtype, const void* k, const void* v, long long k_s
                                                head_dim, page_size, s));
 }
 
-TIE_API int tie_qk_norm_rope_append(int dtype, void* qkv, long long stride, const float* qw, const float* kw,
+TIE_API int tie_qk_norm_rope_append(int dtype, void* qkv, long long stride, const float* part, long long part_stride,
+                                    int splits, long long part_ld, const float* qw, const float* kw,
                                     float q_eps, float k_eps, const float* inv_freq, int rot, const int* pos,
                                     const int* slots, void* k_cache, void* v_cache, int tokens, int q_heads,
                                     int kv_heads, int head_dim, int page_size, int write_kv, cudaStream_t s) {
@@ -360,9 +399,10 @@ TIE_API int tie_qk_norm_rope_append(int dtype, void* qkv, long long stride, cons
   TIE_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= head_dim,
               "qk_norm_rope_append: rotary dim %d must be even and at most head_dim %d", rot, head_dim);
   TIE_DISPATCH(dtype,
-               launch_qk_norm_rope_append<float>(qkv, stride, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots, k_cache,
+               launch_qk_norm_rope_append<float>(qkv, stride, part, part_stride, splits, part_ld, qw, kw, q_eps, k_eps,
+                                                 inv_freq, rot, pos, slots, k_cache,
                                                  v_cache, tokens, q_heads, kv_heads, head_dim, page_size, write_kv, s),
-               launch_qk_norm_rope_append<__nv_bfloat16>(qkv, stride, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots,
-                                                         k_cache, v_cache, tokens, q_heads, kv_heads, head_dim,
+               launch_qk_norm_rope_append<__nv_bfloat16>(qkv, stride, part, part_stride, splits, part_ld, qw, kw, q_eps,
+                                                         k_eps, inv_freq, rot, pos, slots, k_cache, v_cache, tokens, q_heads, kv_heads, head_dim,
                                                          page_size, write_kv, s));
 }

@@ -1,6 +1,7 @@
 // The last error message of a launcher, per thread, and the library's version probe.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -12,6 +13,13 @@ void set_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_error, sizeof(g_error), fmt, ap);
   va_end(ap);
+}
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("TIE_NO_PDL");
+    return !(v != nullptr && v[0] == '1');
+  }();
+  return on;
 }
 }  // namespace tie
 

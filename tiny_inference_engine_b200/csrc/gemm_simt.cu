@@ -17,6 +17,7 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) gemm_tiled_kernel(const TI* __restrict__ a, const TI* __restrict__ w,
                                                          TO* __restrict__ out, int M, int N, int K, long long lda,
                                                          long long ldw, long long ldo) {
+  pdl_sync();
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float as[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
@@ -70,6 +71,7 @@ template <typename TI, typename TO, int MT>
 __global__ void __launch_bounds__(256) gemm_small_m_kernel(const TI* __restrict__ a, const TI* __restrict__ w,
                                                            TO* __restrict__ out, int M, int N, int K, long long lda,
                                                            long long ldw, long long ldo) {
+  pdl_sync();
   constexpr int V = Vec16<TI>::N;
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -110,13 +112,13 @@ int launch_gemm(const void* a, const void* w, void* out, int M, int N, int K, lo
   if (M <= 16 && vec_ok) {
     const dim3 block(256);
     if (M <= 4) {
-      gemm_small_m_kernel<TI, TO, 4><<<dim3(ceil_div(N, 8), 1), block, 0, s>>>(ap, wp, op, M, N, K, lda, ldw, ldo);
+      TIE_LAUNCH((gemm_small_m_kernel<TI, TO, 4>), dim3(ceil_div(N, 8), 1), block, 0, s, ap, wp, op, M, N, K, lda, ldw, ldo);
     } else {
-      gemm_small_m_kernel<TI, TO, 8><<<dim3(ceil_div(N, 8), ceil_div(M, 8)), block, 0, s>>>(ap, wp, op, M, N, K, lda,
+      TIE_LAUNCH((gemm_small_m_kernel<TI, TO, 8>), dim3(ceil_div(N, 8), ceil_div(M, 8)), block, 0, s, ap, wp, op, M, N, K, lda,
                                                                                             ldw, ldo);
     }
   } else {
-    gemm_tiled_kernel<TI, TO><<<dim3(ceil_div(N, 64), ceil_div(M, 64)), 256, 0, s>>>(ap, wp, op, M, N, K, lda, ldw, ldo);
+    TIE_LAUNCH((gemm_tiled_kernel<TI, TO>), dim3(ceil_div(N, 64), ceil_div(M, 64)), 256, 0, s, ap, wp, op, M, N, K, lda, ldw, ldo);
   }
   TIE_RETURN_LAUNCH("gemm_simt");
 }

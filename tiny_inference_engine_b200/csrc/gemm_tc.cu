@@ -133,7 +133,8 @@ template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, OutT* __restrict__ out,
                float* __restrict__ partial, long long part_stride, long long ldp, int rows_x, int rows_y, int k_blocks,
-               int k_blocks_per_split, long long ldo, int transposed, int* status) {
+               int k_blocks_per_split, long long ldo, int transposed, int silu, int* status) {
+  pdl_launch_dependents();   // the next kernel may get resident now; it waits for this one at its own pdl_wait()
   using C = TcConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -169,10 +170,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t tmem_acc = *tmem_holder;
 
   if (warp == 4) {
-    // ---- TMA producer
+    // ---- TMA producer. The weights never change, so their tiles of the first stages are fetched
+    // before this kernel waits for the one before it; the activations only after.
     if (lane == 0) {
-      int it = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+      const CUtensorMap* map_static = transposed ? &map_x : &map_y;
+      const CUtensorMap* map_dynamic = transposed ? &map_y : &map_x;
+      const int off_static = transposed ? 0 : C::kStageA, off_dynamic = transposed ? C::kStageA : 0;
+      const int row_static = transposed ? i0 : j0, row_dynamic = transposed ? j0 : i0;
+      const int pre = min(C::kStages, kb_end - kb_begin);
+      for (int p = 0; p < pre; ++p) {   // fresh barriers: the stages are free
+        mbar_expect_tx(full + p, C::kStage);
+        tma_load_2d(smem + p * C::kStage + off_static, map_static, (kb_begin + p) * kBK, row_static, full + p);
+      }
+      pdl_wait();
+      for (int p = 0; p < pre; ++p) {
+        tma_load_2d(smem + p * C::kStage + off_dynamic, map_dynamic, (kb_begin + p) * kBK, row_dynamic, full + p);
+      }
+      int it = pre;
+      for (int kb = kb_begin + pre; kb < kb_end; ++kb, ++it) {
         const int s = it % C::kStages;
         const uint32_t parity = ((it / C::kStages) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
         if (!mbar_wait(empty + s, parity, abort_flag, status, 1)) break;
@@ -211,10 +226,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const bool have = kb_end > kb_begin;
     bool ok = true;
     if (have) ok = mbar_wait(acc_full, 0, abort_flag, status, 3);
+    pdl_wait();   // nothing is stored before the kernels ahead in the stream are done
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int i = i0 + warp * 32 + lane;
     float* part = partial ? partial + static_cast<long long>(blockIdx.z) * part_stride : nullptr;
-    if (ok) {
+    if (ok && silu) {
+      // The weight rows come in blocks of 16 gate rows followed by their 16 up rows; the output is
+      // silu(gate) * up, half as wide as the product: out[token, 16 * block + r].
+      if (transposed) {
+        // lanes 0-15 of a warp hold gate rows, lanes 16-31 the matching up rows: exchange, then
+        // the lower half finishes columns 0-7 of each chunk and the upper half columns 8-15
+        const int o = (i0 >> 1) + warp * 16 + (lane & 15);
+        const bool upper = lane >= 16;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (j0 + c0 >= rows_y) break;
+          uint32_t r[16];
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            // the lower lane sends its gate of column e + 8 and receives the up of column e;
+            // the upper lane sends its up of column e and receives the gate of column e + 8
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, upper ? r[e] : r[e + 8], 16);
+            const float g = __uint_as_float(upper ? got : r[e]);
+            const float u = __uint_as_float(upper ? r[e + 8] : got);
+            const int j = j0 + c0 + e + (upper ? 8 : 0);
+            if (j < rows_y && o < (rows_x >> 1)) st(out + static_cast<long long>(j) * ldo + o, g / (1.0f + expf(-g)) * u);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (j0 + c0 >= rows_y) break;
+          uint32_t g[16], u[16];
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, g);
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0 + 16, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (i < rows_x) {
+            float v[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float gv = __uint_as_float(g[e]);
+              v[e] = gv / (1.0f + expf(-gv)) * __uint_as_float(u[e]);
+            }
+            const long long at = static_cast<long long>(i) * ldo + ((j0 + c0) >> 1);
+            if (((at * sizeof(OutT)) & 15) == 0 && sizeof(OutT) == 2) {
+              uint32_t w[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(out + at) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(out + at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) st(out + at + e, v[e]);
+            }
+          }
+        }
+      }
+    } else if (ok) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (j0 + c0 >= rows_y) break;   // uniform over the warp
@@ -288,6 +361,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 template <typename OutT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, long long part_stride, int splits,
                                      OutT* __restrict__ out, long long ldo, int N, long long total) {
+  pdl_sync();
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   float acc = partial[idx];
@@ -340,7 +414,7 @@ static bool ensure_status() {
 
 template <int BN, typename OutT>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, long long part_stride,
-                     long long ldp, int rows_x, int rows_y, int K, long long ldo, int transposed, int splits, cudaStream_t s) {
+                     long long ldp, int rows_x, int rows_y, int K, long long ldo, int transposed, int silu, int splits, cudaStream_t s) {
   using C = TcConfig<BN>;
   static bool configured = false;
   if (!configured) {
@@ -354,8 +428,8 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, fl
   const int k_blocks = ceil_div(K, kBK);
   const int per_split = ceil_div(k_blocks, splits);
   const dim3 grid(ceil_div(rows_x, kBM), ceil_div(rows_y, BN), ceil_div(k_blocks, per_split));
-  gemm_tc_kernel<BN, OutT><<<grid, kThreads, C::kSmem, s>>>(mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
-                                                            rows_x, rows_y, k_blocks, per_split, ldo, transposed,
+  TIE_LAUNCH((gemm_tc_kernel<BN, OutT>), grid, kThreads, C::kSmem, s, mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
+                                                            rows_x, rows_y, k_blocks, per_split, ldo, transposed, silu,
                                                             g_status_dev);
   return kOk;
 }
@@ -365,17 +439,26 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, fl
 using namespace tie;
 
 // out[M, N] (OutT = bfloat16 or float, row stride ldo) = a[M, K] . w[N, K]^T, a and w bfloat16.
-// transposed != 0 puts the weights on the 128-row side (few tokens). splits > 1 needs
-// `scratch` with splits * M * ldo floats... see tie_gemm_tc_scratch_floats. Returns kBadArgument
+// transposed != 0 puts the weights on the 128-row side (few tokens). splits > 1 needs `scratch`
+// with tie_gemm_tc_scratch_floats floats: the float partial sums [splits, M, N]; with reduce == 0
+// they are left there for a consumer that adds them itself (tie_gemm_tc_real_splits says how
+// many there are). silu != 0: w holds blocks of 16 gate rows followed by their 16 up rows and
+// out[M, N / 2] = silu(gate) * up. Returns kBadArgument
 // with a message for sizes it does not take (K or a row stride not a multiple of 8, unaligned
 // pointers): the caller then uses the CUDA-core kernel.
+// How many splits a call with `splits` really makes (the k-blocks are divided evenly).
+TIE_API int tie_gemm_tc_real_splits(int K, int splits) {
+  const int k_blocks = ceil_div(K, kBK);
+  return ceil_div(k_blocks, ceil_div(k_blocks, splits > 0 ? splits : 1));
+}
+
 TIE_API long long tie_gemm_tc_scratch_floats(int M, int N, int splits) {
   return splits > 1 ? static_cast<long long>(splits) * M * N : 0;
 }
 
 TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, int M, int N, int K, long long lda,
-                        long long ldw, long long ldo, int transposed, int bn, int splits, float* scratch,
-                        cudaStream_t s) {
+                        long long ldw, long long ldo, int transposed, int bn, int splits, float* scratch, int silu,
+                        int reduce, cudaStream_t s) {
   TIE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: K=%d and the row strides must be multiples of 8", K);
   TIE_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
@@ -383,6 +466,8 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
   TIE_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm_tc: tile width %d", bn);
   TIE_REQUIRE(splits >= 1 && (splits == 1 || scratch != nullptr), "gemm_tc: splits=%d needs scratch memory", splits);
   TIE_REQUIRE(out_dtype == TIE_BF16 || out_dtype == TIE_F32, "gemm_tc: output dtype code %d", out_dtype);
+  TIE_REQUIRE(!silu || (splits == 1 && N % 32 == 0 && (transposed || bn >= 32)),
+              "gemm_tc: the SiLU epilogue needs unsplit k and weight rows in blocks of 16 gate + 16 up (N=%d)", N);
   TIE_REQUIRE(ensure_status(), "gemm_tc: cannot allocate the status word");
   // row operand X (128 per tile) and column operand Y (bn per tile)
   const void* x = transposed ? w : a;
@@ -399,8 +484,8 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
 #define TIE_TC_CASE(B)                                                                                                \
   case B:                                                                                                             \
     st = out_dtype == TIE_BF16                                                                                        \
-             ? launch_tc<B, __nv_bfloat16>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, splits, s) \
-             : launch_tc<B, float>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, splits, s);  \
+             ? launch_tc<B, __nv_bfloat16>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, silu, splits, s) \
+             : launch_tc<B, float>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, silu, splits, s);  \
     break;
   switch (bn) {
     TIE_TC_CASE(16)
@@ -411,15 +496,15 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
   }
 #undef TIE_TC_CASE
   if (st != kOk) return st;
-  if (splits > 1) {
+  if (splits > 1 && reduce) {
     const int k_blocks = ceil_div(K, kBK);
     const int real_splits = ceil_div(k_blocks, ceil_div(k_blocks, splits));
     const long long total = part_stride;
     if (out_dtype == TIE_BF16) {
-      splitk_reduce_kernel<__nv_bfloat16><<<ceil_div(total, 256), 256, 0, s>>>(
+      TIE_LAUNCH((splitk_reduce_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, 
           partial, part_stride, real_splits, static_cast<__nv_bfloat16*>(out), ldo, N, total);
     } else {
-      splitk_reduce_kernel<float><<<ceil_div(total, 256), 256, 0, s>>>(partial, part_stride, real_splits,
+      TIE_LAUNCH((splitk_reduce_kernel<float>), ceil_div(total, 256), 256, 0, s, partial, part_stride, real_splits,
                                                                       static_cast<float*>(out), ldo, N, total);
     }
   }

@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* __r
                                                                 const unsigned long long* __restrict__ seeds,
                                                                 const unsigned long long* __restrict__ counters,
                                                                 int* __restrict__ out) {
+  pdl_sync();
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ float seg_sum[kSampleThreads];
@@ -159,6 +160,6 @@ TIE_API int tie_sample(const float* logits, long long row_stride, int rows, int 
   TIE_REQUIRE(inv_temperature == nullptr || (seeds != nullptr && counters != nullptr),
               "sample: temperature sampling needs seeds and counters");
   if (rows == 0) return kOk;
-  sample_kernel<<<rows, kSampleThreads, 0, s>>>(logits, row_stride, vocab, inv_temperature, seeds, counters, out);
+  TIE_LAUNCH((sample_kernel), rows, kSampleThreads, 0, s, logits, row_stride, vocab, inv_temperature, seeds, counters, out);
   TIE_RETURN_LAUNCH("sample");
 }

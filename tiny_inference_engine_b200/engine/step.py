@@ -87,6 +87,7 @@ class StepContext:
     logit_ws: Workspace              # buffers of max_logit_rows rows (final norm, logits)
     host: HostStep
     layer_hook: Callable | None = None
+    ws_dtype: torch.dtype | None = None   # the model's compute dtype (set by Model.forward)
     # sampling parameters per logit row (None when the step does not sample)
     inv_temperature: torch.Tensor | None = None
     seeds: torch.Tensor | None = None

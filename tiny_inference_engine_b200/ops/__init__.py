@@ -40,6 +40,25 @@ def _dev(*ts) -> None:
             raise InvalidArgument("kernel arguments must be CUDA tensors: the engine has no CPU path")
 
 
+class SplitSum:
+    """The result of a matrix product whose k range was cut into splits, not yet added up:
+    float32 partial sums [splits, M, N] in scratch memory. Kernels that consume it (the residual
+    add + norm, the q/k norm + RoPE + append) add the splits in order while they read, which saves
+    a reduction kernel and a rounding; `materialize` adds them into a tensor for everyone else."""
+
+    def __init__(self, partial: torch.Tensor, splits: int, M: int, N: int):
+        self.partial, self.splits, self.M, self.N = partial, splits, M, N
+
+    @property
+    def stride(self) -> int:
+        return self.M * self.N
+
+    def materialize(self, out: torch.Tensor) -> torch.Tensor:
+        p = self.partial[:self.splits * self.stride].view(self.splits, self.M, self.N)
+        out.copy_(p.sum(dim=0) if self.splits > 1 else p[0])   # off the product path: toy parts and tests only
+        return out
+
+
 def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
     """out[t] = float(table[ids[t]]); out is the float32 residual stream [T, D]."""
     _dev(table, ids, out)
@@ -52,7 +71,12 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
 
 def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor, rows=None) -> None:
     """x += delta (when given; float32, in place), out = rmsnorm(x) * weight in out's dtype.
-    With `rows` (int32 [R]), out[i] comes from row rows[i] and x is left as it is."""
+    With `rows` (int32 [R]), out[i] comes from row rows[i] and x is left as it is. `delta` may
+    be a SplitSum: its splits are added in order while they are read."""
+    part = None
+    if isinstance(delta, SplitSum):
+        part, delta = delta, None
+        _need(part.M == x.shape[0] and part.N == x.shape[-1], "add_rmsnorm: partial sums do not match x")
     _dev(x, delta, weight, out, rows)
     D = x.shape[-1]
     n = out.shape[0]
@@ -66,8 +90,9 @@ def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: t
         _need(n == x.shape[0], "add_rmsnorm: out must have x's rows")
     else:
         _need(rows.dtype == torch.int32 and rows.numel() == n, "add_rmsnorm: rows must be int32 [n]")
-    call("tie_add_rmsnorm", dtype_code(out), x.data_ptr(), _ptr(delta), _ptr(rows), weight.data_ptr(), float(eps),
-         out.data_ptr(), n, D, _stream())
+    call("tie_add_rmsnorm", dtype_code(out), x.data_ptr(), _ptr(delta), part.partial.data_ptr() if part else 0,
+         part.stride if part else 0, part.splits if part else 0, _ptr(rows), weight.data_ptr(), float(eps), out.data_ptr(),
+         n, D, _stream())
 
 
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -121,10 +146,11 @@ def kv_append(k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor, k_cache: to
 
 def qk_norm_rope_append(qkv: torch.Tensor, q_weight, k_weight, q_eps: float, k_eps: float, inv_freq,
                         positions: torch.Tensor, slots, k_cache, v_cache, q_heads: int, kv_heads: int,
-                        head_dim: int, write_kv: bool = True) -> None:
+                        head_dim: int, write_kv: bool = True, partial: SplitSum | None = None) -> None:
     """Per-head RMSNorm of q and k (weights may be None), RoPE (inv_freq may be None), q back in
     place, k and v into the cache planes. qkv is [T, (q_heads + 2 kv_heads) * head_dim]; with
-    write_kv False it may hold q only and the planes are not touched."""
+    write_kv False it may hold q only and the planes are not touched. With `partial` the values
+    are read from the split product's partial sums [splits, T, width] and only q is written to qkv."""
     _dev(qkv, q_weight, k_weight, inv_freq, positions, slots, k_cache, v_cache)
     T = qkv.shape[0]
     width = (q_heads + (2 * kv_heads if write_kv else 0)) * head_dim
@@ -143,7 +169,11 @@ def qk_norm_rope_append(qkv: torch.Tensor, q_weight, k_weight, q_eps: float, k_e
         _need(k_cache.dtype == qkv.dtype, "qk_norm_rope_append: dtype differs from the cache's")
         _need(slots.dtype == torch.int32 and slots.numel() == T, "qk_norm_rope_append: slots must be int32 [T]")
         page_size = k_cache.shape[2]
-    call("tie_qk_norm_rope_append", dtype_code(qkv), qkv.data_ptr(), qkv.stride(0), _ptr(q_weight), _ptr(k_weight),
+    if partial is not None:
+        _need(partial.M == T and partial.N == width, "qk_norm_rope_append: partial sums do not match the rows")
+    call("tie_qk_norm_rope_append", dtype_code(qkv), qkv.data_ptr(), qkv.stride(0),
+         partial.partial.data_ptr() if partial else 0, partial.stride if partial else 0, partial.splits if partial else 0,
+         partial.N if partial else 0, _ptr(q_weight), _ptr(k_weight),
          float(q_eps), float(k_eps), _ptr(inv_freq), rot, positions.data_ptr(), _ptr(slots) if write_kv else 0,
          _ptr(k_cache) if write_kv else 0, _ptr(v_cache) if write_kv else 0, T, q_heads, kv_heads, head_dim, page_size,
          1 if write_kv else 0, _stream())
@@ -256,7 +286,22 @@ def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=
          out.data_ptr(), _stream())
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """The engine's matrix product: picks the kernel for the dtype and the sizes."""
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=None):
+    """The engine's matrix product: picks the kernel for the dtype and the sizes. With
+    `partial_scratch` (a callable numel -> float32 buffer) a product whose k range is split may
+    come back as a SplitSum (then `out` is untouched); else returns `out`."""
     from . import gemm_select
-    gemm_select.gemm(a, w, out)
+    return gemm_select.gemm(a, w, out, partial_scratch)
+
+
+def gemm_silu(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(a . gate^T) * (a . up^T) in one tensor-core product; w_blocks [2I, K] holds
+    blocks of 16 gate rows followed by their 16 up rows (interleave_gate_up)."""
+    from . import gemm_select
+    gemm_select.gemm_silu(a, w_blocks, out)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K], [I, K] -> [2I, K]: 16 gate rows, their 16 up rows, the next 16 gate rows, ... (I % 16 == 0)."""
+    I, K = gate.shape
+    return torch.stack([gate.view(I // 16, 16, K), up.view(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()

@@ -57,22 +57,36 @@ def _scratch_for(numel: int, device) -> torch.Tensor:
     return buf
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None, bn=None, splits=None, scratch=None) -> None:
-    """The tensor-core product; the tiling can be forced (tests)."""
-    from . import _need, _stream, dtype_code
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None, bn=None, splits=None, scratch=None,
+            silu: bool = False, partial_scratch=None):
+    """The tensor-core product; the tiling can be forced (tests). Returns `out`, or a SplitSum when
+    `partial_scratch` is given and k is split."""
+    from . import SplitSum, _need, _stream, dtype_code
     M, K = a.shape
     N = w.shape[0]
-    _need(w.shape[1] == K and out.shape == (M, N), f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    _need(w.shape[1] == K and out.shape == (M, N // 2 if silu else N),
+          f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm: last axes must be contiguous")
     _need(tc_takes(a, w, out), "gemm_tc: operands must be bfloat16 with K and row strides multiples of 8, 16-byte aligned")
     t, b, s = plan(M, N, K)
     transposed = t if transposed is None else int(transposed)
     bn = b if bn is None else bn
     splits = s if splits is None else splits
-    if splits > 1 and scratch is None:
+    if silu:
+        splits = 1
+        if not transposed:
+            bn = max(bn, 32)
+    leave = splits > 1 and partial_scratch is not None
+    if leave:
+        scratch = partial_scratch(splits * M * N)
+    elif splits > 1 and scratch is None:
         scratch = _scratch_for(splits * M * N, a.device)
     _call("tie_gemm_tc", dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
-                 w.stride(0), out.stride(0), transposed, bn, splits, scratch.data_ptr() if splits > 1 else 0, _stream())
+          w.stride(0), out.stride(0), transposed, bn, splits, scratch.data_ptr() if splits > 1 else 0, 1 if silu else 0,
+          0 if leave else 1, _stream())
+    if leave:
+        return SplitSum(scratch, _library().tie_gemm_tc_real_splits(K, splits), M, N)
+    return out
 
 
 def check_status() -> None:
@@ -84,11 +98,19 @@ def check_status() -> None:
         raise TieError(f"a tensor-core matrix product gave up after its wait limit ({where}); its output is invalid")
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=None):
     from . import gemm_simt
     if a.shape[0] == 0:
-        return
+        return out
     if tc_takes(a, w, out):
-        gemm_tc(a, w, out)
-    else:
-        gemm_simt(a, w, out)
+        return gemm_tc(a, w, out, partial_scratch=partial_scratch)
+    gemm_simt(a, w, out)
+    return out
+
+
+def gemm_silu(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor) -> None:
+    from . import _need
+    _need(w_blocks.shape[0] % 32 == 0 and tc_takes(a, w_blocks, out),
+          "gemm_silu: needs bfloat16 operands TMA can address and gate/up rows in blocks of 16")
+    if a.shape[0] > 0:
+        gemm_tc(a, w_blocks, out, silu=True)

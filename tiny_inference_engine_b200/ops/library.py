@@ -17,17 +17,17 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 _SIGNATURES = {
     "tie_embed": [I, P, P, P, I, I, I, P],
-    "tie_add_rmsnorm": [I, P, P, P, P, F, P, I, I, P],
+    "tie_add_rmsnorm": [I, P, P, P, L, I, P, P, F, P, I, I, P],
     "tie_rmsnorm_rows": [I, P, L, P, F, P, L, I, L, P],
     "tie_silu_mul": [I, P, P, I, I, P],
     "tie_rope": [I, P, L, P, P, I, I, I, I, P],
     "tie_kv_append": [I, P, P, L, L, P, P, P, I, I, I, I, P],
-    "tie_qk_norm_rope_append": [I, P, L, P, P, F, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
+    "tie_qk_norm_rope_append": [I, P, L, P, L, I, L, P, P, F, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
     "tie_gemm_simt": [I, I, P, P, P, I, I, I, L, L, L, P],
     "tie_attention_rows": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_split": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_sample": [P, L, I, I, P, P, P, P, P],
-    "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, P],
+    "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, I, I, P],
     "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_decode_tc": [P, L, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_attention_merge": [I, P, P, P, I, I, I, P, I, I, I, P, P],
@@ -60,6 +60,8 @@ def library() -> ctypes.CDLL:
         lib.tie_compiled_arch.restype = c_int
         lib.tie_gemm_tc_status.restype = c_int
         lib.tie_gemm_tc_status.argtypes = []
+        lib.tie_gemm_tc_real_splits.restype = c_int
+        lib.tie_gemm_tc_real_splits.argtypes = [c_int, c_int]
         for name, args in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = args

@@ -86,9 +86,10 @@ class GQAttention(Mixer):
         if fused:
             width = self.q_dim + (2 * self.kv_dim if cache.writes else 0)
             qkv = ctx.ws.rows("attn.qkv", T, self.q_dim + 2 * self.kv_dim, self.dtype)[:, :width]
-            ops.gemm(h, self.w_qkv if cache.writes else self.w_q, qkv)
+            got = ops.gemm(h, self.w_qkv if cache.writes else self.w_q, qkv,
+                           partial_scratch=lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32))
             ops.qk_norm_rope_append(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, g.slots, cache.k, cache.v, Hq, Hkv,
-                                    Dh, write_kv=cache.writes)
+                                    Dh, write_kv=cache.writes, partial=got if isinstance(got, ops.SplitSum) else None)
             q = qkv[:, :self.q_dim]
         else:
             # Any other norm or position encoding: separate products and the parts' own kernels.
@@ -109,8 +110,7 @@ class GQAttention(Mixer):
         attn = ctx.ws.rows("attn.out", T, self.q_dim, self.dtype)
         self.attend(q, attn, ctx, g, cache)
         out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
-        ops.gemm(attn, self.w_o, out)
-        return out
+        return ops.gemm(attn, self.w_o, out, partial_scratch=lambda n: ctx.ws.flat("mixer.out.partial", n, torch.float32))
 
     def attend(self, q, attn, ctx, g, cache):
         """Rows of sequences that bring several tokens come first in a step, then one row per

@@ -27,11 +27,21 @@ class PreNormBlock(Block):
             p.bind(get)
 
     def forward(self, x, pending, ctx, cache, state):
+        """`pending` and what the parts return may be tensors [T, D] or ops.SplitSum (a split product
+        whose partial sums the next add+norm adds up itself)."""
         h = ctx.ws.rows("block.normed", x.shape[0], x.shape[1], self.dtype)
-        self.mixer_norm.add_norm(x, pending, h)
+        self.mixer_norm.add_norm(x, as_delta(pending, self.mixer_norm, ctx, "block.delta"), h)
         mixed = self.mixer.forward(h, ctx, cache, state)
-        self.ffn_norm.add_norm(x, mixed, h)
+        self.ffn_norm.add_norm(x, as_delta(mixed, self.ffn_norm, ctx, "block.delta"), h)
         return self.ffn.forward(h, ctx)
+
+
+def as_delta(delta, norm, ctx, name):
+    """A SplitSum stays one for norms that add the splits themselves (`takes_split_sum`), else it is added up first."""
+    from .. import ops
+    if isinstance(delta, ops.SplitSum) and not getattr(norm, "takes_split_sum", False):
+        return delta.materialize(ctx.ws.rows(name, delta.M, delta.N, ctx.ws_dtype))
+    return delta
 
 
 register_part("block", "prenorm", PreNormBlock, replace=True)

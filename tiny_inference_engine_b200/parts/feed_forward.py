@@ -27,18 +27,23 @@ class SwiGLU(FeedForward):
     def bind(self, get):
         gate = to_compute(get(self.prefix + "gate_proj.weight"), self.dtype)
         up = to_compute(get(self.prefix + "up_proj.weight"), self.dtype)
-        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        # On the tensor-core path gate and up rows are interleaved in blocks of 16 and SiLU * up
+        # happens in the product's epilogue; else they are stacked and a kernel of its own does it.
+        self.fused = self.dtype == torch.bfloat16 and self.inter % 16 == 0 and self.hidden % 8 == 0
+        self.w_gate_up = ops.interleave_gate_up(gate, up) if self.fused else torch.cat([gate, up], dim=0).contiguous()
         self.w_down = to_compute(get(self.prefix + "down_proj.weight"), self.dtype).contiguous()
 
     def forward(self, h, ctx):
         T = h.shape[0]
-        gu = ctx.ws.rows("ffn.gate_up", T, 2 * self.inter, self.dtype)
-        ops.gemm(h, self.w_gate_up, gu)
         act = ctx.ws.rows("ffn.act", T, self.inter, self.dtype)
-        ops.silu_mul(gu, act)
+        if self.fused:
+            ops.gemm_silu(h, self.w_gate_up, act)
+        else:
+            gu = ctx.ws.rows("ffn.gate_up", T, 2 * self.inter, self.dtype)
+            ops.gemm(h, self.w_gate_up, gu)
+            ops.silu_mul(gu, act)
         out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
-        ops.gemm(act, self.w_down, out)
-        return out
+        return ops.gemm(act, self.w_down, out, partial_scratch=lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32))
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

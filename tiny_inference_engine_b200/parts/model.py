@@ -75,6 +75,7 @@ class Model:
     # -- one step over the rows of ctx; returns float32 logits [R, V] or None when no row is wanted
     def forward(self, ctx, cache, states) -> torch.Tensor | None:
         T, D = ctx.T, self.spec.hidden_size
+        ctx.ws_dtype = self.dtype
         x = ctx.ws.rows("model.x", T, D, torch.float32)
         self.embedding.forward(ctx.tokens, x)
         pending = None
@@ -88,7 +89,8 @@ class Model:
         if ctx.R == 0:
             return None
         last = ctx.logit_ws.rows("model.last", ctx.R, D, self.dtype)
-        self.final_norm.add_norm(x, pending, last, rows=ctx.logit_rows)
+        from .block import as_delta
+        self.final_norm.add_norm(x, as_delta(pending, self.final_norm, ctx, "block.delta"), last, rows=ctx.logit_rows)
         logits = ctx.logit_ws.rows("model.logits", ctx.R, self.spec.vocab_size, torch.float32)
         self.head.forward(last, logits)
         return logits

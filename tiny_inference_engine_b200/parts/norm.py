@@ -11,6 +11,8 @@ from .base import Norm, register_part
 
 
 class RMSNorm(Norm):
+    takes_split_sum = True      # add_norm adds the partial sums of a split product itself
+
     def __init__(self, spec, dtype, prefix: str = ""):
         self.name = prefix + spec["name"]
         self.size = int(spec["size"])
