@@ -117,25 +117,29 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
-template <int BN> struct TcConfig {
+// DEEP: as many stages as fit in the 227 KB one CTA may use (at most 8), one CTA per SM.
+// Not DEEP: about 100 KB of stages, so that two CTAs share an SM and one's start-up and
+// epilogue hide behind the other's streaming.
+template <int BN, bool DEEP> struct TcConfig {
   static constexpr int kStageA = kBM * kBK * 2;
   static constexpr int kStageB = BN * kBK * 2;
   static constexpr int kStage = kStageA + kStageB;
-  // As many stages as fit beside the barriers in the 227 KB a CTA may use, at most 8.
-  static constexpr int kStages = (200 * 1024 / kStage) > 8 ? 8 : (200 * 1024 / kStage);
+  static constexpr int kBudget = DEEP ? 200 * 1024 : 100 * 1024;
+  static constexpr int kFit = kBudget / kStage < 2 ? 2 : kBudget / kStage;
+  static constexpr int kStages = kFit > 8 ? 8 : kFit;
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
   static constexpr size_t kSmem = static_cast<size_t>(kStages) * kStage + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 // out_mode: 0 = OutT out[i * ldo + j] (plain), 1 = OutT out[j * ldo + i] (transposed),
 // and with partial != nullptr the same two layouts in float at partial + z * part_stride.
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool DEEP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, OutT* __restrict__ out,
                float* __restrict__ partial, long long part_stride, long long ldp, int rows_x, int rows_y, int k_blocks,
                int k_blocks_per_split, long long ldo, int transposed, int silu, int* status) {
   pdl_launch_dependents();   // the next kernel may get resident now; it waits for this one at its own pdl_wait()
-  using C = TcConfig<BN>;
+  using C = TcConfig<BN, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStage);
@@ -412,13 +416,13 @@ static bool ensure_status() {
   return cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0) == cudaSuccess;
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool DEEP>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, long long part_stride,
                      long long ldp, int rows_x, int rows_y, int K, long long ldo, int transposed, int silu, int splits, cudaStream_t s) {
-  using C = TcConfig<BN>;
+  using C = TcConfig<BN, DEEP>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(C::kSmem)) != cudaSuccess) {
       set_error("gemm_tc: cannot reserve %zu bytes of shared memory", C::kSmem);
       return kCudaError;
@@ -428,7 +432,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, fl
   const int k_blocks = ceil_div(K, kBK);
   const int per_split = ceil_div(k_blocks, splits);
   const dim3 grid(ceil_div(rows_x, kBM), ceil_div(rows_y, BN), ceil_div(k_blocks, per_split));
-  TIE_LAUNCH((gemm_tc_kernel<BN, OutT>), grid, kThreads, C::kSmem, s, mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
+  TIE_LAUNCH((gemm_tc_kernel<BN, OutT, DEEP>), grid, kThreads, C::kSmem, s, mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
                                                             rows_x, rows_y, k_blocks, per_split, ldo, transposed, silu,
                                                             g_status_dev);
   return kOk;
@@ -443,7 +447,8 @@ using namespace tie;
 // with tie_gemm_tc_scratch_floats floats: the float partial sums [splits, M, N]; with reduce == 0
 // they are left there for a consumer that adds them itself (tie_gemm_tc_real_splits says how
 // many there are). silu != 0: w holds blocks of 16 gate rows followed by their 16 up rows and
-// out[M, N / 2] = silu(gate) * up. Returns kBadArgument
+// out[M, N / 2] = silu(gate) * up. deep != 0: the deepest shared-memory ring (one CTA per SM), else
+// a ring of about 100 KB (two CTAs per SM). Returns kBadArgument
 // with a message for sizes it does not take (K or a row stride not a multiple of 8, unaligned
 // pointers): the caller then uses the CUDA-core kernel.
 // How many splits a call with `splits` really makes (the k-blocks are divided evenly).
@@ -458,7 +463,7 @@ TIE_API long long tie_gemm_tc_scratch_floats(int M, int N, int splits) {
 
 TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, int M, int N, int K, long long lda,
                         long long ldw, long long ldo, int transposed, int bn, int splits, float* scratch, int silu,
-                        int reduce, cudaStream_t s) {
+                        int reduce, int deep, cudaStream_t s) {
   TIE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: K=%d and the row strides must be multiples of 8", K);
   TIE_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
@@ -481,11 +486,14 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
   const long long part_stride = static_cast<long long>(M) * N;
   const long long ldp = N;
   int st = kOk;
-#define TIE_TC_CASE(B)                                                                                                \
-  case B:                                                                                                             \
-    st = out_dtype == TIE_BF16                                                                                        \
-             ? launch_tc<B, __nv_bfloat16>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, silu, splits, s) \
-             : launch_tc<B, float>(mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, silu, splits, s);  \
+#define TIE_TC_ARGS mx, my, out, partial, part_stride, ldp, rows_x, rows_y, K, ldo, transposed, silu, splits, s
+#define TIE_TC_CASE(B)                                                                                     \
+  case B:                                                                                                  \
+    if (deep) {                                                                                            \
+      st = out_dtype == TIE_BF16 ? launch_tc<B, __nv_bfloat16, true>(TIE_TC_ARGS) : launch_tc<B, float, true>(TIE_TC_ARGS);   \
+    } else {                                                                                               \
+      st = out_dtype == TIE_BF16 ? launch_tc<B, __nv_bfloat16, false>(TIE_TC_ARGS) : launch_tc<B, float, false>(TIE_TC_ARGS); \
+    }                                                                                                      \
     break;
   switch (bn) {
     TIE_TC_CASE(16)
@@ -494,6 +502,7 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
     TIE_TC_CASE(128)
     TIE_TC_CASE(256)
   }
+#undef TIE_TC_ARGS
 #undef TIE_TC_CASE
   if (st != kOk) return st;
   if (splits > 1 && reduce) {

@@ -36,14 +36,11 @@ def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
         bn = next(b for b in (16, 32, 64, 128, 256) if b >= M)
         tiles = math.ceil(N / 128)
         splits = 1
-        if tiles < NUM_SMS:
-            # One CTA fits on an SM: as many splits as keep all CTAs resident at once (a second
-            # wave costs more than it gains), while the float partial sums (written and read
-            # once) stay under a tenth of the weight bytes and a split keeps 4 k-blocks.
-            want = NUM_SMS // tiles
-            cap_traffic = max(1, K // (40 * M))
-            cap_depth = max(1, k_blocks // 4)
-            splits = max(1, min(want, cap_traffic, cap_depth))
+        if bn <= 64 and tiles < 2 * NUM_SMS:
+            # Two CTAs share an SM (the ring is about 100 KB): as many splits as keep all CTAs
+            # resident at once, while a split keeps 4 k-blocks and the float partial sums
+            # (written and read once) stay well below the weight bytes.
+            splits = max(1, min(2 * NUM_SMS // tiles, k_blocks // 4, K // (8 * M)))
         return 1, bn, splits
     bn = next((b for b in (16, 32, 64, 128, 256) if b >= N), 256)
     return 0, bn, 1
@@ -58,7 +55,7 @@ def _scratch_for(numel: int, device) -> torch.Tensor:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None, bn=None, splits=None, scratch=None,
-            silu: bool = False, partial_scratch=None):
+            silu: bool = False, partial_scratch=None, deep=None):
     """The tensor-core product; the tiling can be forced (tests). Returns `out`, or a SplitSum when
     `partial_scratch` is given and k is split."""
     from . import SplitSum, _need, _stream, dtype_code
@@ -83,7 +80,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None
         scratch = _scratch_for(splits * M * N, a.device)
     _call("tie_gemm_tc", dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
           w.stride(0), out.stride(0), transposed, bn, splits, scratch.data_ptr() if splits > 1 else 0, 1 if silu else 0,
-          0 if leave else 1, _stream())
+          0 if leave else 1, int(deep if deep is not None else (not transposed or bn >= 128)), _stream())
     if leave:
         return SplitSum(scratch, _library().tie_gemm_tc_real_splits(K, splits), M, N)
     return out
