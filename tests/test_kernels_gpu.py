@@ -387,6 +387,19 @@ def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window)
     ops.attention_decode_tc(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, Hq, Hkv, Dh, scale,
                             dev(np.array([3, 4, 5]), torch.int32), 3, 64, 12, scratch, window)
     assert rel_err(host(out), want) < TOL["bfloat16"]
+    # the TMA-fed decode kernel (pages that are powers of two from 8 up), with 1, 2 and many splits, twice
+    # in a row so that the second launch finds the counters the first one left
+    if ops.attention_decode_tma_takes(qd, Hq, Hkv, Dh, page):
+        from tiny_inference_engine_b200.ops import gemm_select
+        counters = torch.zeros(3 * Hkv, dtype=torch.int32, device="cuda")
+        for split_keys, max_splits in ((64, 12), (512, 2), (1024, 1), (64, 12)):
+            out[n_multi:] = float("nan")
+            ops.attention_decode_tma(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, Hq, Hkv, Dh, scale,
+                                     dev(np.array([3, 4, 5]), torch.int32), 3, split_keys, max_splits, scratch, counters, window)
+            torch.cuda.synchronize()
+            gemm_select.check_status()
+            assert rel_err(host(out), want) < TOL["bfloat16"], f"split_keys={split_keys}"
+            assert not counters.any()
 
 
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 65, 255, 256, 511, 512, 1022, 1023])
@@ -411,6 +424,10 @@ def test_tensor_core_attention_finds_one_far_key(ops, far):
         if n_new == 1:
             scratch = torch.empty(ops.attention_split_scratch_floats(1, Hq, Dh, 4), device="cuda")
             ops.attention_decode_tc(*args, *meta, Hq, Hkv, Dh, 1 / np.sqrt(Dh), dev(np.array([0]), torch.int32), 1, 256, 4, scratch)
+            assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, "cp.async decode kernel"
+            out.zero_()
+            ops.attention_decode_tma(*args, *meta, Hq, Hkv, Dh, 1 / np.sqrt(Dh), dev(np.array([0]), torch.int32), 1, 256, 4,
+                                     scratch, torch.zeros(Hkv, dtype=torch.int32, device="cuda"))
         else:
             ops.attention_prompt_tc(*args, *meta, 1, n_new, Hq, Hkv, Dh, 1 / np.sqrt(Dh))
         assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, f"n_new={n_new}"

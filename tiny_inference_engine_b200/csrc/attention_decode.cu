@@ -1,0 +1,321 @@
+// Attention of sequences that bring one token (decode) over the paged bfloat16 cache: keys and
+// values come page by page through TMA into a ring of shared-memory stages, a producer warp
+// keeps the ring full, four consumer warps run the MMAs, and the CTA that finishes last among
+// the splits of a (sequence, kv head) combines the splits itself. Head sizes 64, 128, 256; up
+// to 16 query heads per kv head; page sizes that are powers of two from 8 up. Other sizes go to
+// the cp.async kernel in attention_tc.cu or to the CUDA-core kernels.
+//
+// What it computes is the reference's paged_attention for one query row per sequence
+// (src/backend/cpu/cpu_backend.cpp:261-319): pos = context_len - 1, keys lo..pos (lo > 0 only
+// with a window), query head h reads kv head h / G, float scores, maximum, sum and accumulator.
+//
+// One CTA = (sequence, kv head, split of `split_keys` keys), 160 threads:
+//   warp 4 (one lane) waits for a free stage (empty barrier), arms the stage's full barrier with
+//       the byte count and issues one TMA box per page and 64-column block for K and for V;
+//   warps 0-3 wait for the full barrier, each takes 16 of the tile's 64 keys (Q K^T, online
+//       softmax, P V on mma.sync m16n8k16), and arrive on the empty barrier.
+// The G query heads of the group are the rows of the MMA tile, so a key or value is read once per
+// group. After the last tile the four warps' partial results are combined in shared memory and
+// written as (acc, max, sum) to scratch; a counter per (sequence, kv head) tells the last CTA
+// to arrive that all splits are there, and it merges them in split order (so the result does not
+// depend on which CTA came last) and writes the output rows. With one split the output is
+// written directly. Every mbarrier wait is bounded; on expiry the status word gets a code.
+#include "attention_mma.cuh"
+#include "tma.cuh"
+
+namespace tie {
+
+constexpr int kDecThreads = 160;
+constexpr int kMaxTablePages = 512;    // pages of one split that the CTA keeps in shared memory
+
+struct DecodeArgs {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  const int* query_start;
+  const int* context_lens;
+  const int* block_tables;
+  const int* seq_list;
+  float* scratch;        // [n_list, q_heads, max_splits, head_dim + 2]
+  int* counters;         // [n_list, kv_heads], zero between launches
+  int* status;
+  long long q_stride;
+  int max_blocks, q_heads, kv_heads, page_size, page_shift, window, split_keys, max_splits;
+  float scale_log2;
+};
+
+template <int DH, int STAGES>
+__global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map,
+                                                                      const __grid_constant__ CUtensorMap v_map, DecodeArgs a) {
+  pdl_sync();
+  using L = HalfLayout<DH>;
+  constexpr int HALVES = DH / 64;
+  constexpr int PLANE_BYTES = HALVES * 64 * 128;       // K (or V) of one 64-key tile
+  constexpr int STAGE_BYTES = 2 * PLANE_BYTES;
+  constexpr int RS = DH + 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_tile = smem + STAGES * STAGE_BYTES;                       // 16 rows x DH, row layout
+  uint64_t* full = reinterpret_cast<uint64_t*>(q_tile + 16 * DH * 2);
+  uint64_t* empty = full + STAGES;
+  int* pages = reinterpret_cast<int*>(empty + STAGES);                 // page ids of this split
+  int* flags = pages + kMaxTablePages;                                 // [0] abort, [1] last-arrival flag
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int li = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int seq = a.seq_list[li];
+  const int G = a.q_heads / a.kv_heads;
+  const int t = a.query_start[seq];
+  const int pos = a.context_lens[seq] - 1;
+  if (pos < 0) {            // a padding sequence: no keys; split 0 writes zeros
+    if (split == 0) {
+      for (int id = threadIdx.x; id < G * DH; id += kDecThreads)
+        a.out[(static_cast<long long>(t) * a.q_heads + kvh * G) * DH + id] = __float2bfloat16_rn(0.0f);
+    }
+    return;
+  }
+  const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int lo = lo0 + split * a.split_keys;
+  if (lo > pos) return;
+  const int hi = min(pos, lo + a.split_keys - 1);
+  const int n_splits = (pos - lo0) / a.split_keys + 1;
+  const int kt_first = lo / kKeysPerTile, kt_last = hi / kKeysPerTile;
+  const int n_tiles = kt_last - kt_first + 1;
+  const int box_rows = min(a.page_size, kKeysPerTile);
+  const int boxes_per_tile = kKeysPerTile / box_rows;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 4);
+    }
+    flags[0] = 0;
+    flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  // page ids of the split's tiles (one per TMA box), zero beyond the table: page 0 is real memory
+  // and keys beyond `hi` are masked, so what it holds does not matter as long as it is finite
+  {
+    const int* table = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
+    const int first_key = kt_first * kKeysPerTile;
+    for (int b = threadIdx.x; b < n_tiles * boxes_per_tile; b += kDecThreads) {
+      const int idx = (first_key + b * box_rows) >> a.page_shift;
+      pages[b] = idx < a.max_blocks ? table[idx] : 0;
+    }
+  }
+  // Q: the G heads of the group, rows G..15 zero
+  constexpr int CPR = DH / 8;
+  for (int id = threadIdx.x; id < 16 * CPR; id += kDecThreads) {
+    const int r = id / CPR, c = id % CPR;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < G) v = *reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t) * a.q_stride + static_cast<long long>(kvh * G + r) * DH + c * 8);
+    *reinterpret_cast<uint4*>(q_tile + RowLayout<DH>::at(r, c)) = v;
+  }
+  __syncthreads();
+  volatile int* abort_flag = flags;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float acc[DH / 8][4];
+#pragma unroll
+  for (int j = 0; j < DH / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int i = 0; i < n_tiles; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, abort_flag, a.status, 11)) break;
+        mbar_expect_tx(full + s, STAGE_BYTES);
+        uint8_t* kdst = smem + s * STAGE_BYTES;
+        for (int b = 0; b < boxes_per_tile; ++b) {
+          const int key = (kt_first + i) * kKeysPerTile + b * box_rows;
+          const int row = (pages[i * boxes_per_tile + b] * a.kv_heads + kvh) * a.page_size + (key & (a.page_size - 1));
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) {
+            tma_load_2d(kdst + h * (64 * 128) + b * box_rows * 128, &k_map, h * 64, row, full + s);
+            tma_load_2d(kdst + PLANE_BYTES + h * (64 * 128) + b * box_rows * 128, &v_map, h * 64, row, full + s);
+          }
+        }
+      }
+    }
+  } else {
+    uint32_t qf[DH / 16][4];
+    const uint32_t q_addr = smem_u32(q_tile);
+#pragma unroll
+    for (int ks = 0; ks < DH / 16; ++ks) ldmatrix_x4(qf[ks], q_addr + RowLayout<DH>::at(lane & 15, ks * 2 + (lane >> 4)));
+    const int tq = lane & 3;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % STAGES;
+      if (!mbar_wait(full + s, (i / STAGES) & 1, abort_flag, a.status, 12)) break;
+      const int key0 = (kt_first + i) * kKeysPerTile + warp * 16;   // this warp's 16 keys of the tile
+      if (key0 <= hi && key0 + 15 >= lo) {
+        const uint32_t k_tile = smem_u32(smem + s * STAGE_BYTES);
+        float sc[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+        qk_tile<DH, 2, L>(sc, qf, k_tile, warp * 16);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = key0 + j * 8 + tq * 2 + (e & 1);
+            sc[j][e] = (key >= lo && key <= hi) ? sc[j][e] * a.scale_log2 : -INFINITY;
+          }
+        }
+        softmax_update<DH, 2>(sc, m, l, acc);
+        pv_tile<DH, 2, L>(acc, sc, k_tile + PLANE_BYTES, warp * 16);
+      }
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + s)) : "memory");
+    }
+  }
+  __syncthreads();   // every stage has been consumed (or a wait gave up): the ring can be reused
+  if (flags[0] != 0) {   // a wait ran out: let copies that are still in flight land before the ring is reused
+    const unsigned long long t0 = clock64();
+    while (clock64() - t0 < 4000000ull) {
+    }
+    __syncthreads();
+  }
+
+  // Combine the four consumer warps in shared memory: [warp][row][DH + 2] floats.
+  float* part = reinterpret_cast<float*>(smem);
+  if (warp < 4) {
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = g + 8 * half;
+      if (r >= G) continue;
+      float* dst = part + (warp * 16 + r) * RS;
+#pragma unroll
+      for (int j = 0; j < DH / 8; ++j) {
+        dst[j * 8 + tq * 2] = acc[j][2 * half];
+        dst[j * 8 + tq * 2 + 1] = acc[j][2 * half + 1];
+      }
+      if (tq == 0) {
+        dst[DH] = m[half];
+        dst[DH + 1] = l[half];
+      }
+    }
+  }
+  __syncthreads();
+  float* split_out = a.scratch + ((static_cast<long long>(li) * a.q_heads + kvh * G) * a.max_splits + split) * RS;
+  for (int id = threadIdx.x; id < G * DH; id += kDecThreads) {
+    const int r = id / DH, d = id % DH;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, part[(w * 16 + r) * RS + DH]);
+    float o = 0.0f, ls = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = part[(w * 16 + r) * RS + DH];
+      const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mx);
+      o += part[(w * 16 + r) * RS + d] * f;
+      ls += part[(w * 16 + r) * RS + DH + 1] * f;
+    }
+    if (n_splits == 1) {
+      a.out[(static_cast<long long>(t) * a.q_heads + kvh * G + r) * DH + d] = __float2bfloat16_rn(ls > 0.0f ? o / ls : 0.0f);
+    } else {
+      float* dst = split_out + static_cast<long long>(r) * a.max_splits * RS;
+      dst[d] = o;
+      if (d == 0) {
+        dst[DH] = mx;          // in log2 units: only this kernel reads it back
+        dst[DH + 1] = ls;
+      }
+    }
+  }
+  if (n_splits == 1) return;
+
+  // The last CTA of this (sequence, kv head) to get here merges all splits, in split order.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(a.counters + li * a.kv_heads + kvh, 1);
+    flags[1] = done == n_splits - 1 ? 1 : 0;
+  }
+  __syncthreads();
+  if (flags[1] == 0) return;
+  __threadfence();
+  float* wgt = part;   // [G][n_splits] weights, then [G] inverse sums
+  const float* base = a.scratch + (static_cast<long long>(li) * a.q_heads + kvh * G) * a.max_splits * RS;
+  if (threadIdx.x < G) {
+    const float* src = base + static_cast<long long>(threadIdx.x) * a.max_splits * RS;
+    float mx = -INFINITY;
+    for (int i = 0; i < n_splits; ++i) mx = fmaxf(mx, __ldcg(src + i * RS + DH));
+    float ls = 0.0f;
+    for (int i = 0; i < n_splits; ++i) {
+      const float w = exp2f(__ldcg(src + i * RS + DH) - mx);
+      wgt[threadIdx.x * a.max_splits + i] = w;
+      ls += __ldcg(src + i * RS + DH + 1) * w;
+    }
+    wgt[G * a.max_splits + threadIdx.x] = ls > 0.0f ? 1.0f / ls : 0.0f;
+  }
+  __syncthreads();
+  for (int id = threadIdx.x; id < G * DH; id += kDecThreads) {
+    const int r = id / DH, d = id % DH;
+    const float* src = base + static_cast<long long>(r) * a.max_splits * RS;
+    float o = 0.0f;
+    for (int i = 0; i < n_splits; ++i) o = fmaf(__ldcg(src + i * RS + d), wgt[r * a.max_splits + i], o);
+    a.out[(static_cast<long long>(t) * a.q_heads + kvh * G + r) * DH + d] = __float2bfloat16_rn(o * wgt[G * a.max_splits + r]);
+  }
+  if (threadIdx.x == 0) a.counters[li * a.kv_heads + kvh] = 0;   // ready for the next launch
+}
+
+template <int DH>
+static int launch_decode_tma(const CUtensorMap& km, const CUtensorMap& vm, const DecodeArgs& a, int n_list, cudaStream_t s) {
+  constexpr int STAGES = DH >= 256 ? 2 : (DH == 128 ? 3 : 4);
+  constexpr size_t ring = static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128;
+  constexpr size_t merge = 4 * 16 * (DH + 2) * sizeof(float);
+  constexpr size_t smem = (ring > merge ? ring : merge) + 16 * DH * 2 + 2 * STAGES * 8 + (kMaxTablePages + 2) * 4 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_decode_tma_kernel<DH, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+      set_error("attention_decode: cannot reserve %zu bytes of shared memory", smem);
+      return kCudaError;
+    }
+    configured = true;
+  }
+  TIE_LAUNCH((attn_decode_tma_kernel<DH, STAGES>), dim3(n_list, a.kv_heads, a.max_splits), kDecThreads, smem, s, km, vm, a);
+  return kOk;
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+// The sequences of seq_list bring one token each. scratch holds n_list * q_heads * max_splits *
+// (head_dim + 2) floats; counters holds n_list * kv_heads ints that are zero before the first
+// launch (the kernel leaves them zero). pages is the number of pages of the cache planes.
+TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                     const int* query_start, const int* context_lens, const int* block_tables,
+                                     int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
+                                     int window, float scale, const int* seq_list, int n_list, int split_keys,
+                                     int max_splits, float* scratch, int* counters, cudaStream_t s) {
+  TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_decode: head_dim %d is not 64, 128 or 256", head_dim);
+  TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
+              "attention_decode: %d query heads over %d kv heads (at most 16 per group)", q_heads, kv_heads);
+  TIE_REQUIRE(page_size >= 8 && (page_size & (page_size - 1)) == 0, "attention_decode: page size %d is not a power of two from 8 up", page_size);
+  TIE_REQUIRE(q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0, "attention_decode: q rows must be 16-byte aligned");
+  TIE_REQUIRE(split_keys > 0 && split_keys % kKeysPerTile == 0 && max_splits > 0 && scratch != nullptr && counters != nullptr,
+              "attention_decode: splits must be positive multiples of %d keys", kKeysPerTile);
+  const int box_rows = page_size < kKeysPerTile ? page_size : kKeysPerTile;
+  TIE_REQUIRE((split_keys / kKeysPerTile + 1) * (kKeysPerTile / box_rows) <= kMaxTablePages && max_splits <= 256,
+              "attention_decode: a split of %d keys over pages of %d (or %d splits) exceeds the kernel's tables", split_keys,
+              page_size, max_splits);
+  if (n_list == 0) return kOk;
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  CUtensorMap km, vm;
+  const long long rows = static_cast<long long>(pages) * kv_heads * page_size;
+  TIE_REQUIRE(make_map_bf16(&km, k_cache, rows, head_dim, head_dim, 64, box_rows) &&
+                  make_map_bf16(&vm, v_cache, rows, head_dim, head_dim, 64, box_rows),
+              "attention_decode: cuTensorMapEncodeTiled failed");
+  TIE_REQUIRE(status_word() != nullptr, "attention_decode: cannot allocate the status word");
+  DecodeArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), query_start, context_lens, block_tables,
+               seq_list, scratch, counters, status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window,
+               split_keys, max_splits, scale * 1.4426950408889634f};
+  int st = kOk;
+  if (head_dim == 64) st = launch_decode_tma<64>(km, vm, a, n_list, s);
+  else if (head_dim == 128) st = launch_decode_tma<128>(km, vm, a, n_list, s);
+  else st = launch_decode_tma<256>(km, vm, a, n_list, s);
+  if (st != kOk) return st;
+  TIE_RETURN_LAUNCH("attention_decode_tma");
+}

@@ -22,9 +22,7 @@
 // tcgen05.commit). Every wait is bounded: when it runs out the kernel records where in a
 // status word, stops waiting, frees its tensor memory and returns; the host reads the word.
 // No TMA multicast is used anywhere.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace tie {
 
@@ -32,52 +30,6 @@ constexpr int kBM = 128;          // rows of the row operand per tile = MMA M
 constexpr int kBK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;        // k per tcgen05.mma for 16-bit inputs
 constexpr int kThreads = 192;
-constexpr unsigned long long kWaitCycles = 4000000000ull;  // about two seconds
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait. Returns false (and records `where`) when the barrier did not flip in time or
-// another role of this CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag != 0) return false;
-    if (clock64() - start > kWaitCycles) {
-      *abort_flag = 1;
-      *reinterpret_cast<volatile int*>(status) = where;
-      return false;
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
 
 // Shared-memory matrix descriptor of a k-major tile with 128-byte swizzle: rows of 128 bytes,
 // groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
@@ -376,46 +328,6 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, long lon
 // ---------------------------------------------------------------------------------------------
 // Host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-  }
-  return fn;
-}
-
-// [rows, K] bfloat16, row stride ld elements; box = 64 k x box_rows rows, 128-byte swizzle, zeros outside.
-static bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-static int* g_status_host = nullptr;   // pinned, mapped: the kernels write it, the host reads it without a copy
-static int* g_status_dev = nullptr;
-
-static bool ensure_status() {
-  if (g_status_host != nullptr) return true;
-  if (cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), sizeof(int), cudaHostAllocMapped) != cudaSuccess) return false;
-  *g_status_host = 0;
-  return cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0) == cudaSuccess;
-}
-
 template <int BN, typename OutT, bool DEEP>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, long long part_stride,
                      long long ldp, int rows_x, int rows_y, int K, long long ldo, int transposed, int silu, int splits, cudaStream_t s) {
@@ -434,7 +346,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, fl
   const dim3 grid(ceil_div(rows_x, kBM), ceil_div(rows_y, BN), ceil_div(k_blocks, per_split));
   TIE_LAUNCH((gemm_tc_kernel<BN, OutT, DEEP>), grid, kThreads, C::kSmem, s, mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
                                                             rows_x, rows_y, k_blocks, per_split, ldo, transposed, silu,
-                                                            g_status_dev);
+                                                            status_word());
   return kOk;
 }
 
@@ -473,14 +385,14 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
   TIE_REQUIRE(out_dtype == TIE_BF16 || out_dtype == TIE_F32, "gemm_tc: output dtype code %d", out_dtype);
   TIE_REQUIRE(!silu || (splits == 1 && N % 32 == 0 && (transposed || bn >= 32)),
               "gemm_tc: the SiLU epilogue needs unsplit k and weight rows in blocks of 16 gate + 16 up (N=%d)", N);
-  TIE_REQUIRE(ensure_status(), "gemm_tc: cannot allocate the status word");
+  TIE_REQUIRE(status_word() != nullptr, "gemm_tc: cannot allocate the status word");
   // row operand X (128 per tile) and column operand Y (bn per tile)
   const void* x = transposed ? w : a;
   const void* y = transposed ? a : w;
   const int rows_x = transposed ? N : M, rows_y = transposed ? M : N;
   const long long ldx = transposed ? ldw : lda, ldy = transposed ? lda : ldw;
   CUtensorMap mx, my;
-  TIE_REQUIRE(make_map(&mx, x, rows_x, K, ldx, kBM) && make_map(&my, y, rows_y, K, ldy, bn),
+  TIE_REQUIRE(make_map_bf16(&mx, x, rows_x, K, ldx, kBK, kBM) && make_map_bf16(&my, y, rows_y, K, ldy, kBK, bn),
               "gemm_tc: cuTensorMapEncodeTiled failed (rows %d/%d, K %d)", rows_x, rows_y, K);
   float* partial = splits > 1 ? scratch : nullptr;
   const long long part_stride = static_cast<long long>(M) * N;
@@ -518,14 +430,4 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
     }
   }
   TIE_RETURN_LAUNCH("gemm_tc");
-}
-
-// 0 when no kernel gave up waiting since the last call; else where the first one did
-// (1 = the TMA producer on a free stage, 2 = the MMA issuer on landed bytes, 3 = the epilogue
-// on the accumulator). Reading clears it. Call after the stream has been synchronized.
-TIE_API int tie_gemm_tc_status() {
-  if (g_status_host == nullptr) return 0;
-  const int v = *reinterpret_cast<volatile int*>(g_status_host);
-  *g_status_host = 0;
-  return v;
 }

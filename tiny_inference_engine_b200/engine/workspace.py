@@ -32,5 +32,14 @@ class Workspace:
             self._flat[key] = buf
         return buf
 
+    def zeros(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer that is zero when first handed out (kernels that use it leave it zero)."""
+        key = (name, dtype, "zeros")
+        buf = self._flat.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.zeros(numel, dtype=dtype, device=self.device)
+            self._flat[key] = buf
+        return buf
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in list(self._rows.values()) + list(self._flat.values()))

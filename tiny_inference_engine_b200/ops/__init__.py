@@ -272,6 +272,29 @@ def attention_decode_tc(q, k_cache, v_cache, out, query_start, context_lens, blo
          head_dim, int(window), seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
 
 
+def attention_decode_tma_takes(q: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the TMA-fed decode kernel takes these operands."""
+    return attention_tc_takes(q, q_heads, kv_heads, head_dim) and page_size >= 8 and page_size & (page_size - 1) == 0
+
+
+def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim,
+                         scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, counters,
+                         window: int = 0) -> None:
+    """Attention of sequences that bring one token each, keys and values fed by TMA, splits merged by
+    the last CTA to finish. `counters` (int32 [>= n_list * kv_heads]) must be zero; it is left zero."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch, counters)
+    _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
+    _need(scratch.dtype == torch.float32 and
+          scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, head_dim, max_splits),
+          "attention: scratch too small")
+    _need(counters.dtype == torch.int32 and counters.numel() >= n_list * kv_heads, "attention: counters too small")
+    call("tie_attention_decode_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+         query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads,
+         head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), seq_list.data_ptr(), n_list, split_keys,
+         max_splits, scratch.data_ptr(), counters.data_ptr(), _stream())
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None) -> None:
     """out[r] = first maximum of row r (inv_temperature None or 0), or a draw from softmax(logits * inv_temperature)
     with the Philox uniform of (seeds[r], counters[r])."""

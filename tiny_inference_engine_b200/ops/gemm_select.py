@@ -88,11 +88,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None
 
 def check_status() -> None:
     """After a synchronize: raises if a tensor-core kernel gave up a bounded wait."""
-    code = _library().tie_gemm_tc_status()
+    code = _library().tie_kernel_status()
     if code:
-        where = {1: "the TMA producer waiting for a free stage", 2: "the MMA issuer waiting for operands",
-                 3: "the epilogue waiting for the accumulator"}.get(code, f"code {code}")
-        raise TieError(f"a tensor-core matrix product gave up after its wait limit ({where}); its output is invalid")
+        where = {1: "a matrix product's TMA producer waiting for a free stage", 2: "a matrix product's MMA issuer waiting "
+                 "for operands", 3: "a matrix product's epilogue waiting for the accumulator",
+                 11: "an attention kernel's TMA producer waiting for a free stage",
+                 12: "an attention kernel waiting for keys and values"}.get(code, f"code {code}")
+        raise TieError(f"a kernel gave up after its wait limit ({where}); its output is invalid")
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=None):

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, I, I, I, P],
     "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_decode_tc": [P, L, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
+    "tie_attention_decode_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P, P],
     "tie_attention_merge": [I, P, P, P, I, I, I, P, I, I, I, P, P],
 }
 
@@ -58,8 +59,8 @@ def library() -> ctypes.CDLL:
         lib.tie_last_error.restype = ctypes.c_char_p
         lib.tie_last_error.argtypes = []
         lib.tie_compiled_arch.restype = c_int
-        lib.tie_gemm_tc_status.restype = c_int
-        lib.tie_gemm_tc_status.argtypes = []
+        lib.tie_kernel_status.restype = c_int
+        lib.tie_kernel_status.argtypes = []
         lib.tie_gemm_tc_real_splits.restype = c_int
         lib.tie_gemm_tc_real_splits.argtypes = [c_int, c_int]
         for name, args in _SIGNATURES.items():

@@ -23,6 +23,7 @@ from .base import CacheNeed, Mixer, build_part, register_part, to_compute
 
 SPLIT_KEYS = 256       # keys per split for sequences that bring one token
 MAX_SPLITS = 64
+NUM_SMS = 148
 
 
 class GQAttention(Mixer):
@@ -128,6 +129,19 @@ class GQAttention(Mixer):
                                    ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale, self.window)
         if ctx.single_count > 0:
             longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
+            page = cache.k.shape[2]
+            if tc and ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, page):
+                # about two CTAs per SM in all: (sequence, kv head) pairs times splits of the keys
+                want = max(1, (2 * NUM_SMS) // (ctx.single_count * Hkv))
+                split_keys = max(SPLIT_KEYS, -(-math.ceil(longest / want) // 64) * 64)
+                max_splits = max(1, math.ceil(longest / split_keys))
+                scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
+                                      torch.float32)
+                counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * Hkv, torch.int32)
+                ops.attention_decode_tma(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq,
+                                         Hkv, Dh, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits,
+                                         scratch, counters, self.window)
+                return
             split_keys = SPLIT_KEYS
             while math.ceil(longest / split_keys) > MAX_SPLITS:
                 split_keys *= 2
