@@ -58,6 +58,8 @@ class ClockSampler:
         self.rows, self.proc = [], None
 
     def start(self):
+        if os.environ.get('TIE_BENCH_NO_CLOCKS') == '1':
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -244,9 +246,12 @@ def main() -> int:
     serving = ServingConfig(max_tokens_per_step=chunk, max_seqs=B)
     engine = Engine(model, cache, Scheduler(cache, SchedulerConfig(serving=serving, policy="fcfs")), serving, states=states,
                     runner=runner)
-    start = CTX - K - W - 1
+    # Prompts are prefilled one portion per step, so requests start decoding up to `stagger` steps apart;
+    # every request still has tokens to generate until the last timed step and ends at the context CTX.
+    stagger = B * ((CTX + chunk - 1) // chunk)
+    start = CTX - K - W - stagger - 1
     for _ in range(B):
-        engine.add_request(rng.integers(0, V, start).tolist(), SamplingParams(max_tokens=K + W + 1))
+        engine.add_request(rng.integers(0, V, start).tolist(), SamplingParams(max_tokens=K + W + stagger + 1))
     while any(s.num_pending > 1 for s in engine.sequences.values()):
         engine.step()                       # prompts (not timed)
     for _ in range(W):
@@ -259,6 +264,9 @@ def main() -> int:
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_tokens = engine.stats().decode_tokens - steps_before
+    print(f"[bench] e2e: {K - 1} steps, {e2e_tokens} tokens, {e2e_s * 1e3 / (K - 1):.3f} ms per step, "
+          f"{len(engine.scheduler.running)} running, {len(engine.scheduler.waiting)} waiting, "
+          f"{engine.stats().preemptions} preemptions", file=sys.stderr, flush=True)
     sb = B
     mb = 16
     while mb < pages_per_seq:

@@ -311,26 +311,55 @@ class StepRunner:
         tables = [sec(f"tables{g}").reshape(S, MB) for g in range(G)]
         for g in range(G):
             tables[g][:] = 0
-        for s, i in enumerate(order):
-            e, n = entries[i], counts[i]
-            tok = np.asarray(e.tokens, dtype=np.int64)
-            if tok.min() < 0 or tok.max() >= self.vocab:
-                bad = int(tok[(tok < 0) | (tok >= self.vocab)][0])
+        windowed = [g.kind == "window" for g in self.cache.groups]
+        if T_real == S_real:
+            # Every sequence brings one token (decode): plain Python numbers, one array assignment per section.
+            toks = [int(e.tokens[0]) for e in entries]
+            if min(toks) < 0 or max(toks) >= self.vocab:
+                bad = next(t for t in toks if t < 0 or t >= self.vocab)
                 raise InvalidArgument(f"token id {bad} outside vocabulary of {self.vocab}")
-            tokens[row:row + n] = tok
-            positions[row:row + n] = np.arange(e.start, e.start + n)
-            seq_of_row[row:row + n] = s
-            row_of[i] = row
-            starts[s] = e.start
-            context_lens[s] = e.start + n
-            state_slots[s] = e.cache.state_slot
+            begin = [e.start for e in entries]
+            tokens[:S_real] = toks
+            positions[:S_real] = begin
+            seq_of_row[:S_real] = query_start[:S_real] = np.arange(S_real, dtype=np.int32)
+            query_start[S_real] = S_real
+            starts[:S_real] = begin
+            context_lens[:S_real] = [b + 1 for b in begin]
+            state_slots[:S_real] = [e.cache.state_slot for e in entries]
             for g in range(G):
-                sec(f"slots{g}")[row:row + n] = self.cache.slots(e.cache, g, e.start, e.start + n)
-                t = e.cache.tables[g]
-                k = min(len(t), MB)
-                tables[g][s, :k] = np.maximum(t.ids[:k], 0)  # pages below a window are never read
-            row += n
-            query_start[s + 1] = row
+                slots_g = []
+                for s, e in enumerate(entries):
+                    t = e.cache.tables[g]
+                    page_id = int(t.ids[e.start // page])
+                    if page_id < 0:
+                        raise InvalidArgument("a position below the window was asked for: its page has been given back")
+                    slots_g.append(page_id * page + e.start % page)
+                    k = min(len(t), MB)
+                    tables[g][s, :k] = np.maximum(t.ids[:k], 0) if windowed[g] else t.ids[:k]
+                sec(f"slots{g}")[:S_real] = slots_g
+            row_of = {i: i for i in range(S_real)}
+            row = S_real
+        else:
+            for s, i in enumerate(order):
+                e, n = entries[i], counts[i]
+                tok = np.asarray(e.tokens, dtype=np.int64)
+                if tok.min() < 0 or tok.max() >= self.vocab:
+                    bad = int(tok[(tok < 0) | (tok >= self.vocab)][0])
+                    raise InvalidArgument(f"token id {bad} outside vocabulary of {self.vocab}")
+                tokens[row:row + n] = tok
+                positions[row:row + n] = np.arange(e.start, e.start + n)
+                seq_of_row[row:row + n] = s
+                row_of[i] = row
+                starts[s] = e.start
+                context_lens[s] = e.start + n
+                state_slots[s] = e.cache.state_slot
+                for g in range(G):
+                    sec(f"slots{g}")[row:row + n] = self.cache.slots(e.cache, g, e.start, e.start + n)
+                    t = e.cache.tables[g]
+                    k = min(len(t), MB)
+                    tables[g][s, :k] = np.maximum(t.ids[:k], 0) if windowed[g] else t.ids[:k]  # pages below a window are never read
+                row += n
+                query_start[s + 1] = row
         for s in range(S_real, S):                  # padding
             tokens[row], positions[row], seq_of_row[row] = 0, 0, s
             context_lens[s], state_slots[s] = 0, -1
