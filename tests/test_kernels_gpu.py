@@ -383,6 +383,14 @@ def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window)
     ops.attention_prompt_tc(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, 3, 129, Hq, Hkv, Dh, scale, window)
     assert rel_err(host(out)[:n_multi], want[:n_multi]) < TOL["bfloat16"]
     assert torch.isnan(out[n_multi:].float()).all()          # rows of other sequences are not touched
+    if ops.attention_decode_tma_takes(qd, Hq, Hkv, Dh, page):
+        from tiny_inference_engine_b200.ops import gemm_select
+        out[:] = float("nan")
+        ops.attention_prompt_tma(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, 3, 129, Hq, Hkv, Dh, scale, window)
+        torch.cuda.synchronize()
+        gemm_select.check_status()
+        assert rel_err(host(out)[:n_multi], want[:n_multi]) < TOL["bfloat16"], "TMA-fed prompt kernel"
+        assert torch.isnan(out[n_multi:].float()).all()
     scratch = torch.empty(ops.attention_split_scratch_floats(3, Hq, Dh, 12), device="cuda")
     ops.attention_decode_tc(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, Hq, Hkv, Dh, scale,
                             dev(np.array([3, 4, 5]), torch.int32), 3, 64, 12, scratch, window)
@@ -430,6 +438,9 @@ def test_tensor_core_attention_finds_one_far_key(ops, far):
                                      scratch, torch.zeros(Hkv, dtype=torch.int32, device="cuda"))
         else:
             ops.attention_prompt_tc(*args, *meta, 1, n_new, Hq, Hkv, Dh, 1 / np.sqrt(Dh))
+            assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, "cp.async prompt kernel"
+            out.zero_()
+            ops.attention_prompt_tma(*args, *meta, 1, n_new, Hq, Hkv, Dh, 1 / np.sqrt(Dh))
         assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, f"n_new={n_new}"
 
 

@@ -273,8 +273,18 @@ def attention_decode_tc(q, k_cache, v_cache, out, query_start, context_lens, blo
 
 
 def attention_decode_tma_takes(q: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
-    """Whether the TMA-fed decode kernel takes these operands."""
+    """Whether the TMA-fed attention kernels (decode and prompt) take these operands."""
     return attention_tc_takes(q, q_heads, kv_heads, head_dim) and page_size >= 8 and page_size & (page_size - 1) == 0
+
+
+def attention_prompt_tma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, n_seqs: int, max_queries: int,
+                         q_heads, kv_heads, head_dim, scale: float, window: int = 0) -> None:
+    """As attention_prompt_tc, keys and values fed by TMA (pages that are powers of two from 8 up)."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables)
+    _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    call("tie_attention_prompt_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+         query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs,
+         max_queries, q_heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _stream())
 
 
 def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim,

@@ -122,8 +122,10 @@ class GQAttention(Mixer):
         if ctx.multi_rows > 0:
             n = ctx.multi_rows
             if tc:
-                ops.attention_prompt_tc(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables,
-                                        ctx.multi_seqs, ctx.multi_max_queries, Hq, Hkv, Dh, self.scale, self.window)
+                tma = ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, cache.k.shape[2])
+                fn = ops.attention_prompt_tma if tma else ops.attention_prompt_tc
+                fn(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, ctx.multi_seqs,
+                   ctx.multi_max_queries, Hq, Hkv, Dh, self.scale, self.window)
             else:
                 ops.attention_rows(q[:n], cache.k, cache.v, attn[:n], ctx.seq_of_row[:n], ctx.query_start,
                                    ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale, self.window)
