@@ -41,8 +41,9 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
   constexpr int STAGE_BYTES = 2 * PLANE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* q_tile = smem + STAGES * STAGE_BYTES;                       // 64 rows x DH, row layout
-  uint64_t* full = reinterpret_cast<uint64_t*>(q_tile + 64 * DH * 2);
+  uint8_t* q_tile = smem;                                              // 64 rows x DH, row layout: borrowed from the ring until the
+                                                                       // consumers hold Q in registers (the producer waits for that)
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
   int* flags = reinterpret_cast<int*>(empty + STAGES);
 
@@ -86,6 +87,13 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
   }
   __syncthreads();
   volatile int* abort_flag = flags;
+  uint32_t qf[DH / 16][4];
+  if (warp < 4) {
+    const uint32_t q_addr = smem_u32(q_tile);
+#pragma unroll
+    for (int ks = 0; ks < DH / 16; ++ks) ldmatrix_x4(qf[ks], q_addr + RowLayout<DH>::at(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+  }
+  __syncthreads();   // Q is in registers: the ring is free for keys and values
 
   if (warp == 4) {
     // ---- producer: lane b fetches box b of every tile (a page, or 64 keys of a larger page)
@@ -113,10 +121,6 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
     }
   } else {
     // ---- consumers: warp w owns rows row0 + 16 w .. + 15
-    uint32_t qf[DH / 16][4];
-    const uint32_t q_addr = smem_u32(q_tile);
-#pragma unroll
-    for (int ks = 0; ks < DH / 16; ++ks) ldmatrix_x4(qf[ks], q_addr + RowLayout<DH>::at(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
     const int g = lane >> 2, tq = lane & 3;
     int row_pos[2];
 #pragma unroll
@@ -194,7 +198,8 @@ template <int DH>
 static int launch_prompt_tma(const CUtensorMap& km, const CUtensorMap& vm, const PromptArgs& a, int n_seqs, int max_rows,
                              cudaStream_t s) {
   constexpr int STAGES = DH >= 256 ? 2 : (DH == 128 ? 3 : 4);
-  constexpr size_t smem = static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128 + 64 * DH * 2 + 2 * STAGES * 8 + 16 + 1024;
+  constexpr size_t smem = static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128 + 2 * STAGES * 8 + 16 + 1024;
+  static_assert(64 * DH * 2 <= STAGES * 2 * (DH / 64) * 64 * 128, "the Q tile borrows the ring");
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_prompt_tma_kernel<DH, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {

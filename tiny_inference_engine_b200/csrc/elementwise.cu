@@ -33,7 +33,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // The delta may also come as float partial sums of a split matrix product: part[z][row][dim],
 // z < splits, part_stride floats apart; they are added in split order.
 template <typename T, int VPT>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ part,
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ part,
                                    long long part_stride, int splits, const int* __restrict__ rows,
                                    const float* __restrict__ w, float eps, T* __restrict__ out, int dim) {
   pdl_sync();
@@ -60,10 +60,33 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int k = threadIdx.x + i * blockDim.x;
-      v[i] = 0.0f;
+      v[i] = k < dim ? xr[k] : 0.0f;
+    }
+    if (dr) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int k = threadIdx.x + i * blockDim.x;
+        if (k < dim) v[i] += ld(dr + k);
+      }
+    } else if (pr) {   // split by split, the VPT loads of a split in flight together; each element still adds in split order
+      float d[VPT];
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) d[i] = 0.0f;
+      for (int z = 0; z < splits; ++z) {
+        const float* pz = pr + static_cast<long long>(z) * part_stride;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int k = threadIdx.x + i * blockDim.x;
+          if (k < dim) d[i] += pz[k];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) v[i] += d[i];
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int k = threadIdx.x + i * blockDim.x;
       if (k < dim) {
-        v[i] = xr[k];
-        if (has_delta) v[i] += delta_at(k);
         if (write_back) xr[k] = v[i];
         ss += v[i] * v[i];
       }
