@@ -79,30 +79,33 @@ template <int BN, bool DEEP> struct TcConfig {
   static constexpr int kBudget = DEEP ? 200 * 1024 : 100 * 1024;
   static constexpr int kFit = kBudget / kStage < 2 ? 2 : kBudget / kStage;
   static constexpr int kStages = kFit > 8 ? 8 : kFit;
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators
   static constexpr size_t kSmem = static_cast<size_t>(kStages) * kStage + 1024 /*alignment*/ + 256 /*barriers*/;
+  static_assert(2 * kStages * 8 + 4 * 8 + 16 <= 256, "barriers do not fit");
 };
 
-// out_mode: 0 = OutT out[i * ldo + j] (plain), 1 = OutT out[j * ldo + i] (transposed),
-// and with partial != nullptr the same two layouts in float at partial + z * part_stride.
+// out: OutT out[i * ldo + j] (plain) or out[j * ldo + i] (transposed); with partial != nullptr the
+// same two layouts in float at partial + z * part_stride (row stride ldp). A CTA walks the
+// output tiles blockIdx.x, blockIdx.x + gridDim.x, ... (tile t covers rows 128 * (t % tiles_x)
+// of the row operand and BN * (t / tiles_x) of the column operand); two accumulators in tensor
+// memory let the MMAs of the next tile run while the epilogue drains the last one.
 template <int BN, typename OutT, bool DEEP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, OutT* __restrict__ out,
                float* __restrict__ partial, long long part_stride, long long ldp, int rows_x, int rows_y, int k_blocks,
-               int k_blocks_per_split, long long ldo, int transposed, int silu, int* status) {
+               int k_blocks_per_split, long long ldo, int transposed, int silu, int tiles_x, int n_tiles, int* status) {
   pdl_launch_dependents();   // the next kernel may get resident now; it waits for this one at its own pdl_wait()
   using C = TcConfig<BN, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStage);
   uint64_t* empty = full + C::kStages;
-  uint64_t* acc_full = empty + C::kStages;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = empty + C::kStages;     // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int i0 = blockIdx.x * kBM;   // first row of the row operand
-  const int j0 = blockIdx.y * BN;    // first row of the column operand
   const int kb_begin = blockIdx.z * k_blocks_per_split;
   const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
 
@@ -111,7 +114,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
-    mbar_init(acc_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, 4);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -123,181 +129,203 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_acc = *tmem_holder;
+  const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 4) {
     // ---- TMA producer. The weights never change, so their tiles of the first stages are fetched
     // before this kernel waits for the one before it; the activations only after.
     if (lane == 0) {
-      const CUtensorMap* map_static = transposed ? &map_x : &map_y;
-      const CUtensorMap* map_dynamic = transposed ? &map_y : &map_x;
-      const int off_static = transposed ? 0 : C::kStageA, off_dynamic = transposed ? C::kStageA : 0;
-      const int row_static = transposed ? i0 : j0, row_dynamic = transposed ? j0 : i0;
-      const int pre = min(C::kStages, kb_end - kb_begin);
-      for (int p = 0; p < pre; ++p) {   // fresh barriers: the stages are free
-        mbar_expect_tx(full + p, C::kStage);
-        tma_load_2d(smem + p * C::kStage + off_static, map_static, (kb_begin + p) * kBK, row_static, full + p);
-      }
-      pdl_wait();
-      for (int p = 0; p < pre; ++p) {
-        tma_load_2d(smem + p * C::kStage + off_dynamic, map_dynamic, (kb_begin + p) * kBK, row_dynamic, full + p);
-      }
-      int it = pre;
-      for (int kb = kb_begin + pre; kb < kb_end; ++kb, ++it) {
-        const int s = it % C::kStages;
-        const uint32_t parity = ((it / C::kStages) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
-        if (!mbar_wait(empty + s, parity, abort_flag, status, 1)) break;
-        uint8_t* sa = smem + s * C::kStage;
-        mbar_expect_tx(full + s, C::kStage);
-        tma_load_2d(sa, &map_x, kb * kBK, i0, full + s);
-        tma_load_2d(sa + C::kStageA, &map_y, kb * kBK, j0, full + s);
+      int it = 0;
+      bool first = true, ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int i0 = (tile % tiles_x) * kBM, j0 = (tile / tiles_x) * BN;
+        int kb = kb_begin;
+        if (first) {
+          first = false;
+          const CUtensorMap* map_static = transposed ? &map_x : &map_y;
+          const CUtensorMap* map_dynamic = transposed ? &map_y : &map_x;
+          const int off_static = transposed ? 0 : C::kStageA, off_dynamic = transposed ? C::kStageA : 0;
+          const int row_static = transposed ? i0 : j0, row_dynamic = transposed ? j0 : i0;
+          const int pre = min(C::kStages, kb_end - kb_begin);
+          for (int p = 0; p < pre; ++p) {   // fresh barriers: the stages are free
+            mbar_expect_tx(full + p, C::kStage);
+            tma_load_2d(smem + p * C::kStage + off_static, map_static, (kb_begin + p) * kBK, row_static, full + p);
+          }
+          pdl_wait();
+          for (int p = 0; p < pre; ++p) {
+            tma_load_2d(smem + p * C::kStage + off_dynamic, map_dynamic, (kb_begin + p) * kBK, row_dynamic, full + p);
+          }
+          it = pre;
+          kb = kb_begin + pre;
+        }
+        for (; kb < kb_end; ++kb, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t parity = ((it / C::kStages) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
+          if (!mbar_wait(empty + s, parity, abort_flag, status, 1)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * C::kStage;
+          mbar_expect_tx(full + s, C::kStage);
+          tma_load_2d(sa, &map_x, kb * kBK, i0, full + s);
+          tma_load_2d(sa + C::kStageA, &map_y, kb * kBK, j0, full + s);
+        }
       }
     }
   } else if (warp == 5) {
     // ---- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
-      int it = 0;
+      int it = 0, local = 0;
       bool ok = true;
-      for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-        const int s = it % C::kStages;
-        if (!mbar_wait(full + s, (it / C::kStages) & 1, abort_flag, status, 2)) {
-          ok = false;
-          break;
-        }
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (!mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2)) break;   // the epilogue has drained it
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(smem + s * C::kStage);
-        const uint32_t b_addr = a_addr + C::kStageA;
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const int s = it % C::kStages;
+          if (!mbar_wait(full + s, (it / C::kStages) & 1, abort_flag, status, 2)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(smem + s * C::kStage);
+          const uint32_t b_addr = a_addr + C::kStageA;
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          umma_bf16(tmem_acc, smem_desc_sw128(a_addr + k * kUmmaK * 2), smem_desc_sw128(b_addr + k * kUmmaK * 2), idesc,
-                    (it > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            umma_bf16(tmem_acc, smem_desc_sw128(a_addr + k * kUmmaK * 2), smem_desc_sw128(b_addr + k * kUmmaK * 2), idesc,
+                      (kb > kb_begin || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty + s);   // arrives once the MMAs above have read the stage
         }
-        umma_commit(empty + s);   // arrives once the MMAs above have read the stage
+        if (ok) umma_commit(acc_full + buf);
       }
-      if (ok) umma_commit(acc_full);
     }
   } else {
     // ---- epilogue: warp w reads lanes 32w..32w+31, 16 columns at a time
-    const bool have = kb_end > kb_begin;
-    bool ok = true;
-    if (have) ok = mbar_wait(acc_full, 0, abort_flag, status, 3);
-    pdl_wait();   // nothing is stored before the kernels ahead in the stream are done
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int i = i0 + warp * 32 + lane;
     float* part = partial ? partial + static_cast<long long>(blockIdx.z) * part_stride : nullptr;
-    if (ok && silu) {
-      // The weight rows come in blocks of 16 gate rows followed by their 16 up rows; the output is
-      // silu(gate) * up, half as wide as the product: out[token, 16 * block + r].
-      if (transposed) {
-        // lanes 0-15 of a warp hold gate rows, lanes 16-31 the matching up rows: exchange, then
-        // the lower half finishes columns 0-7 of each chunk and the upper half columns 8-15
-        const int o = (i0 >> 1) + warp * 16 + (lane & 15);
-        const bool upper = lane >= 16;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int i0 = (tile % tiles_x) * kBM, j0 = (tile / tiles_x) * BN;
+      if (!mbar_wait(acc_full + buf, (local >> 1) & 1, abort_flag, status, 3)) break;
+      if (local == 0) pdl_wait();   // nothing is stored before the kernels ahead in the stream are done
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + buf * BN;
+      const int i = i0 + warp * 32 + lane;
+      if (silu) {
+        // The weight rows come in blocks of 16 gate rows followed by their 16 up rows; the output is
+        // silu(gate) * up, half as wide as the product: out[token, 16 * block + r].
+        if (transposed) {
+          // lanes 0-15 of a warp hold gate rows, lanes 16-31 the matching up rows: exchange, then
+          // the lower half finishes columns 0-7 of each chunk and the upper half columns 8-15
+          const int o = (i0 >> 1) + warp * 16 + (lane & 15);
+          const bool upper = lane >= 16;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          if (j0 + c0 >= rows_y) break;
-          uint32_t r[16];
-          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (j0 + c0 >= rows_y) break;
+            uint32_t r[16];
+            tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            // the lower lane sends its gate of column e + 8 and receives the up of column e;
-            // the upper lane sends its up of column e and receives the gate of column e + 8
-            const uint32_t got = __shfl_xor_sync(0xffffffffu, upper ? r[e] : r[e + 8], 16);
-            const float g = __uint_as_float(upper ? got : r[e]);
-            const float u = __uint_as_float(upper ? r[e + 8] : got);
-            const int j = j0 + c0 + e + (upper ? 8 : 0);
-            if (j < rows_y && o < (rows_x >> 1)) st(out + static_cast<long long>(j) * ldo + o, g / (1.0f + expf(-g)) * u);
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (j0 + c0 >= rows_y) break;
-          uint32_t g[16], u[16];
-          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, g);
-          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0 + 16, u);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (i < rows_x) {
-            float v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const float gv = __uint_as_float(g[e]);
-              v[e] = gv / (1.0f + expf(-gv)) * __uint_as_float(u[e]);
-            }
-            const long long at = static_cast<long long>(i) * ldo + ((j0 + c0) >> 1);
-            if (((at * sizeof(OutT)) & 15) == 0 && sizeof(OutT) == 2) {
-              uint32_t w[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                w[e] = *reinterpret_cast<const uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(out + at) = make_uint4(w[0], w[1], w[2], w[3]);
-              *reinterpret_cast<uint4*>(out + at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 16; ++e) st(out + at + e, v[e]);
+            for (int e = 0; e < 8; ++e) {
+              // the lower lane sends its gate of column e + 8 and receives the up of column e;
+              // the upper lane sends its up of column e and receives the gate of column e + 8
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, upper ? r[e] : r[e + 8], 16);
+              const float g = __uint_as_float(upper ? got : r[e]);
+              const float u = __uint_as_float(upper ? r[e + 8] : got);
+              const int j = j0 + c0 + e + (upper ? 8 : 0);
+              if (j < rows_y && o < (rows_x >> 1)) st(out + static_cast<long long>(j) * ldo + o, g / (1.0f + expf(-g)) * u);
             }
           }
-        }
-      }
-    } else if (ok) {
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (j0 + c0 >= rows_y) break;   // uniform over the warp
-        uint32_t r[16];
-        if (have) {
-          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            if (j0 + c0 >= rows_y) break;
+            uint32_t g[16], u[16];
+            tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, g);
+            tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0 + 16, u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (i < rows_x) {
+              float v[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) r[e] = 0u;
-        }
-        if (i < rows_x) {
-          if (transposed) {
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int j = j0 + c0 + e;
-              if (j < rows_y) {
-                if (part) part[static_cast<long long>(j) * ldp + i] = __uint_as_float(r[e]);
-                else st(out + static_cast<long long>(j) * ldo + i, __uint_as_float(r[e]));
+              for (int e = 0; e < 16; ++e) {
+                const float gv = __uint_as_float(g[e]);
+                v[e] = gv / (1.0f + expf(-gv)) * __uint_as_float(u[e]);
               }
-            }
-          } else {
-            const long long at = static_cast<long long>(i) * ldo + j0 + c0;
-            const int n = min(16, rows_y - (j0 + c0));
-            if (part) {
-              const long long pat = static_cast<long long>(i) * ldp + j0 + c0;
-              if (n == 16 && (pat & 3) == 0) {
-#pragma unroll
-                for (int e = 0; e < 16; e += 4)
-                  *reinterpret_cast<uint4*>(part + pat + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
-              } else {
-                for (int e = 0; e < n; ++e) part[pat + e] = __uint_as_float(r[e]);
-              }
-            } else if (n == 16 && ((at * sizeof(OutT)) & 15) == 0) {
-              if constexpr (sizeof(OutT) == 2) {
+              const long long at = static_cast<long long>(i) * ldo + ((j0 + c0) >> 1);
+              if (((at * sizeof(OutT)) & 15) == 0 && sizeof(OutT) == 2) {
                 uint32_t w[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                  const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
                   w[e] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 *reinterpret_cast<uint4*>(out + at) = make_uint4(w[0], w[1], w[2], w[3]);
                 *reinterpret_cast<uint4*>(out + at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
               } else {
 #pragma unroll
-                for (int e = 0; e < 16; e += 4)
-                  *reinterpret_cast<uint4*>(out + at + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                for (int e = 0; e < 16; ++e) st(out + at + e, v[e]);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (j0 + c0 >= rows_y) break;   // uniform over the warp
+          uint32_t r[16];
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (i < rows_x) {
+            if (transposed) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const int j = j0 + c0 + e;
+                if (j < rows_y) {
+                  if (part) part[static_cast<long long>(j) * ldp + i] = __uint_as_float(r[e]);
+                  else st(out + static_cast<long long>(j) * ldo + i, __uint_as_float(r[e]));
+                }
               }
             } else {
-              for (int e = 0; e < n; ++e) st(out + at + e, __uint_as_float(r[e]));
+              const long long at = static_cast<long long>(i) * ldo + j0 + c0;
+              const int n = min(16, rows_y - (j0 + c0));
+              if (part) {
+                const long long pat = static_cast<long long>(i) * ldp + j0 + c0;
+                if (n == 16 && (pat & 3) == 0) {
+#pragma unroll
+                  for (int e = 0; e < 16; e += 4)
+                    *reinterpret_cast<uint4*>(part + pat + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                } else {
+                  for (int e = 0; e < n; ++e) part[pat + e] = __uint_as_float(r[e]);
+                }
+              } else if (n == 16 && ((at * sizeof(OutT)) & 15) == 0) {
+                if constexpr (sizeof(OutT) == 2) {
+                  uint32_t w[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+                    w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                  }
+                  *reinterpret_cast<uint4*>(out + at) = make_uint4(w[0], w[1], w[2], w[3]);
+                  *reinterpret_cast<uint4*>(out + at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 16; e += 4)
+                    *reinterpret_cast<uint4*>(out + at + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                }
+              } else {
+                for (int e = 0; e < n; ++e) st(out + at + e, __uint_as_float(r[e]));
+              }
             }
           }
         }
       }
+      // this accumulator may be overwritten by the tile after next
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(acc_empty + buf)) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -309,7 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
   }
   if (warp == 4) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(C::kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
   }
 }
 
@@ -343,10 +371,16 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, fl
   }
   const int k_blocks = ceil_div(K, kBK);
   const int per_split = ceil_div(k_blocks, splits);
-  const dim3 grid(ceil_div(rows_x, kBM), ceil_div(rows_y, BN), ceil_div(k_blocks, per_split));
+  const int tiles_x = ceil_div(rows_x, kBM), n_tiles = tiles_x * ceil_div(rows_y, BN);
+  const int z = ceil_div(k_blocks, per_split);
+  // one CTA per SM walks the tiles when there are more tiles than SMs (deep ring); the narrow
+  // rings (two CTAs per SM) get one CTA per tile
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  const int ctas = DEEP ? (n_tiles * z > sms ? max(1, sms / z) : n_tiles) : n_tiles;
+  const dim3 grid(min(ctas, n_tiles), 1, z);
   TIE_LAUNCH((gemm_tc_kernel<BN, OutT, DEEP>), grid, kThreads, C::kSmem, s, mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
-                                                            rows_x, rows_y, k_blocks, per_split, ldo, transposed, silu,
-                                                            status_word());
+             rows_x, rows_y, k_blocks, per_split, ldo, transposed, silu, tiles_x, n_tiles, status_word());
   return kOk;
 }
 
