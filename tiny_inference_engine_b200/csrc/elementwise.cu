@@ -115,6 +115,97 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
   }
 }
 
+// The same for rows whose length is a multiple of 4: every thread owns whole 16-byte pieces of the
+// float row (and the matching 8 or 16 bytes of delta and output), NV of them, and the partial
+// sums of a split product are read one 16-byte piece per split.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(t.x << 16), __uint_as_float(t.x & 0xffff0000u), __uint_as_float(t.y << 16),
+                       __uint_as_float(t.y & 0xffff0000u));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+  }
+};
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                                                const float* __restrict__ part, long long part_stride,
+                                                                int splits, const int* __restrict__ rows,
+                                                                const float* __restrict__ w, float eps, T* __restrict__ out,
+                                                                int dim) {
+  pdl_sync();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[t] : t) * dim;
+  float* xr = x + src;
+  const T* dr = delta ? delta + src : nullptr;
+  const float* pr = part ? part + src : nullptr;
+  T* o = out + static_cast<size_t>(t) * dim;
+  const bool write_back = (dr != nullptr || pr != nullptr) && rows == nullptr;
+  const int pieces = dim >> 2;
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < pieces ? *reinterpret_cast<const float4*>(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (dr) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < pieces) {
+        const float4 d = Vec4<T>::load(dr + 4 * c);
+        v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
+      }
+    }
+  } else if (pr) {
+    float4 d[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) d[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int z = 0; z < splits; ++z) {   // every element still adds its splits in order
+      const float* pz = pr + static_cast<long long>(z) * part_stride;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < pieces) {
+          const float4 q = *reinterpret_cast<const float4*>(pz + 4 * c);
+          d[i].x += q.x; d[i].y += q.y; d[i].z += q.z; d[i].w += q.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) { v[i].x += d[i].x; v[i].y += d[i].y; v[i].z += d[i].z; v[i].w += d[i].w; }
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < pieces) {
+      if (write_back) *reinterpret_cast<float4*>(xr + 4 * c) = v[i];
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < pieces) {
+      const float4 ww = *reinterpret_cast<const float4*>(w + 4 * c);
+      Vec4<T>::store(o + 4 * c, make_float4((v[i].x * inv) * ww.x, (v[i].y * inv) * ww.y, (v[i].z * inv) * ww.z, (v[i].w * inv) * ww.w));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // RMSNorm of n rows of `size` elements of T (stride `row_stride`), one warp per row. Used for
 // norms over something else than the residual stream (per-head norms outside the fused kernel).
@@ -214,10 +305,22 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
   pdl_sync();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
-  if (item >= total) return;
-  const long long t = item / heads_per_token;
-  const int head = static_cast<int>(item - t * heads_per_token);
+  const int warps = blockDim.x >> 5;
+  const long long t = blockIdx.x;
+  const int head = blockIdx.y * warps + warp;
+  // the token's rotation, once for the heads of this block: cos at [0, half), sin at [half, 2 half)
+  float* cs = smem + warps * head_dim;
+  const int half = inv_freq ? rot / 2 : 0;
+  if (half > 0) {
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float angle = pos * inv_freq[i];
+      cs[i] = cosf(angle);
+      cs[half + i] = sinf(angle);
+    }
+  }
+  __syncthreads();
+  if (head >= heads_per_token) return;
   T* src = qkv + t * row_stride + static_cast<long long>(head) * head_dim;
   const float* psrc = part ? part + t * part_ld + static_cast<long long>(head) * head_dim : nullptr;
   auto value = [&](int i) -> float {
@@ -260,12 +363,9 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
     for (int i = lane; i < head_dim; i += 32) buf[i] = (buf[i] * inv) * w[i];
   }
   __syncwarp();
-  const int half = inv_freq ? rot / 2 : 0;
   if (half > 0) {
-    const float pos = static_cast<float>(positions[t]);
     for (int i = lane; i < half; i += 32) {
-      const float angle = pos * inv_freq[i];
-      const float c = cosf(angle), s = sinf(angle);
+      const float c = cs[i], s = cs[half + i];
       const float x1 = buf[i], x2 = buf[i + half];
       st(dst + i, x1 * c - x2 * s);
       st(dst + i + half, x2 * c + x1 * s);
@@ -286,9 +386,24 @@ template <typename T>
 int launch_add_rmsnorm(float* x, const void* delta, const float* part, long long part_stride, int splits,
                        const int* rows, const float* w, float eps, void* out, int n, int dim, cudaStream_t s) {
   if (n == 0) return kOk;
-  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
   const T* d = static_cast<const T*>(delta);
   T* o = static_cast<T*>(out);
+  const bool aligned = dim % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(delta) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(part) % 16 == 0 && part_stride % 4 == 0;
+  if (aligned && dim <= 16384) {
+    // few rows (decode): many threads per row keep the latency short; many rows: 256 threads per row
+    const int pieces = dim / 4;
+    int threads = n <= 512 ? 1024 : 256;
+    while (threads < 1024 && pieces > 4 * threads) threads *= 2;
+    while (threads > 32 && threads / 2 >= pieces) threads /= 2;
+    const int nv = (pieces + threads - 1) / threads;
+    if (nv <= 1) TIE_LAUNCH((add_rmsnorm_vec4_kernel<T, 1>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
+    else if (nv <= 2) TIE_LAUNCH((add_rmsnorm_vec4_kernel<T, 2>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
+    else TIE_LAUNCH((add_rmsnorm_vec4_kernel<T, 4>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
+    TIE_RETURN_LAUNCH("add_rmsnorm");
+  }
+  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
   if (dim <= 4 * threads) TIE_LAUNCH((add_rmsnorm_kernel<T, 4>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
   else if (dim <= 16 * threads) TIE_LAUNCH((add_rmsnorm_kernel<T, 16>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
   else TIE_LAUNCH((add_rmsnorm_kernel<T, 0>), n, threads, 0, s, x, d, part, part_stride, splits, rows, w, eps, o, dim);
@@ -342,9 +457,9 @@ int launch_qk_norm_rope_append(void* qkv, long long stride, const float* part, l
   const int heads_per_token = write_kv ? q_heads + 2 * kv_heads : q_heads;
   const long long total = static_cast<long long>(tokens) * heads_per_token;
   if (total == 0) return kOk;
-  const int warps = 4;
-  const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
-  TIE_LAUNCH((qk_norm_rope_append_kernel<T>), ceil_div(total, warps), warps * 32, smem, s, 
+  const int warps = 8;
+  const size_t smem = (static_cast<size_t>(warps) * head_dim + rot) * sizeof(float);
+  TIE_LAUNCH((qk_norm_rope_append_kernel<T>), dim3(tokens, ceil_div(heads_per_token, warps)), warps * 32, smem, s, 
       static_cast<T*>(qkv), stride, part, part_stride, splits, part_ld, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots,
       static_cast<T*>(kc),
       static_cast<T*>(vc), q_heads, kv_heads, head_dim, page_size, heads_per_token, total);
