@@ -312,7 +312,8 @@ def test_refusals_are_clear(ops):
 
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 @pytest.mark.parametrize("M,N,K", [(1, 503, 96), (3, 311, 144), (8, 1000, 520), (16, 72, 200), (33, 300, 64), (77, 130, 1000),
-                                   (128, 256, 512), (200, 96, 72), (300, 503, 96), (700, 311, 136)])
+                                   (128, 256, 512), (200, 96, 72), (300, 503, 96), (700, 311, 136), (513, 256, 64),
+                                   (1100, 777, 520)])
 def test_gemm_tensor_cores(ops, out_dtype, M, N, K):
     """tcgen05 product with the tiling the engine would pick, at sizes that end inside a tile in
     every direction (rows, columns, k)."""
@@ -341,6 +342,34 @@ def test_gemm_tensor_cores_every_tiling(ops, transposed, bn, splits):
     gemm_select.check_status()
     assert rel_err(host(out), plain.linear(a, w)) < 2e-5
     assert (wide[:, :8] == 7).all() and (wide[:, 8 + N:] == 7).all()      # nothing is written beside the output
+
+
+@pytest.mark.parametrize("silu", [False, True])
+def test_gemm_on_pairs_of_sms(ops, silu):
+    """The cta_group::2 kernel on more tiles than there are pairs of SMs (each pair walks several,
+    alternating its two accumulators), ragged in rows, columns and k, into a strided output; equal,
+    bit for bit, to the one-CTA kernel, which adds the same products in the same order."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(5 + silu)
+    M, N, K = 2300, 4000 + 96 * silu, 328
+    a = dev(as_stored(rng.standard_normal((M, K)), "bfloat16"), torch.bfloat16)
+    w = dev(as_stored(rng.standard_normal((N, K)) * 0.1, "bfloat16"), torch.bfloat16)
+    cols = N // 2 if silu else N
+    wide = torch.full((M, cols + 24), 7.0, device="cuda", dtype=torch.bfloat16)
+    out, want = wide[:, 8:8 + cols], torch.empty(M, cols, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        gemm_select.gemm_tc(a, w, out, silu=silu, pair=True)
+    gemm_select.gemm_tc(a, w, want, silu=silu, pair=False)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert torch.equal(out, want)
+    assert (wide[:, :8] == 7).all() and (wide[:, 8 + cols:] == 7).all()
+    rows = slice(M - 300, M)
+    ref = plain.linear(host(a)[rows], host(w))
+    if silu:
+        ref = ref.reshape(300, -1, 2, 16)
+        ref = plain.swiglu(ref[:, :, 0].reshape(300, -1), ref[:, :, 1].reshape(300, -1))
+    assert rel_err(host(out)[rows], ref) < TOL["bfloat16"]
 
 
 def test_gemm_falls_back_when_tma_cannot_address_the_operands(ops):

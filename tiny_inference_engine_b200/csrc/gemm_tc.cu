@@ -22,7 +22,7 @@
 // tcgen05.commit). Every wait is bounded: when it runs out the kernel records where in a
 // status word, stops waiting, frees its tensor memory and returns; the host reads the word.
 // No TMA multicast is used anywhere.
-#include "tma.cuh"
+#include "umma.cuh"
 
 namespace tie {
 
@@ -30,44 +30,6 @@ constexpr int kBM = 128;          // rows of the row operand per tile = MMA M
 constexpr int kBK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;        // k per tcgen05.mma for 16-bit inputs
 constexpr int kThreads = 192;
-
-// Shared-memory matrix descriptor of a k-major tile with 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);        // start address, 16-byte units
-  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset: unused with swizzle
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;                      // version
-  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor: float accumulator, bfloat16 A and B, both k-major, M = 128, N = BN.
-__host__ __device__ constexpr uint32_t instr_desc(int bn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-}
 
 // DEEP: as many stages as fit in the 227 KB one CTA may use (at most 8), one CTA per SM.
 // Not DEEP: about 100 KB of stages, so that two CTAs share an SM and one's start-up and

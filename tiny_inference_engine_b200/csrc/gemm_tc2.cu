@@ -1,0 +1,322 @@
+// bfloat16 matrix products for many rows (prompt portions) on pairs of SMs: tcgen05.mma with
+// cta_group::2. Two CTAs of a cluster compute one 256 x 256 tile of out[M, N] = a[M, K] . w[N, K]^T:
+// each CTA stages its own 128 rows of a and its own 128 of the 256 rows of w (32 KB per 64-deep
+// k-block instead of the 48 KB a lone CTA needs for 128 x 256), one thread of the leader CTA
+// issues the MMAs for both, and each CTA's tensor memory receives its 128 x 256 float
+// accumulator. A third less operand traffic from L2 per flop is what this buys; the 1-CTA
+// kernel in gemm_tc.cu is limited by exactly that feed.
+//
+// Per CTA: warps 0-3 epilogue (tcgen05.ld, optional SiLU * up, stores), warp 4 TMA producer,
+// warp 5 (leader CTA only) MMA issuer. Barriers: full[s] lives in the leader and counts the
+// bytes of BOTH CTAs' loads (the loads carry .cta_group::2 and name the leader's barrier);
+// empty[s] and acc_full[b] exist in both CTAs and are signalled by tcgen05.commit with a
+// cluster multicast mask; acc_empty[b] lives in the leader and collects the eight epilogue
+// warps of the pair. A pair walks the tiles pair, pair + pairs, ...; two accumulators let a
+// tile's epilogue overlap the next tile's MMAs. Every wait is bounded (status word as in
+// gemm_tc.cu). No TMA multicast: every CTA fetches its own operands.
+#include "umma.cuh"
+
+namespace tie {
+
+constexpr int k2Threads = 192;
+constexpr int k2BK = 64;
+constexpr int k2Stages = 7;
+constexpr int k2StageA = 128 * k2BK * 2;      // this CTA's 128 rows of a
+constexpr int k2StageB = 128 * k2BK * 2;      // this CTA's 128 of the tile's 256 rows of w
+constexpr int k2Stage = k2StageA + k2StageB;
+constexpr int k2TmemCols = 512;               // two 256-column accumulators
+constexpr size_t k2Smem = static_cast<size_t>(k2Stages) * k2Stage + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address of `p` (in this CTA's shared memory) as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far retire.
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(k2Threads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
+                int M, int N, int k_blocks, long long ldo, int silu, int tiles_m, int n_tiles, int* status) {
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + k2Stages * k2Stage);   // used in the leader
+  uint64_t* empty = full + k2Stages;                                         // both CTAs
+  uint64_t* acc_full = empty + k2Stages;                                     // [2], both CTAs
+  uint64_t* acc_empty = acc_full + 2;                                        // [2], used in the leader
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < k2Stages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, 8);     // four epilogue warps of each CTA of the pair
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(k2TmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();      // both CTAs' barriers exist before anyone signals across the pair
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 4) {
+    // ---- TMA producer (both CTAs): own rows of a, own half of the tile's rows of w; bytes count on the leader's barrier
+    if (lane == 0) {
+      int it = 0;
+      bool first = true, ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += pairs) {
+        const int row_a = (tile % tiles_m) * 256 + static_cast<int>(rank) * 128;
+        const int row_w = (tile / tiles_m) * 256 + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % k2Stages;
+          if (!mbar_wait(empty + s, ((it / k2Stages) & 1) ^ 1, abort_flag, status, 1)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = map_to_cta(full + s, 0);
+          if (rank == 0) mbar_expect_tx(full + s, 2 * k2Stage);
+          uint8_t* sa = smem + s * k2Stage;
+          tma_load_2d_pair(sa + k2StageA, &map_w, kb * k2BK, row_w, bar);      // weights never change: before the wait
+          if (first) {
+            first = false;
+            pdl_wait();
+          }
+          tma_load_2d_pair(sa, &map_a, kb * k2BK, row_a, bar);
+        }
+      }
+      if (first) pdl_wait();
+    }
+  } else if (warp == 5) {
+    // ---- MMA issuer: one thread of the leader CTA drives both CTAs' tensor cores
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = instr_desc(256, 256);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += pairs, ++local) {
+        const int buf = local & 1;
+        if (!mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_acc = tmem_base + buf * 256;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % k2Stages;
+          if (!mbar_wait(full + s, (it / k2Stages) & 1, abort_flag, status, 2)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(smem + s * k2Stage);
+          const uint32_t b_addr = a_addr + k2StageA;
+#pragma unroll
+          for (int k = 0; k < k2BK / 16; ++k) {
+            umma2_bf16(tmem_acc, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma2_commit_both(empty + s);
+        }
+        if (ok) umma2_commit_both(acc_full + buf);
+      }
+    }
+  } else {
+    // ---- epilogue (both CTAs): rows i0 .. i0 + 127 of the pair's tile, all 256 columns
+    int local = 0;
+    for (int tile = pair; tile < n_tiles; tile += pairs, ++local) {
+      const int buf = local & 1;
+      const int i0 = (tile % tiles_m) * 256 + static_cast<int>(rank) * 128, j0 = (tile / tiles_m) * 256;
+      if (!mbar_wait(acc_full + buf, (local >> 1) & 1, abort_flag, status, 3)) break;
+      if (local == 0) pdl_wait();
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + buf * 256;
+      const int i = i0 + warp * 32 + lane;
+      if (silu) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < 256; c0 += 32) {
+          if (j0 + c0 >= N) break;
+          uint32_t g[16], u[16];
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, g);
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0 + 16, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (i < M) {
+            float v[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float gv = __uint_as_float(g[e]);
+              v[e] = gv / (1.0f + expf(-gv)) * __uint_as_float(u[e]);
+            }
+            const long long at = static_cast<long long>(i) * ldo + ((j0 + c0) >> 1);
+            if (((at * sizeof(OutT)) & 15) == 0 && sizeof(OutT) == 2) {
+              uint32_t w[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(out + at) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(out + at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) st(out + at + e, v[e]);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < 256; c0 += 16) {
+          if (j0 + c0 >= N) break;
+          uint32_t r[16];
+          tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (i < M) {
+            const long long at = static_cast<long long>(i) * ldo + j0 + c0;
+            const int n = min(16, N - (j0 + c0));
+            if (n == 16 && ((at * sizeof(OutT)) & 15) == 0) {
+              if constexpr (sizeof(OutT) == 2) {
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+                  w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(out + at) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(out + at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 16; e += 4)
+                  *reinterpret_cast<uint4*>(out + at + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+              }
+            } else {
+              for (int e = 0; e < n; ++e) st(out + at + e, __uint_as_float(r[e]));
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) remote_arrive(map_to_cta(acc_empty + buf, 0));   // the leader's MMA thread may reuse this accumulator
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long t0 = clock64();
+    while (clock64() - t0 < 4000000ull) {
+    }
+  }
+  cluster_sync();      // neither CTA leaves while its partner may still touch its shared or tensor memory
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(k2TmemCols) : "memory");
+  }
+}
+
+template <typename OutT>
+static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int silu,
+                      cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2Smem)) != cudaSuccess) {
+      set_error("gemm_tc2: cannot reserve %zu bytes of shared memory", k2Smem);
+      return kCudaError;
+    }
+    configured = true;
+  }
+  const int tiles_m = ceil_div(M, 256), n_tiles = tiles_m * ceil_div(N, 256);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(k2Threads);
+  cfg.dynamicSmemBytes = k2Smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  // pairs that can be resident at once (SMs pair up inside a GPC, so it may be fewer than half the SMs)
+  static int resident_pairs = 0;
+  if (resident_pairs == 0) {
+    cfg.gridDim = dim3(2 * 74);
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<OutT>, &cfg) != cudaSuccess || n < 1) {
+      set_error("gemm_tc2: no pair of SMs can hold the kernel (%s)", cudaGetErrorString(cudaGetLastError()));
+      return kCudaError;
+    }
+    resident_pairs = n;
+  }
+  const int pairs = n_tiles < resident_pairs ? n_tiles : resident_pairs;
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<OutT>, ma, mw, static_cast<OutT*>(out), M, N, ceil_div(K, k2BK), ldo, silu, tiles_m,
+                     n_tiles, status_word());
+  return kOk;
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+// out[M, N] (or, with silu, out[M, N / 2] = silu(gate) * up for w in blocks of 16 gate + 16 up rows)
+// = a[M, K] . w[N, K]^T on pairs of SMs. a, w bfloat16 with K and row strides multiples of 8.
+TIE_API int tie_gemm_tc2(int out_dtype, const void* a, const void* w, void* out, int M, int N, int K, long long lda,
+                         long long ldw, long long ldo, int silu, cudaStream_t s) {
+  TIE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc2: bad sizes M=%d N=%d K=%d", M, N, K);
+  TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc2: K=%d and the row strides must be multiples of 8", K);
+  TIE_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
+              "gemm_tc2: operands must be 16-byte aligned");
+  TIE_REQUIRE(out_dtype == TIE_BF16 || out_dtype == TIE_F32, "gemm_tc2: output dtype code %d", out_dtype);
+  TIE_REQUIRE(!silu || N % 32 == 0, "gemm_tc2: the SiLU epilogue needs weight rows in blocks of 16 gate + 16 up (N=%d)", N);
+  TIE_REQUIRE(status_word() != nullptr, "gemm_tc2: cannot allocate the status word");
+  CUtensorMap ma, mw;
+  TIE_REQUIRE(make_map_bf16(&ma, a, M, K, lda, k2BK, 128) && make_map_bf16(&mw, w, N, K, ldw, k2BK, 128),
+              "gemm_tc2: cuTensorMapEncodeTiled failed (M %d, N %d, K %d)", M, N, K);
+  const int st = out_dtype == TIE_BF16 ? launch_tc2<__nv_bfloat16>(ma, mw, out, M, N, K, ldo, silu, s)
+                                       : launch_tc2<float>(ma, mw, out, M, N, K, ldo, silu, s);
+  if (st != kOk) return st;
+  TIE_RETURN_LAUNCH("gemm_tc2");
+}

@@ -7,6 +7,7 @@ row strides multiples of 8 elements, 16-byte aligned bases), else on the CUDA co
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -54,8 +55,15 @@ def _scratch_for(numel: int, device) -> torch.Tensor:
     return buf
 
 
+PAIR_MIN_ROWS = 512     # from this many tokens on, 256 x 256 tiles on pairs of SMs (cta_group::2)
+
+
+def pair_takes(M: int, N: int) -> bool:
+    return M >= PAIR_MIN_ROWS and N >= 256 and os.environ.get("TIE_NO_PAIR_GEMM") != "1"
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None, bn=None, splits=None, scratch=None,
-            silu: bool = False, partial_scratch=None, deep=None):
+            silu: bool = False, partial_scratch=None, deep=None, pair=None):
     """The tensor-core product; the tiling can be forced (tests). Returns `out`, or a SplitSum when
     `partial_scratch` is given and k is split."""
     from . import SplitSum, _need, _stream, dtype_code
@@ -65,6 +73,12 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None
           f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm: last axes must be contiguous")
     _need(tc_takes(a, w, out), "gemm_tc: operands must be bfloat16 with K and row strides multiples of 8, 16-byte aligned")
+    if pair is None:
+        pair = transposed is None and bn is None and splits is None and pair_takes(M, N)
+    if pair:
+        _call("tie_gemm_tc2", dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
+              w.stride(0), out.stride(0), 1 if silu else 0, _stream())
+        return out
     t, b, s = plan(M, N, K)
     transposed = t if transposed is None else int(transposed)
     bn = b if bn is None else bn
