@@ -420,6 +420,13 @@ def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window)
         gemm_select.check_status()
         assert rel_err(host(out)[:n_multi], want[:n_multi]) < TOL["bfloat16"], "TMA-fed prompt kernel"
         assert torch.isnan(out[n_multi:].float()).all()
+        if Dh in (64, 128):
+            out[:] = float("nan")
+            ops.attention_prompt_umma(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, 3, 129, Hq, Hkv, Dh, scale, window)
+            torch.cuda.synchronize()
+            gemm_select.check_status()
+            assert rel_err(host(out)[:n_multi], want[:n_multi]) < TOL["bfloat16"], "tcgen05 prompt kernel"
+            assert torch.isnan(out[n_multi:].float()).all()
     scratch = torch.empty(ops.attention_split_scratch_floats(3, Hq, Dh, 12), device="cuda")
     ops.attention_decode_tc(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, Hq, Hkv, Dh, scale,
                             dev(np.array([3, 4, 5]), torch.int32), 3, 64, 12, scratch, window)
@@ -470,7 +477,64 @@ def test_tensor_core_attention_finds_one_far_key(ops, far):
             assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, "cp.async prompt kernel"
             out.zero_()
             ops.attention_prompt_tma(*args, *meta, 1, n_new, Hq, Hkv, Dh, 1 / np.sqrt(Dh))
+            assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, "TMA-fed prompt kernel"
+            out.zero_()
+            ops.attention_prompt_umma(*args, *meta, 1, n_new, Hq, Hkv, Dh, 1 / np.sqrt(Dh))
         assert np.abs(host(out)[-1] - want[-1]).max() < 2e-2, f"n_new={n_new}"
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(8, 2, 128, 16, 0), (6, 2, 64, 8, 0), (3, 3, 128, 64, 0), (16, 1, 64, 128, 0),
+                                                  (8, 2, 128, 16, 70), (10, 2, 64, 32, 333)])
+def test_tcgen05_prompt_attention_on_long_portions(ops, Hq, Hkv, Dh, page, window):
+    """Portions that fill several 256-row tiles and end inside one: a whole prompt, a portion over a long
+    cached prefix, a portion whose rows end one short of a tile, and a short one; scattered pages."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(Hq + Dh + page + window)
+    ctx = [333, 900, 64 * 3 - 1, 21]
+    new = [333, 257, 64 * 3 - 1, 5]
+    kc, vc, bt, ks, vs = paged_cache(rng, "bfloat16", ctx, Hkv, Dh, page, sum(-(-c // page) for c in ctx) + 5)
+    T = sum(new)
+    qkv = as_stored(rng.standard_normal((T, Hq * Dh + 2 * Hkv * Dh)), "bfloat16")
+    q = qkv[:, :Hq * Dh]
+    qs = np.concatenate([[0], np.cumsum(new)])
+    want = np.concatenate([dense_reference(q[qs[i]:qs[i + 1]], ks[i], vs[i], Hq, Hkv, Dh, new[i], window) for i in range(4)])
+    qd = dev(qkv, torch.bfloat16)[:, :Hq * Dh]
+    out = torch.full((T + 3, Hq * Dh), float("nan"), device="cuda", dtype=torch.bfloat16)
+    meta = (dev(qs, torch.int32), dev(np.array(ctx), torch.int32), dev(bt, torch.int32))
+    assert ops.attention_prompt_umma_takes(qd, Hq, Hkv, Dh, page, max(new))
+    for _ in range(2):
+        ops.attention_prompt_umma(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out[:T], *meta, 4, max(new), Hq, Hkv, Dh,
+                                  1 / np.sqrt(Dh), window)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(out)[:T], want) < TOL["bfloat16"]
+    assert torch.isnan(out[T:].float()).all()
+
+
+def test_tcgen05_prompt_attention_when_the_maximum_keeps_growing(ops):
+    """Scores that rise along the keys by about 3 (in powers of two) a key: every tile moves the
+    reference point of the exponentials, so the accumulator in tensor memory is rescaled again and again;
+    and scores that fall, so that it never is after the first tile."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(11)
+    Hq, Hkv, Dh, page, n = 4, 1, 64, 16, 640
+    for rising in (True, False):
+        kc, vc, bt, ks, vs = paged_cache(rng, "bfloat16", [n], Hkv, Dh, page, 48)
+        u = rng.standard_normal(Dh)
+        u /= np.linalg.norm(u)
+        ramp = np.arange(n) if rising else n - np.arange(n)
+        keys = as_stored(ramp[:, None] * u[None, :] * 0.25 + 0.05 * rng.standard_normal((n, Dh)), "bfloat16")
+        for t in range(n):                                  # overwrite the cached keys in their pages
+            kc[bt[0, t // page], 0, t % page] = keys[t]
+        q = as_stored(np.tile(u * 8.0 * np.sqrt(Dh) * np.log(2), (n, Hq)) + 0.1 * rng.standard_normal((n, Hq * Dh)), "bfloat16")
+        want = dense_reference(q, keys.reshape(n, Hkv, Dh), vs[0], Hq, Hkv, Dh, n)
+        out = torch.zeros(n, Hq * Dh, device="cuda", dtype=torch.bfloat16)
+        ops.attention_prompt_umma(dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out,
+                                  dev(np.array([0, n]), torch.int32), dev(np.array([n]), torch.int32), dev(bt, torch.int32), 1, n,
+                                  Hq, Hkv, Dh, 1 / np.sqrt(Dh))
+        torch.cuda.synchronize()
+        gemm_select.check_status()
+        assert rel_err(host(out), want) < TOL["bfloat16"], f"rising={rising}"
 
 
 def test_tensor_core_attention_refuses_other_sizes(ops):

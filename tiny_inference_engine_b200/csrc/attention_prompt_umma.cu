@@ -1,0 +1,422 @@
+// Causal attention of prompt portions on the 5th-generation tensor cores: S = Q K^T and O += P V are
+// tcgen05.mma with the scores and the output accumulator in tensor memory; keys and values come page by
+// page through TMA. Head sizes 64 and 128, up to 16 query heads per kv head, pages that are powers
+// of two from 8 up; other sizes stay with the mma.sync kernels.
+//
+// Contract as in attention_prompt.cu (the reference's paged_attention,
+// src/backend/cpu/cpu_backend.cpp:261-319): row t of sequence s sits at
+// pos = context_len[s] - n_queries(s) + (t - query_start[s]) and sees keys 0..pos (window w > 0:
+// pos-w+1..pos), all read from the pages.
+//
+// One CTA owns 256 rows (rows = queries x the query heads of one kv head) as two tiles of 128, so
+// that the tensor cores work on one tile while the other tile's softmax runs, and both share every
+// key/value tile of 64 keys. Ten warps:
+//   0-3, 4-7  softmax of tile 0 and 1: thread = one row. Reads its 64 scores out of tensor memory,
+//             masks, exponentiates in float, writes P as bfloat16 into shared memory (the layout the
+//             MMA reads), keeps the row sum. The accumulator O stays in tensor memory; it is rescaled
+//             only when a row's maximum has grown by more than 2^8 since the value it was last
+//             scaled for (any reference point gives the same O / sum, as long as nothing overflows).
+//   8         TMA producer: lane b fetches box b (a page, or 64 keys of a larger page) of every tile.
+//   9         one thread issues the MMAs: Q K^T of tile i + 1 ahead of P V of tile i.
+// Barriers: kv_full/kv_empty per stage, and for each row tile s_full (scores written), s_empty
+// (scores read), p_full (P written, O rescaled), p_empty (P V retired). Every wait is bounded.
+#include "attention_mma.cuh"
+#include "umma.cuh"
+
+namespace tie {
+
+constexpr int kUmmaAttnThreads = 320;
+
+struct UmmaPromptArgs {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  const int* query_start;
+  const int* context_lens;
+  const int* block_tables;
+  int* status;
+  long long q_stride;
+  int max_blocks, q_heads, kv_heads, page_size, page_shift, window;
+  float scale_log2;
+};
+
+// Descriptor of an operand stored with its MN extent contiguous (V as [key][head dim]): 64 elements of
+// MN per 128-byte row, 8 rows (k) per 1024-byte swizzle atom; `mn_block_bytes` apart lie successive blocks
+// of 64 along MN.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((mn_block_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                         // stride byte offset: next 8 k
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int DH, int STAGES>
+__global__ void __launch_bounds__(kUmmaAttnThreads, 1)
+attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, UmmaPromptArgs a) {
+  pdl_sync();
+  constexpr int HALVES = DH / 64;
+  constexpr int Q_BYTES = HALVES * 128 * 128;     // one tile of 128 rows: column blocks of 64, rows of 128 bytes
+  constexpr int P_BYTES = 128 * 128;              // 128 rows x 64 keys
+  constexpr int PLANE_BYTES = HALVES * 64 * 128;  // 64 keys
+  constexpr int STAGE_BYTES = 2 * PLANE_BYTES;
+  constexpr int O_COL = 128;                      // columns 0..127: the two score tiles; then the two accumulators
+  constexpr uint32_t TMEM_COLS = (O_COL + 2 * DH) <= 256 ? 256 : 512;
+  constexpr float kRescaleStep = 8.0f;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* p_smem = q_smem + 2 * Q_BYTES;
+  uint8_t* ring = p_smem + 2 * P_BYTES;
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(ring + STAGES * STAGE_BYTES);
+  uint64_t* kv_empty = kv_full + STAGES;
+  uint64_t* s_full = kv_empty + STAGES;   // [2]
+  uint64_t* s_empty = s_full + 2;
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* p_empty = p_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(p_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.z, kvh = blockIdx.y;
+  const int G = a.q_heads / a.kv_heads;
+  const int t0 = a.query_start[seq];
+  const int nq = a.query_start[seq + 1] - t0;
+  const int rows = nq * G;
+  const int row0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * 256;   // last rows (most keys) first
+  if (row0 >= rows) return;
+  const int pos0 = a.context_lens[seq] - nq;
+
+  // key tiles each row tile needs: first[q]..last[q]; the CTA walks first[0]..last[1] (or last[0])
+  bool has[2];
+  int first[2], last[2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int r0 = row0 + 128 * q;
+    has[q] = r0 < rows;
+    const int lo_pos = pos0 + r0 / G, hi_pos = pos0 + min(rows - 1, r0 + 127) / G;
+    first[q] = a.window > 0 ? max(0, lo_pos - a.window + 1) / kKeysPerTile : 0;
+    last[q] = hi_pos / kKeysPerTile;
+  }
+  const int kt_first = first[0], kt_last = has[1] ? last[1] : last[0];
+  const int n_tiles = kt_last - kt_first + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(kv_full + s, 1);
+      mbar_init(kv_empty + s, 1);
+    }
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(s_full + q, 1);
+      mbar_init(s_empty + q, 4);
+      mbar_init(p_full + q, 4);
+      mbar_init(p_empty + q, 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // Q rows of both tiles in the layout the MMA reads (rows beyond the sequence: zeros)
+  constexpr int CPR = DH / 8;
+  for (int id = threadIdx.x; id < 256 * CPR; id += kUmmaAttnThreads) {
+    const int r = id / CPR, c = id % CPR;
+    const int row = row0 + r;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows)
+      v = *reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t0 + row / G) * a.q_stride +
+                                          static_cast<long long>(kvh * G + row % G) * DH + c * 8);
+    const int rr = r & 127;
+    *reinterpret_cast<uint4*>(q_smem + (r >> 7) * Q_BYTES + (c >> 3) * (128 * 128) + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 8) {
+    // ---- producer
+    const int box_rows = min(a.page_size, kKeysPerTile);
+    const int boxes_per_tile = kKeysPerTile / box_rows;
+    const int* table = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % STAGES;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(kv_empty + s, ((i / STAGES) & 1) ^ 1, abort_flag, a.status, 11) ? 1 : 0;
+        if (ok) mbar_expect_tx(kv_full + s, STAGE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < boxes_per_tile) {
+        const int key = (kt_first + i) * kKeysPerTile + lane * box_rows;
+        const int idx = key >> a.page_shift;
+        const int page = idx < a.max_blocks ? table[idx] : 0;   // beyond the table: any real page; those keys are masked
+        const int row = (page * a.kv_heads + kvh) * a.page_size + (key & (a.page_size - 1));
+        uint8_t* kdst = ring + s * STAGE_BYTES + lane * box_rows * 128;
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+          tma_load_2d(kdst + h * (64 * 128), &k_map, h * 64, row, kv_full + s);
+          tma_load_2d(kdst + PLANE_BYTES + h * (64 * 128), &v_map, h * 64, row, kv_full + s);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = instr_desc(kKeysPerTile);          // 128 x 64, both operands k-major
+      constexpr uint32_t idesc_pv = instr_desc(DH) | (1u << 16);       // 128 x DH, B (= V) with its N extent contiguous
+      int n_qk[2] = {0, 0}, n_pv[2] = {0, 0};
+      bool ok = true;
+      for (int i = 0; i <= n_tiles && ok; ++i) {
+        if (i < n_tiles) {
+          const int s = i % STAGES, t = kt_first + i;
+          if (!mbar_wait(kv_full + s, (i / STAGES) & 1, abort_flag, a.status, 12)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t k_addr = smem_u32(ring + s * STAGE_BYTES);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (!(has[q] && t >= first[q] && t <= last[q])) continue;
+            if (!mbar_wait(s_empty + q, (n_qk[q] & 1) ^ 1, abort_flag, a.status, 14)) {
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t q_addr = smem_u32(q_smem + q * Q_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < DH / 16; ++ks) {
+              umma_bf16(tmem_base + q * kKeysPerTile, smem_desc_sw128(q_addr + (ks >> 2) * (128 * 128) + (ks & 3) * 32),
+                        smem_desc_sw128(k_addr + (ks >> 2) * (64 * 128) + (ks & 3) * 32), idesc_qk, ks > 0 ? 1u : 0u);
+            }
+            umma_commit(s_full + q);
+            ++n_qk[q];
+          }
+          if (!ok) break;
+        }
+        if (i >= 1) {
+          const int j = i - 1, s = j % STAGES, t = kt_first + j;
+          const uint32_t v_addr = smem_u32(ring + s * STAGE_BYTES + PLANE_BYTES);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (!(has[q] && t >= first[q] && t <= last[q])) continue;
+            if (!mbar_wait(p_full + q, n_pv[q] & 1, abort_flag, a.status, 14)) {
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t p_addr = smem_u32(p_smem + q * P_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < kKeysPerTile / 16; ++kk) {
+              umma_bf16(tmem_base + O_COL + q * DH, smem_desc_sw128(p_addr + kk * 32),
+                        smem_desc_sw128_mn(v_addr + kk * (16 * 128), 64 * 128), idesc_pv, (n_pv[q] > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(p_empty + q);
+            ++n_pv[q];
+          }
+          if (!ok) break;
+          umma_commit(kv_empty + s);   // both products of tile j have read the stage once everything issued so far retires
+        }
+      }
+    }
+  } else {
+    // ---- softmax: warps 0-3 own tile 0, warps 4-7 tile 1; thread = row
+    const int q = warp >> 2, wq = warp & 3;
+    const int rr = wq * 32 + lane;                           // row inside the tile = lane of tensor memory
+    const int row = row0 + 128 * q + rr;
+    const int pos = row < rows ? pos0 + row / G : -1;       // rows beyond the sequence see no key
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_base + q * kKeysPerTile;
+    const uint32_t o_tmem = tmem_base + lane_base + O_COL + q * DH;
+    uint8_t* p_row = p_smem + q * P_BYTES + rr * 128;
+    float m_run = -INFINITY, m_used = -INFINITY, l = 0.0f;
+    bool ok = has[q];
+    const int my_tiles = has[q] ? last[q] - first[q] + 1 : 0;
+    for (int n = 0; n < my_tiles && ok; ++n) {
+      const int key0 = (first[q] + n) * kKeysPerTile;
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full + q, n & 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t sr[64];
+      {
+        uint32_t c0[16], c1[16], c2[16], c3[16];
+        tmem_ld16(s_tmem, c0);
+        tmem_ld16(s_tmem + 16, c1);
+        tmem_ld16(s_tmem + 32, c2);
+        tmem_ld16(s_tmem + 48, c3);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          sr[e] = c0[e];
+          sr[16 + e] = c1[e];
+          sr[32 + e] = c2[e];
+          sr[48 + e] = c3[e];
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(s_empty + q)) : "memory");
+
+      const bool full_tile = key0 + 63 <= pos && (a.window <= 0 || key0 > pos - a.window);
+      if (!full_tile) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int key = key0 + c;
+          const bool seen = key <= pos && (a.window <= 0 || key > pos - a.window);
+          sr[c] = seen ? sr[c] : 0xff800000u;   // -inf
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+      m_run = fmaxf(m_run, mx * a.scale_log2);
+      const bool need = m_run > m_used + kRescaleStep;       // also: the first finite maximum of the row
+      // P V of the tile before has retired: P may be overwritten and O touched
+      ok = __all_sync(0xffffffffu, mbar_wait(p_empty + q, (n & 1) ^ 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
+      if (!ok) break;
+      if (__any_sync(0xffffffffu, need)) {
+        float f = 1.0f;
+        if (need) {
+          f = m_used == -INFINITY ? 1.0f : ex2(m_used - m_run);
+          m_used = m_run;
+          l *= f;
+        }
+        if (n > 0) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+          for (int c0 = 0; c0 < DH; c0 += 16) {
+            uint32_t o[16];
+            tmem_ld16(o_tmem + c0, o);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+            tmem_st16(o_tmem + c0, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      const float base = m_used == -INFINITY ? 0.0f : m_used;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, -base));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, -base));
+        sum += p0 + p1;
+        sr[c >> 1] = pack_bf16(p0, p1);
+      }
+      l += sum;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (rr & 7)) << 4)) = make_uint4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(p_full + q)) : "memory");
+    }
+    if (ok && my_tiles > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(p_empty + q, (my_tiles & 1) ^ 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        __nv_bfloat16* o_row = row < rows ? a.out + (static_cast<long long>(t0 + row / G) * a.q_heads + kvh * G + row % G) * DH : nullptr;
+#pragma unroll 1
+        for (int c0 = 0; c0 < DH; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(o_tmem + c0, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (o_row) {
+            uint32_t w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) w[e] = pack_bf16(__uint_as_float(o[2 * e]) * inv, __uint_as_float(o[2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(o_row + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(o_row + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag != 0) {   // a wait ran out: let copies and MMAs that are still in flight finish before the CTA goes away
+    const unsigned long long t_start = clock64();
+    while (clock64() - t_start < 4000000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+template <int DH>
+static int launch_prompt_umma(const CUtensorMap& km, const CUtensorMap& vm, const UmmaPromptArgs& a, int n_seqs, int max_rows,
+                              cudaStream_t s) {
+  constexpr int STAGES = DH == 128 ? 4 : 6;
+  constexpr size_t smem = 2 * (DH / 64) * 128 * 128 + 2 * 128 * 128 + static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128 +
+                          (2 * STAGES + 8) * 8 + 16 + 1024;
+  static_assert(smem <= 227 * 1024, "shared memory of one CTA");
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_prompt_umma_kernel<DH, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+      set_error("attention_prompt_umma: cannot reserve %zu bytes of shared memory", smem);
+      return kCudaError;
+    }
+    configured = true;
+  }
+  TIE_LAUNCH((attn_prompt_umma_kernel<DH, STAGES>), dim3(ceil_div(max_rows, 256), a.kv_heads, n_seqs), kUmmaAttnThreads, smem, s, km, vm, a);
+  return kOk;
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+// Rows [0, rows) of the step belong to sequences 0..n_seqs-1, each bringing several tokens;
+// max_queries is the largest number of tokens one of them brings; pages is the number of pages
+// of the cache planes.
+TIE_API int tie_attention_prompt_umma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      const int* query_start, const int* context_lens, const int* block_tables,
+                                      int max_blocks, int n_seqs, int max_queries, int q_heads, int kv_heads, int head_dim,
+                                      int page_size, int pages, int window, float scale, cudaStream_t s) {
+  TIE_REQUIRE(head_dim == 64 || head_dim == 128, "attention_prompt_umma: head_dim %d is not 64 or 128", head_dim);
+  TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
+              "attention_prompt_umma: %d query heads over %d kv heads (at most 16 per group)", q_heads, kv_heads);
+  TIE_REQUIRE(page_size >= 8 && (page_size & (page_size - 1)) == 0, "attention_prompt_umma: page size %d is not a power of two from 8 up", page_size);
+  TIE_REQUIRE(q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0,
+              "attention_prompt_umma: q and out rows must be 16-byte aligned");
+  TIE_REQUIRE(scale > 0.0f, "attention_prompt_umma: the scale must be positive");
+  if (n_seqs == 0 || max_queries == 0) return kOk;
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  const int box_rows = page_size < kKeysPerTile ? page_size : kKeysPerTile;
+  CUtensorMap km, vm;
+  const long long rows = static_cast<long long>(pages) * kv_heads * page_size;
+  TIE_REQUIRE(make_map_bf16(&km, k_cache, rows, head_dim, head_dim, 64, box_rows) &&
+                  make_map_bf16(&vm, v_cache, rows, head_dim, head_dim, 64, box_rows),
+              "attention_prompt_umma: cuTensorMapEncodeTiled failed");
+  TIE_REQUIRE(status_word() != nullptr, "attention_prompt_umma: cannot allocate the status word");
+  UmmaPromptArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), query_start, context_lens, block_tables,
+                   status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window, scale * 1.4426950408889634f};
+  const int max_rows = max_queries * (q_heads / kv_heads);
+  const int st = head_dim == 64 ? launch_prompt_umma<64>(km, vm, a, n_seqs, max_rows, s) : launch_prompt_umma<128>(km, vm, a, n_seqs, max_rows, s);
+  if (st != kOk) return st;
+  TIE_RETURN_LAUNCH("attention_prompt_umma");
+}

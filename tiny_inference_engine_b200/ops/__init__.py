@@ -4,6 +4,8 @@ Tensors are torch CUDA tensors used as typed device memory; nothing here compute
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..errors import InvalidArgument
@@ -283,6 +285,29 @@ def attention_prompt_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
     _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables)
     _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
     call("tie_attention_prompt_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+         query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs,
+         max_queries, q_heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _stream())
+
+
+UMMA_MIN_ROWS = 128     # rows (queries x heads of a group) from which the tcgen05 prompt kernel pays
+
+
+def attention_prompt_umma_takes(q: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, page_size: int,
+                                max_queries: int) -> bool:
+    """Whether the tcgen05 prompt kernel takes these operands and the portions are long enough for its
+    256-row tiles."""
+    return (attention_decode_tma_takes(q, q_heads, kv_heads, head_dim, page_size) and head_dim in (64, 128)
+            and max_queries * (q_heads // kv_heads) >= UMMA_MIN_ROWS and os.environ.get("TIE_NO_UMMA_ATTENTION") != "1")
+
+
+def attention_prompt_umma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, n_seqs: int, max_queries: int,
+                          q_heads, kv_heads, head_dim, scale: float, window: int = 0) -> None:
+    """As attention_prompt_tma with both products on tcgen05 and the accumulators in tensor memory
+    (head sizes 64 and 128)."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables)
+    _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    _need(out.is_contiguous(), "attention: out must be contiguous")
+    call("tie_attention_prompt_umma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
          query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs,
          max_queries, q_heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _stream())
 

@@ -124,6 +124,8 @@ class GQAttention(Mixer):
             if tc:
                 tma = ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, cache.k.shape[2])
                 fn = ops.attention_prompt_tma if tma else ops.attention_prompt_tc
+                if tma and ops.attention_prompt_umma_takes(q, Hq, Hkv, Dh, cache.k.shape[2], ctx.multi_max_queries):
+                    fn = ops.attention_prompt_umma
                 fn(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, ctx.multi_seqs,
                    ctx.multi_max_queries, Hq, Hkv, Dh, self.scale, self.window)
             else:
