@@ -10,16 +10,19 @@
 //
 // One CTA owns 256 rows (rows = queries x the query heads of one kv head) as two tiles of 128, so
 // that the tensor cores work on one tile while the other tile's softmax runs, and both share every
-// key/value tile of 64 keys. Ten warps:
-//   0-3, 4-7  softmax of tile 0 and 1: thread = one row. Reads its 64 scores out of tensor memory,
-//             masks, exponentiates in float, writes P as bfloat16 into shared memory (the layout the
-//             MMA reads), keeps the row sum. The accumulator O stays in tensor memory; it is rescaled
-//             only when a row's maximum has grown by more than 2^8 since the value it was last
-//             scaled for (any reference point gives the same O / sum, as long as nothing overflows).
+// key/value tile of 64 keys. The MMAs' operand reads are what shared memory has to feed, so Q, which
+// every key tile needs again, sits in tensor memory (the A operand of Q K^T comes from there) and only
+// K, V and P are read from shared memory. Ten warps:
+//   0-3, 4-7  softmax of tile 0 and 1: thread = one row. Puts its Q row into tensor memory once. Per key
+//             tile it reads its 64 scores out of tensor memory, masks, exponentiates in float, writes P as
+//             bfloat16 into one of two shared-memory buffers (the layout the MMA reads) and keeps the row
+//             sum. The accumulator O stays in tensor memory; it is rescaled only when a row's maximum has
+//             grown by more than 2^8 since the value it was last scaled for (any reference point gives
+//             the same O / sum, as long as nothing overflows).
 //   8         TMA producer: lane b fetches box b (a page, or 64 keys of a larger page) of every tile.
 //   9         one thread issues the MMAs: Q K^T of tile i + 1 ahead of P V of tile i.
 // Barriers: kv_full/kv_empty per stage, and for each row tile s_full (scores written), s_empty
-// (scores read), p_full (P written, O rescaled), p_empty (P V retired). Every wait is bounded.
+// (scores read), p_full[2] (P written, O rescaled), p_empty[2] (P V retired). Every wait is bounded.
 #include "attention_mma.cuh"
 #include "umma.cuh"
 
@@ -60,6 +63,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// D[tmem_d] (+)= A[tmem_a] . B: the A operand read from tensor memory (lane = row, a 32-bit column = two
+// consecutive k of 16 bits), B from shared memory.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -71,26 +85,26 @@ __global__ void __launch_bounds__(kUmmaAttnThreads, 1)
 attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, UmmaPromptArgs a) {
   pdl_sync();
   constexpr int HALVES = DH / 64;
-  constexpr int Q_BYTES = HALVES * 128 * 128;     // one tile of 128 rows: column blocks of 64, rows of 128 bytes
   constexpr int P_BYTES = 128 * 128;              // 128 rows x 64 keys
   constexpr int PLANE_BYTES = HALVES * 64 * 128;  // 64 keys
   constexpr int STAGE_BYTES = 2 * PLANE_BYTES;
-  constexpr int O_COL = 128;                      // columns 0..127: the two score tiles; then the two accumulators
-  constexpr uint32_t TMEM_COLS = (O_COL + 2 * DH) <= 256 ? 256 : 512;
+  constexpr int Q_COL = 128;                      // columns 0..127: the two score tiles; then Q of both tiles (two
+  constexpr int O_COL = Q_COL + DH;               // elements a column); then the two accumulators
+  constexpr uint32_t TMEM_COLS = 512;
+  static_assert(O_COL + 2 * DH <= 512, "tensor memory");
   constexpr float kRescaleStep = 8.0f;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* q_smem = smem;
-  uint8_t* p_smem = q_smem + 2 * Q_BYTES;
-  uint8_t* ring = p_smem + 2 * P_BYTES;
+  uint8_t* p_smem = smem;                 // [row tile][buffer]
+  uint8_t* ring = p_smem + 4 * P_BYTES;
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(ring + STAGES * STAGE_BYTES);
   uint64_t* kv_empty = kv_full + STAGES;
   uint64_t* s_full = kv_empty + STAGES;   // [2]
   uint64_t* s_empty = s_full + 2;
-  uint64_t* p_full = s_empty + 2;
-  uint64_t* p_empty = p_full + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(p_empty + 2);
+  uint64_t* p_full = s_empty + 2;         // [row tile][buffer]
+  uint64_t* p_empty = p_full + 4;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(p_empty + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -125,8 +139,10 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     for (int q = 0; q < 2; ++q) {
       mbar_init(s_full + q, 1);
       mbar_init(s_empty + q, 4);
-      mbar_init(p_full + q, 4);
-      mbar_init(p_empty + q, 1);
+    }
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(p_full + b, 4);
+      mbar_init(p_empty + b, 1);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -135,23 +151,33 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // Q rows of both tiles in the layout the MMA reads (rows beyond the sequence: zeros)
-  constexpr int CPR = DH / 8;
-  for (int id = threadIdx.x; id < 256 * CPR; id += kUmmaAttnThreads) {
-    const int r = id / CPR, c = id % CPR;
-    const int row = row0 + r;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row < rows)
-      v = *reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t0 + row / G) * a.q_stride +
-                                          static_cast<long long>(kvh * G + row % G) * DH + c * 8);
-    const int rr = r & 127;
-    *reinterpret_cast<uint4*>(q_smem + (r >> 7) * Q_BYTES + (c >> 3) * (128 * 128) + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v;
-  }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
+  if (warp < 8) {
+    // Q: every softmax thread puts its own row into tensor memory (rows beyond the sequence: zeros)
+    const int q = warp >> 2, rr = (warp & 3) * 32 + lane;
+    const int row = row0 + 128 * q + rr;
+    const uint4* src = row < rows ? reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t0 + row / G) * a.q_stride +
+                                                                  static_cast<long long>(kvh * G + row % G) * DH)
+                                  : nullptr;
+    const uint32_t q_tmem = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + Q_COL + q * (DH / 2);
+#pragma unroll
+    for (int c0 = 0; c0 < DH / 2; c0 += 16) {
+      uint32_t w[16];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint4 v = src ? src[c0 / 4 + e] : make_uint4(0u, 0u, 0u, 0u);
+        w[4 * e] = v.x, w[4 * e + 1] = v.y, w[4 * e + 2] = v.z, w[4 * e + 3] = v.w;
+      }
+      tmem_st16(q_tmem + c0, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
   if (warp == 8) {
     // ---- producer
@@ -185,14 +211,21 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc(kKeysPerTile);          // 128 x 64, both operands k-major
       constexpr uint32_t idesc_pv = instr_desc(DH) | (1u << 16);       // 128 x DH, B (= V) with its N extent contiguous
+      // Descriptors as (low word, constant high word): one thread issues every MMA, so what it computes
+      // per MMA is on the critical path of the tensor cores.
+      const uint32_t k_lo0 = desc_lo_sw128(smem_u32(ring));
+      const uint32_t v_lo0 = desc_lo_sw128(smem_u32(ring + PLANE_BYTES), 64 * 128);   // blocks of 64 head-dim columns lie 64 rows apart
+      const uint32_t p_lo0 = desc_lo_sw128(smem_u32(p_smem));
       int n_qk[2] = {0, 0}, n_pv[2] = {0, 0};
+      int s_qk = 0, s_pv = 0;
+      uint32_t parity_qk = 0;
       bool ok = true;
       for (int i = 0; i <= n_tiles && ok; ++i) {
         if (i < n_tiles) {
-          const int s = i % STAGES, t = kt_first + i;
-          if (!mbar_wait(kv_full + s, (i / STAGES) & 1, abort_flag, a.status, 12)) break;
+          const int t = kt_first + i;
+          if (!mbar_wait(kv_full + s_qk, parity_qk, abort_flag, a.status, 12)) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t k_addr = smem_u32(ring + s * STAGE_BYTES);
+          const uint32_t k_lo = k_lo0 + s_qk * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             if (!(has[q] && t >= first[q] && t <= last[q])) continue;
@@ -201,39 +234,46 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
               break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t q_addr = smem_u32(q_smem + q * Q_BYTES);
 #pragma unroll
             for (int ks = 0; ks < DH / 16; ++ks) {
-              umma_bf16(tmem_base + q * kKeysPerTile, smem_desc_sw128(q_addr + (ks >> 2) * (128 * 128) + (ks & 3) * 32),
-                        smem_desc_sw128(k_addr + (ks >> 2) * (64 * 128) + (ks & 3) * 32), idesc_qk, ks > 0 ? 1u : 0u);
+              umma_bf16_a_tmem(tmem_base + q * kKeysPerTile, tmem_base + Q_COL + q * (DH / 2) + ks * 8,
+                               desc_from_words(k_lo + (((ks >> 2) * (64 * 128) + (ks & 3) * 32) >> 4), kDescHiSw128), idesc_qk,
+                               ks > 0 ? 1u : 0u);
             }
             umma_commit(s_full + q);
             ++n_qk[q];
           }
           if (!ok) break;
+          if (++s_qk == STAGES) {
+            s_qk = 0;
+            parity_qk ^= 1;
+          }
         }
         if (i >= 1) {
-          const int j = i - 1, s = j % STAGES, t = kt_first + j;
-          const uint32_t v_addr = smem_u32(ring + s * STAGE_BYTES + PLANE_BYTES);
+          const int t = kt_first + i - 1;
+          const uint32_t v_lo = v_lo0 + s_pv * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             if (!(has[q] && t >= first[q] && t <= last[q])) continue;
-            if (!mbar_wait(p_full + q, n_pv[q] & 1, abort_flag, a.status, 14)) {
+            const int pb = 2 * q + (n_pv[q] & 1);        // the tile's P buffer, used for the (n_pv / 2)-th time
+            if (!mbar_wait(p_full + pb, (n_pv[q] >> 1) & 1, abort_flag, a.status, 14)) {
               ok = false;
               break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t p_addr = smem_u32(p_smem + q * P_BYTES);
+            const uint32_t p_lo = p_lo0 + pb * (P_BYTES >> 4);
+            const uint32_t keep = n_pv[q] > 0 ? 1u : 0u;
 #pragma unroll
             for (int kk = 0; kk < kKeysPerTile / 16; ++kk) {
-              umma_bf16(tmem_base + O_COL + q * DH, smem_desc_sw128(p_addr + kk * 32),
-                        smem_desc_sw128_mn(v_addr + kk * (16 * 128), 64 * 128), idesc_pv, (n_pv[q] > 0 || kk > 0) ? 1u : 0u);
+              umma_bf16(tmem_base + O_COL + q * DH, desc_from_words(p_lo + ((kk * 32) >> 4), kDescHiSw128),
+                        desc_from_words(v_lo + ((kk * 16 * 128) >> 4), kDescHiSw128), idesc_pv, kk > 0 ? 1u : keep);
             }
-            umma_commit(p_empty + q);
+            umma_commit(p_empty + pb);
             ++n_pv[q];
           }
           if (!ok) break;
-          umma_commit(kv_empty + s);   // both products of tile j have read the stage once everything issued so far retires
+          umma_commit(kv_empty + s_pv);   // both products of the tile have read the stage once everything issued so far retires
+          if (++s_pv == STAGES) s_pv = 0;
         }
       }
     }
@@ -246,7 +286,7 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_base + q * kKeysPerTile;
     const uint32_t o_tmem = tmem_base + lane_base + O_COL + q * DH;
-    uint8_t* p_row = p_smem + q * P_BYTES + rr * 128;
+    uint8_t* p_rows = p_smem + 2 * q * P_BYTES + rr * 128;
     float m_run = -INFINITY, m_used = -INFINITY, l = 0.0f;
     bool ok = has[q];
     const int my_tiles = has[q] ? last[q] - first[q] + 1 : 0;
@@ -284,14 +324,14 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
           sr[c] = seen ? sr[c] : 0xff800000u;   // -inf
         }
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
-      m_run = fmaxf(m_run, mx * a.scale_log2);
+      for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(sr[c + e]));
+      }
+      m_run = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2);
       const bool need = m_run > m_used + kRescaleStep;       // also: the first finite maximum of the row
-      // P V of the tile before has retired: P may be overwritten and O touched
-      ok = __all_sync(0xffffffffu, mbar_wait(p_empty + q, (n & 1) ^ 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
-      if (!ok) break;
       if (__any_sync(0xffffffffu, need)) {
         float f = 1.0f;
         if (need) {
@@ -300,6 +340,9 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
           l *= f;
         }
         if (n > 0) {
+          // O may be touched once P V of the tile before has retired
+          ok = __all_sync(0xffffffffu, mbar_wait(p_empty + 2 * q + ((n - 1) & 1), ((n - 1) >> 1) & 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
+          if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
           for (int c0 = 0; c0 < DH; c0 += 16) {
@@ -314,25 +357,33 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         }
       }
       const float base = m_used == -INFINITY ? 0.0f : m_used;
-      float sum = 0.0f;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, -base));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, -base));
-        sum += p0 + p1;
-        sr[c >> 1] = pack_bf16(p0, p1);
+      for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2(fmaf(__uint_as_float(sr[c + 2 * e]), a.scale_log2, -base));
+          const float p1 = ex2(fmaf(__uint_as_float(sr[c + 2 * e + 1]), a.scale_log2, -base));
+          sum4[e] += p0 + p1;
+          sr[(c >> 1) + e] = pack_bf16(p0, p1);
+        }
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // this buffer held P of the tile before the last one: its P V has to have retired
+      const int pb = 2 * q + (n & 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(p_empty + pb, ((n >> 1) & 1) ^ 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
+      if (!ok) break;
+      uint8_t* p_row = p_rows + (n & 1) * P_BYTES;
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         *reinterpret_cast<uint4*>(p_row + ((c ^ (rr & 7)) << 4)) = make_uint4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(p_full + q)) : "memory");
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(p_full + pb)) : "memory");
     }
     if (ok && my_tiles > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(p_empty + q, (my_tiles & 1) ^ 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
+      ok = __all_sync(0xffffffffu, mbar_wait(p_empty + 2 * q + ((my_tiles - 1) & 1), ((my_tiles - 1) >> 1) & 1, abort_flag, a.status, 13) ? 1 : 0) != 0;
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -370,8 +421,7 @@ template <int DH>
 static int launch_prompt_umma(const CUtensorMap& km, const CUtensorMap& vm, const UmmaPromptArgs& a, int n_seqs, int max_rows,
                               cudaStream_t s) {
   constexpr int STAGES = DH == 128 ? 4 : 6;
-  constexpr size_t smem = 2 * (DH / 64) * 128 * 128 + 2 * 128 * 128 + static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128 +
-                          (2 * STAGES + 8) * 8 + 16 + 1024;
+  constexpr size_t smem = 4 * 128 * 128 + static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128 + (2 * STAGES + 12) * 8 + 16 + 1024;
   static_assert(smem <= 227 * 1024, "shared memory of one CTA");
   static bool configured = false;
   if (!configured) {

@@ -138,6 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ---- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
+      const uint32_t ring_lo = desc_lo_sw128(smem_u32(smem));   // descriptors as (low word, constant high word)
       int it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
@@ -152,12 +153,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(smem + s * C::kStage);
-          const uint32_t b_addr = a_addr + C::kStageA;
+          const uint32_t a_lo = ring_lo + s * (C::kStage >> 4), b_lo = a_lo + (C::kStageA >> 4);
+          const uint32_t keep = kb > kb_begin ? 1u : 0u;
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
-            umma_bf16(tmem_acc, smem_desc_sw128(a_addr + k * kUmmaK * 2), smem_desc_sw128(b_addr + k * kUmmaK * 2), idesc,
-                      (kb > kb_begin || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_acc, desc_from_words(a_lo + ((k * kUmmaK * 2) >> 4), kDescHiSw128),
+                      desc_from_words(b_lo + ((k * kUmmaK * 2) >> 4), kDescHiSw128), idesc, k > 0 ? 1u : keep);
           }
           umma_commit(empty + s);   // arrives once the MMAs above have read the stage
         }

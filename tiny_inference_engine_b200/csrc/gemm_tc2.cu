@@ -137,6 +137,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ---- MMA issuer: one thread of the leader CTA drives both CTAs' tensor cores
     if (rank == 0 && lane == 0) {
       constexpr uint32_t idesc = instr_desc(256, 256);
+      const uint32_t ring_lo = desc_lo_sw128(smem_u32(smem));   // descriptors as (low word, constant high word)
       int it = 0, local = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += pairs, ++local) {
@@ -151,11 +152,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(smem + s * k2Stage);
-          const uint32_t b_addr = a_addr + k2StageA;
+          const uint32_t a_lo = ring_lo + s * (k2Stage >> 4), b_lo = a_lo + (k2StageA >> 4);
+          const uint32_t keep = kb > 0 ? 1u : 0u;
 #pragma unroll
           for (int k = 0; k < k2BK / 16; ++k) {
-            umma2_bf16(tmem_acc, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma2_bf16(tmem_acc, desc_from_words(a_lo + 2 * k, kDescHiSw128), desc_from_words(b_lo + 2 * k, kDescHiSw128), idesc,
+                       k > 0 ? 1u : keep);
           }
           umma2_commit_both(empty + s);
         }

@@ -18,6 +18,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   return d;
 }
 
+// The same descriptor as two words, for issue loops: the high word is constant, and an operand tile
+// that lies `bytes` further on (inside the 256 KB of shared memory) has `bytes >> 4` more in the low word.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t addr, uint32_t leading_bytes = 16) {
+  return ((addr >> 4) & 0x3FFF) | ((leading_bytes >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t desc_from_words(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor: float accumulator, bfloat16 A and B, both k-major, M = bm, N = bn.
 __host__ __device__ constexpr uint32_t instr_desc(int bn, int bm = 128) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(bm >> 4) << 24);
