@@ -135,34 +135,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
     }
   } else if (warp == 5) {
-    // ---- MMA issuer
-    if (lane == 0) {
+    // ---- MMA issuer: the whole warp walks the loop (uniform), one elected lane issues
+    {
       constexpr uint32_t idesc = instr_desc(BN);
       const uint32_t ring_lo = desc_lo_sw128(smem_u32(smem));   // descriptors as (low word, constant high word)
       int it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
         const int buf = local & 1;
-        if (!mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2)) break;   // the epilogue has drained it
+        // the epilogue has drained this accumulator
+        if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2) ? 1 : 0)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_acc = tmem_base + buf * BN;
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % C::kStages;
-          if (!mbar_wait(full + s, (it / C::kStages) & 1, abort_flag, status, 2)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(full + s, (it / C::kStages) & 1, abort_flag, status, 2) ? 1 : 0)) {
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_lo = ring_lo + s * (C::kStage >> 4), b_lo = a_lo + (C::kStageA >> 4);
           const uint32_t keep = kb > kb_begin ? 1u : 0u;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            umma_bf16(tmem_acc, desc_from_words(a_lo + ((k * kUmmaK * 2) >> 4), kDescHiSw128),
-                      desc_from_words(b_lo + ((k * kUmmaK * 2) >> 4), kDescHiSw128), idesc, k > 0 ? 1u : keep);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              umma_bf16(tmem_acc, desc_from_words(a_lo + ((k * kUmmaK * 2) >> 4), kDescHiSw128),
+                        desc_from_words(b_lo + ((k * kUmmaK * 2) >> 4), kDescHiSw128), idesc, k > 0 ? 1u : keep);
+            }
+            umma_commit(empty + s);   // arrives once the MMAs above have read the stage
           }
-          umma_commit(empty + s);   // arrives once the MMAs above have read the stage
+          __syncwarp();
         }
-        if (ok) umma_commit(acc_full + buf);
+        if (ok && elect_one()) umma_commit(acc_full + buf);
+        __syncwarp();
       }
     }
   } else {

@@ -134,34 +134,38 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (first) pdl_wait();
     }
   } else if (warp == 5) {
-    // ---- MMA issuer: one thread of the leader CTA drives both CTAs' tensor cores
-    if (rank == 0 && lane == 0) {
+    // ---- MMA issuer: a warp of the leader CTA walks the loop (uniform), one elected lane drives both CTAs' tensor cores
+    if (rank == 0) {
       constexpr uint32_t idesc = instr_desc(256, 256);
       const uint32_t ring_lo = desc_lo_sw128(smem_u32(smem));   // descriptors as (low word, constant high word)
       int it = 0, local = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += pairs, ++local) {
         const int buf = local & 1;
-        if (!mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2) ? 1 : 0)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_acc = tmem_base + buf * 256;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % k2Stages;
-          if (!mbar_wait(full + s, (it / k2Stages) & 1, abort_flag, status, 2)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(full + s, (it / k2Stages) & 1, abort_flag, status, 2) ? 1 : 0)) {
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_lo = ring_lo + s * (k2Stage >> 4), b_lo = a_lo + (k2StageA >> 4);
           const uint32_t keep = kb > 0 ? 1u : 0u;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < k2BK / 16; ++k) {
-            umma2_bf16(tmem_acc, desc_from_words(a_lo + 2 * k, kDescHiSw128), desc_from_words(b_lo + 2 * k, kDescHiSw128), idesc,
-                       k > 0 ? 1u : keep);
+            for (int k = 0; k < k2BK / 16; ++k) {
+              umma2_bf16(tmem_acc, desc_from_words(a_lo + 2 * k, kDescHiSw128), desc_from_words(b_lo + 2 * k, kDescHiSw128), idesc,
+                         k > 0 ? 1u : keep);
+            }
+            umma2_commit_both(empty + s);
           }
-          umma2_commit_both(empty + s);
+          __syncwarp();
         }
-        if (ok) umma2_commit_both(acc_full + buf);
+        if (ok && elect_one()) umma2_commit_both(acc_full + buf);
+        __syncwarp();
       }
     }
   } else {
