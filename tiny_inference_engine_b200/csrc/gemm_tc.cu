@@ -96,8 +96,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   if (warp == 4) {
     // ---- TMA producer. The weights never change, so their tiles of the first stages are fetched
     // before this kernel waits for the one before it; the activations only after.
-    if (lane == 0) {
-      int it = 0;
+    // The whole warp walks the loop (uniform) and one elected lane issues, so that addresses and
+    // coordinates live in uniform registers.
+    {
+      int s = 0;
+      uint32_t parity = 1;   // a fresh barrier passes a wait on parity 1
       bool first = true, ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const int i0 = (tile % tiles_x) * kBM, j0 = (tile / tiles_x) * BN;
@@ -109,28 +112,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           const int off_static = transposed ? 0 : C::kStageA, off_dynamic = transposed ? C::kStageA : 0;
           const int row_static = transposed ? i0 : j0, row_dynamic = transposed ? j0 : i0;
           const int pre = min(C::kStages, kb_end - kb_begin);
-          for (int p = 0; p < pre; ++p) {   // fresh barriers: the stages are free
-            mbar_expect_tx(full + p, C::kStage);
-            tma_load_2d(smem + p * C::kStage + off_static, map_static, (kb_begin + p) * kBK, row_static, full + p);
+          if (elect_one()) {
+            for (int p = 0; p < pre; ++p) {   // fresh barriers: the stages are free
+              mbar_expect_tx(full + p, C::kStage);
+              tma_load_2d(smem + p * C::kStage + off_static, map_static, (kb_begin + p) * kBK, row_static, full + p);
+            }
           }
+          __syncwarp();
           pdl_wait();
-          for (int p = 0; p < pre; ++p) {
-            tma_load_2d(smem + p * C::kStage + off_dynamic, map_dynamic, (kb_begin + p) * kBK, row_dynamic, full + p);
+          if (elect_one()) {
+            for (int p = 0; p < pre; ++p) {
+              tma_load_2d(smem + p * C::kStage + off_dynamic, map_dynamic, (kb_begin + p) * kBK, row_dynamic, full + p);
+            }
           }
-          it = pre;
+          __syncwarp();
           kb = kb_begin + pre;
+          s = pre;
+          if (s == C::kStages) {
+            s = 0;
+            parity = 0;
+          }
         }
-        for (; kb < kb_end; ++kb, ++it) {
-          const int s = it % C::kStages;
-          const uint32_t parity = ((it / C::kStages) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
-          if (!mbar_wait(empty + s, parity, abort_flag, status, 1)) {
+        for (; kb < kb_end; ++kb) {
+          if (!__all_sync(0xffffffffu, mbar_wait(empty + s, parity, abort_flag, status, 1) ? 1 : 0)) {
             ok = false;
             break;
           }
-          uint8_t* sa = smem + s * C::kStage;
-          mbar_expect_tx(full + s, C::kStage);
-          tma_load_2d(sa, &map_x, kb * kBK, i0, full + s);
-          tma_load_2d(sa + C::kStageA, &map_y, kb * kBK, j0, full + s);
+          if (elect_one()) {
+            uint8_t* sa = smem + s * C::kStage;
+            mbar_expect_tx(full + s, C::kStage);
+            tma_load_2d(sa, &map_x, kb * kBK, i0, full + s);
+            tma_load_2d(sa + C::kStageA, &map_y, kb * kBK, j0, full + s);
+          }
+          __syncwarp();
+          if (++s == C::kStages) {
+            s = 0;
+            parity ^= 1;
+          }
         }
       }
     }
@@ -139,7 +157,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     {
       constexpr uint32_t idesc = instr_desc(BN);
       const uint32_t ring_lo = desc_lo_sw128(smem_u32(smem));   // descriptors as (low word, constant high word)
-      int it = 0, local = 0;
+      int s = 0, local = 0;
+      uint32_t parity = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
         const int buf = local & 1;
@@ -147,9 +166,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2) ? 1 : 0)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-          const int s = it % C::kStages;
-          if (!__all_sync(0xffffffffu, mbar_wait(full + s, (it / C::kStages) & 1, abort_flag, status, 2) ? 1 : 0)) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!__all_sync(0xffffffffu, mbar_wait(full + s, parity, abort_flag, status, 2) ? 1 : 0)) {
             ok = false;
             break;
           }
@@ -165,6 +183,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             umma_commit(empty + s);   // arrives once the MMAs above have read the stage
           }
           __syncwarp();
+          if (++s == C::kStages) {
+            s = 0;
+            parity ^= 1;
+          }
         }
         if (ok && elect_one()) umma_commit(acc_full + buf);
         __syncwarp();

@@ -108,27 +108,36 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (warp == 4) {
     // ---- TMA producer (both CTAs): own rows of a, own half of the tile's rows of w; bytes count on the leader's barrier
-    if (lane == 0) {
-      int it = 0;
+    // The whole warp walks the loop (uniform) and one elected lane issues.
+    {
+      int s = 0;
+      uint32_t parity = 1;   // a fresh barrier passes a wait on parity 1
       bool first = true, ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += pairs) {
         const int row_a = (tile % tiles_m) * 256 + static_cast<int>(rank) * 128;
         const int row_w = (tile / tiles_m) * 256 + static_cast<int>(rank) * 128;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % k2Stages;
-          if (!mbar_wait(empty + s, ((it / k2Stages) & 1) ^ 1, abort_flag, status, 1)) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!__all_sync(0xffffffffu, mbar_wait(empty + s, parity, abort_flag, status, 1) ? 1 : 0)) {
             ok = false;
             break;
           }
           const uint32_t bar = map_to_cta(full + s, 0);
-          if (rank == 0) mbar_expect_tx(full + s, 2 * k2Stage);
           uint8_t* sa = smem + s * k2Stage;
-          tma_load_2d_pair(sa + k2StageA, &map_w, kb * k2BK, row_w, bar);      // weights never change: before the wait
+          if (elect_one()) {
+            if (rank == 0) mbar_expect_tx(full + s, 2 * k2Stage);
+            tma_load_2d_pair(sa + k2StageA, &map_w, kb * k2BK, row_w, bar);      // weights never change: before the wait
+          }
+          __syncwarp();
           if (first) {
             first = false;
             pdl_wait();
           }
-          tma_load_2d_pair(sa, &map_a, kb * k2BK, row_a, bar);
+          if (elect_one()) tma_load_2d_pair(sa, &map_a, kb * k2BK, row_a, bar);
+          __syncwarp();
+          if (++s == k2Stages) {
+            s = 0;
+            parity ^= 1;
+          }
         }
       }
       if (first) pdl_wait();
@@ -138,16 +147,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (rank == 0) {
       constexpr uint32_t idesc = instr_desc(256, 256);
       const uint32_t ring_lo = desc_lo_sw128(smem_u32(smem));   // descriptors as (low word, constant high word)
-      int it = 0, local = 0;
+      int s = 0, local = 0;
+      uint32_t parity = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += pairs, ++local) {
         const int buf = local & 1;
         if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2) ? 1 : 0)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_acc = tmem_base + buf * 256;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % k2Stages;
-          if (!__all_sync(0xffffffffu, mbar_wait(full + s, (it / k2Stages) & 1, abort_flag, status, 2) ? 1 : 0)) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!__all_sync(0xffffffffu, mbar_wait(full + s, parity, abort_flag, status, 2) ? 1 : 0)) {
             ok = false;
             break;
           }
@@ -163,6 +172,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             umma2_commit_both(empty + s);
           }
           __syncwarp();
+          if (++s == k2Stages) {
+            s = 0;
+            parity ^= 1;
+          }
         }
         if (ok && elect_one()) umma2_commit_both(acc_full + buf);
         __syncwarp();
