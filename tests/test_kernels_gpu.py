@@ -124,9 +124,11 @@ def paged_cache(rng, dtype, n_tokens_per_seq, kv_heads, head_dim, page, n_pages)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_kv_append_and_fused_norm_rope_append(ops, dtype):
+@pytest.mark.parametrize("Hq,Hkv,Dh", [(6, 3, 48), (4, 2, 64), (8, 2, 128), (2, 1, 256)])
+def test_kv_append_and_fused_norm_rope_append(ops, dtype, Hq, Hkv, Dh):
+    """Head size 48 runs the general kernel, 64 / 128 / 256 the one that holds a head in a warp's registers."""
     rng = np.random.default_rng(4)
-    Hq, Hkv, Dh, page, T = 6, 3, 48, 8, 21
+    page, T = 8, 21
     qkv = as_stored(rng.standard_normal((T, (Hq + 2 * Hkv) * Dh)), dtype)
     qw, kw = (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32), (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32)
     pos = rng.integers(0, 3000, T)

@@ -374,6 +374,82 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
   for (int i = 2 * half + lane; i < head_dim; i += 32) st(dst + i, buf[i]);
 }
 
+// The same for head sizes 64, 128 and 256 with the whole head rotated (or none of it), read from qkv:
+// a lane holds VEC = head_dim / 32 neighbouring elements (one vector load and store), lanes 0-15 the
+// first half of the head and lanes 16-31 the second, so a rotation pair is one shuffle apart.
+template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof(T) * VEC) HeadSlice {
+  T v[VEC];
+};
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, long long row_stride,
+                                                                      const float* __restrict__ qw, const float* __restrict__ kw,
+                                                                      float q_eps, float k_eps, const float* __restrict__ inv_freq,
+                                                                      const int* __restrict__ positions, const int* __restrict__ slots,
+                                                                      T* __restrict__ k_cache, T* __restrict__ v_cache, int q_heads,
+                                                                      int kv_heads, int page_size, int heads_per_token) {
+  pdl_sync();
+  constexpr int DH = 32 * VEC, HALF = DH / 2;
+  using Slice = HeadSlice<T, VEC>;
+  __shared__ float cs[DH];   // the token's rotation: cos at [0, HALF), sin at [HALF, DH)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = blockIdx.x;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (inv_freq) {
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < HALF; i += blockDim.x) {
+      const float angle = pos * inv_freq[i];
+      cs[i] = cosf(angle);
+      cs[HALF + i] = sinf(angle);
+    }
+  }
+  __syncthreads();
+  if (head >= heads_per_token) return;
+  T* src = qkv + t * row_stride + static_cast<long long>(head) * DH + lane * VEC;
+  const bool is_q = head < q_heads;
+  const bool is_k = !is_q && head < q_heads + kv_heads;
+  T* dst = src;
+  if (!is_q) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int h = is_k ? head - q_heads : head - q_heads - kv_heads;
+    const long long page = slot / page_size, off = slot % page_size;
+    dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + h) * page_size + off) * DH + lane * VEC;
+  }
+  const Slice in = *reinterpret_cast<const Slice*>(src);
+  if (!is_q && !is_k) {   // values are stored as they are
+    *reinterpret_cast<Slice*>(dst) = in;
+    return;
+  }
+  float x[VEC];
+  float ss = 0.0f;
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    x[e] = Elem<T>::load(in.v + e);
+    ss += x[e] * x[e];
+  }
+  const float* w = is_q ? qw : kw;
+  if (w) {
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(DH) + (is_q ? q_eps : k_eps));
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) x[e] = (x[e] * inv) * w[lane * VEC + e];
+  }
+  if (inv_freq) {
+    const int i0 = (lane & 15) * VEC;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+      const float c = cs[i0 + e], sn = cs[HALF + i0 + e];
+      x[e] = lane < 16 ? x[e] * c - other * sn : x[e] * c + other * sn;
+    }
+  }
+  Slice out;
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) Elem<T>::store(out.v + e, x[e]);
+  *reinterpret_cast<Slice*>(dst) = out;
+}
+
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 int launch_embed(const void* table, const int* ids, float* x, int tokens, int dim, int vocab, cudaStream_t s) {
@@ -458,6 +534,28 @@ int launch_qk_norm_rope_append(void* qkv, long long stride, const float* part, l
   const long long total = static_cast<long long>(tokens) * heads_per_token;
   if (total == 0) return kOk;
   const int warps = 8;
+  const int vec = head_dim / 32;
+  const size_t slice = sizeof(T) * vec > 16 ? 16 : sizeof(T) * vec;
+  const bool whole = part == nullptr && (head_dim == 64 || head_dim == 128 || head_dim == 256) && (inv_freq == nullptr || rot == head_dim) &&
+                     stride % vec == 0 && reinterpret_cast<uintptr_t>(qkv) % slice == 0 && reinterpret_cast<uintptr_t>(kc) % slice == 0 &&
+                     reinterpret_cast<uintptr_t>(vc) % slice == 0;
+  if (whole) {
+    const dim3 grid(tokens, ceil_div(heads_per_token, warps));
+    T* q = static_cast<T*>(qkv);
+    T* k = static_cast<T*>(kc);
+    T* v = static_cast<T*>(vc);
+    if (vec == 2) {
+      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 2>), grid, warps * 32, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
+                 q_heads, kv_heads, page_size, heads_per_token);
+    } else if (vec == 4) {
+      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 4>), grid, warps * 32, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
+                 q_heads, kv_heads, page_size, heads_per_token);
+    } else {
+      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 8>), grid, warps * 32, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
+                 q_heads, kv_heads, page_size, heads_per_token);
+    }
+    TIE_RETURN_LAUNCH("qk_norm_rope_append");
+  }
   const size_t smem = (static_cast<size_t>(warps) * head_dim + rot) * sizeof(float);
   TIE_LAUNCH((qk_norm_rope_append_kernel<T>), dim3(tokens, ceil_div(heads_per_token, warps)), warps * 32, smem, s, 
       static_cast<T*>(qkv), stride, part, part_stride, splits, part_ld, qw, kw, q_eps, k_eps, inv_freq, rot, pos, slots,
