@@ -46,7 +46,11 @@ struct DecodeArgs {
 template <int DH, int STAGES>
 __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                       const __grid_constant__ CUtensorMap v_map, DecodeArgs a) {
-  pdl_sync();
+  // Keys and values of earlier tokens, the tables and the lengths do not depend on the kernels just ahead in
+  // the stream (those write this step's q and the newest token's cache slot), so the ring starts filling before
+  // this kernel waits for them; the wait comes before q is read, before the tile with the newest key is
+  // fetched, and before anything is written.
+  pdl_launch_dependents();
   using L = HalfLayout<DH>;
   constexpr int HALVES = DH / 64;
   constexpr int PLANE_BYTES = HALVES * 64 * 128;       // K (or V) of one 64-key tile
@@ -67,6 +71,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   const int t = a.query_start[seq];
   const int pos = a.context_lens[seq] - 1;
   if (pos < 0) {            // a padding sequence: no keys; split 0 writes zeros
+    pdl_wait();
     if (split == 0) {
       for (int id = threadIdx.x; id < G * DH; id += kDecThreads)
         a.out[(static_cast<long long>(t) * a.q_heads + kvh * G) * DH + id] = __float2bfloat16_rn(0.0f);
@@ -103,14 +108,6 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
       pages[b] = idx < a.max_blocks ? table[idx] : 0;
     }
   }
-  // Q: the G heads of the group, rows G..15 zero
-  constexpr int CPR = DH / 8;
-  for (int id = threadIdx.x; id < 16 * CPR; id += kDecThreads) {
-    const int r = id / CPR, c = id % CPR;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < G) v = *reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t) * a.q_stride + static_cast<long long>(kvh * G + r) * DH + c * 8);
-    *reinterpret_cast<uint4*>(q_tile + RowLayout<DH>::at(r, c)) = v;
-  }
   __syncthreads();
   volatile int* abort_flag = flags;
 
@@ -124,6 +121,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
       for (int i = 0; i < n_tiles; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, abort_flag, a.status, 11)) break;
+        if (hi == pos && i == n_tiles - 1) pdl_wait();   // the tile with the newest key
         mbar_expect_tx(full + s, STAGE_BYTES);
         uint8_t* kdst = smem + s * STAGE_BYTES;
         for (int b = 0; b < boxes_per_tile; ++b) {
@@ -138,6 +136,16 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
       }
     }
   } else {
+    // Q: the G heads of the group, rows G..15 zero
+    pdl_wait();
+    constexpr int CPR = DH / 8;
+    for (int id = threadIdx.x; id < 16 * CPR; id += 128) {
+      const int r = id / CPR, c = id % CPR;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < G) v = *reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t) * a.q_stride + static_cast<long long>(kvh * G + r) * DH + c * 8);
+      *reinterpret_cast<uint4*>(q_tile + RowLayout<DH>::at(r, c)) = v;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four consumer warps
     uint32_t qf[DH / 16][4];
     const uint32_t q_addr = smem_u32(q_tile);
 #pragma unroll
@@ -169,6 +177,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
     }
   }
   __syncthreads();   // every stage has been consumed (or a wait gave up): the ring can be reused
+  pdl_wait();        // (the producer warp may not have waited yet)
   if (flags[0] != 0) {   // a wait ran out: let copies that are still in flight land before the ring is reused
     const unsigned long long t0 = clock64();
     while (clock64() - t0 < 4000000ull) {
