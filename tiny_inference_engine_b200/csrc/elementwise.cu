@@ -141,7 +141,16 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restric
                                                                 int splits, const int* __restrict__ rows,
                                                                 const float* __restrict__ w, float eps, T* __restrict__ out,
                                                                 int dim) {
-  pdl_sync();
+  // the norm weights do not depend on the kernels ahead in the stream: fetch them before waiting
+  pdl_launch_dependents();
+  const int pieces = dim >> 2;
+  float4 wv[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    wv[i] = c < pieces ? *reinterpret_cast<const float4*>(w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[t] : t) * dim;
@@ -150,7 +159,6 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restric
   const float* pr = part ? part + src : nullptr;
   T* o = out + static_cast<size_t>(t) * dim;
   const bool write_back = (dr != nullptr || pr != nullptr) && rows == nullptr;
-  const int pieces = dim >> 2;
   float4 v[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -170,7 +178,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restric
     float4 d[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) d[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
+#pragma unroll 8
     for (int z = 0; z < splits; ++z) {   // every element still adds its splits in order
       const float* pz = pr + static_cast<long long>(z) * part_stride;
 #pragma unroll
@@ -200,7 +208,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_vec4_kernel(float* __restric
   for (int i = 0; i < NV; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < pieces) {
-      const float4 ww = *reinterpret_cast<const float4*>(w + 4 * c);
+      const float4 ww = wv[i];
       Vec4<T>::store(o + 4 * c, make_float4((v[i].x * inv) * ww.x, (v[i].y * inv) * ww.y, (v[i].z * inv) * ww.z, (v[i].w * inv) * ww.w));
     }
   }
@@ -302,7 +310,7 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
                                            const int* __restrict__ positions, const int* __restrict__ slots,
                                            T* __restrict__ k_cache, T* __restrict__ v_cache, int q_heads, int kv_heads,
                                            int head_dim, int page_size, int heads_per_token, long long total) {
-  pdl_sync();
+  pdl_launch_dependents();   // positions and frequencies are the step's own inputs: the rotation table is made before the wait
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -319,6 +327,7 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
       cs[half + i] = sinf(angle);
     }
   }
+  pdl_wait();
   __syncthreads();
   if (head >= heads_per_token) return;
   T* src = qkv + t * row_stride + static_cast<long long>(head) * head_dim;
@@ -388,7 +397,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restr
                                                                       const int* __restrict__ positions, const int* __restrict__ slots,
                                                                       T* __restrict__ k_cache, T* __restrict__ v_cache, int q_heads,
                                                                       int kv_heads, int page_size, int heads_per_token) {
-  pdl_sync();
+  pdl_launch_dependents();   // positions and frequencies are the step's own inputs: the rotation table is made before the wait
   constexpr int DH = 32 * VEC, HALF = DH / 2;
   using Slice = HeadSlice<T, VEC>;
   __shared__ float cs[DH];   // the token's rotation: cos at [0, HALF), sin at [HALF, DH)
@@ -403,6 +412,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restr
       cs[HALF + i] = sinf(angle);
     }
   }
+  pdl_wait();
   __syncthreads();
   if (head >= heads_per_token) return;
   T* src = qkv + t * row_stride + static_cast<long long>(head) * DH + lane * VEC;
