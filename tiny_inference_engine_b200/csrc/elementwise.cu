@@ -383,7 +383,7 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
   for (int i = 2 * half + lane; i < head_dim; i += 32) st(dst + i, buf[i]);
 }
 
-// The same for head sizes 64, 128 and 256 with the whole head rotated (or none of it), read from qkv:
+// The same for head sizes 64, 128 and 256 with the whole head rotated (or none of it):
 // a lane holds VEC = head_dim / 32 neighbouring elements (one vector load and store), lanes 0-15 the
 // first half of the head and lanes 16-31 the second, so a rotation pair is one shuffle apart.
 template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof(T) * VEC) HeadSlice {
@@ -392,6 +392,8 @@ template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof
 
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, long long row_stride,
+                                                                      const float* __restrict__ part, long long part_stride,
+                                                                      int splits, long long part_ld,
                                                                       const float* __restrict__ qw, const float* __restrict__ kw,
                                                                       float q_eps, float k_eps, const float* __restrict__ inv_freq,
                                                                       const int* __restrict__ positions, const int* __restrict__ slots,
@@ -426,18 +428,33 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restr
     const long long page = slot / page_size, off = slot % page_size;
     dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + h) * page_size + off) * DH + lane * VEC;
   }
-  const Slice in = *reinterpret_cast<const Slice*>(src);
+  float x[VEC];
+  if (part) {   // the sum of the split product's partial sums, in split order
+    using FloatSlice = HeadSlice<float, VEC>;
+    const float* psrc = part + t * part_ld + static_cast<long long>(head) * DH + lane * VEC;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) x[e] = 0.0f;
+#pragma unroll 4
+    for (int z = 0; z < splits; ++z) {
+      const FloatSlice p = *reinterpret_cast<const FloatSlice*>(psrc + static_cast<long long>(z) * part_stride);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) x[e] += p.v[e];
+    }
+  } else {
+    const Slice in = *reinterpret_cast<const Slice*>(src);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) x[e] = Elem<T>::load(in.v + e);
+  }
   if (!is_q && !is_k) {   // values are stored as they are
-    *reinterpret_cast<Slice*>(dst) = in;
+    Slice out;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) Elem<T>::store(out.v + e, x[e]);
+    *reinterpret_cast<Slice*>(dst) = out;
     return;
   }
-  float x[VEC];
   float ss = 0.0f;
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) {
-    x[e] = Elem<T>::load(in.v + e);
-    ss += x[e] * x[e];
-  }
+  for (int e = 0; e < VEC; ++e) ss += x[e] * x[e];
   const float* w = is_q ? qw : kw;
   if (w) {
     ss = warp_sum(ss);
@@ -546,7 +563,9 @@ int launch_qk_norm_rope_append(void* qkv, long long stride, const float* part, l
   const int warps = 8;
   const int vec = head_dim / 32;
   const size_t slice = sizeof(T) * vec > 16 ? 16 : sizeof(T) * vec;
-  const bool whole = part == nullptr && (head_dim == 64 || head_dim == 128 || head_dim == 256) && (inv_freq == nullptr || rot == head_dim) &&
+  const size_t fslice = sizeof(float) * vec > 16 ? 16 : sizeof(float) * vec;
+  const bool part_ok = part == nullptr || (reinterpret_cast<uintptr_t>(part) % fslice == 0 && part_stride % vec == 0 && part_ld % vec == 0);
+  const bool whole = part_ok && (head_dim == 64 || head_dim == 128 || head_dim == 256) && (inv_freq == nullptr || rot == head_dim) &&
                      stride % vec == 0 && reinterpret_cast<uintptr_t>(qkv) % slice == 0 && reinterpret_cast<uintptr_t>(kc) % slice == 0 &&
                      reinterpret_cast<uintptr_t>(vc) % slice == 0;
   if (whole) {
@@ -555,13 +574,13 @@ int launch_qk_norm_rope_append(void* qkv, long long stride, const float* part, l
     T* k = static_cast<T*>(kc);
     T* v = static_cast<T*>(vc);
     if (vec == 2) {
-      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 2>), grid, warps * 32, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
+      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 2>), grid, warps * 32, 0, s, q, stride, part, part_stride, splits, part_ld, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
                  q_heads, kv_heads, page_size, heads_per_token);
     } else if (vec == 4) {
-      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 4>), grid, warps * 32, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
+      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 4>), grid, warps * 32, 0, s, q, stride, part, part_stride, splits, part_ld, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
                  q_heads, kv_heads, page_size, heads_per_token);
     } else {
-      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 8>), grid, warps * 32, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
+      TIE_LAUNCH((qk_norm_rope_append_vec_kernel<T, 8>), grid, warps * 32, 0, s, q, stride, part, part_stride, splits, part_ld, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v,
                  q_heads, kv_heads, page_size, heads_per_token);
     }
     TIE_RETURN_LAUNCH("qk_norm_rope_append");
