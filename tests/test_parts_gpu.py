@@ -319,3 +319,115 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
     cache.reserve(rc, 40)
     out = runner.run([StepEntry(rc, a, 0, list(range(40)))]).float().cpu().numpy()
     assert_logits_close(out, plain_forward(a), "float32", "toy mixer, slot used again")
+
+
+def test_a_toy_feed_forward_with_routing_and_another_position_encoding():
+    """Two more parts the framework has never seen, registered from here and chosen for one layer only:
+    a feed-forward that routes every token to one of three experts (router logits and softmax in
+    float32), and a position encoding that is no rotation (it adds a sinusoid of the position to q and
+    k), so the attention part takes its unfused path. The other layer stays Qwen3's. Stepped whole, in
+    portions and beside another request."""
+    import dataclasses
+
+    from tiny_inference_engine_b200 import StepEntry
+    from tiny_inference_engine_b200.config import LayerSpec, ModelSpec, PartSpec
+    from tiny_inference_engine_b200.parts import FeedForward, PositionEncoding, register_part
+    from tiny_inference_engine_b200.weights import TensorNeed
+
+    class TopOneExperts(FeedForward):
+        def __init__(self, spec, dtype, prefix=""):
+            p = spec.params if hasattr(spec, "params") else spec
+            self.prefix, self.d, self.e, self.dtype = p["prefix"], p["hidden_size"], p["experts"], dtype
+
+        def needs(self):
+            return {self.prefix + "router.weight": TensorNeed((self.e, self.d)),
+                    self.prefix + "experts.weight": TensorNeed((self.e, self.d, self.d))}
+
+        def bind(self, get):
+            self.router, self.experts = get(self.prefix + "router.weight").float(), get(self.prefix + "experts.weight").float()
+
+        def forward(self, h, ctx):
+            x = h.float()
+            probs = torch.softmax(x @ self.router.T, dim=-1)            # a toy: plain torch
+            top = probs.argmax(dim=-1)
+            out = torch.einsum("td,tod->to", x, self.experts[top]) * probs.gather(1, top[:, None])
+            return out.to(h.dtype)
+
+    class AddedSinusoid(PositionEncoding):
+        def __init__(self, spec, dtype, prefix=""):
+            p = spec.params if hasattr(spec, "params") else spec
+            self.amp, self.base = p["amplitude"], p["base"]
+
+        def apply(self, x, positions, heads, head_dim):
+            freq = self.base ** (-torch.arange(head_dim, device=x.device, dtype=torch.float32) / head_dim)
+            wave = self.amp * torch.sin(positions.float()[:, None] * freq[None, :])
+            view = x.unflatten(1, (heads, head_dim))
+            view.add_(wave[:, None, :].to(x.dtype))
+
+    register_part("feed_forward", "top_one_experts", TopOneExperts, replace=True)
+    register_part("position", "added_sinusoid", AddedSinusoid, replace=True)
+
+    cfg = plain.normalise_config(plain.TINY_B)
+    w = plain.random_weights(cfg, 21, std=0.1)
+    D, E = cfg["hidden_size"], 3
+    Hq, Hkv, Dh, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    rng = np.random.default_rng(5)
+    w["model.layers.1.moe.router.weight"] = rng.standard_normal((E, D)).astype(np.float32)
+    w["model.layers.1.moe.experts.weight"] = (rng.standard_normal((E, D, D)) * 0.1).astype(np.float32)
+    for k in [k for k in w if k.startswith("model.layers.1.mlp.")]:
+        del w[k]
+    base = qwen_spec(cfg)
+    l1 = base.layers[1]
+    mixer_params = dict(l1.mixer.params)
+    mixer_params["position"] = PartSpec("added_sinusoid", {"amplitude": 0.5, "base": 50.0})
+    toy = dataclasses.replace(l1, mixer=PartSpec(l1.mixer.kind, mixer_params),
+                              ffn=PartSpec("top_one_experts", {"prefix": "model.layers.1.moe.", "hidden_size": D, "experts": E}))
+    spec = ModelSpec(**{**base.__dict__, "layers": (base.layers[0], toy, base.layers[2])})
+    margins = []
+
+    def plain_forward(toks):
+        T, pos = len(toks), np.arange(len(toks))
+        x = plain.embed(w["model.embed_tokens.weight"], toks)
+        x = plain.decoder_layer(x, w, 0, cfg, pos)
+        p = "model.layers.1."
+        h = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+        q, k, v = (plain.linear(h, w[p + f"self_attn.{n}_proj.weight"]) for n in "qkv")
+        q = plain.rms_norm(q.reshape(T * Hq, Dh), w[p + "self_attn.q_norm.weight"], eps).reshape(T, Hq, Dh)
+        k = plain.rms_norm(k.reshape(T * Hkv, Dh), w[p + "self_attn.k_norm.weight"], eps).reshape(T, Hkv, Dh)
+        wave = 0.5 * np.sin(pos[:, None] * 50.0 ** (-np.arange(Dh) / Dh)[None, :])
+        q, k = (q + wave[:, None, :]).reshape(T, -1), (k + wave[:, None, :]).reshape(T, -1)
+        x = x + plain.linear(plain.causal_attention(q, k, v, Hq, Hkv, Dh), w[p + "self_attn.o_proj.weight"])
+        h = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+        logits = h @ w[p + "moe.router.weight"].astype(np.float64).T
+        probs = np.exp(logits - logits.max(-1, keepdims=True))
+        probs /= probs.sum(-1, keepdims=True)
+        top = probs.argmax(-1)
+        srt = np.sort(logits, -1)
+        margins.append((srt[:, -1] - srt[:, -2]).min())
+        experts = w[p + "moe.experts.weight"].astype(np.float64)
+        x = x + np.einsum("td,tod->to", h, experts[top]) * probs[np.arange(T), top][:, None]
+        x = plain.decoder_layer(x, w, 2, cfg, pos)
+        return plain.linear(plain.rms_norm(x, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+    model, cache, runner = build(spec, w, "float32", page=8, pages=48)
+    toks_a, toks_b = rng.integers(0, cfg["vocab_size"], 45).tolist(), rng.integers(0, cfg["vocab_size"], 30).tolist()
+    want_a, want_b = plain_forward(toks_a), plain_forward(toks_b)
+    assert min(margins) > 1e-3, "choose other weights: a router decision is too close to call"
+    assert_logits_close(run_whole(runner, cache, toks_a), want_a, "float32", "toy parts, whole")
+    assert_logits_close(run_whole(runner, cache, toks_a, cuts=[7, 2, 1, 20, 15]), want_a, "float32", "toy parts, in portions")
+    ra, rb = cache.new_request(), cache.new_request()
+    got_a, got_b, pa, pb = [], [], 0, 0
+    for na, nb in [(30, 0), (1, 12), (1, 1), (13, 17)]:
+        entries = []
+        if na:
+            cache.reserve(ra, pa + na)
+            entries.append(StepEntry(ra, toks_a[pa:pa + na], pa, list(range(na))))
+        if nb:
+            cache.reserve(rb, pb + nb)
+            entries.append(StepEntry(rb, toks_b[pb:pb + nb], pb, list(range(nb))))
+        out = runner.run(entries).float().cpu().numpy()
+        # entries are given in this order; rows come back in the order of the entries
+        got_a.append(out[:na]), got_b.append(out[na:])
+        pa, pb = pa + na, pb + nb
+    assert_logits_close(np.concatenate(got_a), want_a, "float32", "toy parts, request a beside b")
+    assert_logits_close(np.concatenate(got_b), want_b, "float32", "toy parts, request b beside a")
