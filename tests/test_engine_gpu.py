@@ -67,6 +67,41 @@ def test_batched_requests_generate_what_each_generates_alone(tiny_models, pages,
     assert eng.cache.num_free() == pages and st.steps > 0 and st.decode_tokens > 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("pages", [256, 9])
+def test_steps_queued_ahead_change_no_token(tiny_models, dtype, pages):
+    """With run_ahead the next decode step is queued before this one's tokens are read and takes them
+    from the device. Same tokens as without, for requests that end by length, by a stop token (one step
+    runs in vain) and at different times, with plenty of pages and with so few that requests are
+    preempted; no page is lost."""
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig
+    cfg, page, w, d = tiny_models["tiny_b"]
+    rng = np.random.default_rng(14)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (3, 17, 8, 25, 1, 11)]
+    params = [SamplingParams(max_tokens=5 + 4 * i, temperature=0.7 if i % 2 else 0.0, seed=50 + i) for i in range(6)]
+    plain_run = engine_for(d, dtype=dtype, num_pages=64, page_size=page, serving=ServingConfig(16, 8, run_ahead=False))
+    free_run = plain_run.generate_batch(prompts, params)
+    stop = [free_run[3][6], free_run[5][10]]              # tokens that two of the requests do generate
+    outs = {}
+    for ahead in (False, True):
+        eng = engine_for(d, dtype=dtype, num_pages=pages, page_size=page, stop_tokens=stop, policy="fcfs",
+                         serving=ServingConfig(16, 8, run_ahead=ahead))
+        outs[ahead] = eng.generate_batch(prompts, params)
+        st = eng.stats()
+        assert (st.steps_ahead > 0) == ahead
+        while eng.has_work():                               # a step may still be queued for requests that have ended
+            eng.step()
+        assert eng.cache.num_free() == pages
+        assert st.decode_tokens > 0 and (st.preemptions > 0) == (pages == 9)
+    assert outs[True] == outs[False]
+    assert any(len(o) < p.max_tokens for o, p in zip(outs[True], params)), "no request was stopped by a stop token"
+    # one request alone, through generate(), ended by a stop token while a step is queued ahead; then the next one
+    eng = engine_for(d, dtype=dtype, num_pages=64, page_size=page, stop_tokens=[free_run[1][5]])
+    assert eng.generate(prompts[1], params[1]) == free_run[1][:free_run[1].index(free_run[1][5]) + 1]
+    assert eng.generate(prompts[2], params[2]) == plain_run.generate(prompts[2], params[2])
+    assert eng.stats().steps_ahead > 0
+
+
 def test_a_failed_step_is_rolled_back_and_the_requests_still_finish(tiny_models):
     from tiny_inference_engine_b200 import SamplingParams, ServingConfig
     cfg, page, w, d = tiny_models["tiny_a"]

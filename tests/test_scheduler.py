@@ -37,11 +37,11 @@ class Rig:
         self.finish_step(b)
         return [(q.id, n) for q, n in b.seqs]
 
-    def finish_step(self, b):
+    def finish_step(self, b, still_in_flight=None):
         for q, n in b.seqs:
             q.num_computed += n
             self.cache.advance_window(q.cache, q.num_computed)
-        self.s.complete(b)
+        self.s.complete(b, still_in_flight)
         for q, n in b.seqs:
             if q.num_computed == len(q.tokens):
                 q.tokens.append(0)
@@ -236,3 +236,46 @@ def test_randomized_simulation_keeps_the_invariants(seed):
     assert not r.s.has_work(), "not every request finished"
     assert all(q.state == SeqState.FINISHED for q in r.seqs)
     assert all(p.num_free == p.num_blocks for p in r.cache.pools)
+
+
+def test_schedule_ahead_only_when_the_next_decision_is_certain():
+    """The same requests one token further while their step is in flight: only if nothing waits, the batch
+    is every running request, each decodes and cannot end by length with the token in flight, and pages
+    for all can be had; otherwise nothing is taken."""
+    r = Rig(pages=6, tokens=16, seqs=4)
+    a, b = r.add(6, max_tokens=100), r.add(3, max_tokens=100)
+    batch = r.s.schedule()                                   # both prompts whole
+    assert r.s.schedule_ahead(batch) is None                 # prompts, not decodes
+    r.finish_step(batch)
+    batch = r.s.schedule()
+    assert [(q.id, n) for q, n in batch.seqs] == [(a.id, 1), (b.id, 1)]
+    held = r.cache.num_free()
+    ahead = r.s.schedule_ahead(batch)
+    assert ahead is not None and [(q.id, n) for q, n in ahead.seqs] == [(a.id, 1), (b.id, 1)] and ahead.id != batch.id
+    for q, _ in ahead.seqs:                                   # pages for the token in flight and the one after it
+        assert all(len(t) >= blocks_for(q.num_computed + 2, PAGE) for t in q.cache.tables)
+    assert r.cache.num_free() == held - 1                    # a: 8 tokens fit its two pages; b: 5 tokens need a second
+    r.finish_step(batch, still_in_flight=ahead)
+    assert r.s._busy(a) and r.s._busy(b)
+    r.finish_step(ahead)
+    assert not r.s._busy(a) and not r.s._busy(b)
+    # something waits: the next decision may admit it
+    c = r.add(2, max_tokens=100)
+    batch = r.s.schedule()
+    assert r.s.schedule_ahead(batch) is None
+    r.finish_step(batch)
+    # a request that ends by length with the token in flight
+    a.params.max_tokens = a.num_generated + 1
+    batch = r.s.schedule()
+    assert r.s.schedule_ahead(batch) is None
+    a.params.max_tokens = 100
+    r.finish_step(batch)
+    # the pool cannot give every request its page: nothing is taken
+    r = Rig(pages=3, tokens=16, seqs=4)
+    a, b = r.add(3, max_tokens=100), r.add(3, max_tokens=100)
+    r.finish_step(r.s.schedule())
+    batch = r.s.schedule()                                   # position 3 of both: the last slot of their first page
+    assert [(q.id, n) for q, n in batch.seqs] == [(a.id, 1), (b.id, 1)] and r.cache.num_free() == 1
+    assert r.s.schedule_ahead(batch) is None                 # position 4 needs a second page for each; one is free
+    assert r.cache.num_free() == 1 and all(len(t) == 1 for q in (a, b) for t in q.cache.tables)
+    r.finish_step(batch)

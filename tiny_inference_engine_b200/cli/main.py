@@ -38,6 +38,7 @@ generate options:
   --policy fcfs|srpt-aging  admission order (default srpt-aging)
   --aging N             srpt-aging priority gained per step waited, in tokens (default 16)
   --stop-ids IDS        token ids that end generation
+  --no-run-ahead        read every step's tokens before the next step is queued
 """
 
 
@@ -86,6 +87,7 @@ def run_generate(argv) -> int:
     ap.add_argument("--policy", default="srpt-aging")
     ap.add_argument("--aging", type=int, default=16)
     ap.add_argument("--stop-ids", default="")
+    ap.add_argument("--no-run-ahead", action="store_true")
     try:
         o = ap.parse_args(argv)
     except SystemExit:
@@ -101,7 +103,7 @@ def run_generate(argv) -> int:
 
     t0 = time.perf_counter()
     engine = load_engine(o.model, dtype=o.dtype, kv_mem=parse_size(o.kv_mem), page_size=o.page_size,
-                         serving=ServingConfig(o.max_tokens_per_step, o.max_seqs), policy=o.policy, aging=o.aging,
+                         serving=ServingConfig(o.max_tokens_per_step, o.max_seqs, run_ahead=not o.no_run_ahead), policy=o.policy, aging=o.aging,
                          stop_tokens=parse_ids(o.stop_ids), random_weights=o.random_weights, seed=o.seed)
     load_s = time.perf_counter() - t0
     if o.prompt is not None:

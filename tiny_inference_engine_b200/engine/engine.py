@@ -29,6 +29,17 @@ class EngineStats:
     decode_tokens: int = 0
     step_seconds: float = 0.0  # time in the step function and sampling
     preemptions: int = 0
+    steps_ahead: int = 0       # steps queued before the tokens of the step ahead of them were read
+
+
+@dataclass
+class _Pending:
+    """A step on the GPU whose tokens have not been read yet."""
+    batch: ScheduledBatch
+    sampled: list
+    tokens: object           # StepRunner.fetch's handle
+    prefill: int
+    decode: int
 
 
 class Engine:
@@ -48,6 +59,7 @@ class Engine:
         self.sequences: dict[int, Sequence] = {}
         self._next_id = 0
         self._stepping = False
+        self._ahead: _Pending | None = None      # a decode step queued before the one ahead of it was read
         self._on_token: Callable[[int, int], None] | None = None
         self._stats = EngineStats()
         self.max_blocks_per_seq = blocks_for(model.spec.max_positions, cache.page_size)
@@ -89,7 +101,7 @@ class Engine:
             raise InvalidArgument(f"no sequence with id {seq_id}") from None
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._ahead is not None
 
     def set_token_callback(self, callback: Callable[[int, int], None] | None) -> None:
         self._on_token = callback
@@ -116,24 +128,60 @@ class Engine:
             raise InvalidArgument(f"scheduler gave {total} tokens; a step allows at most {self.serving.max_tokens_per_step}")
 
     def step(self) -> None:
+        """One step: a batch is decided, run, and its tokens are handed out. With `serving.run_ahead`, while
+        a pure decode batch runs and the scheduler is certain of the next one (`Scheduler.schedule_ahead`),
+        that next step is queued on the GPU before this one's tokens are read; it takes its input tokens
+        from the device and is finished by the next call. Tokens come out in the same order with the same
+        values either way; a request that stops runs at most one step in vain."""
         if self._stepping:
             raise InvalidArgument("step() called during a step (e.g. from a token callback)")
-        batch = self.scheduler.schedule()
-        if batch.empty():
-            return
         self._stepping = True
         try:
-            self._run(batch)
+            pending, self._ahead = self._ahead, None
+            if pending is not None and all(seq.state == SeqState.FINISHED for seq, _ in pending.batch.seqs):
+                self._complete(pending)      # queued ahead for requests that have all ended since: nothing to hand out
+                pending = None
+            if pending is None:
+                batch = self.scheduler.schedule()
+                if batch.empty():
+                    return
+                pending = self._launch(batch)
+            launch_error = None
+            if self.serving.run_ahead:
+                nxt = self.scheduler.schedule_ahead(pending.batch)
+                if nxt is not None:
+                    try:
+                        self._ahead = self._launch(nxt, ahead_of=pending)
+                        self._stats.steps_ahead += 1
+                    except Exception as e:       # its reservation has been given back; the step in flight still counts
+                        launch_error = e
+            try:
+                self._complete(pending)
+            except BaseException:
+                self._drop_ahead()
+                raise
+            if launch_error is not None:
+                raise launch_error
         finally:
             self._stepping = False
 
-    def _run(self, batch: ScheduledBatch) -> None:
+    def _launch(self, batch: ScheduledBatch, ahead_of: "_Pending | None" = None) -> "_Pending":
+        """Queues the batch on the GPU and the copy of its sampled ids to the host. With `ahead_of` (the
+        step in flight, same requests in the same order) every request is one token further than its
+        bookkeeping says and its input token is the one that step samples."""
         sampled: list[Sequence] = []
         prefill = decode = 0
         try:
-            self._check_batch(batch)
+            if ahead_of is None:
+                self._check_batch(batch)
             entries = []
             for seq, n in batch.seqs:
+                if ahead_of is not None:
+                    begin = seq.num_computed + 1
+                    entries.append(StepEntry(seq.cache, (0,), begin, (0,)))
+                    sampled.append(seq)
+                    decode += 1
+                    continue
                 begin, end = seq.num_computed, seq.num_computed + n
                 samples = end == len(seq.tokens)   # its whole pending input is in the cache after this step
                 entries.append(StepEntry(seq.cache, seq.tokens[begin:end], begin, (n - 1,) if samples else ()))
@@ -144,36 +192,67 @@ class Engine:
                 else:
                     prefill += n
             t0 = time.perf_counter()
-            sampling = [(s.params, s.num_generated) for s in sampled]
-            logits, ids = self.runner.run(entries, sampling)
-            tokens = self.runner.tokens_of(logits, ids, sampling)
+            extra = 1 if ahead_of is not None else 0
+            sampling = [(s.params, s.num_generated + extra) for s in sampled]
+            logits, ids = self.runner.run(entries, sampling, device_tokens=ahead_of is not None)
+            tokens = self.runner.fetch(logits, ids, sampling)
+            self._stats.step_seconds += time.perf_counter() - t0
+        except BaseException:
+            self._give_back(batch, ahead=ahead_of is not None)
+            raise
+        return _Pending(batch, sampled, tokens, prefill, decode)
+
+    def _give_back(self, batch: ScheduledBatch, ahead: bool = False) -> None:
+        """The step did not run: give back what the scheduler reserved and let it be scheduled again.
+        State of fixed size may be half-updated, so requests that keep some start over."""
+        for seq, _ in batch.seqs:
+            if seq.state == SeqState.FINISHED:
+                continue
+            if self.states is not None and self.states.bytes_per_slot > 0 and not ahead:
+                self.cache.reset(seq.cache)
+                seq.num_computed = 0
+            else:
+                self.cache.truncate(seq.cache, seq.num_computed + (1 if ahead else 0))
+        if not ahead:
+            self.scheduler.abandon(batch)
+
+    def _drop_ahead(self) -> None:
+        """Forgets the step queued ahead (its results will never be read) once the GPU is done with it."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is None:
+            return
+        torch.cuda.current_stream().synchronize()
+        for seq, _ in ahead.batch.seqs:
+            if seq.state != SeqState.FINISHED:
+                self.cache.truncate(seq.cache, seq.num_computed)
+        self.scheduler.abandon(ahead.batch)
+
+    def _complete(self, pending: "_Pending") -> None:
+        """Waits for the step's tokens and hands them out; finishes what ends."""
+        batch, sampled = pending.batch, pending.sampled
+        try:
+            t0 = time.perf_counter()
+            tokens = pending.tokens.result()
             self._stats.step_seconds += time.perf_counter() - t0
             self._stats.steps += 1
             self._stats.seqs_scheduled += len(batch.seqs)
-            self._stats.prefill_tokens += prefill
-            self._stats.decode_tokens += decode
+            self._stats.prefill_tokens += pending.prefill
+            self._stats.decode_tokens += pending.decode
         except BaseException:
-            # The step did not run: give back what the scheduler reserved and let it be scheduled again.
-            # State of fixed size may be half-updated, so requests that keep some start over.
-            for seq, _ in batch.seqs:
-                if seq.state == SeqState.FINISHED:
-                    continue
-                if self.states is not None and self.states.bytes_per_slot > 0:
-                    self.cache.reset(seq.cache)
-                    seq.num_computed = 0
-                else:
-                    self.cache.truncate(seq.cache, seq.num_computed)
-            self.scheduler.abandon(batch)
+            self._drop_ahead()
+            self._give_back(batch)
             raise
 
         for seq, n in batch.seqs:
+            if seq.state == SeqState.FINISHED:
+                continue   # it ended while this step, queued ahead, was in flight: the step ran in vain for it
             seq.num_computed += n
             self.cache.advance_window(seq.cache, seq.num_computed)
-        self.scheduler.complete(batch)
+        self.scheduler.complete(batch, still_in_flight=self._ahead.batch if self._ahead is not None else None)
 
         for i, seq in enumerate(sampled):
             if seq.state == SeqState.FINISHED:
-                continue  # cancelled by an earlier token callback of this step
+                continue  # cancelled by an earlier token callback of this step, or ended a step ago
             token = tokens[i]
             try:
                 seq.tokens.append(token)

@@ -37,6 +37,7 @@ class ServingConfig:
     (src/engine/serving_config.h:12-22)."""
     max_tokens_per_step: int = 512
     max_seqs: int = 64
+    run_ahead: bool = True      # queue the next decode step before the host has seen this one's tokens
 
     def validate(self) -> None:
         if self.max_tokens_per_step <= 0:
@@ -226,10 +227,39 @@ class Scheduler:
             self._in_flight.add(seq.id)
         return batch
 
-    def complete(self, batch: ScheduledBatch) -> None:
-        """The engine advanced num_computed of every sequence of the batch."""
+    def schedule_ahead(self, batch: ScheduledBatch) -> ScheduledBatch | None:
+        """While `batch` is in flight and its tokens are not known yet: the same requests, each one token
+        further, if that is certainly what `schedule` would decide once the batch is back, else None.
+        Certain means: nothing waits; the batch holds every running request; each decodes one token, is
+        sampled on the device and cannot reach its max_tokens with the token in flight; and pages for
+        one more token can be had for all of them (all or nothing; preemption is left to `schedule`).
+        A request that turns out to have stopped with the token in flight runs this one step in vain."""
+        if self.waiting or len(batch.seqs) != len(self.running) or not batch.seqs:
+            return None
+        for seq, n in batch.seqs:
+            if n != 1 or seq.state != SeqState.DECODING or seq.num_pending != 1 or not seq.params.on_device:
+                return None
+            if seq.num_generated + 1 >= seq.params.max_tokens:
+                return None
+        taken = []
         for seq, _ in batch.seqs:
-            self._in_flight.discard(seq.id)
+            if not self.cache.reserve(seq.cache, seq.num_computed + 2):
+                for s in taken:
+                    self.cache.truncate(s.cache, s.num_computed + 1)
+                return None
+            taken.append(seq)
+        self.step_no += 1
+        ahead = ScheduledBatch(id=self._next_batch, seqs=[(seq, 1) for seq, _ in batch.seqs])
+        self._next_batch += 1
+        return ahead
+
+    def complete(self, batch: ScheduledBatch, still_in_flight: ScheduledBatch | None = None) -> None:
+        """The engine advanced num_computed of every sequence of the batch. Requests of `still_in_flight`
+        (a batch queued ahead) stay busy."""
+        keep = {seq.id for seq, _ in still_in_flight.seqs} if still_in_flight is not None else ()
+        for seq, _ in batch.seqs:
+            if seq.id not in keep:
+                self._in_flight.discard(seq.id)
 
     def abandon(self, batch: ScheduledBatch) -> None:
         """The step failed; tables were trimmed back to num_computed."""

@@ -105,6 +105,29 @@ def _bucket(n: int, limit: int) -> int:
     return min(b, limit) if n <= limit else n
 
 
+class PendingTokens:
+    """The sampled ids of a step on their way to the host."""
+
+    def __init__(self, runner, host, event, logits, sampling):
+        self.runner, self.host, self.event, self.logits, self.sampling = runner, host, event, logits, sampling
+
+    def result(self) -> list[int]:
+        """Waits for the copy; rows that need the host filter (top-k, top-p) are sampled from their logits
+        (no other step may have been queued since for those). Checks the kernels' status words."""
+        from ..sampling.sampler import sample_host
+        R = len(self.sampling)
+        if R == 0:
+            return []
+        host_rows = [r for r, (p, _) in enumerate(self.sampling) if not p.on_device]
+        host_logits = self.logits[host_rows].cpu().numpy() if host_rows else None
+        self.event.synchronize()
+        gemm_select.check_status()
+        out = self.host[:R].tolist()
+        for j, r in enumerate(host_rows):
+            out[r] = sample_host(host_logits[j], self.sampling[r][0], self.sampling[r][1])
+        return out
+
+
 class StepRunner:
     """Owns the workspace, the staging buffers and the decode graphs; `run(entries)` is the step function."""
 
@@ -129,7 +152,9 @@ class StepRunner:
         words = 4 * max_tokens + 6 * self.max_seqs + 6 * self.max_logit_rows + G * (max_tokens + self.max_seqs * mb) + 64 * (8 + 2 * G)
         self._dev = torch.zeros(words, dtype=torch.int32, device=device)
         self._ids = torch.zeros(self.max_logit_rows, dtype=torch.int32, device=device)
-        self._ids_host = torch.zeros(self.max_logit_rows, dtype=torch.int32, pin_memory=True)
+        self._ids_host = [(torch.zeros(self.max_logit_rows, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                          for _ in range(2)]
+        self._ids_turn = 0
         self.layer_hook = None
         self.fail_hook = None     # tests: called after the batch is built, may raise
         # Per-request state is updated by plain torch code in toy mixers: no graphs then.
@@ -156,16 +181,23 @@ class StepRunner:
         return slot
 
     # -- the step function
-    def run(self, entries: Sequence[StepEntry], sampling: Sequence[tuple[SamplingParams, int]] | None = None):
+    def run(self, entries: Sequence[StepEntry], sampling: Sequence[tuple[SamplingParams, int]] | None = None,
+            device_tokens: bool = False):
         """Runs one step. Returns float32 logits [R, V] on the device in the order of the entries and
         of their `want` (None when nothing is wanted). With `sampling` (one (parameters, index of
         the generated token) per wanted row) returns (logits, ids): ids is an int32 device tensor
         [R] picked by the sampling kernel (greedy or temperature); rows whose parameters ask for
-        top-k or top-p are to be sampled from the logits by the caller."""
+        top-k or top-p are to be sampled from the logits by the caller.
+
+        With `device_tokens` every entry brings one token and entry i's token is the id that the step
+        before sampled for its row i (still on the device, perhaps not computed yet): the step can be
+        queued before the host has seen those ids. The entries' own `tokens` are placeholders then."""
+        if device_tokens and (sampling is None or any(len(e.tokens) != 1 for e in entries)):
+            raise InvalidArgument("device tokens are for steps in which every entry brings one token and samples")
         graph_key = self._graph_key(entries, sampling)
         if graph_key is not None:
-            return self._run_graph(entries, sampling, graph_key)
-        ctx = self.prepare(entries, sampling)
+            return self._run_graph(entries, sampling, graph_key, device_tokens)
+        ctx = self.prepare(entries, sampling, device_tokens=device_tokens)
         logits = self.model.forward(ctx, self.cache, self.states)
         if sampling is None:
             return logits
@@ -177,22 +209,21 @@ class StepRunner:
         ops.sample(logits, self._ids, ctx.inv_temperature, ctx.seeds, ctx.counters)
         return self._ids[:ctx.R]
 
+    def fetch(self, logits, ids, sampling) -> "PendingTokens":
+        """Queues the copy of a step's sampled ids to the host (into one of two pinned buffers used in
+        turn) and returns a handle; `result()` waits for it. Another step may be queued in between."""
+        R = len(sampling)
+        self._ids_turn ^= 1
+        host, event = self._ids_host[self._ids_turn]
+        if R > 0:
+            host[:R].copy_(ids[:R], non_blocking=True)
+        event.record()
+        return PendingTokens(self, host, event, logits, list(sampling))
+
     def tokens_of(self, logits, ids, sampling) -> list[int]:
         """Brings the sampled ids to the host (one copy, one synchronize) and samples rows that need
         the host filter (top-k, top-p) from their logits. Checks the kernels' status words."""
-        from ..sampling.sampler import sample_host
-        R = len(sampling)
-        if R == 0:
-            return []
-        self._ids_host[:R].copy_(ids[:R], non_blocking=True)
-        host_rows = [r for r, (p, _) in enumerate(sampling) if not p.on_device]
-        host_logits = logits[host_rows].cpu().numpy() if host_rows else None
-        torch.cuda.current_stream().synchronize()
-        gemm_select.check_status()
-        out = self._ids_host[:R].tolist()
-        for j, r in enumerate(host_rows):
-            out[r] = sample_host(host_logits[j], sampling[r][0], sampling[r][1])
-        return out
+        return self.fetch(logits, ids, sampling).result()
 
     def check(self) -> None:
         """After a synchronize: raises if a kernel of an earlier step gave up a bounded wait."""
@@ -217,9 +248,9 @@ class StepRunner:
         mb = max(16, _bucket(need, 1 << 30))
         return (sb, mb, sampling is not None)
 
-    def _run_graph(self, entries, sampling, key):
+    def _run_graph(self, entries, sampling, key, device_tokens=False):
         sb, mb, sampled = key
-        ctx = self.prepare(entries, sampling, pad_seqs=sb, table_len=mb)
+        ctx = self.prepare(entries, sampling, pad_seqs=sb, table_len=mb, device_tokens=device_tokens)
         if key not in self._graphs:
             # one eager run allocates every buffer and loads every kernel, then the capture
             logits = self.model.forward(ctx, self.cache, self.states)
@@ -244,7 +275,7 @@ class StepRunner:
 
     # -- building the flat batch
     def prepare(self, entries: Sequence[StepEntry], sampling=None, pad_seqs: int | None = None,
-                table_len: int | None = None) -> StepContext:
+                table_len: int | None = None, device_tokens: bool = False) -> StepContext:
         S_real = len(entries)
         if not 1 <= S_real <= self.max_seqs:
             raise CapacityError(f"step has {S_real} sequences; the step function allows 1 to {self.max_seqs}")
@@ -314,7 +345,7 @@ class StepRunner:
         windowed = [g.kind == "window" for g in self.cache.groups]
         if T_real == S_real:
             # Every sequence brings one token (decode): plain Python numbers, one array assignment per section.
-            toks = [int(e.tokens[0]) for e in entries]
+            toks = [0] * S_real if device_tokens else [int(e.tokens[0]) for e in entries]
             if min(toks) < 0 or max(toks) >= self.vocab:
                 bad = next(t for t in toks if t < 0 or t >= self.vocab)
                 raise InvalidArgument(f"token id {bad} outside vocabulary of {self.vocab}")
@@ -394,6 +425,11 @@ class StepRunner:
 
         dev[:total].copy_(slot[0][:total], non_blocking=True)
         slot[2].record()
+        if device_tokens:
+            if T_real != S_real:
+                raise InvalidArgument("device tokens are for steps in which every entry brings one token")
+            o = offs["tokens"][0]
+            dev[o:o + S_real].copy_(self._ids[:S_real])     # row i of the step before -> entry i of this one
 
         def dsec(name, n=None):
             o, full = offs[name]
