@@ -206,27 +206,39 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
     }
   }
   __syncthreads();
-  float* split_out = a.scratch + ((static_cast<long long>(li) * a.q_heads + kvh * G) * a.max_splits + split) * RS;
-  for (int id = threadIdx.x; id < G * DH; id += kDecThreads) {
-    const int r = id / DH, d = id % DH;
+  // per row: the warps' common maximum, the factor that brings each warp's sums to it, and the row sum
+  float* fac = part + 4 * 16 * RS;          // [G][4] factors, then [G] maxima, then [G] sums
+  if (threadIdx.x < G) {
+    const int r = threadIdx.x;
     float mx = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) mx = fmaxf(mx, part[(w * 16 + r) * RS + DH]);
-    float o = 0.0f, ls = 0.0f;
+    float ls = 0.0f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = part[(w * 16 + r) * RS + DH];
       const float f = mw == -INFINITY ? 0.0f : exp2f(mw - mx);
-      o += part[(w * 16 + r) * RS + d] * f;
+      fac[r * 4 + w] = f;
       ls += part[(w * 16 + r) * RS + DH + 1] * f;
     }
+    fac[4 * G + r] = mx;
+    fac[5 * G + r] = ls;
+  }
+  __syncthreads();
+  float* split_out = a.scratch + ((static_cast<long long>(li) * a.q_heads + kvh * G) * a.max_splits + split) * RS;
+  for (int id = threadIdx.x; id < G * DH; id += kDecThreads) {
+    const int r = id / DH, d = id % DH;
+    float o = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) o += part[(w * 16 + r) * RS + d] * fac[r * 4 + w];
+    const float ls = fac[5 * G + r];
     if (n_splits == 1) {
       a.out[(static_cast<long long>(t) * a.q_heads + kvh * G + r) * DH + d] = __float2bfloat16_rn(ls > 0.0f ? o / ls : 0.0f);
     } else {
       float* dst = split_out + static_cast<long long>(r) * a.max_splits * RS;
       dst[d] = o;
       if (d == 0) {
-        dst[DH] = mx;          // in log2 units: only this kernel reads it back
+        dst[DH] = fac[4 * G + r];          // in log2 units: only this kernel reads it back
         dst[DH + 1] = ls;
       }
     }
@@ -243,27 +255,41 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   __syncthreads();
   if (flags[1] == 0) return;
   __threadfence();
-  float* wgt = part;   // [G][n_splits] weights, then [G] inverse sums
+  // Every split's maximum and sum come in with one round of loads (a thread per row and split); then a thread
+  // per row turns them into weights, adding in split order.
+  float* wgt = part;                                   // [G][max_splits] weights
+  float* msm = wgt + G * a.max_splits;                 // [G][max_splits] maxima
+  float* lsm = msm + G * a.max_splits;                 // [G][max_splits] sums
+  float* inv = lsm + G * a.max_splits;                 // [G] 1 / row sum
   const float* base = a.scratch + (static_cast<long long>(li) * a.q_heads + kvh * G) * a.max_splits * RS;
+  for (int id = threadIdx.x; id < G * n_splits; id += kDecThreads) {
+    const int r = id / n_splits, i = id % n_splits;
+    const float* src = base + (static_cast<long long>(r) * a.max_splits + i) * RS;
+    msm[r * a.max_splits + i] = __ldcg(src + DH);
+    lsm[r * a.max_splits + i] = __ldcg(src + DH + 1);
+  }
+  __syncthreads();
   if (threadIdx.x < G) {
-    const float* src = base + static_cast<long long>(threadIdx.x) * a.max_splits * RS;
+    const int r = threadIdx.x;
     float mx = -INFINITY;
-    for (int i = 0; i < n_splits; ++i) mx = fmaxf(mx, __ldcg(src + i * RS + DH));
+    for (int i = 0; i < n_splits; ++i) mx = fmaxf(mx, msm[r * a.max_splits + i]);
     float ls = 0.0f;
     for (int i = 0; i < n_splits; ++i) {
-      const float w = exp2f(__ldcg(src + i * RS + DH) - mx);
-      wgt[threadIdx.x * a.max_splits + i] = w;
-      ls += __ldcg(src + i * RS + DH + 1) * w;
+      const float w = exp2f(msm[r * a.max_splits + i] - mx);
+      wgt[r * a.max_splits + i] = w;
+      ls += lsm[r * a.max_splits + i] * w;
     }
-    wgt[G * a.max_splits + threadIdx.x] = ls > 0.0f ? 1.0f / ls : 0.0f;
+    inv[r] = ls > 0.0f ? 1.0f / ls : 0.0f;
   }
   __syncthreads();
   for (int id = threadIdx.x; id < G * DH; id += kDecThreads) {
     const int r = id / DH, d = id % DH;
-    const float* src = base + static_cast<long long>(r) * a.max_splits * RS;
+    const float* src = base + static_cast<long long>(r) * a.max_splits * RS + d;
+    const float* wr = wgt + r * a.max_splits;
     float o = 0.0f;
-    for (int i = 0; i < n_splits; ++i) o = fmaf(__ldcg(src + i * RS + d), wgt[r * a.max_splits + i], o);
-    a.out[(static_cast<long long>(t) * a.q_heads + kvh * G + r) * DH + d] = __float2bfloat16_rn(o * wgt[G * a.max_splits + r]);
+#pragma unroll 4
+    for (int i = 0; i < n_splits; ++i) o = fmaf(__ldcg(src + i * RS), wr[i], o);
+    a.out[(static_cast<long long>(t) * a.q_heads + kvh * G + r) * DH + d] = __float2bfloat16_rn(o * inv[r]);
   }
   if (threadIdx.x == 0) a.counters[li * a.kv_heads + kvh] = 0;   // ready for the next launch
 }
@@ -272,7 +298,9 @@ template <int DH>
 static int launch_decode_tma(const CUtensorMap& km, const CUtensorMap& vm, const DecodeArgs& a, int n_list, cudaStream_t s) {
   constexpr int STAGES = DH >= 256 ? 2 : (DH == 128 ? 3 : 4);
   constexpr size_t ring = static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128;
-  constexpr size_t merge = 4 * 16 * (DH + 2) * sizeof(float);
+  constexpr size_t combine = (4 * 16 * (DH + 2) + 6 * 16) * sizeof(float);          // the four warps' results and factors
+  constexpr size_t weights = (3 * 16 * 256 + 16) * sizeof(float);                    // the last CTA's merge: 16 rows, 256 splits at most
+  constexpr size_t merge = combine > weights ? combine : weights;
   constexpr size_t smem = (ring > merge ? ring : merge) + 16 * DH * 2 + 2 * STAGES * 8 + (kMaxTablePages + 2) * 4 + 1024;
   static bool configured = false;
   if (!configured) {
