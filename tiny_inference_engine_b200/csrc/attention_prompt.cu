@@ -10,7 +10,8 @@
 // 0..pos (window w > 0: pos-w+1..pos); the cached prefix and this step's own keys are both read
 // from the pages, where the kernel before this one has put them.
 //
-// grid = (row tiles of 64, kv heads, sequences); the tiles with the most keys are started first.
+// grid = (kv heads, row tiles of 64, sequences); CTAs start in that order with the last row tiles first, so the
+// tiles with the most keys of every kv head run first.
 // Tiles of keys that lie wholly below every row's position (and inside the window) need no mask.
 #include "attention_mma.cuh"
 #include "tma.cuh"
@@ -48,12 +49,12 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
   int* flags = reinterpret_cast<int*>(empty + STAGES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.z, kvh = blockIdx.y;
+  const int seq = blockIdx.z, kvh = blockIdx.x;
   const int G = a.q_heads / a.kv_heads;
   const int t0 = a.query_start[seq];
   const int nq = a.query_start[seq + 1] - t0;
   const int rows = nq * G;
-  const int row0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * 64;   // last rows (most keys) first
+  const int row0 = (static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y)) * 64;   // last rows (most keys) first
   if (row0 >= rows) return;
   const int pos0 = a.context_lens[seq] - nq;                      // position of the sequence's first query of this step
   const int last_row = min(rows, row0 + 64) - 1;
@@ -208,7 +209,7 @@ static int launch_prompt_tma(const CUtensorMap& km, const CUtensorMap& vm, const
     }
     configured = true;
   }
-  TIE_LAUNCH((attn_prompt_tma_kernel<DH, STAGES>), dim3(ceil_div(max_rows, 64), a.kv_heads, n_seqs), kPromptThreads, smem, s, km, vm, a);
+  TIE_LAUNCH((attn_prompt_tma_kernel<DH, STAGES>), dim3(a.kv_heads, ceil_div(max_rows, 64), n_seqs), kPromptThreads, smem, s, km, vm, a);
   return kOk;
 }
 
@@ -229,6 +230,7 @@ TIE_API int tie_attention_prompt_tma(const void* q, long long q_stride, const vo
   TIE_REQUIRE(page_size >= 8 && (page_size & (page_size - 1)) == 0, "attention_prompt: page size %d is not a power of two from 8 up", page_size);
   TIE_REQUIRE(q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0, "attention_prompt: q rows must be 16-byte aligned");
   if (n_seqs == 0 || max_queries == 0) return kOk;
+  TIE_REQUIRE(static_cast<long long>(max_queries) * (q_heads / kv_heads) <= 65535LL * 64, "attention_prompt: %d queries in one portion are too many", max_queries);
   int shift = 0;
   while ((1 << shift) < page_size) ++shift;
   const int box_rows = page_size < kKeysPerTile ? page_size : kKeysPerTile;

@@ -23,6 +23,8 @@
 //   9         one thread issues the MMAs: Q K^T of tile i + 1 ahead of P V of tile i.
 // Barriers: kv_full/kv_empty per stage, and for each row tile s_full (scores written), s_empty
 // (scores read), p_full[2] (P written, O rescaled), p_empty[2] (P V retired). Every wait is bounded.
+// grid = (kv heads, row tiles, sequences): CTAs start in that order with the last row tiles first, so the
+// tiles with the most keys of every kv head run first.
 #include "attention_mma.cuh"
 #include "umma.cuh"
 
@@ -108,12 +110,12 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.z, kvh = blockIdx.y;
+  const int seq = blockIdx.z, kvh = blockIdx.x;
   const int G = a.q_heads / a.kv_heads;
   const int t0 = a.query_start[seq];
   const int nq = a.query_start[seq + 1] - t0;
   const int rows = nq * G;
-  const int row0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * 256;   // last rows (most keys) first
+  const int row0 = (static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y)) * 256;   // last rows (most keys) first
   if (row0 >= rows) return;
   const int pos0 = a.context_lens[seq] - nq;
 
@@ -444,7 +446,7 @@ static int launch_prompt_umma(const CUtensorMap& km, const CUtensorMap& vm, cons
     }
     configured = true;
   }
-  TIE_LAUNCH((attn_prompt_umma_kernel<DH, STAGES>), dim3(ceil_div(max_rows, 256), a.kv_heads, n_seqs), kUmmaAttnThreads, smem, s, km, vm, a);
+  TIE_LAUNCH((attn_prompt_umma_kernel<DH, STAGES>), dim3(a.kv_heads, ceil_div(max_rows, 256), n_seqs), kUmmaAttnThreads, smem, s, km, vm, a);
   return kOk;
 }
 
@@ -467,6 +469,7 @@ TIE_API int tie_attention_prompt_umma(const void* q, long long q_stride, const v
               "attention_prompt_umma: q and out rows must be 16-byte aligned");
   TIE_REQUIRE(scale > 0.0f, "attention_prompt_umma: the scale must be positive");
   if (n_seqs == 0 || max_queries == 0) return kOk;
+  TIE_REQUIRE(static_cast<long long>(max_queries) * (q_heads / kv_heads) <= 65535LL * 256, "attention_prompt_umma: %d queries in one portion are too many", max_queries);
   int shift = 0;
   while ((1 << shift) < page_size) ++shift;
   const int box_rows = page_size < kKeysPerTile ? page_size : kKeysPerTile;
