@@ -23,8 +23,19 @@ def dtype_code(t: torch.Tensor) -> int:
         raise InvalidArgument(f"dtype {t.dtype} is not one of float32, bfloat16") from None
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_DEVICE_INDEX = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The current stream's handle. (torch.cuda.current_stream() builds a Stream object each time, several
+    microseconds per kernel launch; the raw accessor does not.)"""
+    global _DEVICE_INDEX
+    if _RAW_STREAM is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _DEVICE_INDEX is None:
+        _DEVICE_INDEX = torch.cuda.current_device()
+    return _RAW_STREAM(_DEVICE_INDEX)
 
 
 def _ptr(t) -> int:
@@ -289,6 +300,7 @@ def attention_prompt_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
          max_queries, q_heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _stream())
 
 
+_NO_UMMA_ATTENTION = os.environ.get("TIE_NO_UMMA_ATTENTION") == "1"
 UMMA_MIN_ROWS = 128     # rows (queries x heads of a group) from which the tcgen05 prompt kernel pays
 
 
@@ -297,7 +309,7 @@ def attention_prompt_umma_takes(q: torch.Tensor, q_heads: int, kv_heads: int, he
     """Whether the tcgen05 prompt kernel takes these operands and the portions are long enough for its
     256-row tiles."""
     return (attention_decode_tma_takes(q, q_heads, kv_heads, head_dim, page_size) and head_dim in (64, 128)
-            and max_queries * (q_heads // kv_heads) >= UMMA_MIN_ROWS and os.environ.get("TIE_NO_UMMA_ATTENTION") != "1")
+            and max_queries * (q_heads // kv_heads) >= UMMA_MIN_ROWS and not _NO_UMMA_ATTENTION)
 
 
 def attention_prompt_umma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, n_seqs: int, max_queries: int,

@@ -26,15 +26,16 @@ def tc_takes(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
-    """(transposed, tile width, splits) for out[M, N] = a[M, K] w[N, K]^T.
+    """(transposed, tile width, splits) for out[M, N] = a[M, K] w[N, K]^T on one CTA per tile.
 
-    Up to 256 tokens the weights take the 128-row side of the MMA and the tokens the narrow side
-    (width = the smallest of 16, 32, 64, 128, 256 that holds them): the product is bound by
-    streaming the weights, and k is cut into splits so that every SM has a CTA pulling bytes.
-    More tokens: 128-token row tiles against 256-wide weight tiles."""
+    Up to 128 tokens the weights take the 128-row side of the MMA and the tokens the narrow side
+    (width = the smallest of 16, 32, 64, 128 that holds them): the product is bound by streaming the
+    weights, and k is cut into splits so that every SM has a CTA pulling bytes. More tokens: 128-token
+    row tiles against 128-wide weight tiles while those are one wave of CTAs or less (k split to fill
+    the SMs), else against 256-wide ones. (Measured on Qwen3-8B's four shapes at 160 to 1,024 tokens.)"""
     k_blocks = math.ceil(K / 64)
-    if M <= 256:
-        bn = next(b for b in (16, 32, 64, 128, 256) if b >= M)
+    if M <= 128:
+        bn = next(b for b in (16, 32, 64, 128) if b >= M)
         tiles = math.ceil(N / 128)
         splits = 1
         if bn <= 64 and tiles < 2 * NUM_SMS:
@@ -42,9 +43,13 @@ def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
             # resident at once, while a split keeps 4 k-blocks and the float partial sums
             # (written and read once) stay well below the weight bytes.
             splits = max(1, min(2 * NUM_SMS // tiles, k_blocks // 4, K // (8 * M)))
+        elif bn == 128 and tiles < NUM_SMS:
+            splits = max(1, min(NUM_SMS // tiles, k_blocks // 16))      # one CTA per SM at this width
         return 1, bn, splits
-    bn = next((b for b in (16, 32, 64, 128, 256) if b >= N), 256)
-    return 0, bn, 1
+    tiles = math.ceil(M / 128) * math.ceil(N / 128)
+    if tiles <= NUM_SMS:
+        return 0, 128 if N > 64 else next(b for b in (16, 32, 64) if b >= N), max(1, min(NUM_SMS // tiles, k_blocks // 16))
+    return 0, next((b for b in (16, 32, 64, 128, 256) if b >= N), 256), 1
 
 
 def _scratch_for(numel: int, device) -> torch.Tensor:
@@ -58,21 +63,31 @@ def _scratch_for(numel: int, device) -> torch.Tensor:
 PAIR_MIN_ROWS = 512     # from this many tokens on, 256 x 256 tiles on pairs of SMs (cta_group::2)
 
 
+_NO_PAIR = os.environ.get("TIE_NO_PAIR_GEMM") == "1"
+_ops = None
+
+
 def pair_takes(M: int, N: int) -> bool:
-    return M >= PAIR_MIN_ROWS and N >= 256 and os.environ.get("TIE_NO_PAIR_GEMM") != "1"
+    """Pairs of SMs once the 128 x 128 tiles of the product are more than one wave of CTAs."""
+    return M >= PAIR_MIN_ROWS and N >= 256 and not _NO_PAIR and math.ceil(M / 128) * math.ceil(N / 128) > NUM_SMS
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None, bn=None, splits=None, scratch=None,
-            silu: bool = False, partial_scratch=None, deep=None, pair=None):
+            silu: bool = False, partial_scratch=None, deep=None, pair=None, checked: bool = False):
     """The tensor-core product; the tiling can be forced (tests). Returns `out`, or a SplitSum when
     `partial_scratch` is given and k is split."""
-    from . import SplitSum, _need, _stream, dtype_code
+    global _ops
+    if _ops is None:
+        from . import SplitSum, _need, _stream, dtype_code      # once: this runs hundreds of times in an eager step
+        _ops = (SplitSum, _need, _stream, dtype_code)
+    SplitSum, _need, _stream, dtype_code = _ops
     M, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and out.shape == (M, N // 2 if silu else N),
           f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm: last axes must be contiguous")
-    _need(tc_takes(a, w, out), "gemm_tc: operands must be bfloat16 with K and row strides multiples of 8, 16-byte aligned")
+    _need(checked or tc_takes(a, w, out),
+          "gemm_tc: operands must be bfloat16 with K and row strides multiples of 8, 16-byte aligned")
     if pair is None:
         pair = transposed is None and bn is None and splits is None and pair_takes(M, N)
     if pair:
@@ -116,7 +131,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=No
     if a.shape[0] == 0:
         return out
     if tc_takes(a, w, out):
-        return gemm_tc(a, w, out, partial_scratch=partial_scratch)
+        return gemm_tc(a, w, out, partial_scratch=partial_scratch, checked=True)
     gemm_simt(a, w, out)
     return out
 

@@ -101,12 +101,17 @@ def launch_count() -> int:
     return _LAUNCHES
 
 
+_ENTRY: dict = {}     # name -> bound entry point (looked up once: eager steps make hundreds of calls)
+
+
 def call(name: str, *args) -> None:
     global _LAUNCHES
-    lib = library()
+    fn = _ENTRY.get(name)
+    if fn is None:
+        fn = _ENTRY[name] = getattr(library(), name)
     _LAUNCHES += 1
-    status = getattr(lib, name)(*args)
+    status = fn(*args)
     if status != 0:
         from ..errors import InvalidArgument, TieError
-        msg = lib.tie_last_error().decode()
+        msg = library().tie_last_error().decode()
         raise (InvalidArgument if status == 1 else TieError)(msg)
