@@ -546,6 +546,32 @@ def test_tensor_core_attention_refuses_other_sizes(ops):
     assert not ops.attention_tc_takes(torch.zeros(4, 128, device="cuda"), 2, 1, 64)
 
 
+@pytest.mark.parametrize("M", [100, 200, 300])
+def test_split_products_of_many_tokens_feed_the_norm(ops, M):
+    """Between 65 and a few hundred tokens a product with few output tiles cuts k as well (128-token row
+    tiles, or the weights on the 128-row side up to 128 tokens): the partial sums reach the add+norm
+    kernel as they are."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(M)
+    D, K = 520, 4096
+    transposed, bn, splits = gemm_select.plan(M, D, K)
+    assert splits > 1 and transposed == (M <= 128)
+    a, w = as_stored(rng.standard_normal((M, K)), "bfloat16"), as_stored(rng.standard_normal((D, K)) * 0.05, "bfloat16")
+    buf = {}
+    got = ops.gemm(dev(a, torch.bfloat16), dev(w, torch.bfloat16), torch.empty(M, D, device="cuda", dtype=torch.bfloat16),
+                   partial_scratch=lambda n: buf.setdefault("p", torch.full((n,), float("nan"), device="cuda")))
+    assert isinstance(got, ops.SplitSum) and 1 < got.splits <= splits and (got.M, got.N) == (M, D)
+    prod = plain.linear(a, w)
+    x = rng.standard_normal((M, D)).astype(np.float32)
+    wn = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    xd, out = dev(x), torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
+    ops.add_rmsnorm(xd, got, dev(wn), 1e-6, out)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert np.abs(host(xd) - (x + prod)).max() < 1e-4 * np.abs(prod).max()
+    assert rel_err(host(out), plain.rms_norm(x + prod, wn, 1e-6)) < TOL["bfloat16"]
+
+
 def test_split_products_hand_partial_sums_to_their_consumers(ops):
     """A decode-sized product whose k range is cut leaves float partial sums; the add+norm kernel and
     the q/k norm + RoPE + append kernel add them up themselves. Same numbers as the unsplit way."""
