@@ -222,73 +222,70 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       int s_qk = 0, s_pv = 0;
       uint32_t parity_qk = 0;
       bool ok = true;
-      // Step i: for each row tile, P V of key tile i - 1 and right behind it Q K^T of key tile i + 1, so
-      // that the scores a softmax group needs next are under way as soon as it has handed in its P.
-      // (Before the loop: Q K^T of key tile 0.) Key tile i + 1 is waited for once, before the first use.
+      // Step i: Q K^T of key tile i for both row tiles, then P V of key tile i - 1 for both. The scores of
+      // tile i are asked for as soon as the softmax group has taken those of tile i - 1 out of tensor memory
+      // (early in its work on them), so they are there when it comes back for them; P V of tile i - 1 has to
+      // wait for the group to finish that tile anyway.
       for (int i = 0; i <= n_tiles && ok; ++i) {
-        const bool with_qk = i < n_tiles;                 // Q K^T of key tile i (index i of the walk)
-        const bool with_pv = i >= 1;                      // P V of key tile i - 1
-        uint32_t k_lo = 0;
-        if (with_qk) {
+        if (i < n_tiles) {
+          const int t = kt_first + i;
           if (!__all_sync(0xffffffffu, mbar_wait(kv_full + s_qk, parity_qk, abort_flag, a.status, 12) ? 1 : 0)) break;
-          k_lo = k_lo0 + s_qk * (STAGE_BYTES >> 4);
-        }
-        const uint32_t v_lo = v_lo0 + s_pv * (STAGE_BYTES >> 4);
+          const uint32_t k_lo = k_lo0 + s_qk * (STAGE_BYTES >> 4);
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          if (with_pv) {
-            const int t = kt_first + i - 1;
-            if (has[q] && t >= first[q] && t <= last[q]) {
-              const int pb = 2 * q + (n_pv[q] & 1);        // the tile's P buffer, used for the (n_pv / 2)-th time
-              if (!__all_sync(0xffffffffu, mbar_wait(p_full + pb, (n_pv[q] >> 1) & 1, abort_flag, a.status, 14) ? 1 : 0)) {
-                ok = false;
-                break;
-              }
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-              const uint32_t p_lo = p_lo0 + pb * (P_BYTES >> 4);
-              const uint32_t keep = n_pv[q] > 0 ? 1u : 0u;
-              if (elect_one()) {
-#pragma unroll
-                for (int kk = 0; kk < kKeysPerTile / 16; ++kk) {
-                  umma_bf16(tmem_base + O_COL + q * DH, desc_from_words(p_lo + ((kk * 32) >> 4), kDescHiSw128),
-                            desc_from_words(v_lo + ((kk * 16 * 128) >> 4), kDescHiSw128), idesc_pv, kk > 0 ? 1u : keep);
-                }
-                umma_commit(p_empty + pb);
-              }
-              __syncwarp();
-              ++n_pv[q];
+          for (int q = 0; q < 2; ++q) {
+            if (!(has[q] && t >= first[q] && t <= last[q])) continue;
+            if (!__all_sync(0xffffffffu, mbar_wait(s_empty + q, (n_qk[q] & 1) ^ 1, abort_flag, a.status, 14) ? 1 : 0)) {
+              ok = false;
+              break;
             }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (elect_one()) {
+#pragma unroll
+              for (int ks = 0; ks < DH / 16; ++ks) {
+                umma_bf16_a_tmem(tmem_base + q * kKeysPerTile, tmem_base + Q_COL + q * (DH / 2) + ks * 8,
+                                 desc_from_words(k_lo + (((ks >> 2) * (64 * 128) + (ks & 3) * 32) >> 4), kDescHiSw128), idesc_qk,
+                                 ks > 0 ? 1u : 0u);
+              }
+              umma_commit(s_full + q);
+            }
+            __syncwarp();
+            ++n_qk[q];
           }
-          if (with_qk) {
-            const int t = kt_first + i;
-            if (has[q] && t >= first[q] && t <= last[q]) {
-              if (!__all_sync(0xffffffffu, mbar_wait(s_empty + q, (n_qk[q] & 1) ^ 1, abort_flag, a.status, 14) ? 1 : 0)) {
-                ok = false;
-                break;
-              }
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-              if (elect_one()) {
-#pragma unroll
-                for (int ks = 0; ks < DH / 16; ++ks) {
-                  umma_bf16_a_tmem(tmem_base + q * kKeysPerTile, tmem_base + Q_COL + q * (DH / 2) + ks * 8,
-                                   desc_from_words(k_lo + (((ks >> 2) * (64 * 128) + (ks & 3) * 32) >> 4), kDescHiSw128), idesc_qk,
-                                   ks > 0 ? 1u : 0u);
-                }
-                umma_commit(s_full + q);
-              }
-              __syncwarp();
-              ++n_qk[q];
-            }
+          if (!ok) break;
+          if (++s_qk == STAGES) {
+            s_qk = 0;
+            parity_qk ^= 1;
           }
         }
-        if (!ok) break;
-        if (with_pv) {
+        if (i >= 1) {
+          const int t = kt_first + i - 1;
+          const uint32_t v_lo = v_lo0 + s_pv * (STAGE_BYTES >> 4);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (!(has[q] && t >= first[q] && t <= last[q])) continue;
+            const int pb = 2 * q + (n_pv[q] & 1);        // the tile's P buffer, used for the (n_pv / 2)-th time
+            if (!__all_sync(0xffffffffu, mbar_wait(p_full + pb, (n_pv[q] >> 1) & 1, abort_flag, a.status, 14) ? 1 : 0)) {
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t p_lo = p_lo0 + pb * (P_BYTES >> 4);
+            const uint32_t keep = n_pv[q] > 0 ? 1u : 0u;
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < kKeysPerTile / 16; ++kk) {
+                umma_bf16(tmem_base + O_COL + q * DH, desc_from_words(p_lo + ((kk * 32) >> 4), kDescHiSw128),
+                          desc_from_words(v_lo + ((kk * 16 * 128) >> 4), kDescHiSw128), idesc_pv, kk > 0 ? 1u : keep);
+              }
+              umma_commit(p_empty + pb);
+            }
+            __syncwarp();
+            ++n_pv[q];
+          }
+          if (!ok) break;
           if (elect_one()) umma_commit(kv_empty + s_pv);   // both products of key tile i - 1 have read the stage once everything issued so far retires
+          __syncwarp();
           if (++s_pv == STAGES) s_pv = 0;
-        }
-        if (with_qk && ++s_qk == STAGES) {
-          s_qk = 0;
-          parity_qk ^= 1;
         }
       }
     }
