@@ -223,23 +223,24 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       uint32_t parity_qk = 0;
       bool ok = true;
       // Step i: Q K^T of key tile i for both row tiles, then P V of key tile i - 1 for both. The scores of
-      // tile i are asked for as soon as the softmax group has taken those of tile i - 1 out of tensor memory
-      // (early in its work on them), so they are there when it comes back for them; P V of tile i - 1 has to
-      // wait for the group to finish that tile anyway.
+      // tile i are asked for as soon as the softmax groups have taken those of tile i - 1 out of tensor memory
+      // (early in their work on them), so they are there when the groups come back for them; P V of tile i - 1
+      // has to wait for the groups to finish that tile anyway. What a step waits for it waits for at once: a
+      // wait costs this one thread a couple of hundred cycles even when the barrier has long flipped.
       for (int i = 0; i <= n_tiles && ok; ++i) {
         if (i < n_tiles) {
           const int t = kt_first + i;
-          if (!__all_sync(0xffffffffu, mbar_wait(kv_full + s_qk, parity_qk, abort_flag, a.status, 12) ? 1 : 0)) break;
+          const bool on0 = has[0] && t >= first[0] && t <= last[0], on1 = has[1] && t >= first[1] && t <= last[1];
+          const BarrierPhase w0{kv_full + s_qk, parity_qk, true};
+          const BarrierPhase w1{s_empty + 0, static_cast<uint32_t>((n_qk[0] & 1) ^ 1), on0};
+          const BarrierPhase w2{s_empty + 1, static_cast<uint32_t>((n_qk[1] & 1) ^ 1), on1};
+          if (!__all_sync(0xffffffffu, mbar_wait_all(w0, w1, w2, abort_flag, a.status, 12) ? 1 : 0)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t k_lo = k_lo0 + s_qk * (STAGE_BYTES >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            if (!(has[q] && t >= first[q] && t <= last[q])) continue;
-            if (!__all_sync(0xffffffffu, mbar_wait(s_empty + q, (n_qk[q] & 1) ^ 1, abort_flag, a.status, 14) ? 1 : 0)) {
-              ok = false;
-              break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (elect_one()) {
+            for (int q = 0; q < 2; ++q) {
+              if (!(q == 0 ? on0 : on1)) continue;
 #pragma unroll
               for (int ks = 0; ks < DH / 16; ++ks) {
                 umma_bf16_a_tmem(tmem_base + q * kKeysPerTile, tmem_base + Q_COL + q * (DH / 2) + ks * 8,
@@ -248,10 +249,10 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
               }
               umma_commit(s_full + q);
             }
-            __syncwarp();
-            ++n_qk[q];
           }
-          if (!ok) break;
+          __syncwarp();
+          n_qk[0] += on0 ? 1 : 0;
+          n_qk[1] += on1 ? 1 : 0;
           if (++s_qk == STAGES) {
             s_qk = 0;
             parity_qk ^= 1;
@@ -259,19 +260,21 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         }
         if (i >= 1) {
           const int t = kt_first + i - 1;
+          const bool on0 = has[0] && t >= first[0] && t <= last[0], on1 = has[1] && t >= first[1] && t <= last[1];
+          const int pb0 = n_pv[0] & 1, pb1 = 2 + (n_pv[1] & 1);          // the tiles' P buffers, each used for the (n_pv / 2)-th time
+          const BarrierPhase w0{p_full + pb0, static_cast<uint32_t>((n_pv[0] >> 1) & 1), on0};
+          const BarrierPhase w1{p_full + pb1, static_cast<uint32_t>((n_pv[1] >> 1) & 1), on1};
+          const BarrierPhase w2{nullptr, 0u, false};
+          if (!__all_sync(0xffffffffu, mbar_wait_all(w0, w1, w2, abort_flag, a.status, 14) ? 1 : 0)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t v_lo = v_lo0 + s_pv * (STAGE_BYTES >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            if (!(has[q] && t >= first[q] && t <= last[q])) continue;
-            const int pb = 2 * q + (n_pv[q] & 1);        // the tile's P buffer, used for the (n_pv / 2)-th time
-            if (!__all_sync(0xffffffffu, mbar_wait(p_full + pb, (n_pv[q] >> 1) & 1, abort_flag, a.status, 14) ? 1 : 0)) {
-              ok = false;
-              break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t p_lo = p_lo0 + pb * (P_BYTES >> 4);
-            const uint32_t keep = n_pv[q] > 0 ? 1u : 0u;
-            if (elect_one()) {
+            for (int q = 0; q < 2; ++q) {
+              if (!(q == 0 ? on0 : on1)) continue;
+              const int pb = q == 0 ? pb0 : pb1;
+              const uint32_t p_lo = p_lo0 + pb * (P_BYTES >> 4);
+              const uint32_t keep = n_pv[q] > 0 ? 1u : 0u;
 #pragma unroll
               for (int kk = 0; kk < kKeysPerTile / 16; ++kk) {
                 umma_bf16(tmem_base + O_COL + q * DH, desc_from_words(p_lo + ((kk * 32) >> 4), kDescHiSw128),
@@ -279,12 +282,11 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
               }
               umma_commit(p_empty + pb);
             }
-            __syncwarp();
-            ++n_pv[q];
+            umma_commit(kv_empty + s_pv);   // both products of key tile i - 1 have read the stage once everything issued so far retires
           }
-          if (!ok) break;
-          if (elect_one()) umma_commit(kv_empty + s_pv);   // both products of key tile i - 1 have read the stage once everything issued so far retires
           __syncwarp();
+          n_pv[0] += on0 ? 1 : 0;
+          n_pv[1] += on1 ? 1 : 0;
           if (++s_pv == STAGES) s_pv = 0;
         }
       }

@@ -48,6 +48,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// Bounded wait for up to three barriers at once (entries with `on` false are skipped): one round of polling
+// and one return for what would otherwise be three waits in a row, each with its own latency.
+struct BarrierPhase {
+  uint64_t* bar;
+  uint32_t parity;
+  bool on;
+};
+__device__ __forceinline__ bool mbar_wait_all(const BarrierPhase& a, const BarrierPhase& b, const BarrierPhase& c,
+                                              volatile int* abort_flag, int* status, int where) {
+  bool da = !a.on, db = !b.on, dc = !c.on;
+  const unsigned long long start = clock64();
+  for (;;) {
+    if (!da) da = mbar_try_wait(a.bar, a.parity);
+    if (!db) db = mbar_try_wait(b.bar, b.parity);
+    if (!dc) dc = mbar_try_wait(c.bar, c.parity);
+    if (da && db && dc) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - start > kWaitCycles) {
+      *abort_flag = 1;
+      *reinterpret_cast<volatile int*>(status) = where;
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
