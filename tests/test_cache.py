@@ -159,3 +159,23 @@ def test_state_slots_misuse():
     with pytest.raises(InvalidArgument, match="while free"):
         s.release(a)
     assert s.bytes_per_slot == 0 and s.tensor(0) is None
+
+
+def test_workspace_keeps_outgrown_buffers_and_sizes_by_capacity():
+    """A flat buffer that has to grow leaves the old one alive (a captured graph may still use its address);
+    with a capacity given it never has to."""
+    import torch
+
+    from tiny_inference_engine_b200.engine.workspace import Workspace
+    ws = Workspace(8, "cpu")
+    a = ws.flat("x", 10, torch.float32)
+    assert ws.flat("x", 5, torch.float32) is a
+    b = ws.flat("x", 50, torch.float32)
+    assert b is not a and b.numel() >= 50 and any(t is a for t in ws._retired)
+    c = ws.flat("y", 10, torch.float32, capacity=1000)
+    assert c.numel() == 1000 and ws.flat("y", 1000, torch.float32, capacity=1000) is c
+    z = ws.zeros("z", 4, torch.int32)
+    assert not z.any() and ws.zeros("z", 4, torch.int32) is z
+    assert ws.rows("r", 8, 3, torch.float32).shape == (8, 3)
+    with pytest.raises(ValueError, match="rows asked"):
+        ws.rows("r", 9, 3, torch.float32)

@@ -102,6 +102,40 @@ def test_steps_queued_ahead_change_no_token(tiny_models, dtype, pages):
     assert eng.stats().steps_ahead > 0
 
 
+@pytest.mark.timeout(300)
+def test_mixed_steps_at_full_width_with_wide_layers(tmp_path):
+    """Layers as wide as Qwen3-8B's (two of them, random weights), 512 tokens a step, sixteen requests at once:
+    steps that mix two prompt portions with decoded tokens run the matrix products on pairs of SMs beside the
+    decode kernels. Three runs give the same tokens with and without steps queued ahead, and nothing is lost."""
+    import json
+
+    from tiny_inference_engine_b200 import (Engine, SamplingParams, Scheduler, SchedulerConfig, ServingConfig, StepRunner,
+                                            load_model, make_cache)
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 32000, "hidden_size": 4096,
+           "intermediate_size": 12288, "num_hidden_layers": 2, "num_attention_heads": 32, "num_key_value_heads": 8,
+           "head_dim": 128, "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+           "tie_word_embeddings": False}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    model = load_model(str(tmp_path), "bfloat16", random_weights=True, seed=0)
+    rng = np.random.default_rng(1)
+    reqs = [(rng.integers(0, 32000, int(rng.integers(1, 700))).tolist(),
+             SamplingParams(max_tokens=40 + 5 * i, temperature=[0.0, 0.9][i % 2], seed=i)) for i in range(16)]
+    outs = []
+    for ahead in (False, True, True):
+        cache, states = make_cache(model, page_size=16, num_pages=1200, max_requests=32)
+        serving = ServingConfig(512, 16, run_ahead=ahead)
+        runner = StepRunner(model, cache, 512, 16, 16, states=states)
+        eng = Engine(model, cache, Scheduler(cache, SchedulerConfig(serving=serving, policy="fcfs")), serving, states=states,
+                     runner=runner)
+        outs.append(eng.generate_batch([p for p, _ in reqs], [q for _, q in reqs]))
+        while eng.has_work():
+            eng.step()
+        assert cache.num_free() == 1200 and eng.stats().prefill_tokens == sum(len(p) for p, _ in reqs)
+        assert (eng.stats().steps_ahead > 0) == ahead
+    assert outs[0] == outs[1] == outs[2]
+    assert all(len(o) == q.max_tokens for o, (_, q) in zip(outs[0], reqs))
+
+
 def test_a_failed_step_is_rolled_back_and_the_requests_still_finish(tiny_models):
     from tiny_inference_engine_b200 import SamplingParams, ServingConfig
     cfg, page, w, d = tiny_models["tiny_a"]

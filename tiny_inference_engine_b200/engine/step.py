@@ -21,6 +21,8 @@ write nothing.
 """
 from __future__ import annotations
 
+import gc
+
 from dataclasses import dataclass
 from typing import Callable, Sequence
 
@@ -259,10 +261,19 @@ class StepRunner:
             torch.cuda.synchronize()
             before = ops.library.launch_count()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, self.cache, self.states)
-                if sampled:
-                    self._sample(ctx, logits)
+            # No garbage collection while capturing: collecting an older runner's graphs frees their memory
+            # pools, a CUDA call that is not allowed during a capture and invalidates it.
+            gc_was_on = gc.isenabled()
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self.model.forward(ctx, self.cache, self.states)
+                    if sampled:
+                        self._sample(ctx, logits)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.kernels_in_graph[key] = ops.library.launch_count() - before
             self._graphs[key] = (graph, logits)
         graph, logits = self._graphs[key]

@@ -364,6 +364,12 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=No
     return gemm_select.gemm(a, w, out, partial_scratch)
 
 
+def partial_capacity(max_rows: int, N: int, K: int) -> int:
+    """The largest scratch (floats) a split product of up to max_rows tokens with [N, K] weights asks for."""
+    from . import gemm_select
+    return gemm_select.partial_capacity(int(max_rows), int(N), int(K))
+
+
 def gemm_silu(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, I] = silu(a . gate^T) * (a . up^T) in one tensor-core product; w_blocks [2I, K] holds
     blocks of 16 gate rows followed by their 16 up rows (interleave_gate_up)."""

@@ -6,6 +6,7 @@ row strides multiples of 8 elements, 16-byte aligned bases), else on the CUDA co
 """
 from __future__ import annotations
 
+import functools
 import math
 import os
 
@@ -52,12 +53,31 @@ def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
     return 0, next((b for b in (16, 32, 64, 128, 256) if b >= N), 256), 1
 
 
+_retired: list = []
+
+
 def _scratch_for(numel: int, device) -> torch.Tensor:
+    """Scratch for split products whose caller gave none. An outgrown buffer is kept: a captured CUDA graph
+    may still use its address."""
     buf = _scratch.get(device)
     if buf is None or buf.numel() < numel:
-        buf = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
+        if buf is not None:
+            _retired.append(buf)
+        buf = torch.empty(max(numel, 1 << 20, 2 * buf.numel() if buf is not None else 0), dtype=torch.float32, device=device)
         _scratch[device] = buf
     return buf
+
+
+@functools.lru_cache(maxsize=None)
+def partial_capacity(max_rows: int, N: int, K: int) -> int:
+    """The most float partial sums a product of up to `max_rows` tokens with these weights leaves
+    (splits x tokens x N over every token count): what its scratch buffer is sized for once."""
+    most = 0
+    for M in range(1, max_rows + 1):
+        splits = plan(M, N, K)[2]
+        if splits > 1:
+            most = max(most, splits * M * N)
+    return most
 
 
 PAIR_MIN_ROWS = 512     # from this many tokens on, 256 x 256 tiles on pairs of SMs (cta_group::2)

@@ -88,7 +88,8 @@ class GQAttention(Mixer):
             width = self.q_dim + (2 * self.kv_dim if cache.writes else 0)
             qkv = ctx.ws.rows("attn.qkv", T, self.q_dim + 2 * self.kv_dim, self.dtype)[:, :width]
             got = ops.gemm(h, self.w_qkv if cache.writes else self.w_q, qkv,
-                           partial_scratch=lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32))
+                           partial_scratch=lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32,
+                                                                  ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape)))
             ops.qk_norm_rope_append(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, g.slots, cache.k, cache.v, Hq, Hkv,
                                     Dh, write_kv=cache.writes, partial=got if isinstance(got, ops.SplitSum) else None)
             q = qkv[:, :self.q_dim]
@@ -111,7 +112,8 @@ class GQAttention(Mixer):
         attn = ctx.ws.rows("attn.out", T, self.q_dim, self.dtype)
         self.attend(q, attn, ctx, g, cache)
         out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
-        return ops.gemm(attn, self.w_o, out, partial_scratch=lambda n: ctx.ws.flat("mixer.out.partial", n, torch.float32))
+        return ops.gemm(attn, self.w_o, out, partial_scratch=lambda n: ctx.ws.flat(
+            "mixer.out.partial", n, torch.float32, ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape)))
 
     def attend(self, q, attn, ctx, g, cache):
         """Rows of sequences that bring several tokens come first in a step, then one row per

@@ -43,7 +43,8 @@ class SwiGLU(FeedForward):
             ops.gemm(h, self.w_gate_up, gu)
             ops.silu_mul(gu, act)
         out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
-        return ops.gemm(act, self.w_down, out, partial_scratch=lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32))
+        return ops.gemm(act, self.w_down, out, partial_scratch=lambda n: ctx.ws.flat(
+            "ffn.out.partial", n, torch.float32, ops.partial_capacity(ctx.ws.max_rows, *self.w_down.shape)))
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
