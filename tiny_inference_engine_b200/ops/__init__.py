@@ -359,7 +359,10 @@ def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=None):
     """The engine's matrix product: picks the kernel for the dtype and the sizes. With
     `partial_scratch` (a callable numel -> float32 buffer) a product whose k range is split may
-    come back as a SplitSum (then `out` is untouched); else returns `out`."""
+    come back as a SplitSum (then `out` is untouched); else returns `out`.
+
+    `w` is taken for a weight: the tensor-core kernels start fetching it before the kernel ahead of them
+    in the stream has finished, so it must not be something that kernel writes."""
     from . import gemm_select
     return gemm_select.gemm(a, w, out, partial_scratch)
 
