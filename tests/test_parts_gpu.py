@@ -431,3 +431,53 @@ def test_a_toy_feed_forward_with_routing_and_another_position_encoding():
         pa, pb = pa + na, pb + nb
     assert_logits_close(np.concatenate(got_a), want_a, "float32", "toy parts, request a beside b")
     assert_logits_close(np.concatenate(got_b), want_b, "float32", "toy parts, request b beside a")
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_layer_as_wide_as_the_large_model_against_the_plain_implementation(dtype):
+    """One layer with Qwen3-8B's widths (hidden 4096, 32/8 heads of 128, intermediate 12288; a small vocabulary),
+    in 32-bit (CUDA-core kernels) and in bfloat16: a 512-token portion (matrix products on pairs of SMs, prompt attention on tcgen05), then portions of
+    two requests together, a portion beside a decoded token, and decoded tokens of both (split products whose
+    partial sums feed the norm kernels, TMA decode attention). Every logit row against the plain implementation
+    with the same storage."""
+    from tiny_inference_engine_b200 import StepEntry
+    cfg = plain.normalise_config({"vocab_size": 1000, "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 1,
+                                  "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+                                  "max_position_embeddings": 2048, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+                                  "tie_word_embeddings": False})
+    w = plain.random_weights(cfg, 3)
+    w["model.layers.0.self_attn.q_norm.weight"] *= 3.0            # scores a few units apart: attention is not flat
+    model, cache, runner = build(qwen_spec(cfg), w, dtype, page=16, pages=96, max_tokens=512, max_seqs=4)
+    rng = np.random.default_rng(9)
+    a, b = rng.integers(0, 1000, 640).tolist(), rng.integers(0, 1000, 420).tolist()
+    want_a, want_b = plain.forward(w, cfg, a, storage=dtype), plain.forward(w, cfg, b, storage=dtype)
+    ra, rb = cache.new_request(), cache.new_request()
+    got = {"a": [], "b": []}
+
+    def step(parts):
+        entries = []
+        for name, req, toks, start, n, want in parts:
+            assert cache.reserve(req, start + n)
+            entries.append(StepEntry(req, toks[start:start + n], start, want))
+        out = runner.run(entries).float().cpu().numpy()
+        row = 0
+        for name, req, toks, start, n, want in parts:
+            for k in want:
+                got[name].append((start + k, out[row]))
+                row += 1
+        assert row == out.shape[0]
+
+    step([("a", ra, a, 0, 512, [0, 1, 255, 300, 510, 511])])
+    step([("a", ra, a, 512, 100, [0, 50, 99]), ("b", rb, b, 0, 180, [0, 100, 179])])          # 280 tokens
+    step([("a", ra, a, 612, 1, [0]), ("b", rb, b, 180, 220, [0, 219])])                        # a decodes beside a portion
+    pa, pb = 613, 400
+    for _ in range(12):                                                                          # both decode
+        step([("a", ra, a, pa, 1, [0]), ("b", rb, b, pb, 1, [0])])
+        pa, pb = pa + 1, pb + 1
+    from tiny_inference_engine_b200.ops import gemm_select
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    for name, want in (("a", want_a), ("b", want_b)):
+        pos = [p for p, _ in got[name]]
+        assert_logits_close(np.stack([g for _, g in got[name]]), want[pos], dtype, f"wide layer, request {name}")
