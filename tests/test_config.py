@@ -116,3 +116,21 @@ def test_another_architecture_can_be_registered():
     assert arch.build_spec(arch.parse_config(plain.TINY_A)).architecture == "ToyForCausalLM"
     with pytest.raises(ValueError, match="already registered"):
         register_architecture(Architecture("ToyForCausalLM", parse_config=dict, build_spec=spec_of))
+
+
+def test_decode_attention_splits_respect_the_kernel_limits():
+    """However long the context, however many sequences and whatever the page size: splits are whole 64-key
+    tiles, their page ids fit the kernel's shared-memory table and there are at most MAX_SPLITS of them."""
+    from tiny_inference_engine_b200.parts import attention as att
+    for page in (8, 16, 32, 64, 128, 256):
+        boxes = 64 // min(page, 64)
+        for sequences in (1, 3, 8, 64, 256):
+            for kv_heads in (1, 8):
+                for longest in (1, 63, 64, 65, 1000, 4096, 8128, 8129, 40960, 131072):
+                    split_keys, max_splits = att.decode_splits(longest, sequences, kv_heads, page)
+                    assert split_keys % 64 == 0 and split_keys >= 64
+                    fits = (split_keys // 64 + 1) * boxes <= att.TMA_DECODE_TABLE_ENTRIES
+                    assert fits or max_splits == att.MAX_SPLITS    # only a context beyond every configuration gets there
+                    assert 1 <= max_splits <= att.MAX_SPLITS and max_splits * split_keys >= longest
+                    if longest <= 40960:
+                        assert (split_keys // 64 + 1) * boxes <= att.TMA_DECODE_TABLE_ENTRIES

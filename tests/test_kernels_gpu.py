@@ -539,6 +539,32 @@ def test_tcgen05_prompt_attention_when_the_maximum_keeps_growing(ops):
         assert rel_err(host(out), want) < TOL["bfloat16"], f"rising={rising}"
 
 
+@pytest.mark.parametrize("page", [8, 16, 64])
+def test_decode_attention_over_long_contexts_with_the_longest_splits(ops, page):
+    """Contexts beyond what one split may hold (the kernel keeps a split's page ids in shared memory): the part's
+    choice of split size stays inside the limit and the result is the dense one."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    from tiny_inference_engine_b200.parts.attention import decode_splits
+    rng = np.random.default_rng(page)
+    Hq, Hkv, Dh = 4, 2, 64
+    split_keys, max_splits = decode_splits(9000, 200, Hkv, page)          # so many sequences that each gets one CTA per kv head
+    assert max_splits >= 2 or page >= 64          # pages of 64 keys and more: one box a tile, 32,704 keys fit a split
+    ctx = [9000, split_keys + 1, split_keys, 4000, 10, 1]
+    kc, vc, bt, ks, vs = paged_cache(rng, "bfloat16", ctx, Hkv, Dh, page, sum(-(-c // page) for c in ctx) + 3)
+    S = len(ctx)
+    q = as_stored(rng.standard_normal((S, Hq * Dh)), "bfloat16")
+    want = np.concatenate([dense_reference(q[i:i + 1], ks[i], vs[i], Hq, Hkv, Dh, 1) for i in range(S)])
+    out = torch.full((S, Hq * Dh), float("nan"), device="cuda", dtype=torch.bfloat16)
+    scratch = torch.empty(ops.attention_split_scratch_floats(S, Hq, Dh, max_splits), device="cuda")
+    counters = torch.zeros(S * Hkv, dtype=torch.int32, device="cuda")
+    ops.attention_decode_tma(dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out,
+                             dev(np.arange(S + 1), torch.int32), dev(np.array(ctx), torch.int32), dev(bt, torch.int32), Hq, Hkv, Dh,
+                             1 / np.sqrt(Dh), dev(np.arange(S), torch.int32), S, split_keys, max_splits, scratch, counters)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(out), want) < TOL["bfloat16"] and not counters.any()
+
+
 def test_tensor_core_attention_refuses_other_sizes(ops):
     q = torch.zeros(4, 2 * 48, device="cuda", dtype=torch.bfloat16)
     assert not ops.attention_tc_takes(q, 2, 1, 48)

@@ -23,6 +23,7 @@ from .base import CacheNeed, Mixer, build_part, register_part, to_compute
 
 SPLIT_KEYS = 256       # keys per split for sequences that bring one token
 MAX_SPLITS = 64
+TMA_DECODE_TABLE_ENTRIES = 512     # csrc/attention_decode.cu: kMaxTablePages
 NUM_SMS = 148
 
 
@@ -137,10 +138,7 @@ class GQAttention(Mixer):
             longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
             page = cache.k.shape[2]
             if tc and ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, page):
-                # about two CTAs per SM in all: (sequence, kv head) pairs times splits of the keys
-                want = max(1, (2 * NUM_SMS) // (ctx.single_count * Hkv))
-                split_keys = max(SPLIT_KEYS, -(-math.ceil(longest / want) // 64) * 64)
-                max_splits = max(1, math.ceil(longest / split_keys))
+                split_keys, max_splits = decode_splits(longest, ctx.single_count, Hkv, page)
                 scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
                                       torch.float32)
                 counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * Hkv, torch.int32)
@@ -157,6 +155,20 @@ class GQAttention(Mixer):
             fn = ops.attention_decode_tc if tc else ops.attention_split
             fn(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale,
                ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, self.window)
+
+
+def decode_splits(longest: int, sequences: int, kv_heads: int, page_size: int) -> tuple[int, int]:
+    """(keys per split, most splits of a sequence) for the TMA decode kernel: about two CTAs per SM in all
+    ((sequence, kv head) pairs times splits), splits of whole 64-key tiles and at least SPLIT_KEYS keys, no
+    longer than the page ids the kernel keeps in shared memory allow (TMA_DECODE_TABLE_ENTRIES boxes, one per
+    page or per 64 keys of a larger page) and no more than MAX_SPLITS of them."""
+    want = max(1, (2 * NUM_SMS) // max(1, sequences * kv_heads))
+    split_keys = max(SPLIT_KEYS, -(-math.ceil(longest / want) // 64) * 64)
+    boxes_per_tile = 64 // min(page_size, 64)
+    split_keys = min(split_keys, (TMA_DECODE_TABLE_ENTRIES // boxes_per_tile - 1) * 64)
+    while math.ceil(longest / split_keys) > MAX_SPLITS:
+        split_keys += 64
+    return split_keys, max(1, math.ceil(longest / split_keys))
 
 
 register_part("mixer", "gqa_attention", GQAttention, replace=True)
