@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, Qwen3-8B shape, random bfloat16 weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload serving [--requests 64] [--kv-pages P]     (the Qwen3-4B serving mix; its own line)
 
 One JSON line on stdout. `value` is decoded tokens per second at batch 8 with the timed steps
 ending at the benchmark context (device time, CUDA events around K decode steps through the
@@ -32,6 +33,8 @@ QWEN3_8B = {
     "head_dim": 128, "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
     "tie_word_embeddings": False,
 }
+# BASELINE.json configs[3]: the Qwen3-4B shape of the serving mix (`--workload serving`).
+QWEN3_4B = dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True)
 FULL_LAYERS = 36
 PAGE = 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -102,6 +105,69 @@ def prefill_flops(cfg, layers, T):
     return gemm + attn
 
 
+def serving_mix(args) -> int:
+    """The serving workload of the reference's own bench (bench/workload.cpp, bench/report.h:29-36) on the
+    Qwen3-4B shape: `--requests` requests at once, prompt lengths uniform in [128, 4096] of uniform random ids,
+    256 new tokens each at temperature 0.7, continuous batching with 512 tokens a step. One JSON line: generated
+    tokens per second over the whole run, time to first token, time between tokens and request latency
+    percentiles, mean sequences per step, preemptions."""
+    import numpy as np
+    import torch
+    from tiny_inference_engine_b200 import (Engine, SamplingParams, Scheduler, SchedulerConfig, ServingConfig, StepRunner,
+                                            load_model, make_cache)
+    cfg = dict(QWEN3_4B, num_hidden_layers=args.layers)
+    with tempfile.TemporaryDirectory() as d:
+        (Path(d) / "config.json").write_text(json.dumps(cfg))
+        model = load_model(d, "bfloat16", random_weights=True, seed=0)
+    n, new_tokens, budget = args.requests, 256, 512
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(128, 4097, n)
+    prompts = [rng.integers(0, cfg["vocab_size"], int(m)).tolist() for m in lengths]
+    pages = int(sum((m + new_tokens) // PAGE + 2 for m in lengths)) if args.kv_pages <= 0 else args.kv_pages
+    cache, states = make_cache(model, page_size=PAGE, num_pages=pages, max_requests=2 * n)
+    serving = ServingConfig(max_tokens_per_step=budget, max_seqs=min(n, budget))
+    runner = StepRunner(model, cache, budget, serving.max_seqs, serving.max_seqs, states=states)
+    engine = Engine(model, cache, Scheduler(cache, SchedulerConfig(serving=serving)), serving, states=states, runner=runner)
+
+    def run():
+        stamps = {}
+        engine.set_token_callback(lambda i, t: stamps.setdefault(i, []).append(time.perf_counter()))
+        before = engine.stats()
+        torch.cuda.synchronize()
+        start = time.perf_counter()
+        ids = [engine.add_request(p, SamplingParams(temperature=0.7, seed=k, max_tokens=new_tokens)) for k, p in enumerate(prompts)]
+        while engine.has_work():
+            engine.step()
+        torch.cuda.synchronize()
+        total = time.perf_counter() - start
+        for i in ids:
+            engine.release(i)
+        return start, total, [stamps[i] for i in ids], before, engine.stats()
+
+    run()                                                    # warm-up: kernels loaded, every decode graph captured
+    start, total, stamps, st0, st1 = run()
+    ttft = np.array([s[0] - start for s in stamps]) * 1e3
+    itl = np.concatenate([np.diff(s) for s in stamps]) * 1e3
+    e2e = np.array([s[-1] - start for s in stamps])
+    generated = sum(len(s) for s in stamps)
+    steps = st1.steps - st0.steps
+
+    def pct(a):
+        return {"p50": round(float(np.percentile(a, 50)), 2), "p90": round(float(np.percentile(a, 90)), 2),
+                "p99": round(float(np.percentile(a, 99)), 2)}
+
+    print(json.dumps({
+        "metric": "generated tok/s, serving mix (Qwen3-4B bf16, 1 B200)", "value": round(generated / total, 1), "unit": "tokens/s",
+        "requests": n, "prompt_tokens": int(lengths.sum()), "generated_tokens": generated, "seconds": round(total, 3),
+        "total_tok_s": round((int(lengths.sum()) + generated) / total, 1), "ttft_ms": pct(ttft), "itl_ms": pct(itl), "e2e_s": pct(e2e),
+        "steps": steps, "mean_seqs_per_step": round((st1.seqs_scheduled - st0.seqs_scheduled) / max(1, steps), 2),
+        "preemptions": st1.preemptions - st0.preemptions, "steps_queued_ahead": st1.steps_ahead - st0.steps_ahead,
+        "config": {"model": "Qwen3-4B shape", "layers": args.layers, "max_tokens_per_step": budget, "max_seqs": serving.max_seqs,
+                   "kv_pages": pages, "page_size": PAGE, "temperature": 0.7, "new_tokens": new_tokens},
+        "data": "synthetic (random weights N(0,0.02), uniform random token ids, all requests at time 0)"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -113,6 +179,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported in config)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="decode: the contract line (default); serving: the Qwen3-4B serving mix, its own line")
+    ap.add_argument("--requests", type=int, default=64, help="serving mix: concurrent requests")
+    ap.add_argument("--kv-pages", type=int, default=0, help="serving mix: cache pages (0: enough for every request at once)")
     ap.add_argument("--profile", choices=["decode", "prefill"], help="run two steps of one kind, kernel by kernel, between "
                     "cudaProfilerStart/Stop (for ncu --profile-from-start off) and print no bench line")
     args = ap.parse_args()
@@ -126,6 +196,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "serving":
+        return serving_mix(args)
 
     import numpy as np
     import torch
