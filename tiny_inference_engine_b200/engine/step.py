@@ -384,6 +384,27 @@ class StepRunner:
         else:
             for s, i in enumerate(order):
                 e, n = entries[i], counts[i]
+                if n == 1:
+                    # one token beside others' portions: plain numbers, no array per sequence
+                    t0 = int(e.tokens[0])
+                    if not 0 <= t0 < self.vocab:
+                        raise InvalidArgument(f"token id {t0} outside vocabulary of {self.vocab}")
+                    tokens[row], positions[row], seq_of_row[row] = t0, e.start, s
+                    row_of[i] = row
+                    starts[s] = e.start
+                    context_lens[s] = e.start + 1
+                    state_slots[s] = e.cache.state_slot
+                    for g in range(G):
+                        t = e.cache.tables[g]
+                        page_id = int(t.ids[e.start // page])
+                        if page_id < 0:
+                            raise InvalidArgument("a position below the window was asked for: its page has been given back")
+                        sec(f"slots{g}")[row] = page_id * page + e.start % page
+                        k = min(len(t), MB)
+                        tables[g][s, :k] = np.maximum(t.ids[:k], 0) if windowed[g] else t.ids[:k]
+                    row += 1
+                    query_start[s + 1] = row
+                    continue
                 tok = np.asarray(e.tokens, dtype=np.int64)
                 if tok.min() < 0 or tok.max() >= self.vocab:
                     bad = int(tok[(tok < 0) | (tok >= self.vocab)][0])
