@@ -134,3 +134,9 @@ def test_decode_attention_splits_respect_the_kernel_limits():
                     assert 1 <= max_splits <= att.MAX_SPLITS and max_splits * split_keys >= longest
                     if longest <= 40960:
                         assert (split_keys // 64 + 1) * boxes <= att.TMA_DECODE_TABLE_ENTRIES
+    # with the sequences' own lengths: a few long ones among short ones are cut up, and all CTAs fit at once
+    lens = [3000, 2900] + [200] * 28
+    sk, ms = att.decode_splits(3000, 30, 8, 16, lens)
+    assert sk < 3000 and sk % 64 == 0 and ms == -(-3000 // sk) and sum(-(-c // sk) for c in lens) * 8 <= 2 * att.NUM_SMS
+    assert att.decode_splits(3000, 30, 8, 16) == (3008, 1)
+    assert att.decode_splits(4096, 8, 8, 16, [4096] * 8) == att.decode_splits(4096, 8, 8, 16)

@@ -94,6 +94,7 @@ class StepContext:
     inv_temperature: torch.Tensor | None = None
     seeds: torch.Tensor | None = None
     counters: torch.Tensor | None = None
+    single_contexts: tuple | None = None   # context lengths of the sequences that bring one token, when the step is not a captured graph
 
 
 def _round_up(n: int, m: int) -> int:
@@ -475,6 +476,7 @@ class StepRunner:
                           state_slots=dsec("state_slots"), single_seqs=dsec("single_seqs"), groups=groups,
                           multi_rows=multi_rows, multi_seqs=n_multi,
                           multi_max_queries=max((c for c in counts if c > 1), default=0), single_count=n_single, single_max_context=single_max_ctx,
+                          single_contexts=None if table_len is not None else tuple(int(c) for c in context_lens[n_multi:S]),
                           max_context=max_ctx, max_seqs=self.max_seqs, ws=self.ws, logit_ws=self.logit_ws, host=hs,
                           layer_hook=self.layer_hook)
         if sampling is not None:

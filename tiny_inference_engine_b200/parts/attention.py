@@ -138,7 +138,8 @@ class GQAttention(Mixer):
             longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
             page = cache.k.shape[2]
             if tc and ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, page):
-                split_keys, max_splits = decode_splits(longest, ctx.single_count, Hkv, page)
+                lens = ctx.single_contexts if self.window <= 0 else None
+                split_keys, max_splits = decode_splits(longest, ctx.single_count, Hkv, page, lens)
                 scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
                                       torch.float32)
                 counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * Hkv, torch.int32)
@@ -157,15 +158,25 @@ class GQAttention(Mixer):
                ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, self.window)
 
 
-def decode_splits(longest: int, sequences: int, kv_heads: int, page_size: int) -> tuple[int, int]:
+def decode_splits(longest: int, sequences: int, kv_heads: int, page_size: int, contexts=None) -> tuple[int, int]:
     """(keys per split, most splits of a sequence) for the TMA decode kernel: about two CTAs per SM in all
     ((sequence, kv head) pairs times splits), splits of whole 64-key tiles and at least SPLIT_KEYS keys, no
     longer than the page ids the kernel keeps in shared memory allow (TMA_DECODE_TABLE_ENTRIES boxes, one per
-    page or per 64 keys of a larger page) and no more than MAX_SPLITS of them."""
-    want = max(1, (2 * NUM_SMS) // max(1, sequences * kv_heads))
-    split_keys = max(SPLIT_KEYS, -(-math.ceil(longest / want) // 64) * 64)
+    page or per 64 keys of a larger page) and no more than MAX_SPLITS of them. With the sequences' own context
+    lengths (steps that are not captured graphs) the split is the shortest that keeps all CTAs resident at
+    once, so that a few long sequences among short ones are cut up instead of setting the pace alone."""
+    slots = 2 * NUM_SMS
     boxes_per_tile = 64 // min(page_size, 64)
-    split_keys = min(split_keys, (TMA_DECODE_TABLE_ENTRIES // boxes_per_tile - 1) * 64)
+    cap = (TMA_DECODE_TABLE_ENTRIES // boxes_per_tile - 1) * 64
+    if contexts:
+        split_keys = SPLIT_KEYS
+        while split_keys < longest and sum(-(-c // split_keys) for c in contexts) * kv_heads > slots:
+            split_keys += max(64, split_keys // 8 // 64 * 64)
+        split_keys = min(split_keys, max(SPLIT_KEYS, -(-longest // 64) * 64))
+    else:
+        want = max(1, slots // max(1, sequences * kv_heads))
+        split_keys = max(SPLIT_KEYS, -(-math.ceil(longest / want) // 64) * 64)
+    split_keys = min(split_keys, cap)
     while math.ceil(longest / split_keys) > MAX_SPLITS:
         split_keys += 64
     return split_keys, max(1, math.ceil(longest / split_keys))
