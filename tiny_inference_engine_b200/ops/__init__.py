@@ -367,6 +367,12 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=No
     return gemm_select.gemm(a, w, out, partial_scratch)
 
 
+def bound_gemm(w: torch.Tensor, silu: bool = False):
+    """A matrix product bound to one weight (gemm_select.BoundGemm): checked once, called every step."""
+    from . import gemm_select
+    return gemm_select.BoundGemm(w, silu)
+
+
 def partial_capacity(max_rows: int, N: int, K: int) -> int:
     """The largest scratch (floats) a split product of up to max_rows tokens with [N, K] weights asks for."""
     from . import gemm_select

@@ -162,3 +162,68 @@ def gemm_silu(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor) -> Non
           "gemm_silu: needs bfloat16 operands TMA can address and gate/up rows in blocks of 16")
     if a.shape[0] > 0:
         gemm_tc(a, w_blocks, out, silu=True)
+
+
+class BoundGemm:
+    """out = a . w^T for one weight matrix, checked once: what the parts call hundreds of times a step.
+
+    The weight's address, sizes and kernel family are fixed when the part binds its tensors; a call looks up
+    the tiling of its token count (computed once per count) and goes straight to the launcher. `a` and `out`
+    come from the step's workspace: rows contiguous, 16-byte aligned, the compute dtype (the parts' contract);
+    anything the tensor-core kernels do not take falls back to `gemm` with its full checks."""
+
+    def __init__(self, w: torch.Tensor, silu: bool = False):
+        self.w, self.silu = w, silu
+        self.N, self.K = w.shape
+        self.fast = (w.dtype == torch.bfloat16 and w.stride(1) == 1 and self.K % 8 == 0 and w.stride(0) % 8 == 0
+                     and w.data_ptr() % 16 == 0 and (not silu or self.N % 32 == 0))
+        self.w_ptr, self.ldw = w.data_ptr(), w.stride(0)
+        self._plans: dict[int, tuple] = {}
+
+    def _plan(self, M: int):
+        pair = pair_takes(M, self.N)
+        t, bn, splits = plan(M, self.N, self.K)
+        if self.silu:
+            splits = 1
+            if not t:
+                bn = max(bn, 32)
+        real = _library().tie_gemm_tc_real_splits(self.K, splits) if splits > 1 else 1
+        p = (pair, t, bn, splits, int(not t or bn >= 128), real)
+        self._plans[M] = p
+        return p
+
+    def __call__(self, a: torch.Tensor, out: torch.Tensor, partial_scratch=None):
+        M = a.shape[0]
+        if M == 0:
+            return out
+        if not (self.fast and a.dtype == torch.bfloat16 and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+                and out.stride(1) == 1 and a.shape[1] == self.K and out.shape[1] == (self.N // 2 if self.silu else self.N)
+                and out.shape[0] == M and out.dtype in (torch.bfloat16, torch.float32)):
+            if self.silu:
+                gemm_silu(a, self.w, out)
+                return out
+            return gemm(a, self.w, out, partial_scratch)
+        global _ops
+        if _ops is None:
+            from . import SplitSum, _need, _stream, dtype_code
+            _ops = (SplitSum, _need, _stream, dtype_code)
+        SplitSum, _, _stream, dtype_code = _ops
+        pair, t, bn, splits, deep, real = self._plans.get(M) or self._plan(M)
+        code = 1 if out.dtype == torch.bfloat16 else 0
+        if pair:
+            _call("tie_gemm_tc2", code, a.data_ptr(), self.w_ptr, out.data_ptr(), M, self.N, self.K, a.stride(0), self.ldw,
+                  out.stride(0), 1 if self.silu else 0, _stream())
+            return out
+        leave = splits > 1 and partial_scratch is not None
+        scratch = 0
+        if leave:
+            buf = partial_scratch(splits * M * self.N)
+            scratch = buf.data_ptr()
+        elif splits > 1:
+            buf = _scratch_for(splits * M * self.N, a.device)
+            scratch = buf.data_ptr()
+        _call("tie_gemm_tc", code, a.data_ptr(), self.w_ptr, out.data_ptr(), M, self.N, self.K, a.stride(0), self.ldw, out.stride(0),
+              t, bn, splits, scratch, 1 if self.silu else 0, 0 if leave else 1, deep, _stream())
+        if leave:
+            return SplitSum(buf, real, M, self.N)
+        return out

@@ -66,6 +66,9 @@ class GQAttention(Mixer):
         self.w_k = self.w_qkv[self.q_dim:self.q_dim + self.kv_dim]
         self.w_v = self.w_qkv[self.q_dim + self.kv_dim:]
         self.w_o = to_compute(get(self.prefix + "o_proj.weight"), self.dtype).contiguous()
+        self.gemm_qkv, self.gemm_q, self.gemm_k, self.gemm_v, self.gemm_o = (
+            ops.bound_gemm(w) for w in (self.w_qkv, self.w_q, self.w_k, self.w_v, self.w_o))
+        self._capacity = None       # (q/k/v product, output product): the most partial sums a step can leave
         for part in (self.q_norm, self.k_norm, self.position):
             if part is not None:
                 part.bind(get)
@@ -88,24 +91,26 @@ class GQAttention(Mixer):
         if fused:
             width = self.q_dim + (2 * self.kv_dim if cache.writes else 0)
             qkv = ctx.ws.rows("attn.qkv", T, self.q_dim + 2 * self.kv_dim, self.dtype)[:, :width]
-            got = ops.gemm(h, self.w_qkv if cache.writes else self.w_q, qkv,
-                           partial_scratch=lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32,
-                                                                  ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape)))
+            if self._capacity is None:
+                self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape),
+                                  ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape))
+            got = (self.gemm_qkv if cache.writes else self.gemm_q)(
+                h, qkv, lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32, self._capacity[0]))
             ops.qk_norm_rope_append(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, g.slots, cache.k, cache.v, Hq, Hkv,
                                     Dh, write_kv=cache.writes, partial=got if isinstance(got, ops.SplitSum) else None)
             q = qkv[:, :self.q_dim]
         else:
             # Any other norm or position encoding: separate products and the parts' own kernels.
             q = ctx.ws.rows("attn.q", T, self.q_dim, self.dtype)
-            ops.gemm(h, self.w_q, q)
+            self.gemm_q(h, q)
             if self.q_norm is not None:
                 self.q_norm.rows(q.view(T * Hq, Dh), q.view(T * Hq, Dh))
             self.position.apply(q, ctx.positions, Hq, Dh)
             if cache.writes:
                 k = ctx.ws.rows("attn.k", T, self.kv_dim, self.dtype)
                 v = ctx.ws.rows("attn.v", T, self.kv_dim, self.dtype)
-                ops.gemm(h, self.w_k, k)
-                ops.gemm(h, self.w_v, v)
+                self.gemm_k(h, k)
+                self.gemm_v(h, v)
                 if self.k_norm is not None:
                     self.k_norm.rows(k.view(T * Hkv, Dh), k.view(T * Hkv, Dh))
                 self.position.apply(k, ctx.positions, Hkv, Dh)
@@ -113,8 +118,10 @@ class GQAttention(Mixer):
         attn = ctx.ws.rows("attn.out", T, self.q_dim, self.dtype)
         self.attend(q, attn, ctx, g, cache)
         out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
-        return ops.gemm(attn, self.w_o, out, partial_scratch=lambda n: ctx.ws.flat(
-            "mixer.out.partial", n, torch.float32, ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape)))
+        if self._capacity is None:
+            self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape),
+                              ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape))
+        return self.gemm_o(attn, out, lambda n: ctx.ws.flat("mixer.out.partial", n, torch.float32, self._capacity[1]))
 
     def attend(self, q, attn, ctx, g, cache):
         """Rows of sequences that bring several tokens come first in a step, then one row per

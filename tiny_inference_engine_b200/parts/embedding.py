@@ -41,6 +41,7 @@ class LMHead(Part):
 
     def bind(self, get):
         self.weight = self.embedding.table if self.tied else to_compute(get(self.name), self.dtype).contiguous()
+        self.product = ops.bound_gemm(self.weight)
 
     def forward(self, last, logits):
-        ops.gemm(last, self.weight, logits)
+        self.product(last, logits)

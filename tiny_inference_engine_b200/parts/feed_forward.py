@@ -32,19 +32,22 @@ class SwiGLU(FeedForward):
         self.fused = self.dtype == torch.bfloat16 and self.inter % 16 == 0 and self.hidden % 8 == 0
         self.w_gate_up = ops.interleave_gate_up(gate, up) if self.fused else torch.cat([gate, up], dim=0).contiguous()
         self.w_down = to_compute(get(self.prefix + "down_proj.weight"), self.dtype).contiguous()
+        self.gate_up, self.down = ops.bound_gemm(self.w_gate_up, silu=self.fused), ops.bound_gemm(self.w_down)
+        self._partial_capacity = None
 
     def forward(self, h, ctx):
         T = h.shape[0]
         act = ctx.ws.rows("ffn.act", T, self.inter, self.dtype)
         if self.fused:
-            ops.gemm_silu(h, self.w_gate_up, act)
+            self.gate_up(h, act)
         else:
             gu = ctx.ws.rows("ffn.gate_up", T, 2 * self.inter, self.dtype)
-            ops.gemm(h, self.w_gate_up, gu)
+            self.gate_up(h, gu)
             ops.silu_mul(gu, act)
         out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
-        return ops.gemm(act, self.w_down, out, partial_scratch=lambda n: ctx.ws.flat(
-            "ffn.out.partial", n, torch.float32, ops.partial_capacity(ctx.ws.max_rows, *self.w_down.shape)))
+        if self._partial_capacity is None:
+            self._partial_capacity = ops.partial_capacity(ctx.ws.max_rows, *self.w_down.shape)
+        return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
