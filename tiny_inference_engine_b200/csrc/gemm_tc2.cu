@@ -15,11 +15,12 @@
 // tile's epilogue overlap the next tile's MMAs. Every wait is bounded (status word as in
 // gemm_tc.cu). No TMA multicast: every CTA fetches its own operands.
 //
-// This kernel takes no part in programmatic dependent launch: it starts when the kernel ahead of it has
-// finished and the kernel behind it starts when it has finished. With either overlap switched on, steps of 512
-// tokens that mixed two prompt portions with decoded tokens (Qwen3-8B shapes: 48 pairs of CTAs for the q/k/v
-// product) hung now and then, with no bounded wait expired; without it, and with it on every other kernel,
-// they do not. The prologue it would hide is a few microseconds of a product that takes hundreds.
+// Programmatic dependent launch: the kernel behind this one may start while it runs (launch_dependents at the
+// top), but this kernel itself is launched without the attribute and so starts only when the kernel ahead of it
+// has finished. Started early, steps of 512 tokens that mixed two prompt portions with decoded tokens (Qwen3-8B
+// shapes: 48 pairs of CTAs for the q/k/v product) hung about once in five runs with no bounded wait expired; as
+// it is, hundreds of runs of the same steps are clean. The prologue this gives up is a few microseconds of a
+// product that takes hundreds.
 #include "umma.cuh"
 
 namespace tie {
@@ -75,6 +76,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(k2Threads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                 int M, int N, int k_blocks, long long ldo, int silu, int tiles_m, int n_tiles, int* status) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + k2Stages * k2Stage);   // used in the leader
@@ -315,7 +317,7 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, i
   }
   const int pairs = n_tiles < resident_pairs ? n_tiles : resident_pairs;
   cfg.gridDim = dim3(2 * pairs);
-  cfg.numAttrs = 1;   // clusters only: see the note on programmatic dependent launch at the top of this file
+  cfg.numAttrs = 1;   // clusters only, no early start: see the note at the top of this file
   cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<OutT>, ma, mw, static_cast<OutT*>(out), M, N, ceil_div(K, k2BK), ldo, silu, tiles_m,
                      n_tiles, status_word());
   return kOk;
