@@ -124,17 +124,21 @@ def paged_cache(rng, dtype, n_tokens_per_seq, kv_heads, head_dim, page, n_pages)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("Hq,Hkv,Dh", [(6, 3, 48), (4, 2, 64), (8, 2, 128), (2, 1, 256)])
-def test_kv_append_and_fused_norm_rope_append(ops, dtype, Hq, Hkv, Dh):
-    """Head size 48 runs the general kernel, 64 / 128 / 256 the one that holds a head in a warp's registers."""
+@pytest.mark.parametrize("T", [21, 300])
+@pytest.mark.parametrize("Hq,Hkv,Dh", [(6, 3, 48), (4, 2, 64), (5, 3, 64), (8, 2, 128), (3, 1, 128), (2, 1, 256)])
+def test_kv_append_and_fused_norm_rope_append(ops, dtype, T, Hq, Hkv, Dh):
+    """Head size 48 runs the general kernel, 64 / 128 / 256 the one that holds a head in a warp's registers, and
+    with hundreds of tokens the one that works on a token's heads side by side (odd head counts put a query head
+    and a key head, or a value head and nothing, into one warp)."""
     rng = np.random.default_rng(4)
-    page, T = 8, 21
+    page = 8
+    n_pages = max(12, T // page + 5)
     qkv = as_stored(rng.standard_normal((T, (Hq + 2 * Hkv) * Dh)), dtype)
     qw, kw = (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32), (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32)
     pos = rng.integers(0, 3000, T)
-    slots = rng.permutation(12 * page)[:T]
+    slots = rng.permutation(n_pages * page)[:T]
     slots[5] = -1                                  # a padding row writes nothing
-    kc = torch.zeros(12, Hkv, page, Dh, device="cuda", dtype=DT[dtype])
+    kc = torch.zeros(n_pages, Hkv, page, Dh, device="cuda", dtype=DT[dtype])
     vc = torch.zeros_like(kc)
     inv = plain.rope_inv_freq(1e6, Dh)
     qd = dev(qkv, DT[dtype])
@@ -152,7 +156,7 @@ def test_kv_append_and_fused_norm_rope_append(ops, dtype, Hq, Hkv, Dh):
         assert rel_err(got_k[p, :, o].reshape(1, -1), want_k[t].reshape(1, -1)) < TOL[dtype]
         assert np.array_equal(got_v[p, :, o].reshape(-1), v[t])
     written = {(s // page, s % page) for s in slots if s >= 0}
-    for p in range(12):
+    for p in range(n_pages):
         for o in range(page):
             if (p, o) not in written:
                 assert not got_k[p, :, o].any() and not got_v[p, :, o].any()

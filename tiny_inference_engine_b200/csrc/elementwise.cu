@@ -477,6 +477,99 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restr
   *reinterpret_cast<Slice*>(dst) = out;
 }
 
+// The same for many tokens, where the kernel above is bound by the instructions it issues (about 250 a
+// head), not by memory. One block a token; a lane holds 8 neighbouring elements, so a head takes
+// LPH = DH / 8 lanes and a warp works on 32 / LPH heads at once; what does not depend on the head (the
+// lane's cos and sin, its norm weights, the token's place in the cache) is made once per thread.
+template <typename T, int DH>
+__global__ void __launch_bounds__(256) qk_norm_rope_append_rows_kernel(T* __restrict__ qkv, long long row_stride,
+                                                                       const float* __restrict__ qw, const float* __restrict__ kw,
+                                                                       float q_eps, float k_eps, const float* __restrict__ inv_freq,
+                                                                       const int* __restrict__ positions, const int* __restrict__ slots,
+                                                                       T* __restrict__ k_cache, T* __restrict__ v_cache, int q_heads,
+                                                                       int kv_heads, int page_size, int heads_per_token) {
+  pdl_launch_dependents();
+  constexpr int E = 8, LPH = DH / E, HALF = DH / 2, WARP_HEADS = 32 / LPH;
+  using Slice = HeadSlice<T, E>;
+  __shared__ float cs[DH];   // the token's rotation: cos at [0, HALF), sin at [HALF, DH)
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = blockIdx.x;
+  // positions, frequencies, slots and weights do not come from the kernel ahead
+  if (inv_freq) {
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf(pos * inv_freq[i], cs + HALF + i, cs + i);
+  }
+  const int e0 = (lane % LPH) * E;        // this lane's elements of its head
+  float qwv[E], kwv[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    qwv[e] = qw ? qw[e0 + e] : 1.0f;
+    kwv[e] = kw ? kw[e0 + e] : 1.0f;
+  }
+  const int slot = slots ? slots[t] : -1;
+  const long long cache_row = slot >= 0 ? static_cast<long long>(slot / page_size) * kv_heads * page_size + slot % page_size : 0;
+  pdl_wait();
+  __syncthreads();
+  float c[E], sn[E];   // x' = x * c + partner * sn, the sine with the sign of the lane's half
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    c[e] = inv_freq ? cs[e0 % HALF + e] : 1.0f;
+    sn[e] = inv_freq ? (e0 < HALF ? -cs[HALF + e0 % HALF + e] : cs[HALF + e0 % HALF + e]) : 0.0f;
+  }
+  for (int base = warp * WARP_HEADS; base < heads_per_token; base += warps * WARP_HEADS) {   // uniform over the warp
+    const int head = base + lane / LPH;
+    const bool is_q = head < q_heads;
+    const bool is_v = head >= q_heads + kv_heads;
+    T* src = qkv + t * row_stride + static_cast<long long>(head) * DH + e0;
+    T* dst = nullptr;
+    if (head < heads_per_token) {
+      if (is_q) {
+        dst = src;
+      } else if (slot >= 0) {
+        const int h = is_v ? head - q_heads - kv_heads : head - q_heads;
+        dst = (is_v ? v_cache : k_cache) + (cache_row + static_cast<long long>(h) * page_size) * DH + e0;
+      }
+    }
+    if (__all_sync(0xffffffffu, is_v || dst == nullptr)) {   // a warp of value heads only copies
+      if (dst != nullptr) *reinterpret_cast<Slice*>(dst) = *reinterpret_cast<const Slice*>(src);
+      continue;
+    }
+    float x[E];
+    if (dst != nullptr) {
+      const Slice in = *reinterpret_cast<const Slice*>(src);
+#pragma unroll
+      for (int e = 0; e < E; ++e) x[e] = Elem<T>::load(in.v + e);
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) x[e] = 0.0f;
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) ss += x[e] * x[e];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const bool normed = !is_v && (is_q ? qw : kw) != nullptr;   // values are stored as they are
+    const float inv = normed ? 1.0f / sqrtf(ss / static_cast<float>(DH) + (is_q ? q_eps : k_eps)) : 1.0f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const float w = is_q ? qwv[e] : kwv[e];
+      x[e] = normed ? (x[e] * inv) * w : x[e];
+    }
+    const bool rotated = !is_v && inv_freq != nullptr;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[e], LPH / 2);
+      x[e] = rotated ? x[e] * c[e] + other * sn[e] : x[e];
+    }
+    if (dst != nullptr) {
+      Slice out;
+#pragma unroll
+      for (int e = 0; e < E; ++e) Elem<T>::store(out.v + e, x[e]);
+      *reinterpret_cast<Slice*>(dst) = out;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 int launch_embed(const void* table, const int* ids, float* x, int tokens, int dim, int vocab, cudaStream_t s) {
@@ -568,6 +661,23 @@ int launch_qk_norm_rope_append(void* qkv, long long stride, const float* part, l
   const bool whole = part_ok && (head_dim == 64 || head_dim == 128 || head_dim == 256) && (inv_freq == nullptr || rot == head_dim) &&
                      stride % vec == 0 && reinterpret_cast<uintptr_t>(qkv) % slice == 0 && reinterpret_cast<uintptr_t>(kc) % slice == 0 &&
                      reinterpret_cast<uintptr_t>(vc) % slice == 0;
+  // many tokens, nothing to sum: the kernel that issues the fewest instructions a head
+  const size_t wide = sizeof(T) * 8 > 16 ? 16 : sizeof(T) * 8;
+  const bool rows = whole && part == nullptr && tokens >= 256 && stride % 8 == 0 && reinterpret_cast<uintptr_t>(qkv) % wide == 0 &&
+                    reinterpret_cast<uintptr_t>(kc) % wide == 0 && reinterpret_cast<uintptr_t>(vc) % wide == 0;
+  if (rows) {
+    T* q = static_cast<T*>(qkv);
+    T* k = static_cast<T*>(kc);
+    T* v = static_cast<T*>(vc);
+#define TIE_QK_ROWS(D)                                                                                                       \
+  TIE_LAUNCH((qk_norm_rope_append_rows_kernel<T, D>), tokens, 256, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v, \
+             q_heads, kv_heads, page_size, heads_per_token)
+    if (head_dim == 64) TIE_QK_ROWS(64);
+    else if (head_dim == 128) TIE_QK_ROWS(128);
+    else TIE_QK_ROWS(256);
+#undef TIE_QK_ROWS
+    TIE_RETURN_LAUNCH("qk_norm_rope_append");
+  }
   if (whole) {
     const dim3 grid(tokens, ceil_div(heads_per_token, warps));
     T* q = static_cast<T*>(qkv);
