@@ -299,6 +299,52 @@ def test_sampling_kernel_frequencies(ops):
     assert np.abs(np.bincount(out.cpu().numpy(), minlength=5) / 2000 - p).max() < 0.03
 
 
+def _filtered_case(ops, z, rows, counter):
+    """rows: (temperature, top_k, top_p, seed) for each row of z; the kernels against the sampler on the host."""
+    from tiny_inference_engine_b200.sampling import SamplingParams
+    from tiny_inference_engine_b200.sampling.sampler import sample_host
+    R = len(rows)
+    params = [SamplingParams(temperature=t, top_k=k, top_p=p, seed=s) for t, k, p, s in rows]
+    inv = np.array([q.inv_temperature() for q in params], dtype=np.float32)
+    seeds = np.array([q.seed for q in params], dtype=np.uint64)
+    out = torch.full((R,), -1, dtype=torch.int32, device="cuda")
+    ops.sample(dev(z), out, dev(inv), torch.from_numpy(seeds.view(np.int64)).cuda(), dev(np.full(R, counter), torch.int64),
+               dev(np.array([q.top_k for q in params]), torch.int32), dev(np.array([q.top_p for q in params], dtype=np.float32)))
+    want = [sample_host(z[r], params[r], counter) for r in range(R)]
+    assert out.tolist() == want, [(rows[r], out[r].item(), want[r]) for r in range(R) if out[r].item() != want[r]]
+
+
+def test_sampling_kernel_top_k_and_top_p(ops):
+    """Few kept candidates are sorted in shared memory; more than 1,024, or top-p alone, are found by selection
+    over the whole row. Equal logits are taken in id order; -inf logits weigh nothing."""
+    rng = np.random.default_rng(11)
+    V = 1531
+    rows = []
+    for k in (0, 1, 5, 200, 1024, 1100, V, 5000):
+        for p in (1.0, 0.9, 0.3, 1e-6):
+            rows.append((float(rng.choice([0.3, 0.8, 1.0, 2.5])), k, p, int(rng.integers(0, 2 ** 62))))
+    rows += [(0.0, 5, 0.5, 3), (1e-45, 5, 0.5, 3)]                       # greedy whatever the filters say
+    R = len(rows)
+    z = (rng.standard_normal((R, V)) * 2.5).astype(np.float32)
+    z[:, 40:60] = z[:, 700:701]                                          # twenty equal logits in every row
+    z[::3, 100:400] = -np.inf
+    z[5] = 0.25                                                          # a row of equal logits: the cut falls among ties
+    z[6] = np.round(z[6])                                                # many ties at every value
+    for counter in (0, 1, 2, 3, 77, 2 ** 33):
+        _filtered_case(ops, z, rows, counter)
+    z[7, 3] = np.inf                                                     # a certain token
+    _filtered_case(ops, z, rows, 5)
+
+
+def test_sampling_kernel_filters_over_a_large_vocabulary(ops):
+    rng = np.random.default_rng(12)
+    V = 151936
+    rows = [(0.7, 20, 0.8, 1), (0.7, 0, 0.9, 2), (1.0, 5000, 0.95, 3), (1.3, 0, 0.5, 4), (0.7, 20, 1.0, 5), (1.0, 2000, 1.0, 6)]
+    z = (rng.standard_normal((len(rows), V)) * np.array([3, 3, 0.01, 0.01, 5, 1])[:, None]).astype(np.float32)
+    for counter in (0, 1, 2):
+        _filtered_case(ops, z, rows, counter)
+
+
 def test_refusals_are_clear(ops):
     from tiny_inference_engine_b200.errors import InvalidArgument
     q = torch.zeros(1, 2 * 20, device="cuda")

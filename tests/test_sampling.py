@@ -26,8 +26,8 @@ def test_generator_matches_the_published_vectors_and_the_plain_one():
 def test_subnormal_temperature_is_greedy_and_device_path_choice():
     assert SamplingParams(temperature=1e-45).inv_temperature() == 0.0
     assert SamplingParams(temperature=0.5).inv_temperature() == 2.0
-    assert SamplingParams(temperature=0.7).on_device and not SamplingParams(top_k=5).on_device
-    assert not SamplingParams(top_p=0.9).on_device
+    assert not SamplingParams(temperature=0.7).filters and not SamplingParams(top_k=5).filters   # greedy takes the maximum
+    assert SamplingParams(temperature=0.7, top_k=5).filters and SamplingParams(temperature=0.7, top_p=0.9).filters
 
 
 def test_host_sampler_follows_the_plain_one():

@@ -230,14 +230,14 @@ class Scheduler:
     def schedule_ahead(self, batch: ScheduledBatch) -> ScheduledBatch | None:
         """While `batch` is in flight and its tokens are not known yet: the same requests, each one token
         further, if that is certainly what `schedule` would decide once the batch is back, else None.
-        Certain means: nothing waits; the batch holds every running request; each decodes one token, is
-        sampled on the device and cannot reach its max_tokens with the token in flight; and pages for
+        Certain means: nothing waits; the batch holds every running request; each decodes one token
+        and cannot reach its max_tokens with the token in flight; and pages for
         one more token can be had for all of them (all or nothing; preemption is left to `schedule`).
         A request that turns out to have stopped with the token in flight runs this one step in vain."""
         if self.waiting or len(batch.seqs) != len(self.running) or not batch.seqs:
             return None
         for seq, n in batch.seqs:
-            if n != 1 or seq.state != SeqState.DECODING or seq.num_pending != 1 or not seq.params.on_device:
+            if n != 1 or seq.state != SeqState.DECODING or seq.num_pending != 1:
                 return None
             if seq.num_generated + 1 >= seq.params.max_tokens:
                 return None

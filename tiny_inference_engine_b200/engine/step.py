@@ -94,6 +94,8 @@ class StepContext:
     inv_temperature: torch.Tensor | None = None
     seeds: torch.Tensor | None = None
     counters: torch.Tensor | None = None
+    top_k: torch.Tensor | None = None              # given only when a row filters (top-k, top-p)
+    top_p: torch.Tensor | None = None
     single_contexts: tuple | None = None   # context lengths of the sequences that bring one token, when the step is not a captured graph
 
 
@@ -115,20 +117,13 @@ class PendingTokens:
         self.runner, self.host, self.event, self.logits, self.sampling = runner, host, event, logits, sampling
 
     def result(self) -> list[int]:
-        """Waits for the copy; rows that need the host filter (top-k, top-p) are sampled from their logits
-        (no other step may have been queued since for those). Checks the kernels' status words."""
-        from ..sampling.sampler import sample_host
+        """Waits for the copy and checks the kernels' status words."""
         R = len(self.sampling)
         if R == 0:
             return []
-        host_rows = [r for r, (p, _) in enumerate(self.sampling) if not p.on_device]
-        host_logits = self.logits[host_rows].cpu().numpy() if host_rows else None
         self.event.synchronize()
         gemm_select.check_status()
-        out = self.host[:R].tolist()
-        for j, r in enumerate(host_rows):
-            out[r] = sample_host(host_logits[j], self.sampling[r][0], self.sampling[r][1])
-        return out
+        return self.host[:R].tolist()
 
 
 class StepRunner:
@@ -189,8 +184,7 @@ class StepRunner:
         """Runs one step. Returns float32 logits [R, V] on the device in the order of the entries and
         of their `want` (None when nothing is wanted). With `sampling` (one (parameters, index of
         the generated token) per wanted row) returns (logits, ids): ids is an int32 device tensor
-        [R] picked by the sampling kernel (greedy or temperature); rows whose parameters ask for
-        top-k or top-p are to be sampled from the logits by the caller.
+        [R] picked by the sampling kernels (greedy, temperature, top-k, top-p).
 
         With `device_tokens` every entry brings one token and entry i's token is the id that the step
         before sampled for its row i (still on the device, perhaps not computed yet): the step can be
@@ -209,7 +203,7 @@ class StepRunner:
     def _sample(self, ctx: StepContext, logits):
         if logits is None:
             return None
-        ops.sample(logits, self._ids, ctx.inv_temperature, ctx.seeds, ctx.counters)
+        ops.sample(logits, self._ids, ctx.inv_temperature, ctx.seeds, ctx.counters, ctx.top_k, ctx.top_p)
         return self._ids[:ctx.R]
 
     def fetch(self, logits, ids, sampling) -> "PendingTokens":
@@ -225,7 +219,7 @@ class StepRunner:
 
     def tokens_of(self, logits, ids, sampling) -> list[int]:
         """Brings the sampled ids to the host (one copy, one synchronize) and samples rows that need
-        the host filter (top-k, top-p) from their logits. Checks the kernels' status words."""
+        Checks the kernels' status words."""
         return self.fetch(logits, ids, sampling).result()
 
     def check(self) -> None:
@@ -249,10 +243,11 @@ class StepRunner:
         if sb > self.max_logit_rows or sb > self.max_tokens:
             return None
         mb = max(16, _bucket(need, 1 << 30))
-        return (sb, mb, sampling is not None)
+        filtered = sampling is not None and any(p.filters for p, _ in sampling)   # one more kernel in the graph
+        return (sb, mb, sampling is not None, filtered)
 
     def _run_graph(self, entries, sampling, key, device_tokens=False):
-        sb, mb, sampled = key
+        sb, mb, sampled, _ = key
         ctx = self.prepare(entries, sampling, pad_seqs=sb, table_len=mb, device_tokens=device_tokens)
         if key not in self._graphs:
             # one eager run allocates every buffer and loads every kernel, then the capture
@@ -330,7 +325,8 @@ class StepRunner:
         # layout of the staging buffer (int32 words); 64-bit sections are 8-byte aligned because every section is 16-byte aligned
         sizes = [("tokens", T), ("positions", T), ("seq_of_row", T), ("query_start", S + 1), ("context_lens", S),
                  ("logit_rows", max(R, 1)), ("state_slots", S), ("single_seqs", max(S, 1)),
-                 ("inv_t", max(R, 1)), ("seeds", 2 * max(R, 1)), ("counters", 2 * max(R, 1))]
+                 ("inv_t", max(R, 1)), ("seeds", 2 * max(R, 1)), ("counters", 2 * max(R, 1)),
+                 ("top_k", max(R, 1)), ("top_p", max(R, 1))]
         for g in range(G):
             sizes += [(f"slots{g}", T), (f"tables{g}", S * MB)]
         offs, total = {}, 0
@@ -455,6 +451,12 @@ class StepRunner:
             inv_t[:], seeds[:], counters[:] = 0.0, 0, 0
             for r, (p, index) in enumerate(sampling):
                 inv_t[r], seeds[r], counters[r] = p.inv_temperature(), p.seed, index
+            filtered = any(p.filters for p, _ in sampling)
+            if filtered:
+                top_k, top_p = sec("top_k"), sec("top_p").view(np.float32)
+                top_k[:], top_p[:] = 0, 1.0
+                for r, (p, _) in enumerate(sampling):
+                    top_k[r], top_p[r] = min(p.top_k, 2 ** 31 - 1), p.top_p
 
         dev[:total].copy_(slot[0][:total], non_blocking=True)
         slot[2].record()
@@ -483,6 +485,8 @@ class StepRunner:
             ctx.inv_temperature = dsec("inv_t", R).view(torch.float32)
             ctx.seeds = dsec("seeds", 2 * R).view(torch.int64)
             ctx.counters = dsec("counters", 2 * R).view(torch.int64)
+            if filtered:
+                ctx.top_k, ctx.top_p = dsec("top_k", R), dsec("top_p", R).view(torch.float32)
         if self.fail_hook is not None:
             self.fail_hook(ctx)
         return ctx

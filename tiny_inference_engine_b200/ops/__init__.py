@@ -342,10 +342,12 @@ def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
          max_splits, scratch.data_ptr(), counters.data_ptr(), _stream())
 
 
-def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None) -> None:
+def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None, top_k=None,
+           top_p=None) -> None:
     """out[r] = first maximum of row r (inv_temperature None or 0), or a draw from softmax(logits * inv_temperature)
-    with the Philox uniform of (seeds[r], counters[r])."""
-    _dev(logits, out, inv_temperature, seeds, counters)
+    with the Philox uniform of (seeds[r], counters[r]). With top_k (int32) and top_p (float32) the rows whose
+    top_k is in (0, vocab) or whose top_p is below 1 draw from the candidates those keep, most likely first."""
+    _dev(logits, out, inv_temperature, seeds, counters, top_k, top_p)
     R, V = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be float32 rows")
     _need(out.dtype == torch.int32 and out.numel() >= R, "sample: out must be int32 [R]")
@@ -354,6 +356,13 @@ def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=
               "sample: inv_temperature float32, seeds and counters int64")
     call("tie_sample", logits.data_ptr(), logits.stride(0), R, V, _ptr(inv_temperature), _ptr(seeds), _ptr(counters),
          out.data_ptr(), _stream())
+    if top_k is not None or top_p is not None:
+        _need(inv_temperature is not None and top_k is not None and top_p is not None,
+              "sample: top_k and top_p come together, with temperatures")
+        _need(top_k.dtype == torch.int32 and top_p.dtype == torch.float32 and top_k.numel() >= R and top_p.numel() >= R,
+              "sample: top_k int32 [R], top_p float32 [R]")
+        call("tie_sample_filtered", logits.data_ptr(), logits.stride(0), R, V, inv_temperature.data_ptr(), top_k.data_ptr(),
+             top_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _stream())
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=None):

@@ -29,11 +29,11 @@ class SamplingParams:
             raise InvalidArgument(f"max_tokens must be >= 1, got {self.max_tokens}")
 
     @property
-    def on_device(self) -> bool:
-        """Greedy and plain temperature sampling run in the sampling kernel; top-k and top-p
-        filter on the host. Which one serves a request depends on its parameters only, so its
-        tokens never depend on what else is in a batch."""
-        return self.top_k == 0 and self.top_p >= 1.0
+    def filters(self) -> bool:
+        """Whether top-k or top-p narrows the candidates (with a temperature; greedy takes the first maximum
+        whatever they say). Such rows run one more kernel after the plain draw. It depends on the request's
+        parameters only, so its tokens never depend on what else is in a batch."""
+        return self.temperature != 0.0 and (self.top_k > 0 or self.top_p < 1.0)
 
     def inv_temperature(self) -> float:
         """1/T as a float32 value; 0 stands for greedy (T == 0, or so small that 1/T is not finite)."""

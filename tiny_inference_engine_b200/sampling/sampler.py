@@ -1,7 +1,8 @@
-"""Sampling on the host, with top-k and top-p. (Greedy and plain temperature sampling run in the
-sampling kernel inside the step: engine/step.py.)
+"""The sampler on the host: what the sampling kernels compute, restated with numpy. The engine samples on
+the device (greedy, temperature, top-k and top-p run in kernels inside the step: engine/step.py); this
+function is what tests hold those kernels against, and a way to sample from logits one has on the host.
 
-The host path restates the reference's sampler (src/sampling/sampler.cpp:18-81): NaN or empty
+It restates the reference's sampler (src/sampling/sampler.cpp:18-81): NaN or empty
 logits and all -inf are errors, a +inf logit is certain, greedy is the first maximum,
 otherwise shift by the maximum and scale by 1/T, keep the top_k most likely (ties by id),
 then the smallest prefix whose weight reaches top_p of the total, and walk the candidates
@@ -43,7 +44,7 @@ def sample_host(logits: np.ndarray, params: SamplingParams, index: int) -> int:
     total = float(weights.sum())
     if params.top_p < 1.0:
         cum = np.cumsum(weights)
-        keep = min(int(np.searchsorted(cum, np.float32(params.top_p) * total, side="left")) + 1, weights.size)
+        keep = min(int(np.searchsorted(cum, float(np.float32(params.top_p)) * total, side="left")) + 1, weights.size)
         weights, total = weights[:keep], float(cum[keep - 1])
     r = uniform(params.seed, index) * total
     cum = np.cumsum(weights)
