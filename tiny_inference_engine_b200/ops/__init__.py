@@ -376,16 +376,17 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=No
     return gemm_select.gemm(a, w, out, partial_scratch)
 
 
-def bound_gemm(w: torch.Tensor, silu: bool = False):
-    """A matrix product bound to one weight (gemm_select.BoundGemm): checked once, called every step."""
+def bound_gemm(w: torch.Tensor, silu: bool = False, split_many: bool = True):
+    """A matrix product bound to one weight (gemm_select.BoundGemm): checked once, called every step.
+    `split_many` False: above 128 tokens k is never split (the consumer wants the finished product)."""
     from . import gemm_select
-    return gemm_select.BoundGemm(w, silu)
+    return gemm_select.BoundGemm(w, silu, split_many)
 
 
-def partial_capacity(max_rows: int, N: int, K: int) -> int:
+def partial_capacity(max_rows: int, N: int, K: int, split_many: bool = True) -> int:
     """The largest scratch (floats) a split product of up to max_rows tokens with [N, K] weights asks for."""
     from . import gemm_select
-    return gemm_select.partial_capacity(int(max_rows), int(N), int(K))
+    return gemm_select.partial_capacity(int(max_rows), int(N), int(K), bool(split_many))
 
 
 def gemm_silu(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor) -> None:

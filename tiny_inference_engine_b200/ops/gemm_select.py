@@ -26,14 +26,35 @@ def tc_takes(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
+# Microseconds on one B200, fitted to a sweep of Qwen3-4B's and 8B's products at 160 to 2,048 tokens (8 % mean
+# error): a k-block of a 128 x 128 or 128 x 256 tile, the prologue and epilogue of a wave of tiles, and writing
+# and reading back a million float partial sums.
+_US_K_BLOCK = {128: 0.225, 256: 0.356}
+_US_WAVE = {128: 3.2, 256: 7.0}
+_US_MEGA_PARTIAL = 0.68
+
+
+def _plain_cost(M: int, N: int, k_blocks: int, bn: int, splits: int) -> float:
+    """Estimated time of the plain tiling: the launcher gives every split NUM_SMS // splits CTAs, each of which
+    walks its tiles in turn."""
+    per = math.ceil(k_blocks / splits)
+    real = math.ceil(k_blocks / per)
+    tiles = math.ceil(M / 128) * math.ceil(N / bn)
+    ctas = tiles if tiles * real <= NUM_SMS else max(1, NUM_SMS // real)
+    waves = math.ceil(tiles / min(ctas, tiles))
+    return waves * (per * _US_K_BLOCK[bn] + _US_WAVE[bn]) + (real * M * N / 1e6 * _US_MEGA_PARTIAL if real > 1 else 0.0)
+
+
+@functools.lru_cache(maxsize=None)
+def plan(M: int, N: int, K: int, split_many: bool = True) -> tuple[int, int, int]:
     """(transposed, tile width, splits) for out[M, N] = a[M, K] w[N, K]^T on one CTA per tile.
 
     Up to 128 tokens the weights take the 128-row side of the MMA and the tokens the narrow side
     (width = the smallest of 16, 32, 64, 128 that holds them): the product is bound by streaming the
     weights, and k is cut into splits so that every SM has a CTA pulling bytes. More tokens: 128-token
-    row tiles against 128-wide weight tiles while those are one wave of CTAs or less (k split to fill
-    the SMs), else against 256-wide ones. (Measured on Qwen3-8B's four shapes at 160 to 1,024 tokens.)"""
+    row tiles against 128- or 256-wide weight tiles with k cut into up to four splits, whichever the
+    cost estimate above puts first: what matters there is how many waves of tiles the SMs need.
+    `split_many` False keeps k whole above 128 tokens (for a consumer that wants the finished product)."""
     k_blocks = math.ceil(K / 64)
     if M <= 128:
         bn = next(b for b in (16, 32, 64, 128) if b >= M)
@@ -47,10 +68,19 @@ def plan(M: int, N: int, K: int) -> tuple[int, int, int]:
         elif bn == 128 and tiles < NUM_SMS:
             splits = max(1, min(NUM_SMS // tiles, k_blocks // 16))      # one CTA per SM at this width
         return 1, bn, splits
-    tiles = math.ceil(M / 128) * math.ceil(N / 128)
-    if tiles <= NUM_SMS:
-        return 0, 128 if N > 64 else next(b for b in (16, 32, 64) if b >= N), max(1, min(NUM_SMS // tiles, k_blocks // 16))
-    return 0, next((b for b in (16, 32, 64, 128, 256) if b >= N), 256), 1
+    if N <= 128:
+        tiles = math.ceil(M / 128)
+        bn = next(b for b in (16, 32, 64, 128) if b >= N)
+        return 0, bn, max(1, min(NUM_SMS // tiles, k_blocks // 16)) if split_many else 1
+    best = None
+    for bn in (128, 256):
+        for splits in range(1, 5 if split_many else 2):
+            if splits > 1 and k_blocks // splits < 8:
+                break
+            cost = _plain_cost(M, N, k_blocks, bn, splits)
+            if best is None or cost < best[0] - 1e-6:
+                best = (cost, bn, splits)
+    return 0, best[1], best[2]
 
 
 _retired: list = []
@@ -69,12 +99,12 @@ def _scratch_for(numel: int, device) -> torch.Tensor:
 
 
 @functools.lru_cache(maxsize=None)
-def partial_capacity(max_rows: int, N: int, K: int) -> int:
+def partial_capacity(max_rows: int, N: int, K: int, split_many: bool = True) -> int:
     """The most float partial sums a product of up to `max_rows` tokens with these weights leaves
     (splits x tokens x N over every token count): what its scratch buffer is sized for once."""
     most = 0
     for M in range(1, max_rows + 1):
-        splits = plan(M, N, K)[2]
+        splits = plan(M, N, K, split_many)[2]
         if splits > 1:
             most = max(most, splits * M * N)
     return most
@@ -172,8 +202,8 @@ class BoundGemm:
     come from the step's workspace: rows contiguous, 16-byte aligned, the compute dtype (the parts' contract);
     anything the tensor-core kernels do not take falls back to `gemm` with its full checks."""
 
-    def __init__(self, w: torch.Tensor, silu: bool = False):
-        self.w, self.silu = w, silu
+    def __init__(self, w: torch.Tensor, silu: bool = False, split_many: bool = True):
+        self.w, self.silu, self.split_many = w, silu, split_many
         self.N, self.K = w.shape
         self.fast = (w.dtype == torch.bfloat16 and w.stride(1) == 1 and self.K % 8 == 0 and w.stride(0) % 8 == 0
                      and w.data_ptr() % 16 == 0 and (not silu or self.N % 32 == 0))
@@ -182,7 +212,7 @@ class BoundGemm:
 
     def _plan(self, M: int):
         pair = pair_takes(M, self.N)
-        t, bn, splits = plan(M, self.N, self.K)
+        t, bn, splits = plan(M, self.N, self.K, self.split_many)
         if self.silu:
             splits = 1
             if not t:

@@ -67,7 +67,7 @@ class GQAttention(Mixer):
         self.w_v = self.w_qkv[self.q_dim + self.kv_dim:]
         self.w_o = to_compute(get(self.prefix + "o_proj.weight"), self.dtype).contiguous()
         self.gemm_qkv, self.gemm_q, self.gemm_k, self.gemm_v, self.gemm_o = (
-            ops.bound_gemm(w) for w in (self.w_qkv, self.w_q, self.w_k, self.w_v, self.w_o))
+            ops.bound_gemm(w, split_many=w is self.w_o) for w in (self.w_qkv, self.w_q, self.w_k, self.w_v, self.w_o))
         self._capacity = None       # (q/k/v product, output product): the most partial sums a step can leave
         for part in (self.q_norm, self.k_norm, self.position):
             if part is not None:
@@ -92,7 +92,7 @@ class GQAttention(Mixer):
             width = self.q_dim + (2 * self.kv_dim if cache.writes else 0)
             qkv = ctx.ws.rows("attn.qkv", T, self.q_dim + 2 * self.kv_dim, self.dtype)[:, :width]
             if self._capacity is None:
-                self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape),
+                self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape, split_many=False),
                                   ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape))
             got = (self.gemm_qkv if cache.writes else self.gemm_q)(
                 h, qkv, lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32, self._capacity[0]))
@@ -119,7 +119,7 @@ class GQAttention(Mixer):
         self.attend(q, attn, ctx, g, cache)
         out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
         if self._capacity is None:
-            self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape),
+            self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape, split_many=False),
                               ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape))
         return self.gemm_o(attn, out, lambda n: ctx.ws.flat("mixer.out.partial", n, torch.float32, self._capacity[1]))
 
