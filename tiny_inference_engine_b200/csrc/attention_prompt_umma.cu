@@ -42,6 +42,7 @@ struct UmmaPromptArgs {
   long long q_stride;
   int max_blocks, q_heads, kv_heads, page_size, page_shift, window;
   float scale_log2;
+  int cta_rows;   // 256: a CTA works on two row tiles side by side; 128: on one (more CTAs when there are few rows)
 };
 
 // Descriptor of an operand stored with its MN extent contiguous (V as [key][head dim]): 64 elements of
@@ -115,7 +116,7 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   const int t0 = a.query_start[seq];
   const int nq = a.query_start[seq + 1] - t0;
   const int rows = nq * G;
-  const int row0 = (static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y)) * 256;   // last rows (most keys) first
+  const int row0 = (static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y)) * a.cta_rows;   // last rows (most keys) first
   if (row0 >= rows) return;
   const int pos0 = a.context_lens[seq] - nq;
 
@@ -125,7 +126,7 @@ attn_prompt_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
   for (int q = 0; q < 2; ++q) {
     const int r0 = row0 + 128 * q;
-    has[q] = r0 < rows;
+    has[q] = r0 < rows && 128 * q < a.cta_rows;
     const int lo_pos = pos0 + r0 / G, hi_pos = pos0 + min(rows - 1, r0 + 127) / G;
     first[q] = a.window > 0 ? max(0, lo_pos - a.window + 1) / kKeysPerTile : 0;
     last[q] = hi_pos / kKeysPerTile;
@@ -445,7 +446,7 @@ static int launch_prompt_umma(const CUtensorMap& km, const CUtensorMap& vm, cons
     }
     configured = true;
   }
-  TIE_LAUNCH((attn_prompt_umma_kernel<DH, STAGES>), dim3(a.kv_heads, ceil_div(max_rows, 256), n_seqs), kUmmaAttnThreads, smem, s, km, vm, a);
+  TIE_LAUNCH((attn_prompt_umma_kernel<DH, STAGES>), dim3(a.kv_heads, ceil_div(max_rows, a.cta_rows), n_seqs), kUmmaAttnThreads, smem, s, km, vm, a);
   return kOk;
 }
 
@@ -479,8 +480,12 @@ TIE_API int tie_attention_prompt_umma(const void* q, long long q_stride, const v
               "attention_prompt_umma: cuTensorMapEncodeTiled failed");
   TIE_REQUIRE(status_word() != nullptr, "attention_prompt_umma: cannot allocate the status word");
   UmmaPromptArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), query_start, context_lens, block_tables,
-                   status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window, scale * 1.4426950408889634f};
+                   status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window, scale * 1.4426950408889634f, 256};
   const int max_rows = max_queries * (q_heads / kv_heads);
+  // Few rows: with two row tiles a CTA, half of the SMs or more would have none
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  if (static_cast<long long>(kv_heads) * ceil_div(max_rows, 256) * n_seqs * 2 <= sms) a.cta_rows = 128;
   const int st = head_dim == 64 ? launch_prompt_umma<64>(km, vm, a, n_seqs, max_rows, s) : launch_prompt_umma<128>(km, vm, a, n_seqs, max_rows, s);
   if (st != kOk) return st;
   TIE_RETURN_LAUNCH("attention_prompt_umma");
