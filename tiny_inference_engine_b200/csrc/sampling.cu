@@ -1,7 +1,7 @@
 // Picking the next token on the device: the first maximum (greedy), or a draw from
 // softmax(logits / T) by inverse CDF with a Philox4x32-10 uniform keyed by the request's
 // seed and the index of the generated token. One block per row of logits, a fixed block
-// size and fixed segment boundaries, so a row's result never depends on the rows beside it.
+// size and fixed chunk boundaries, so a row's result never depends on the rows beside it.
 //
 // The reference samples on the host (src/sampling/sampler.cpp:18-81): greedy is the first
 // maximum (ties go to the lowest id); otherwise logits are shifted by their maximum and
@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* __r
   pdl_sync();
   __shared__ float sv[32];
   __shared__ int si[32];
-  __shared__ float seg_sum[kSampleThreads];
+  __shared__ float seg_sum[32];
+  __shared__ float batch_sum[32][64];
   __shared__ int chosen;
   const int r = blockIdx.x;
   const float* z = logits + static_cast<long long>(r) * row_stride;
@@ -93,7 +94,20 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* __r
 
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = tid; i < vocab; i += kSampleThreads) arg_better(best, best_i, z[i], i);
+  // eight loads in flight per thread: one block reads the row, so what bounds it is the latency of its loads
+  for (int i0 = tid; i0 < vocab; i0 += 8 * kSampleThreads) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * kSampleThreads;
+      v[j] = i < vocab ? z[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * kSampleThreads;
+      if (i < vocab) arg_better(best, best_i, v[j], i);
+    }
+  }
   block_argmax(best, best_i, sv, si);
   const float inv_t = inv_temperature ? inv_temperature[r] : 0.0f;
   if (!(inv_t > 0.0f) || isinf(inv_t) || best == INFINITY) {  // greedy, or a certain token
@@ -101,51 +115,82 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* __r
     return;
   }
 
-  // Thread `tid` owns the contiguous ids [tid * seg, (tid + 1) * seg).
-  const int seg = (vocab + kSampleThreads - 1) / kSampleThreads;
-  const int begin = min(vocab, tid * seg), end = min(vocab, begin + seg);
-  float mine = 0.0f;
-  for (int i = begin; i < end; ++i) mine += expf((z[i] - best) * inv_t);
-  seg_sum[tid] = mine;
+  // Warp w owns the contiguous ids [w * chunk, (w + 1) * chunk) and reads them in batches of 256 * m ids
+  // (32 lanes x 8 loads in flight, m times; m = 1 up to 524,288 ids), keeping each batch's weight. The chunks'
+  // weights are scanned; the warp whose chunk holds the target finds the batch among its (at most 64) batch
+  // weights and reads only that batch again, 32 ids a step, for the id at which the running weight passes.
+  const int lane = tid & 31, warp = tid >> 5;
+  const int chunk = ((vocab + kSampleThreads - 1) / kSampleThreads) * 32;
+  const int m = (chunk + 64 * 256 - 1) / (64 * 256);
+  const int batch = 256 * m;
+  const int begin = min(vocab, warp * chunk), end = min(vocab, begin + chunk);
+  float chunk_sum = 0.0f;
+  for (int b0 = begin, nb = 0; b0 < end; b0 += batch, ++nb) {
+    float mine = 0.0f;
+    for (int i0 = b0 + lane; i0 < min(end, b0 + batch); i0 += 256) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = i0 + 32 * j < min(end, b0 + batch) ? z[i0 + 32 * j] : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mine += i0 + 32 * j < min(end, b0 + batch) ? expf((v[j] - best) * inv_t) : 0.0f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) batch_sum[warp][nb] = mine;
+    chunk_sum += mine;
+  }
+  if (lane == 0) seg_sum[warp] = chunk_sum;
   if (tid == 0) chosen = -1;
   __syncthreads();
-  // Exclusive scan of the 1024 segment sums by warp 0: 32 per lane, then across lanes.
-  if (tid < 32) {
-    float local = 0.0f;
-    for (int i = 0; i < 32; ++i) local += seg_sum[tid * 32 + i];
-    float incl = local;
+  // every warp scans the 32 chunk sums itself
+  const float own = seg_sum[lane];
+  float incl = own;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (tid >= o) incl += n;
-    }
-    float run = incl - local;
-    for (int i = 0; i < 32; ++i) {
-      const float v = seg_sum[tid * 32 + i];
-      seg_sum[tid * 32 + i] = run;  // exclusive prefix
-      run += v;
-    }
-    if (tid == 31) sv[1] = run;  // total
+  for (int o = 1; o < 32; o <<= 1) {
+    const float n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
   }
-  __syncthreads();
-  const float total = sv[1];
+  const float total = __shfl_sync(0xffffffffu, incl, 31);
   uint32_t c[4] = {static_cast<uint32_t>(counters[r]), static_cast<uint32_t>(counters[r] >> 32), 0u, 0u};
   philox4x32_10(c, static_cast<uint32_t>(seeds[r]), static_cast<uint32_t>(seeds[r] >> 32));
   const float u = static_cast<float>(c[0] >> 8) * (1.0f / 16777216.0f);
   const float target = u * total;
-  const float start = seg_sum[tid];
-  const float stop = tid + 1 < kSampleThreads ? seg_sum[tid + 1] : total;
-  if (begin < end && target >= start && target < stop) {
+  const float start = __shfl_sync(0xffffffffu, incl - own, warp);   // the weight before this warp's chunk
+  const float stop = warp == 31 ? total : __shfl_sync(0xffffffffu, incl, warp);
+  if (begin < end && target >= start && target < stop) {   // the ranges [start, stop) are disjoint: one warp
     float run = start;
-    int pick = end - 1;
-    for (int i = begin; i < end; ++i) {
-      run += expf((z[i] - best) * inv_t);
-      if (target < run) {
-        pick = i;
-        break;
-      }
+    int b0 = begin;
+    for (int nb = 0; b0 + batch < end; b0 += batch, ++nb) {   // the last batch takes what rounding leaves over
+      const float w = batch_sum[warp][nb];
+      if (target < run + w) break;
+      run += w;
     }
-    chosen = pick;  // the ranges [start, stop) are disjoint: one writer
+    const int b1 = min(end, b0 + batch);
+    int pick = b1 - 1;
+    for (int i0 = b0; i0 < b1; i0 += 256) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = i0 + 32 * j + lane < b1 ? z[i0 + 32 * j + lane] : -INFINITY;
+      bool found = false;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + 32 * j + lane;
+        float in = i < b1 ? expf((v[j] - best) * inv_t) : 0.0f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float n = __shfl_up_sync(0xffffffffu, in, o);
+          if (lane >= o) in += n;
+        }
+        const unsigned int passed = __ballot_sync(0xffffffffu, i < b1 && target < run + in);
+        if (passed && !found) {
+          pick = i0 + 32 * j + __ffs(passed) - 1;
+          found = true;
+        }
+        run += __shfl_sync(0xffffffffu, in, 31);
+      }
+      if (found) break;
+    }
+    if (lane == 0) chosen = pick;
   }
   __syncthreads();
   if (tid == 0) out[r] = chosen >= 0 ? chosen : best_i;  // rounding left target at the very end
