@@ -183,7 +183,8 @@ def main() -> int:
                     help="decode: the contract line (default); serving: the Qwen3-4B serving mix, its own line")
     ap.add_argument("--requests", type=int, default=64, help="serving mix: concurrent requests")
     ap.add_argument("--kv-pages", type=int, default=0, help="serving mix: cache pages (0: enough for every request at once)")
-    ap.add_argument("--profile", choices=["decode", "prefill"], help="run two steps of one kind, kernel by kernel, between "
+    ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], help="run two steps of one kind (mixed: 30 requests "
+                    "decoding at context 2,048 beside a 482-token portion of a prompt, the serving default of 512 tokens a step), kernel by kernel, between "
                     "cudaProfilerStart/Stop (for ncu --profile-from-start off) and print no bench line")
     args = ap.parse_args()
 
@@ -220,6 +221,8 @@ def main() -> int:
 
     V = cfg["vocab_size"]
     max_batch = B if args.no_points else max(B, 64)
+    if args.profile == "mixed":
+        max_batch = 32
     pages_per_seq = (CTX + PAGE - 1) // PAGE + 1
     cache, states = make_cache(model, page_size=PAGE, num_pages=max_batch * pages_per_seq + 8, max_requests=max_batch * 2)
     chunk = max(args.prefill_tokens, 2048)
@@ -269,16 +272,22 @@ def main() -> int:
         if args.profile == "decode":
             reqs = fill(B, CTX - 4)
             steps = [[StepEntry(r, [int(rng.integers(0, V))], CTX - 4 + i, [0]) for r in reqs] for i in range(3)]
+        elif args.profile == "mixed":
+            reqs = fill(30, 2048)
+            prompt = fill(1, 1024)[0]
+            greedy = [(SamplingParams(), 0)] * 30
+            steps = [[StepEntry(r, [int(rng.integers(0, V))], 2048 + i, [0]) for r in reqs] +
+                     [StepEntry(prompt, rng.integers(0, V, 482), 1024 + 482 * i, [])] for i in range(3)]
         else:
             reqs = [cache.new_request() for _ in range(3)]
             for r in reqs:
                 cache.reserve(r, args.prefill_tokens)
             steps = [[StepEntry(r, rng.integers(0, V, args.prefill_tokens), 0, [args.prefill_tokens - 1])] for r in reqs]
-        runner.run(steps[0], greedy if args.profile == "decode" else None)      # warm-up, not profiled
+        runner.run(steps[0], greedy if args.profile != "prefill" else None)      # warm-up, not profiled
         torch.cuda.synchronize()
         torch.cuda.profiler.start()
         for st in steps[1:]:
-            runner.run(st, greedy if args.profile == "decode" else None)
+            runner.run(st, greedy if args.profile != "prefill" else None)
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
         runner.check()

@@ -140,3 +140,24 @@ def test_decode_attention_splits_respect_the_kernel_limits():
     assert sk < 3000 and sk % 64 == 0 and ms == -(-3000 // sk) and sum(-(-c // sk) for c in lens) * 8 <= 2 * att.NUM_SMS
     assert att.decode_splits(3000, 30, 8, 16) == (3008, 1)
     assert att.decode_splits(4096, 8, 8, 16, [4096] * 8) == att.decode_splits(4096, 8, 8, 16)
+
+
+def test_matrix_product_plans_are_ones_the_kernel_takes():
+    """Whatever the sizes: a tile width the kernel has, splits that leave every split k-blocks to do, k whole where
+    the caller asks for it, and no more partial sums than the capacity the parts size their scratch for."""
+    from tiny_inference_engine_b200.ops import gemm_select as gs
+    for N, K in ((6144, 4096), (4096, 12288), (2560, 9728), (151936, 4096), (72, 200), (130, 75), (300, 64), (1000, 520)):
+        k_blocks = -(-K // 64)
+        for M in (1, 7, 8, 64, 128, 129, 200, 256, 384, 512, 513, 1000, 2048, 8192):
+            for split_many in (True, False):
+                transposed, bn, splits = gs.plan(M, N, K, split_many)
+                assert bn in (16, 32, 64, 128, 256) and 1 <= splits <= max(1, k_blocks)
+                assert transposed == (1 if M <= 128 else 0)
+                if M > 128:
+                    assert splits <= 4 or N <= 128
+                    assert splits == 1 or (split_many and k_blocks // splits >= 8)
+                if splits > 1:
+                    assert splits * M * N <= gs.partial_capacity(max(M, 512), N, K, split_many)
+    # the shapes the cost estimate was fitted on: the measured best, or close to it
+    assert gs.plan(512, 2560, 9728)[1:] == (256, 3) and gs.plan(384, 4096, 12288)[1:] == (256, 3)
+    assert gs.plan(2048, 24576, 4096)[2] == 1

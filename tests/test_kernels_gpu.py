@@ -396,6 +396,30 @@ def test_gemm_tensor_cores_every_tiling(ops, transposed, bn, splits):
     assert (wide[:, :8] == 7).all() and (wide[:, 8 + N:] == 7).all()      # nothing is written beside the output
 
 
+@pytest.mark.parametrize("bn,splits", [(128, 4), (256, 3), (256, 4)])
+def test_gemm_tensor_cores_split_products_of_many_tokens(ops, bn, splits):
+    """More tiles times splits than SMs: every split's CTAs walk several tiles, and the sizes end inside a tile in
+    every direction. Both the finished product and the partial sums left for a consumer."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(bn + splits)
+    M, N, K = 700, 2000, 1096
+    a, w = as_stored(rng.standard_normal((M, K)), "bfloat16"), as_stored(rng.standard_normal((N, K)), "bfloat16")
+    want = plain.linear(a, w)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm_select.gemm_tc(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out, transposed=0, bn=bn, splits=splits, pair=False)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(out), want) < TOL["bfloat16"]
+    scratch = torch.full((splits * M * N + 16,), float("nan"), device="cuda")
+    got = gemm_select.gemm_tc(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out, transposed=0, bn=bn, splits=splits, pair=False,
+                              partial_scratch=lambda n: scratch[:n])
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert isinstance(got, ops.SplitSum) and got.M == M and got.N == N
+    parts = scratch[:got.splits * M * N].view(got.splits, M, N)
+    assert rel_err(parts.sum(0).cpu().numpy(), want) < 2e-5 and torch.isnan(scratch[got.splits * M * N:]).all()
+
+
 @pytest.mark.parametrize("silu", [False, True])
 def test_gemm_on_pairs_of_sms(ops, silu):
     """The cta_group::2 kernel on more tiles than there are pairs of SMs (each pair walks several,
@@ -536,10 +560,11 @@ def test_tensor_core_attention_finds_one_far_key(ops, far):
 
 
 @pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(8, 2, 128, 16, 0), (6, 2, 64, 8, 0), (3, 3, 128, 64, 0), (16, 1, 64, 128, 0),
-                                                  (8, 2, 128, 16, 70), (10, 2, 64, 32, 333)])
+                                                  (8, 2, 128, 16, 70), (10, 2, 64, 32, 333), (32, 2, 128, 16, 0), (32, 2, 128, 16, 100)])
 def test_tcgen05_prompt_attention_on_long_portions(ops, Hq, Hkv, Dh, page, window):
     """Portions that fill several 256-row tiles and end inside one: a whole prompt, a portion over a long
-    cached prefix, a portion whose rows end one short of a tile, and a short one; scattered pages."""
+    cached prefix, a portion whose rows end one short of a tile, and a short one; scattered pages. With 16 query
+    heads to a key head there are so many rows that a CTA takes two row tiles; with fewer, one."""
     from tiny_inference_engine_b200.ops import gemm_select
     rng = np.random.default_rng(Hq + Dh + page + window)
     ctx = [333, 900, 64 * 3 - 1, 21]
