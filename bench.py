@@ -35,6 +35,9 @@ QWEN3_8B = {
 }
 # BASELINE.json configs[3]: the Qwen3-4B shape of the serving mix (`--workload serving`).
 QWEN3_4B = dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True)
+# A larger shape of the same architecture (`--shape 32b`): 64 layers, 64 query heads over 8 kv heads.
+QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64)
+SHAPES = {"8b": ("Qwen3-8B", QWEN3_8B), "4b": ("Qwen3-4B", QWEN3_4B), "32b": ("Qwen3-32B", QWEN3_32B)}
 FULL_LAYERS = 36
 PAGE = 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -115,6 +118,7 @@ def serving_mix(args) -> int:
     import torch
     from tiny_inference_engine_b200 import (Engine, SamplingParams, Scheduler, SchedulerConfig, ServingConfig, StepRunner,
                                             load_model, make_cache)
+    args.layers = args.layers or QWEN3_4B["num_hidden_layers"]
     cfg = dict(QWEN3_4B, num_hidden_layers=args.layers)
     with tempfile.TemporaryDirectory() as d:
         (Path(d) / "config.json").write_text(json.dumps(cfg))
@@ -176,7 +180,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096, help="context length at which the timed decode steps end")
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported in config)")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: the contract line is the default, 8b")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
@@ -207,7 +212,10 @@ def main() -> int:
     from tiny_inference_engine_b200.ops import library as kernel_library
 
     pk, pk_src = peaks()
-    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    args.layers = args.layers or full_layers
+    cfg = dict(shape, num_hidden_layers=args.layers)
     K, W, B, CTX = args.steps, args.warmup, args.batch, args.context
     rng = np.random.default_rng(0)
     clocks = ClockSampler()
@@ -360,14 +368,14 @@ def main() -> int:
     step_bytes = weight_bytes_per_decode_step(cfg, args.layers) + B * (CTX - K / 2) * kv_bytes_per_token(cfg, args.layers)
     achieved = step_bytes / (ms_step / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, 1 B200)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tok/s at batch {B} ({shape_name} bf16, 1 B200)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
-        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_model": FULL_LAYERS, "hidden": cfg["hidden_size"],
+        "config": {"model": f"{shape_name} shape", "layers": args.layers, "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": V, "global_batch": B, "seq_len": CTX,
                    "context_during_timed_steps": f"{CTX - K}..{CTX}", "page_size": PAGE, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (16 GB of weights per step)", "peaks": pk_src},
+                   "l2": f"inputs larger than L2 ({weight_bytes_per_decode_step(cfg, args.layers) / 1e9:.0f} GB of weights per step)", "peaks": pk_src},
         "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
         "gpu_launches": int(launches),
         "prefill": {"value": round(T / (pre / 1e3), 1), "tokens": T, "ms": round(pre, 3),
