@@ -299,7 +299,7 @@ def test_sampling_kernel_frequencies(ops):
     assert np.abs(np.bincount(out.cpu().numpy(), minlength=5) / 2000 - p).max() < 0.03
 
 
-def _filtered_case(ops, z, rows, counter):
+def _filtered_case(ops, z, rows, counter, one_cta=False):
     """rows: (temperature, top_k, top_p, seed) for each row of z; the kernels against the sampler on the host."""
     from tiny_inference_engine_b200.sampling import SamplingParams
     from tiny_inference_engine_b200.sampling.sampler import sample_host
@@ -309,14 +309,17 @@ def _filtered_case(ops, z, rows, counter):
     seeds = np.array([q.seed for q in params], dtype=np.uint64)
     out = torch.full((R,), -1, dtype=torch.int32, device="cuda")
     ops.sample(dev(z), out, dev(inv), torch.from_numpy(seeds.view(np.int64)).cuda(), dev(np.full(R, counter), torch.int64),
-               dev(np.array([q.top_k for q in params]), torch.int32), dev(np.array([q.top_p for q in params], dtype=np.float32)))
+               dev(np.array([q.top_k for q in params]), torch.int32), dev(np.array([q.top_p for q in params], dtype=np.float32)),
+               one_cta=one_cta)
     want = [sample_host(z[r], params[r], counter) for r in range(R)]
     assert out.tolist() == want, [(rows[r], out[r].item(), want[r]) for r in range(R) if out[r].item() != want[r]]
 
 
-def test_sampling_kernel_top_k_and_top_p(ops):
+@pytest.mark.parametrize("one_cta", [False, True])
+def test_sampling_kernel_top_k_and_top_p(ops, one_cta):
     """Few kept candidates are sorted in shared memory; more than 1,024, or top-p alone, are found by selection
-    over the whole row. Equal logits are taken in id order; -inf logits weigh nothing."""
+    over the whole row. Equal logits are taken in id order; -inf logits weigh nothing. Both kernels: the cluster of
+    8 CTAs a row, and the one-CTA kernel of the largest vocabularies."""
     rng = np.random.default_rng(11)
     V = 1531
     rows = []
@@ -331,9 +334,9 @@ def test_sampling_kernel_top_k_and_top_p(ops):
     z[5] = 0.25                                                          # a row of equal logits: the cut falls among ties
     z[6] = np.round(z[6])                                                # many ties at every value
     for counter in (0, 1, 2, 3, 77, 2 ** 33):
-        _filtered_case(ops, z, rows, counter)
+        _filtered_case(ops, z, rows, counter, one_cta)
     z[7, 3] = np.inf                                                     # a certain token
-    _filtered_case(ops, z, rows, 5)
+    _filtered_case(ops, z, rows, 5, one_cta)
 
 
 def test_sampling_kernel_filters_over_a_large_vocabulary(ops):
@@ -343,6 +346,7 @@ def test_sampling_kernel_filters_over_a_large_vocabulary(ops):
     z = (rng.standard_normal((len(rows), V)) * np.array([3, 3, 0.01, 0.01, 5, 1])[:, None]).astype(np.float32)
     for counter in (0, 1, 2):
         _filtered_case(ops, z, rows, counter)
+    _filtered_case(ops, z, rows, 3, one_cta=True)
 
 
 def test_refusals_are_clear(ops):

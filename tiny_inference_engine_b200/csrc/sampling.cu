@@ -779,15 +779,16 @@ TIE_API int tie_sample(const float* logits, long long row_stride, int rows, int 
 }
 
 // Overwrites out[r] for the rows that filter (top_k[r] in (0, vocab) or top_p[r] < 1, with a temperature);
-// call it after tie_sample on the same rows.
+// call it after tie_sample on the same rows. one_cta != 0 runs the kernel for the largest vocabularies whatever
+// the size (tests).
 TIE_API int tie_sample_filtered(const float* logits, long long row_stride, int rows, int vocab, const float* inv_temperature,
                                 const int* top_k, const float* top_p, const unsigned long long* seeds,
-                                const unsigned long long* counters, int* out, cudaStream_t s) {
+                                const unsigned long long* counters, int* out, int one_cta, cudaStream_t s) {
   TIE_REQUIRE(rows >= 0 && vocab > 0 && vocab < (1 << 24), "sample: bad sizes rows=%d vocab=%d", rows, vocab);
   TIE_REQUIRE(inv_temperature != nullptr && top_k != nullptr && top_p != nullptr && seeds != nullptr && counters != nullptr,
               "sample: filtered sampling needs temperatures, top_k, top_p, seeds and counters");
   if (rows == 0) return kOk;
-  if (vocab <= kClusterCtas * kFilterThreads * kClusterMaxE)
+  if (!one_cta && vocab <= kClusterCtas * kFilterThreads * kClusterMaxE)
     return launch_filtered_cluster(logits, row_stride, rows, vocab, inv_temperature, top_k, top_p, seeds, counters, out, s);
   static bool configured = false;
   if (!configured) {

@@ -343,10 +343,11 @@ def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None, top_k=None,
-           top_p=None) -> None:
+           top_p=None, one_cta: bool = False) -> None:
     """out[r] = first maximum of row r (inv_temperature None or 0), or a draw from softmax(logits * inv_temperature)
     with the Philox uniform of (seeds[r], counters[r]). With top_k (int32) and top_p (float32) the rows whose
-    top_k is in (0, vocab) or whose top_p is below 1 draw from the candidates those keep, most likely first."""
+    top_k is in (0, vocab) or whose top_p is below 1 draw from the candidates those keep, most likely first
+    (`one_cta`: with the kernel that serves the largest vocabularies, whatever the size; for tests)."""
     _dev(logits, out, inv_temperature, seeds, counters, top_k, top_p)
     R, V = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be float32 rows")
@@ -362,7 +363,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=
         _need(top_k.dtype == torch.int32 and top_p.dtype == torch.float32 and top_k.numel() >= R and top_p.numel() >= R,
               "sample: top_k int32 [R], top_p float32 [R]")
         call("tie_sample_filtered", logits.data_ptr(), logits.stride(0), R, V, inv_temperature.data_ptr(), top_k.data_ptr(),
-             top_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _stream())
+             top_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), 1 if one_cta else 0, _stream())
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=None):

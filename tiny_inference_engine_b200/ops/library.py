@@ -27,7 +27,7 @@ _SIGNATURES = {
     "tie_attention_rows": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_split": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_sample": [P, L, I, I, P, P, P, P, P],
-    "tie_sample_filtered": [P, L, I, I, P, P, P, P, P, P, P],
+    "tie_sample_filtered": [P, L, I, I, P, P, P, P, P, P, I, P],
     "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, I, I, I, P],
     "tie_gemm_tc2": [I, P, P, P, I, I, I, L, L, L, I, P],
     "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
