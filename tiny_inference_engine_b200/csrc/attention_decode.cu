@@ -22,6 +22,7 @@
 // written directly. Every mbarrier wait is bounded; on expiry the status word gets a code.
 #include "attention_mma.cuh"
 #include "tma.cuh"
+#include "launchers.h"
 
 namespace tie {
 

@@ -15,6 +15,7 @@
 // Tiles of keys that lie wholly below every row's position (and inside the window) need no mask.
 #include "attention_mma.cuh"
 #include "tma.cuh"
+#include "launchers.h"
 
 namespace tie {
 

@@ -27,6 +27,7 @@
 // tiles with the most keys of every kv head run first.
 #include "attention_mma.cuh"
 #include "umma.cuh"
+#include "launchers.h"
 
 namespace tie {
 

@@ -18,6 +18,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "launchers.h"
 
 namespace tie {
 

@@ -17,6 +17,7 @@
 //                  of every 64-key tile, combine their partial results in shared memory and leave
 //                  (acc, max, sum) per split in scratch memory for attention_merge_kernel.
 #include "attention_mma.cuh"
+#include "launchers.h"
 
 namespace tie {
 

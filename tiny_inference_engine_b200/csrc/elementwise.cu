@@ -7,6 +7,7 @@
 // embed :51-76, rms_norm :141-159, rope_neox :161-193, silu_mul :195-207, add :209-221,
 // gather_rows :223-233, kv_write :235-259. The fusions are this engine's own.
 #include "common.cuh"
+#include "launchers.h"
 
 namespace tie {
 

@@ -6,6 +6,7 @@
 // counterpart is its dot-product matmul (src/backend/cpu/cpu_backend.cpp:78-139): weights
 // in the checkpoint's [out, in] layout, y = x . W^T, no bias.
 #include "common.cuh"
+#include "launchers.h"
 
 namespace tie {
 

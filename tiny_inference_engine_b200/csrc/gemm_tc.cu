@@ -23,6 +23,7 @@
 // status word, stops waiting, frees its tensor memory and returns; the host reads the word.
 // No TMA multicast is used anywhere.
 #include "umma.cuh"
+#include "launchers.h"
 
 namespace tie {
 

@@ -22,6 +22,7 @@
 // it is, hundreds of runs of the same steps are clean. The prologue this gives up is a few microseconds of a
 // product that takes hundreds.
 #include "umma.cuh"
+#include "launchers.h"
 
 namespace tie {
 

@@ -23,7 +23,7 @@ from __future__ import annotations
 
 import gc
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Callable, Sequence
 
 import numpy as np
@@ -97,6 +97,7 @@ class StepContext:
     top_k: torch.Tensor | None = None              # given only when a row filters (top-k, top-p)
     top_p: torch.Tensor | None = None
     single_contexts: tuple | None = None   # context lengths of the sequences that bring one token, when the step is not a captured graph
+    memo: dict = field(default_factory=dict)   # what a part works out once per step and every layer of its kind uses again
 
 
 def _round_up(n: int, m: int) -> int:

@@ -67,6 +67,12 @@ def library() -> ctypes.CDLL:
         lib.tie_kernel_status.argtypes = []
         lib.tie_gemm_tc_real_splits.restype = c_int
         lib.tie_gemm_tc_real_splits.argtypes = [c_int, c_int]
+        lib.tie_replay_launcher_id.restype = c_int
+        lib.tie_replay_launcher_id.argtypes = [ctypes.c_char_p]
+        lib.tie_replay_launcher_args.restype = c_int
+        lib.tie_replay_launcher_args.argtypes = [c_int]
+        lib.tie_replay_layers.restype = c_int
+        lib.tie_replay_layers.argtypes = [P, P, P, P, P, I, P, I, I, P]
         for name, args in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = args
@@ -103,6 +109,7 @@ def launch_count() -> int:
 
 
 _ENTRY: dict = {}     # name -> bound entry point (looked up once: eager steps make hundreds of calls)
+_RECORDING = None     # a list while ops/replay.py records the calls of one layer
 
 
 def call(name: str, *args) -> None:
@@ -116,3 +123,5 @@ def call(name: str, *args) -> None:
         from ..errors import InvalidArgument, TieError
         msg = library().tie_last_error().decode()
         raise (InvalidArgument if status == 1 else TieError)(msg)
+    if _RECORDING is not None:
+        _RECORDING.append((name, args))

@@ -28,6 +28,8 @@ NUM_SMS = 148
 
 
 class GQAttention(Mixer):
+    launches_only = True
+
     def __init__(self, spec, dtype, prefix: str = ""):
         p = spec.params
         self.prefix = prefix + p.get("prefix", "")
@@ -146,7 +148,14 @@ class GQAttention(Mixer):
             page = cache.k.shape[2]
             if tc and ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, page):
                 lens = ctx.single_contexts if self.window <= 0 else None
-                split_keys, max_splits = decode_splits(longest, ctx.single_count, Hkv, page, lens)
+                key = ("decode_splits", longest, ctx.single_count, Hkv, page, lens is None)
+                memo = getattr(ctx, "memo", None)
+                splits = memo.get(key) if memo is not None else None
+                if splits is None:
+                    splits = decode_splits(longest, ctx.single_count, Hkv, page, lens)
+                    if memo is not None:
+                        memo[key] = splits
+                split_keys, max_splits = splits
                 scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
                                       torch.float32)
                 counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * Hkv, torch.int32)
@@ -177,7 +186,8 @@ def decode_splits(longest: int, sequences: int, kv_heads: int, page_size: int, c
     cap = (TMA_DECODE_TABLE_ENTRIES // boxes_per_tile - 1) * 64
     if contexts:
         split_keys = SPLIT_KEYS
-        while split_keys < longest and sum(-(-c // split_keys) for c in contexts) * kv_heads > slots:
+        lens = np.asarray(contexts, dtype=np.int64)
+        while split_keys < longest and int((-(-lens // split_keys)).sum()) * kv_heads > slots:
             split_keys += max(64, split_keys // 8 // 64 * 64)
         split_keys = min(split_keys, max(SPLIT_KEYS, -(-longest // 64) * 64))
     else:

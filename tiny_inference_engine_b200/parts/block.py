@@ -8,6 +8,8 @@ from .base import Block, build_part, register_part
 
 
 class PreNormBlock(Block):
+    launches_only = True
+
     def __init__(self, layer_spec, dtype, prefix: str = ""):
         self.mixer_norm = build_part("norm", layer_spec.mixer_norm, dtype)
         self.mixer = build_part("mixer", layer_spec.mixer, dtype)

@@ -11,6 +11,8 @@ from .base import FeedForward, register_part, to_compute
 
 
 class SwiGLU(FeedForward):
+    launches_only = True
+
     def __init__(self, spec, dtype, prefix: str = ""):
         p = spec.params
         self.prefix = prefix + p.get("prefix", "")

@@ -11,6 +11,7 @@ from .base import Norm, register_part
 
 
 class RMSNorm(Norm):
+    launches_only = True
     takes_split_sum = True      # add_norm adds the partial sums of a split product itself
 
     def __init__(self, spec, dtype, prefix: str = ""):

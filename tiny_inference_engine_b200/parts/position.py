@@ -13,6 +13,8 @@ from .base import PositionEncoding, register_part
 
 
 class RotaryEncoding(PositionEncoding):
+    launches_only = True
+
     def __init__(self, spec, dtype, prefix: str = ""):
         self.theta = float(spec["theta"])
         self.head_dim = int(spec["head_dim"])
@@ -35,6 +37,8 @@ class RotaryEncoding(PositionEncoding):
 
 class NoPositionEncoding(PositionEncoding):
     """Leaves q and k as they are."""
+
+    launches_only = True
 
     def __init__(self, spec=None, dtype=None, prefix: str = ""):
         pass
