@@ -11,7 +11,7 @@ import plain_qwen3 as plain
 from tiny_inference_engine_b200 import load_model, make_cache
 from tiny_inference_engine_b200.errors import InvalidArgument
 from tiny_inference_engine_b200.ops import library, replay
-from tiny_inference_engine_b200.parts.model import LayerRuns, walk_part
+from tiny_inference_engine_b200.parts.layer_runs import LayerRuns, walk_part
 
 
 @pytest.fixture(autouse=True)

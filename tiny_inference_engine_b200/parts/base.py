@@ -41,7 +41,7 @@ class Part:
     # True for a part whose forward does its GPU work through this package's launchers only (no torch
     # operations), with arguments that depend on the step, on sizes and constants that layers built alike
     # share, and on tensors the part holds as attributes. A run of layers made of such parts is issued by
-    # one call after the first two (parts/model.py). Parts that do not say so run layer by layer.
+    # one call after the first two (parts/layer_runs.py). Parts that do not say so run layer by layer.
     launches_only = False
 
     def needs(self) -> dict[str, TensorNeed]:
