@@ -7,10 +7,11 @@
 One JSON line on stdout. `value` is decoded tokens per second at batch 8 with the timed steps
 ending at the benchmark context (device time, CUDA events around K decode steps through the
 step function); `e2e` is the same through the Python entry point (Engine.step: host token
-ids in, sampled ids out, every step). `prefill` is one 2,048-token prompt in one step;
-`roofline` is the bytes a decode step has to read (every weight it uses once, and the cache
-of the live requests) over its time, against the measured copy bandwidth; `points` holds
-decode at batch 1 and 64. Weights are 16 GB and the caches gigabytes, far more than the
+ids in, sampled ids out, every step). `prefill` is one 2,048-token prompt in one step
+(timed first, as a burst); `roofline` is the bytes a decode step has to read (every weight
+it uses once, and the cache of the live requests) over its time, against the measured copy
+bandwidth (`frac_b1`, `frac_b64`: the same for the two points); `points` holds decode at
+batch 1 and 64. Weights are 16 GB and the caches gigabytes, far more than the
 126 MB L2, so no flush is needed between steps.
 """
 import argparse
@@ -303,16 +304,8 @@ def main() -> int:
         return 0
 
     clocks.start()
-    ms_step, launches = decode_device(B, K, W)
-    value = B / (ms_step / 1e3)
-
-    points = {}
-    if not args.no_points:
-        for b in (1, 64):
-            ms_b, _ = decode_device(b, max(16, K // 4), W)
-            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
-
-    # prefill: one prompt, one step, the logits of its last token
+    # prefill: one prompt, one step, the logits of its last token. Timed first: eight steps of some 25 ms are a burst,
+    # which is what the peak it is held against was measured as; the decode runs below go on for seconds under the power cap.
     T = args.prefill_tokens
     pre_ms = []
     for i in range(3 + 5):              # three warm-up steps, five timed ones
@@ -330,6 +323,18 @@ def main() -> int:
     runner.check()
     pre = sorted(pre_ms[3:])[2]          # the median
     flops = prefill_flops(cfg, args.layers, T)
+
+    ms_step, launches = decode_device(B, K, W)
+    value = B / (ms_step / 1e3)
+
+    points, point_fracs = {}, {}
+    if not args.no_points:
+        for b in (1, 64):
+            steps_b = max(16, K // 4)
+            ms_b, _ = decode_device(b, steps_b, W)
+            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+            bytes_b = weight_bytes_per_decode_step(cfg, args.layers) + b * (CTX - steps_b / 2) * kv_bytes_per_token(cfg, args.layers)
+            point_fracs[f"frac_b{b}"] = round(bytes_b / (ms_b / 1e3) / 1e9 / pk["hbm_gbs"], 4)
 
     # end to end through the Python entry point: host token ids in, sampled ids out, every step
     serving = ServingConfig(max_tokens_per_step=chunk, max_seqs=B)
@@ -374,14 +379,14 @@ def main() -> int:
         "config": {"model": f"{shape_name} shape", "layers": args.layers, "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": V, "global_batch": B, "seq_len": CTX,
-                   "context_during_timed_steps": f"{CTX - K}..{CTX}", "page_size": PAGE, "parallelism": "single GPU",
+                   "context_during_timed_steps": f"{CTX - K}..{CTX}", "page_size": PAGE, "parallelism": "single GPU", "order": "prefill timed first, then decode",
                    "l2": f"inputs larger than L2 ({weight_bytes_per_decode_step(cfg, args.layers) / 1e9:.0f} GB of weights per step)", "peaks": pk_src},
         "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
         "gpu_launches": int(launches),
         "prefill": {"value": round(T / (pre / 1e3), 1), "tokens": T, "ms": round(pre, 3),
                     "frac": round(flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+                     "frac": round(achieved / pk["hbm_gbs"], 4), **point_fracs},
         "points": points,
         "clocks": clk,
     }
