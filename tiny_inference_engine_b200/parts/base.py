@@ -40,7 +40,8 @@ class Part:
 
     # True for a part whose forward does its GPU work through this package's launchers only (no torch
     # operations), with arguments that depend on the step, on sizes and constants that layers built alike
-    # share, and on tensors the part holds as attributes. A run of layers made of such parts is issued by
+    # share, and on tensors the part holds as attributes (its own, in a list or tuple, or in a part it holds the
+    # same way; not in a dictionary). A run of layers made of such parts is issued by
     # one call after the first two (parts/layer_runs.py). Parts that do not say so run layer by layer.
     launches_only = False
 

@@ -33,7 +33,10 @@ def walk_part(obj, tensors: list, scalars: list, seen: set) -> bool:
             elif isinstance(item, int):
                 if item < (1 << 32) and not name.endswith("_ptr"):
                     scalars.append((name, item))
-            elif isinstance(item, (str, dict, np.ndarray)):
+            elif isinstance(item, dict):
+                if any(isinstance(x, (torch.Tensor, Part)) for x in item.values()):
+                    ok = False      # tensors in a dictionary have no fixed order to list them in
+            elif isinstance(item, (str, np.ndarray)):
                 continue
             elif hasattr(item, "__dict__") and id(item) not in seen and (
                     isinstance(item, Part) or type(item).__module__.split(".")[0] == _PACKAGE):
