@@ -111,3 +111,34 @@ def test_a_part_that_does_not_promise_to_launch_only_keeps_its_layers_out(tmp_pa
         assert np.array_equal(got[0], got[1])
     finally:
         register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_engine_generates_the_same_tokens_with_repeated_layers(tmp_path, dtype):
+    """Six layers alike under the scheduler: prompts cut into portions of 24 tokens beside decoding requests, a pool
+    so small that requests are preempted and prefilled again, steps queued ahead, greedy and sampled requests. The
+    tokens are those of the same engine with every layer issued from Python, and those of the plain implementation
+    where it generates greedily in 32-bit."""
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig, load_engine
+    from tiny_inference_engine_b200.ops import replay
+    cfg = dict(plain.TINY_D, num_hidden_layers=6)
+    w = sharp_weights(cfg, 8)
+    plain.write_model_dir(tmp_path, cfg, w)
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (5, 61, 30, 47, 2, 90)]
+    params = [SamplingParams(max_tokens=6 + 3 * i, temperature=0.8 if i % 2 else 0.0, seed=70 + i) for i in range(6)]
+    outs = {}
+    for on in (True, False):
+        eng = load_engine(tmp_path, dtype=dtype, num_pages=10, page_size=16, policy="fcfs", serving=ServingConfig(24, 8))
+        eng.model.layer_replay = on
+        before = replay.layers_repeated
+        outs[on] = eng.generate_batch(prompts, params)
+        while eng.has_work():
+            eng.step()
+        st = eng.stats()
+        assert st.preemptions > 0 and st.steps_ahead > 0 and eng.cache.num_free() == 10
+        assert (replay.layers_repeated > before) == on
+    assert outs[True] == outs[False]
+    if dtype == "float32":
+        for i in (0, 2, 4):
+            assert outs[True][i] == plain.generate(w, cfg, prompts[i], params[i].max_tokens)
