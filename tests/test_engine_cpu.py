@@ -1,0 +1,111 @@
+"""The engine's decisions without a GPU: a stand-in for the step function (tests/fake_runner.py) whose tokens depend
+on a request's whole prefix, so that any token fed at a wrong position, taken from a wrong row, sampled with a wrong
+index, lost in a preemption or handed out twice changes what a request generates. Every run is compared with what
+each request generates alone."""
+import random
+
+import pytest
+
+from fake_runner import VOCAB, FakeRunner, generate_alone
+from tiny_inference_engine_b200.cache import CacheManager
+from tiny_inference_engine_b200.engine import Engine, FinishReason, Scheduler, SchedulerConfig, SeqState, ServingConfig
+from tiny_inference_engine_b200.parts import CacheNeed
+from tiny_inference_engine_b200.sampling import SamplingParams
+
+PAGE = 4
+
+
+class _Spec:
+    vocab_size = VOCAB
+    max_positions = 4096
+
+
+class _Model:
+    spec = _Spec()
+
+
+def make_engine(pages=64, tokens=16, seqs=4, policy="fcfs", run_ahead=True, stop=()):
+    cache = CacheManager([CacheNeed("full", 1, 8)], page_size=PAGE, num_pages=pages)
+    serving = ServingConfig(tokens, seqs, run_ahead=run_ahead)
+    runner = FakeRunner(cache, tokens, seqs)
+    return Engine(_Model(), cache, Scheduler(cache, SchedulerConfig(serving, policy)), serving, stop_tokens=stop, runner=runner)
+
+
+def drain(eng):
+    while eng.has_work():
+        eng.step()
+
+
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_batched_requests_generate_what_each_generates_alone(run_ahead):
+    prompts = [[1, 2, 3], list(range(30)), [7] * 9, [5], list(range(100, 121))]
+    params = [SamplingParams(max_tokens=4 + 3 * i, seed=i) for i in range(5)]
+    eng = make_engine(run_ahead=run_ahead)
+    assert eng.generate_batch(prompts, params) == [generate_alone(p, q) for p, q in zip(prompts, params)]
+    drain(eng)
+    assert eng.cache.num_free() == 64
+    assert (eng.stats().steps_ahead > 0) == run_ahead
+    assert eng.stats().prefill_tokens == sum(map(len, prompts))
+    assert eng.stats().decode_tokens == sum(q.max_tokens for q in params) - len(prompts)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_workloads_with_small_pools_stop_tokens_and_cancels(seed):
+    rng = random.Random(seed)
+    n = rng.randint(2, 9)
+    prompts = [[rng.randrange(VOCAB) for _ in range(rng.randint(1, 40))] for _ in range(n)]
+    params = [SamplingParams(max_tokens=rng.randint(1, 30), seed=rng.randrange(100)) for _ in range(n)]
+    free = [generate_alone(p, q) for p, q in zip(prompts, params)]
+    stop = {rng.choice(rng.choice(free)) for _ in range(2)} if rng.random() < 0.6 else set()
+    want = [generate_alone(p, q, stop) for p, q in zip(prompts, params)]
+    longest = max(len(p) + q.max_tokens for p, q in zip(prompts, params))
+    pages = rng.choice([-(-longest // PAGE) + 1, 24, 200])
+    eng = make_engine(pages=pages, tokens=rng.choice([8, 16, 64]), seqs=rng.choice([2, 4, 8]), run_ahead=rng.random() < 0.7,
+                      policy=rng.choice(["fcfs", "srpt-aging"]), stop=stop)
+    ids, arrivals = [], sorted(rng.randint(0, 12) for _ in range(n))
+    cancel_at = {i: rng.randint(1, 5) for i in range(n) if rng.random() < 0.15}    # request -> after how many of its tokens
+    seen = {}
+
+    def on_token(seq_id, token):
+        seen.setdefault(seq_id, []).append(token)
+        i = ids.index(seq_id)
+        if cancel_at.get(i) == len(seen[seq_id]):
+            eng.cancel(seq_id)
+
+    eng.set_token_callback(on_token)
+    step = 0
+    while len(ids) < n or eng.has_work():
+        while len(ids) < n and arrivals[len(ids)] <= step:
+            ids.append(eng.add_request(prompts[len(ids)], params[len(ids)]))
+        eng.step()
+        step += 1
+        assert step < 5000
+    for i, sid in enumerate(ids):
+        seq = eng.sequence(sid)
+        got = seq.tokens[seq.prompt_len:]
+        assert seq.state == SeqState.FINISHED and seen.get(sid, []) == got
+        if i in cancel_at and cancel_at[i] <= len(want[i]):      # its own callback cancelled it, even at its last token
+            assert seq.finish_reason == FinishReason.CANCELLED and got == want[i][:cancel_at[i]]
+        else:
+            assert got == want[i], f"request {i}"
+            assert seq.finish_reason == (FinishReason.STOP if got[-1] in stop else FinishReason.LENGTH)
+    assert eng.cache.num_free() == pages
+
+
+@pytest.mark.parametrize("run_ahead", [False, True])
+@pytest.mark.parametrize("fail_at", [1, 2, 3, 5, 8, 13])
+def test_a_failed_step_is_rolled_back(run_ahead, fail_at):
+    prompts = [list(range(9)), [3] * 20, [200, 100], [9, 8, 7, 6]]
+    params = [SamplingParams(max_tokens=7, seed=i) for i in range(4)]
+    eng = make_engine(tokens=8, seqs=4, run_ahead=run_ahead)
+    eng.runner.fail_at = {fail_at}
+    ids = [eng.add_request(p, q) for p, q in zip(prompts, params)]
+    failures = 0
+    while eng.has_work():
+        try:
+            eng.step()
+        except RuntimeError:
+            failures += 1
+    assert failures == (1 if eng.runner.runs >= fail_at else 0) and eng.runner.runs >= 8
+    assert [eng.sequence(i).tokens[eng.sequence(i).prompt_len:] for i in ids] == [generate_alone(p, q) for p, q in zip(prompts, params)]
+    assert eng.cache.num_free() == 64

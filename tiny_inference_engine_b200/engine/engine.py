@@ -10,7 +10,6 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Sequence as Seq
 
-import torch
 
 from ..cache.manager import CacheManager, blocks_for
 from ..cache.state_slots import StateSlots
@@ -221,7 +220,7 @@ class Engine:
         ahead, self._ahead = self._ahead, None
         if ahead is None:
             return
-        torch.cuda.current_stream().synchronize()
+        self.runner.synchronize()
         for seq, _ in ahead.batch.seqs:
             if seq.state != SeqState.FINISHED:
                 self.cache.truncate(seq.cache, seq.num_computed)

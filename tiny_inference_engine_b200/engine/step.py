@@ -223,6 +223,10 @@ class StepRunner:
         Checks the kernels' status words."""
         return self.fetch(logits, ids, sampling).result()
 
+    def synchronize(self) -> None:
+        """Waits until the GPU is done with every step queued so far."""
+        torch.cuda.current_stream().synchronize()
+
     def check(self) -> None:
         """After a synchronize: raises if a kernel of an earlier step gave up a bounded wait."""
         gemm_select.check_status()
