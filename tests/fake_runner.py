@@ -32,10 +32,12 @@ def generate_alone(prompt, params, stop=()):
 
 
 class _Pending:
-    def __init__(self, ids):
-        self.ids = ids
+    def __init__(self, ids, fail):
+        self.ids, self.fail = ids, fail
 
     def result(self):
+        if self.fail:
+            raise RuntimeError("injected at the read")
         return list(self.ids)
 
 
@@ -47,6 +49,7 @@ class FakeRunner:
         self.ids = []             # sampled ids of the last step ("on the device")
         self.runs = 0
         self.fail_at = set()      # run numbers that raise before anything is changed
+        self.fail_read_at = set() # run numbers whose ids cannot be read (the step itself ran)
         self.synchronized = 0
 
     def run(self, entries, sampling=None, device_tokens=False):
@@ -85,7 +88,7 @@ class FakeRunner:
         return None, list(ids)
 
     def fetch(self, logits, ids, sampling):
-        return _Pending(ids)
+        return _Pending(ids, self.runs in self.fail_read_at)
 
     def synchronize(self):
         self.synchronized += 1

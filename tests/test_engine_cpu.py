@@ -49,7 +49,7 @@ def test_batched_requests_generate_what_each_generates_alone(run_ahead):
     assert eng.stats().decode_tokens == sum(q.max_tokens for q in params) - len(prompts)
 
 
-@pytest.mark.parametrize("seed", range(40))
+@pytest.mark.parametrize("seed", range(120))
 def test_random_workloads_with_small_pools_stop_tokens_and_cancels(seed):
     rng = random.Random(seed)
     n = rng.randint(2, 9)
@@ -93,12 +93,18 @@ def test_random_workloads_with_small_pools_stop_tokens_and_cancels(seed):
 
 
 @pytest.mark.parametrize("run_ahead", [False, True])
-@pytest.mark.parametrize("fail_at", [1, 2, 3, 5, 8, 13])
-def test_a_failed_step_is_rolled_back(run_ahead, fail_at):
+@pytest.mark.parametrize("at_read", [False, True])
+@pytest.mark.parametrize("fail_at", [1, 2, 3, 5, 8, 9, 10, 13])
+def test_a_failed_step_is_rolled_back(run_ahead, fail_at, at_read):
+    """A step that fails while it is being queued, or whose ids cannot be read (with another step already queued behind
+    it): the engine raises once, and every request still generates what it generates alone."""
     prompts = [list(range(9)), [3] * 20, [200, 100], [9, 8, 7, 6]]
     params = [SamplingParams(max_tokens=7, seed=i) for i in range(4)]
     eng = make_engine(tokens=8, seqs=4, run_ahead=run_ahead)
-    eng.runner.fail_at = {fail_at}
+    if at_read:
+        eng.runner.fail_read_at = {fail_at}
+    else:
+        eng.runner.fail_at = {fail_at}
     ids = [eng.add_request(p, q) for p, q in zip(prompts, params)]
     failures = 0
     while eng.has_work():

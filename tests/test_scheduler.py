@@ -37,11 +37,11 @@ class Rig:
         self.finish_step(b)
         return [(q.id, n) for q, n in b.seqs]
 
-    def finish_step(self, b, still_in_flight=None):
+    def finish_step(self, b):
         for q, n in b.seqs:
             q.num_computed += n
             self.cache.advance_window(q.cache, q.num_computed)
-        self.s.complete(b, still_in_flight)
+        self.s.complete(b)
         for q, n in b.seqs:
             if q.num_computed == len(q.tokens):
                 q.tokens.append(0)
@@ -238,44 +238,23 @@ def test_randomized_simulation_keeps_the_invariants(seed):
     assert all(p.num_free == p.num_blocks for p in r.cache.pools)
 
 
-def test_schedule_ahead_only_when_the_next_decision_is_certain():
-    """The same requests one token further while their step is in flight: only if nothing waits, the batch
-    is every running request, each decodes and cannot end by length with the token in flight, and pages
-    for all can be had; otherwise nothing is taken."""
-    r = Rig(pages=6, tokens=16, seqs=4)
+def test_a_batch_that_is_neither_complete_nor_abandoned_keeps_its_requests_out_and_requeue_starts_one_over():
+    """Requests of a batch in flight are skipped by the next decision until the engine calls `complete` (which it
+    does at once when it decides the next step behind a step in flight) or `abandon`; `requeue` puts a request
+    whose pages the engine took back into the waiting queue, wherever it was."""
+    r = Rig(pages=16, tokens=16, seqs=4)
     a, b = r.add(6, max_tokens=100), r.add(3, max_tokens=100)
-    batch = r.s.schedule()                                   # both prompts whole
-    assert r.s.schedule_ahead(batch) is None                 # prompts, not decodes
-    r.finish_step(batch)
     batch = r.s.schedule()
-    assert [(q.id, n) for q, n in batch.seqs] == [(a.id, 1), (b.id, 1)]
-    held = r.cache.num_free()
-    ahead = r.s.schedule_ahead(batch)
-    assert ahead is not None and [(q.id, n) for q, n in ahead.seqs] == [(a.id, 1), (b.id, 1)] and ahead.id != batch.id
-    for q, _ in ahead.seqs:                                   # pages for the token in flight and the one after it
-        assert all(len(t) >= blocks_for(q.num_computed + 2, PAGE) for t in q.cache.tables)
-    assert r.cache.num_free() == held - 1                    # a: 8 tokens fit its two pages; b: 5 tokens need a second
-    r.finish_step(batch, still_in_flight=ahead)
-    assert r.s._busy(a) and r.s._busy(b)
-    r.finish_step(ahead)
-    assert not r.s._busy(a) and not r.s._busy(b)
-    # something waits: the next decision may admit it
-    c = r.add(2, max_tokens=100)
-    batch = r.s.schedule()
-    assert r.s.schedule_ahead(batch) is None
+    assert r.s._busy(a) and r.s._busy(b) and r.s.schedule().empty()
     r.finish_step(batch)
-    # a request that ends by length with the token in flight
-    a.params.max_tokens = a.num_generated + 1
-    batch = r.s.schedule()
-    assert r.s.schedule_ahead(batch) is None
-    a.params.max_tokens = 100
-    r.finish_step(batch)
-    # the pool cannot give every request its page: nothing is taken
-    r = Rig(pages=3, tokens=16, seqs=4)
-    a, b = r.add(3, max_tokens=100), r.add(3, max_tokens=100)
-    r.finish_step(r.s.schedule())
-    batch = r.s.schedule()                                   # position 3 of both: the last slot of their first page
-    assert [(q.id, n) for q, n in batch.seqs] == [(a.id, 1), (b.id, 1)] and r.cache.num_free() == 1
-    assert r.s.schedule_ahead(batch) is None                 # position 4 needs a second page for each; one is free
-    assert r.cache.num_free() == 1 and all(len(t) == 1 for q in (a, b) for t in q.cache.tables)
-    r.finish_step(batch)
+    assert not r.s._busy(a) and [(q.id, n) for q, n in r.s.schedule().seqs] == [(a.id, 1), (b.id, 1)]
+    # the engine's part after a failed step whose bookkeeping had been moved on: pages back, computed again
+    for q in (a, b):
+        r.cache.reset(q.cache)
+        q.num_computed = 0
+    r.s.finish(b)                               # as for a request taken out because its last token was in flight
+    r.s.requeue(a)
+    r.s.requeue(b)
+    assert a not in r.s.running and r.s.waiting == [a, b] and a.state == SeqState.WAITING and not r.s._busy(a)
+    assert r.cache.num_free() == 16
+    assert r.step() == [(a.id, 7), (b.id, 4)]      # prompt and the generated token again

@@ -25,6 +25,15 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = ld(row + i);
 }
 
+// tokens[dst[i]] = ids[src[i]]: a step that is queued before the host has seen the ids sampled by the step ahead
+// of it takes them from the device; dst is the row of a request's token in this step, src its row in that step.
+__global__ void scatter_ids_kernel(int* __restrict__ tokens, const int* __restrict__ dst, const int* __restrict__ src,
+                                   const int* __restrict__ ids, int n) {
+  pdl_sync();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) tokens[dst[i]] = ids[src[i]];
+}
+
 // ---------------------------------------------------------------------------------------------
 // Residual add fused with the norm that follows it:
 //   x[t] += delta[t]  (float sum, written back; skipped when delta is null)
@@ -721,6 +730,13 @@ TIE_API int tie_embed(int dtype, const void* table, const int* ids, float* x, in
   TIE_REQUIRE(tokens >= 0 && dim > 0 && vocab > 0, "embed: bad sizes tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
   TIE_DISPATCH(dtype, launch_embed<float>(table, ids, x, tokens, dim, vocab, s),
                launch_embed<__nv_bfloat16>(table, ids, x, tokens, dim, vocab, s));
+}
+
+TIE_API int tie_scatter_ids(int* tokens, const int* dst, const int* src, const int* ids, int n, cudaStream_t s) {
+  TIE_REQUIRE(n >= 0 && tokens != nullptr && dst != nullptr && src != nullptr && ids != nullptr, "scatter_ids: bad arguments n=%d", n);
+  if (n == 0) return kOk;
+  TIE_LAUNCH(scatter_ids_kernel, ceil_div(n, 128), 128, 0, s, tokens, dst, src, ids, n);
+  TIE_RETURN_LAUNCH("scatter_ids");
 }
 
 // rows may be null (row t of out from row t of x); delta may be null (no add), or given as

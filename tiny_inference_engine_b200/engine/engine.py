@@ -31,14 +31,19 @@ class EngineStats:
     steps_ahead: int = 0       # steps queued before the tokens of the step ahead of them were read
 
 
+PLACEHOLDER = -1      # stands in a request's tokens for the one that a step in flight is sampling
+
+
 @dataclass
 class _Pending:
     """A step on the GPU whose tokens have not been read yet."""
     batch: ScheduledBatch
-    sampled: list
+    sampled: list            # the requests that get a token from this step, in the order of its sampled rows
     tokens: object           # StepRunner.fetch's handle
     prefill: int
     decode: int
+    advanced: bool = False   # the requests' bookkeeping is already past this step (a step was decided behind it)
+    token_at: dict = field(default_factory=dict)   # request id -> where in its tokens the placeholder stands
 
 
 class Engine:
@@ -58,7 +63,7 @@ class Engine:
         self.sequences: dict[int, Sequence] = {}
         self._next_id = 0
         self._stepping = False
-        self._ahead: _Pending | None = None      # a decode step queued before the one ahead of it was read
+        self._ahead: _Pending | None = None      # a step queued before the tokens of the one ahead of it were read
         self._on_token: Callable[[int, int], None] | None = None
         self._stats = EngineStats()
         self.max_blocks_per_seq = blocks_for(model.spec.max_positions, cache.page_size)
@@ -127,11 +132,14 @@ class Engine:
             raise InvalidArgument(f"scheduler gave {total} tokens; a step allows at most {self.serving.max_tokens_per_step}")
 
     def step(self) -> None:
-        """One step: a batch is decided, run, and its tokens are handed out. With `serving.run_ahead`, while
-        a pure decode batch runs and the scheduler is certain of the next one (`Scheduler.schedule_ahead`),
-        that next step is queued on the GPU before this one's tokens are read; it takes its input tokens
-        from the device and is finished by the next call. Tokens come out in the same order with the same
-        values either way; a request that stops runs at most one step in vain."""
+        """One step: a batch is decided, run, and its tokens are handed out. With `serving.run_ahead` the
+        step after it is decided and queued on the GPU before this one's tokens are read: the requests'
+        bookkeeping is moved past the step in flight (`_advance`: its tokens count as computed, and a
+        placeholder stands for every token it is sampling), the scheduler decides as it always does, and a
+        request that goes on decoding takes its input token from the device. The host's work (deciding,
+        index arrays, launches) then overlaps the GPU's step. Tokens come out in the same order with the same
+        values either way, since a request's tokens do not depend on what it is batched with; a request that
+        stops on a stop token or is cancelled runs at most one step in vain."""
         if self._stepping:
             raise InvalidArgument("step() called during a step (e.g. from a token callback)")
         self._stepping = True
@@ -147,10 +155,11 @@ class Engine:
                 pending = self._launch(batch)
             launch_error = None
             if self.serving.run_ahead:
-                nxt = self.scheduler.schedule_ahead(pending.batch)
-                if nxt is not None:
+                self._advance(pending)
+                nxt = self.scheduler.schedule()
+                if not nxt.empty():
                     try:
-                        self._ahead = self._launch(nxt, ahead_of=pending)
+                        self._ahead = self._launch(nxt, behind=pending)
                         self._stats.steps_ahead += 1
                     except Exception as e:       # its reservation has been given back; the step in flight still counts
                         launch_error = e
@@ -164,26 +173,24 @@ class Engine:
         finally:
             self._stepping = False
 
-    def _launch(self, batch: ScheduledBatch, ahead_of: "_Pending | None" = None) -> "_Pending":
-        """Queues the batch on the GPU and the copy of its sampled ids to the host. With `ahead_of` (the
-        step in flight, same requests in the same order) every request is one token further than its
-        bookkeeping says and its input token is the one that step samples."""
+    def _launch(self, batch: ScheduledBatch, behind: "_Pending | None" = None) -> "_Pending":
+        """Queues the batch on the GPU and the copy of its sampled ids to the host. A request whose next token
+        is a placeholder gets it from the row of the step in flight (`behind`) that samples it."""
         sampled: list[Sequence] = []
         prefill = decode = 0
         try:
-            if ahead_of is None:
-                self._check_batch(batch)
+            self._check_batch(batch)
+            rows = {seq.id: r for r, seq in enumerate(behind.sampled)} if behind is not None else {}
             entries = []
             for seq, n in batch.seqs:
-                if ahead_of is not None:
-                    begin = seq.num_computed + 1
-                    entries.append(StepEntry(seq.cache, (0,), begin, (0,)))
-                    sampled.append(seq)
-                    decode += 1
-                    continue
                 begin, end = seq.num_computed, seq.num_computed + n
+                tokens, device_row = seq.tokens[begin:end], None
+                if tokens[0] == PLACEHOLDER:
+                    tokens, device_row = [0] + tokens[1:], rows[seq.id]
+                if PLACEHOLDER in tokens:
+                    raise InvalidArgument(f"sequence {seq.id} was scheduled past a token that is not known yet")
                 samples = end == len(seq.tokens)   # its whole pending input is in the cache after this step
-                entries.append(StepEntry(seq.cache, seq.tokens[begin:end], begin, (n - 1,) if samples else ()))
+                entries.append(StepEntry(seq.cache, tokens, begin, (n - 1,) if samples else (), device_row))
                 if samples:
                     sampled.append(seq)
                 if seq.state == SeqState.DECODING and n == 1:
@@ -191,29 +198,49 @@ class Engine:
                 else:
                     prefill += n
             t0 = time.perf_counter()
-            extra = 1 if ahead_of is not None else 0
-            sampling = [(s.params, s.num_generated + extra) for s in sampled]
-            logits, ids = self.runner.run(entries, sampling, device_tokens=ahead_of is not None)
+            sampling = [(s.params, s.num_generated) for s in sampled]
+            logits, ids = self.runner.run(entries, sampling)
             tokens = self.runner.fetch(logits, ids, sampling)
             self._stats.step_seconds += time.perf_counter() - t0
         except BaseException:
-            self._give_back(batch, ahead=ahead_of is not None)
+            self._give_back(batch)
             raise
         return _Pending(batch, sampled, tokens, prefill, decode)
 
-    def _give_back(self, batch: ScheduledBatch, ahead: bool = False) -> None:
+    def _advance(self, pending: "_Pending") -> None:
+        """Moves the requests' bookkeeping past a step that is still in flight, so that the next one can be
+        decided: its tokens count as computed and a placeholder stands for each token it is sampling. A request
+        that reaches its max_tokens with that token leaves the scheduler now and is finished when the token
+        is there. Pages that a window has passed, or that a preemption in the next decision takes away, may
+        still be read by the step in flight: whoever gets them next is queued behind it on the same stream."""
+        for seq, n in pending.batch.seqs:
+            if seq.state == SeqState.FINISHED:
+                continue
+            seq.num_computed += n
+            self.cache.advance_window(seq.cache, seq.num_computed)
+        for seq in pending.sampled:
+            if seq.state == SeqState.FINISHED:
+                continue
+            pending.token_at[seq.id] = len(seq.tokens)
+            seq.tokens.append(PLACEHOLDER)
+            seq.state = SeqState.DECODING
+            if seq.num_generated >= seq.params.max_tokens:
+                self.scheduler.finish(seq)
+        self.scheduler.complete(pending.batch)
+        pending.advanced = True
+
+    def _give_back(self, batch: ScheduledBatch) -> None:
         """The step did not run: give back what the scheduler reserved and let it be scheduled again.
         State of fixed size may be half-updated, so requests that keep some start over."""
         for seq, _ in batch.seqs:
             if seq.state == SeqState.FINISHED:
                 continue
-            if self.states is not None and self.states.bytes_per_slot > 0 and not ahead:
+            if self.states is not None and self.states.bytes_per_slot > 0:
                 self.cache.reset(seq.cache)
                 seq.num_computed = 0
             else:
-                self.cache.truncate(seq.cache, seq.num_computed + (1 if ahead else 0))
-        if not ahead:
-            self.scheduler.abandon(batch)
+                self.cache.truncate(seq.cache, seq.num_computed)
+        self.scheduler.abandon(batch)
 
     def _drop_ahead(self) -> None:
         """Forgets the step queued ahead (its results will never be read) once the GPU is done with it."""
@@ -221,10 +248,20 @@ class Engine:
         if ahead is None:
             return
         self.runner.synchronize()
-        for seq, _ in ahead.batch.seqs:
-            if seq.state != SeqState.FINISHED:
-                self.cache.truncate(seq.cache, seq.num_computed)
-        self.scheduler.abandon(ahead.batch)
+        self._give_back(ahead.batch)
+
+    def _start_over(self, pending: "_Pending") -> None:
+        """A step whose bookkeeping had been moved on failed: its requests lose their placeholders and are
+        computed again from their first token, like preempted ones."""
+        for seq, _ in pending.batch.seqs:
+            if seq.state == SeqState.FINISHED:
+                continue
+            if seq.tokens and seq.tokens[-1] == PLACEHOLDER:
+                seq.tokens.pop()
+            self.cache.reset(seq.cache)
+            seq.num_computed = 0
+            self.scheduler.requeue(seq)
+        self.scheduler.abandon(pending.batch)
 
     def _complete(self, pending: "_Pending") -> None:
         """Waits for the step's tokens and hands them out; finishes what ends."""
@@ -239,23 +276,30 @@ class Engine:
             self._stats.decode_tokens += pending.decode
         except BaseException:
             self._drop_ahead()
-            self._give_back(batch)
+            if pending.advanced:
+                self._start_over(pending)
+            else:
+                self._give_back(batch)
             raise
 
-        for seq, n in batch.seqs:
-            if seq.state == SeqState.FINISHED:
-                continue   # it ended while this step, queued ahead, was in flight: the step ran in vain for it
-            seq.num_computed += n
-            self.cache.advance_window(seq.cache, seq.num_computed)
-        self.scheduler.complete(batch, still_in_flight=self._ahead.batch if self._ahead is not None else None)
+        if not pending.advanced:
+            for seq, n in batch.seqs:
+                if seq.state == SeqState.FINISHED:
+                    continue   # it ended while this step, queued ahead, was in flight: the step ran in vain for it
+                seq.num_computed += n
+                self.cache.advance_window(seq.cache, seq.num_computed)
+            self.scheduler.complete(batch)
 
         for i, seq in enumerate(sampled):
             if seq.state == SeqState.FINISHED:
                 continue  # cancelled by an earlier token callback of this step, or ended a step ago
             token = tokens[i]
             try:
-                seq.tokens.append(token)
-                seq.state = SeqState.DECODING
+                if pending.advanced:
+                    seq.tokens[pending.token_at[seq.id]] = token
+                else:
+                    seq.tokens.append(token)
+                    seq.state = SeqState.DECODING
                 if self._on_token is not None:
                     self._on_token(seq.id, token)
             except BaseException:
@@ -272,6 +316,8 @@ class Engine:
                 self._finish(seq, FinishReason.LENGTH)
 
     def _finish(self, seq: Sequence, reason: FinishReason) -> None:
+        if seq.tokens and seq.tokens[-1] == PLACEHOLDER:
+            seq.tokens.pop()       # ended while the token was still being sampled: it is never handed out
         seq.state = SeqState.FINISHED
         seq.finish_reason = reason
         self.cache.release(seq.cache)

@@ -20,7 +20,9 @@ tokens (prompt and generated) stay, and it is prefilled again later
 (src/engine/batch_scheduler.cpp:67-76). An older request is never preempted for a newer one.
 The scheduler owns pages while requests run: every (request, n) it returns already has
 pages reserved for num_computed + n tokens. Deciding a step (`schedule`) is separate from
-finishing it (`complete` / `abandon`), so several batches may be in flight.
+finishing it (`complete` / `abandon`); requests of a batch that is neither are skipped by the next
+decision. The engine calls `complete` as soon as a step is queued when it decides the next one while that
+step is still on the GPU: the requests' bookkeeping is then already past it.
 """
 from __future__ import annotations
 
@@ -37,7 +39,7 @@ class ServingConfig:
     (src/engine/serving_config.h:12-22)."""
     max_tokens_per_step: int = 512
     max_seqs: int = 64
-    run_ahead: bool = True      # queue the next decode step before the host has seen this one's tokens
+    run_ahead: bool = True      # decide and queue the next step before the host has seen this one's tokens
 
     def validate(self) -> None:
         if self.max_tokens_per_step <= 0:
@@ -227,44 +229,27 @@ class Scheduler:
             self._in_flight.add(seq.id)
         return batch
 
-    def schedule_ahead(self, batch: ScheduledBatch) -> ScheduledBatch | None:
-        """While `batch` is in flight and its tokens are not known yet: the same requests, each one token
-        further, if that is certainly what `schedule` would decide once the batch is back, else None.
-        Certain means: nothing waits; the batch holds every running request; each decodes one token
-        and cannot reach its max_tokens with the token in flight; and pages for
-        one more token can be had for all of them (all or nothing; preemption is left to `schedule`).
-        A request that turns out to have stopped with the token in flight runs this one step in vain."""
-        if self.waiting or len(batch.seqs) != len(self.running) or not batch.seqs:
-            return None
-        for seq, n in batch.seqs:
-            if n != 1 or seq.state != SeqState.DECODING or seq.num_pending != 1:
-                return None
-            if seq.num_generated + 1 >= seq.params.max_tokens:
-                return None
-        taken = []
+    def complete(self, batch: ScheduledBatch) -> None:
+        """The engine advanced num_computed of every sequence of the batch (when the step's tokens are back, or,
+        to decide the next step while this one is still on the GPU, as soon as it is queued)."""
         for seq, _ in batch.seqs:
-            if not self.cache.reserve(seq.cache, seq.num_computed + 2):
-                for s in taken:
-                    self.cache.truncate(s.cache, s.num_computed + 1)
-                return None
-            taken.append(seq)
-        self.step_no += 1
-        ahead = ScheduledBatch(id=self._next_batch, seqs=[(seq, 1) for seq, _ in batch.seqs])
-        self._next_batch += 1
-        return ahead
-
-    def complete(self, batch: ScheduledBatch, still_in_flight: ScheduledBatch | None = None) -> None:
-        """The engine advanced num_computed of every sequence of the batch. Requests of `still_in_flight`
-        (a batch queued ahead) stay busy."""
-        keep = {seq.id for seq, _ in still_in_flight.seqs} if still_in_flight is not None else ()
-        for seq, _ in batch.seqs:
-            if seq.id not in keep:
-                self._in_flight.discard(seq.id)
+            self._in_flight.discard(seq.id)
 
     def abandon(self, batch: ScheduledBatch) -> None:
         """The step failed; tables were trimmed back to num_computed."""
         for seq, _ in batch.seqs:
             self._in_flight.discard(seq.id)
+
+    def requeue(self, seq: Sequence) -> None:
+        """The engine gave the request's pages back and set num_computed to 0 after a failed step: it waits
+        again, wherever it was (running, waiting, or already taken out because its last token was in flight)."""
+        if seq in self.running:
+            self.running.remove(seq)
+        if seq not in self.waiting:
+            self.waiting.append(seq)
+        seq.state = SeqState.WAITING
+        seq.waiting_since_step = self.step_no
+        self._in_flight.discard(seq.id)
 
     def finish(self, seq: Sequence) -> None:
         """Done or cancelled: forget it."""

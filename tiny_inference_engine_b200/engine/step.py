@@ -41,11 +41,14 @@ from .workspace import Workspace
 @dataclass
 class StepEntry:
     """`tokens` are the request's next tokens; `start` tokens of it are already in the cache;
-    `want` are the places among `tokens` whose logits are asked for."""
+    `want` are the places among `tokens` whose logits are asked for. With `device_row` the first of
+    `tokens` is a placeholder: the real one is the id that the step before this one sampled for its
+    row `device_row`, still on the device (perhaps not computed yet)."""
     cache: RequestCache
     tokens: Sequence[int]
     start: int
     want: Sequence[int] = ()
+    device_row: int | None = None
 
 
 @dataclass
@@ -187,11 +190,11 @@ class StepRunner:
         the generated token) per wanted row) returns (logits, ids): ids is an int32 device tensor
         [R] picked by the sampling kernels (greedy, temperature, top-k, top-p).
 
-        With `device_tokens` every entry brings one token and entry i's token is the id that the step
-        before sampled for its row i (still on the device, perhaps not computed yet): the step can be
-        queued before the host has seen those ids. The entries' own `tokens` are placeholders then."""
-        if device_tokens and (sampling is None or any(len(e.tokens) != 1 for e in entries)):
-            raise InvalidArgument("device tokens are for steps in which every entry brings one token and samples")
+        An entry with `device_row`, and with `device_tokens` every entry i as if it had `device_row` i,
+        takes its first token from the ids that the step before sampled (still on the device, perhaps not
+        computed yet): the step can be queued before the host has seen those ids."""
+        if device_tokens and any(len(e.tokens) != 1 for e in entries):
+            raise InvalidArgument("device_tokens is for steps in which every entry brings one token")
         graph_key = self._graph_key(entries, sampling)
         if graph_key is not None:
             return self._run_graph(entries, sampling, graph_key, device_tokens)
@@ -331,7 +334,7 @@ class StepRunner:
         sizes = [("tokens", T), ("positions", T), ("seq_of_row", T), ("query_start", S + 1), ("context_lens", S),
                  ("logit_rows", max(R, 1)), ("state_slots", S), ("single_seqs", max(S, 1)),
                  ("inv_t", max(R, 1)), ("seeds", 2 * max(R, 1)), ("counters", 2 * max(R, 1)),
-                 ("top_k", max(R, 1)), ("top_p", max(R, 1))]
+                 ("top_k", max(R, 1)), ("top_p", max(R, 1)), ("ids_dst", S), ("ids_src", S)]
         for g in range(G):
             sizes += [(f"slots{g}", T), (f"tables{g}", S * MB)]
         offs, total = {}, 0
@@ -463,17 +466,25 @@ class StepRunner:
                 for r, (p, _) in enumerate(sampling):
                     top_k[r], top_p[r] = min(p.top_k, 2 ** 31 - 1), p.top_p
 
+        # tokens that are still on the device: (row of the token in this step, row of the step before that samples it)
+        from_device = [(row_of[i], i if device_tokens else e.device_row) for i, e in enumerate(entries)
+                       if device_tokens or e.device_row is not None]
+        if from_device:
+            if any(not 0 <= src < self.max_logit_rows for _, src in from_device):
+                raise InvalidArgument(f"a device row outside the {self.max_logit_rows} rows a step samples")
+            ids_dst, ids_src = sec("ids_dst"), sec("ids_src")
+            ids_dst[:len(from_device)] = [d for d, _ in from_device]
+            ids_src[:len(from_device)] = [r for _, r in from_device]
+
         dev[:total].copy_(slot[0][:total], non_blocking=True)
         slot[2].record()
-        if device_tokens:
-            if T_real != S_real:
-                raise InvalidArgument("device tokens are for steps in which every entry brings one token")
-            o = offs["tokens"][0]
-            dev[o:o + S_real].copy_(self._ids[:S_real])     # row i of the step before -> entry i of this one
 
         def dsec(name, n=None):
             o, full = offs[name]
             return dev[o:o + (full if n is None else n)]
+
+        if from_device:
+            ops.scatter_ids(dsec("tokens"), dsec("ids_dst"), dsec("ids_src"), self._ids, len(from_device))
 
         groups = [GroupStep(dsec(f"slots{g}"), dsec(f"tables{g}").view(S, MB)) for g in range(G)]
         hs = HostStep(query_start.copy(), context_lens.copy(), starts, state_slots.copy())

@@ -82,6 +82,15 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
     call("tie_embed", dtype_code(table), table.data_ptr(), ids.data_ptr(), out.data_ptr(), T, D, table.shape[0], _stream())
 
 
+def scatter_ids(tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, ids: torch.Tensor, n: int) -> None:
+    """tokens[dst[i]] = ids[src[i]] for i < n (all int32): sampled ids of the step before become input tokens of
+    this one without a trip to the host."""
+    _dev(tokens, dst, src, ids)
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (tokens, dst, src, ids)) and
+          0 <= n <= min(dst.numel(), src.numel()), "scatter_ids: int32 contiguous arrays, n within dst and src")
+    call("tie_scatter_ids", tokens.data_ptr(), dst.data_ptr(), src.data_ptr(), ids.data_ptr(), n, _stream())
+
+
 def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor, rows=None) -> None:
     """x += delta (when given; float32, in place), out = rmsnorm(x) * weight in out's dtype.
     With `rows` (int32 [R]), out[i] comes from row rows[i] and x is left as it is. `delta` may

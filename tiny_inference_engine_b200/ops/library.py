@@ -17,6 +17,7 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 _SIGNATURES = {
     "tie_embed": [I, P, P, P, I, I, I, P],
+    "tie_scatter_ids": [P, P, P, P, I, P],
     "tie_add_rmsnorm": [I, P, P, P, L, I, P, P, F, P, I, I, P],
     "tie_rmsnorm_rows": [I, P, L, P, F, P, L, I, L, P],
     "tie_silu_mul": [I, P, P, I, I, P],
