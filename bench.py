@@ -361,11 +361,7 @@ def main() -> int:
     print(f"[bench] e2e: {K - 1} steps, {e2e_tokens} tokens, {e2e_s * 1e3 / (K - 1):.3f} ms per step, "
           f"{len(engine.scheduler.running)} running, {len(engine.scheduler.waiting)} waiting, "
           f"{engine.stats().preemptions} preemptions", file=sys.stderr, flush=True)
-    sb = B
-    mb = 16
-    while mb < pages_per_seq:
-        mb *= 2
-    h2d = 4 * (3 * sb + (sb + 1) + 4 * sb + 5 * sb + sb + sb * mb + 64)
+    h2d = runner.last_h2d_bytes          # the index arrays of a timed step: one copy from pinned memory
     while engine.has_work():
         engine.step()
     clk = clocks.stop()

@@ -154,6 +154,7 @@ class StepRunner:
         words = 4 * max_tokens + 6 * self.max_seqs + 6 * self.max_logit_rows + G * (max_tokens + self.max_seqs * mb) + 64 * (8 + 2 * G)
         self._dev = torch.zeros(words, dtype=torch.int32, device=device)
         self._ids = torch.zeros(self.max_logit_rows, dtype=torch.int32, device=device)
+        self.last_h2d_bytes = 0
         self._ids_host = [(torch.zeros(self.max_logit_rows, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
                           for _ in range(2)]
         self._ids_turn = 0
@@ -478,6 +479,7 @@ class StepRunner:
 
         dev[:total].copy_(slot[0][:total], non_blocking=True)
         slot[2].record()
+        self.last_h2d_bytes = 4 * total        # what this step copied to the device (bench.py reports it)
 
         def dsec(name, n=None):
             o, full = offs[name]
