@@ -10,7 +10,6 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Sequence as Seq
 
-
 from ..cache.manager import CacheManager, blocks_for
 from ..cache.state_slots import StateSlots
 from ..errors import CapacityError, InvalidArgument
@@ -108,6 +107,9 @@ class Engine:
         return self.scheduler.has_work() or self._ahead is not None
 
     def set_token_callback(self, callback: Callable[[int, int], None] | None) -> None:
+        """`callback(request id, token)` is called for every generated token, in the order of the step's rows.
+        It may cancel requests. While it runs, the tokens of other requests of the step may still end in
+        PLACEHOLDER (their id is handed out next); its own token is in place."""
         self._on_token = callback
 
     # -- one step
