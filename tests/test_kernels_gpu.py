@@ -43,6 +43,21 @@ def test_embed(ops, dtype):
     assert np.array_equal(host(out), plain.embed(table, ids).astype(np.float32))
 
 
+def test_scatter_ids(ops):
+    """tokens[dst[i]] = ids[src[i]] for the first n pairs; everything else is left as it is."""
+    rng = np.random.default_rng(5)
+    tokens = rng.integers(0, 1000, 700).astype(np.int32)
+    ids = rng.integers(0, 1000, 300).astype(np.int32)
+    dst = rng.permutation(700)[:300].astype(np.int32)
+    src = rng.integers(0, 300, 300).astype(np.int32)
+    for n in (0, 1, 129, 300):
+        t = dev(tokens, torch.int32)
+        ops.scatter_ids(t, dev(dst, torch.int32), dev(src, torch.int32), dev(ids, torch.int32), n)
+        want = tokens.copy()
+        want[dst[:n]] = ids[src[:n]]
+        assert np.array_equal(host(t), want)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("dim", [72, 1000, 5120])
 def test_add_rmsnorm(ops, dtype, dim):

@@ -481,3 +481,37 @@ def test_one_layer_as_wide_as_the_large_model_against_the_plain_implementation(d
     for name, want in (("a", want_a), ("b", want_b)):
         pos = [p for p, _ in got[name]]
         assert_logits_close(np.stack([g for _, g in got[name]]), want[pos], dtype, f"wide layer, request {name}")
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_tokens_taken_from_the_step_before_on_the_device(tiny_models, graphs):
+    """A step whose entries name a `device_row` takes their first token from the ids that the step before it
+    sampled, wherever the entry stands in the step and whatever else the step holds: its logits are those of the
+    same step fed the same ids from the host."""
+    from tiny_inference_engine_b200 import SamplingParams, StepEntry, StepRunner, load_model, make_cache
+    cfg, page, w, d = tiny_models["tiny_d"]
+    model = load_model(d, "bfloat16")
+    rng = np.random.default_rng(9)
+    V = cfg["vocab_size"]
+    prompts = [rng.integers(0, V, n).tolist() for n in (40, 23, 31)]
+    portion = rng.integers(0, V, 17).tolist()
+    out = {}
+    for on_device in (False, True):
+        cache, states = make_cache(model, page_size=page, num_pages=40, max_requests=8)
+        runner = StepRunner(model, cache, 128, 8, 64, states=states, use_graphs=graphs)
+        reqs = [cache.new_request() for _ in range(4)]
+        for r in reqs:
+            assert cache.reserve(r, 64)
+        greedy = [(SamplingParams(), 0)] * 3
+        _, ids = runner.run([StepEntry(r, p, 0, [len(p) - 1]) for r, p in zip(reqs, prompts)], greedy)
+        first = ids.tolist()
+        # the three requests decode in another order, beside a prompt portion of a fourth (no graph), or alone (a graph)
+        order = [2, 0, 1]
+        entries = [StepEntry(reqs[i], [0 if on_device else first[i]], len(prompts[i]), [0], i if on_device else None) for i in order]
+        if not graphs:
+            entries.insert(1, StepEntry(reqs[3], portion, 0, []))
+        logits, ids = runner.run(entries, greedy)
+        out[on_device] = (logits.float().cpu().numpy().copy(), ids.tolist())
+        torch.cuda.synchronize()
+        runner.check()
+    assert np.array_equal(out[True][0], out[False][0]) and out[True][1] == out[False][1]
