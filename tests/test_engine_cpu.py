@@ -115,3 +115,63 @@ def test_a_failed_step_is_rolled_back(run_ahead, fail_at, at_read):
     assert failures == (1 if eng.runner.runs >= fail_at else 0) and eng.runner.runs >= 8
     assert [eng.sequence(i).tokens[eng.sequence(i).prompt_len:] for i in ids] == [generate_alone(p, q) for p, q in zip(prompts, params)]
     assert eng.cache.num_free() == 64
+
+
+def test_generate_one_after_another_with_a_step_still_queued_for_the_one_that_stopped():
+    """generate() returns as soon as its request has ended; the step that was queued behind its last one is dealt with
+    by the next call, and the next request starts from a clean pool."""
+    p1, p2 = [5, 6, 7, 8], list(range(40, 70))
+    q = SamplingParams(max_tokens=12, seed=3)
+    free = generate_alone(p1, q)
+    eng = make_engine(stop={free[4]})
+    assert eng.generate(p1, q) == free[:5]
+    assert eng._ahead is not None            # a step runs in vain for it
+    assert eng.generate(p2, q) == generate_alone(p2, q, {free[4]})
+    drain(eng)
+    assert eng.cache.num_free() == 64 and eng.stats().steps_ahead > 0
+
+
+def test_requests_that_cannot_run_are_refused_and_max_tokens_is_clamped():
+    from tiny_inference_engine_b200.errors import CapacityError, InvalidArgument
+    eng = make_engine(pages=4)
+    with pytest.raises(CapacityError, match="raise --kv-mem"):
+        eng.add_request([1] * 16)
+    with pytest.raises(InvalidArgument, match="outside vocabulary"):
+        eng.add_request([1, VOCAB])
+    with pytest.raises(InvalidArgument, match="empty"):
+        eng.add_request([])
+    a = eng.add_request([1, 2, 3], SamplingParams(max_tokens=500))
+    assert eng.sequence(a).params.max_tokens == 4 * PAGE - 3          # what the pool can hold
+    drain(eng)
+    seq = eng.sequence(a)
+    assert seq.finish_reason == FinishReason.LENGTH and seq.tokens[3:] == generate_alone([1, 2, 3], seq.params)
+    with pytest.raises(InvalidArgument, match="still running|no sequence"):
+        eng.release(99)
+    eng.release(a)
+    assert eng.cache.num_free() == 4
+
+
+def test_a_callback_that_raises_ends_the_requests_that_were_to_get_a_token_and_the_engine_goes_on():
+    prompts = [[1, 2], [3, 4, 5], [6]]
+    q = SamplingParams(max_tokens=6, seed=1)
+    eng = make_engine()
+    ids = [eng.add_request(p, q) for p in prompts]
+    calls = []
+
+    def on_token(seq_id, token):
+        calls.append(seq_id)
+        if len(calls) == 4:
+            raise ValueError("from the callback")
+
+    eng.set_token_callback(on_token)
+    with pytest.raises(ValueError):
+        drain(eng)
+    eng.set_token_callback(None)
+    drain(eng)
+    states = [eng.sequence(i) for i in ids]
+    assert all(s.state == SeqState.FINISHED for s in states) and eng.cache.num_free() == 64
+    assert any(s.finish_reason == FinishReason.ERROR for s in states)
+    assert all(-1 not in s.tokens for s in states)                     # no placeholder is left behind
+    b = eng.add_request([9, 9], q)
+    drain(eng)
+    assert eng.sequence(b).tokens[2:] == generate_alone([9, 9], q)
