@@ -55,8 +55,35 @@ def test_two_layers_are_no_run_and_a_moved_tensor_is_noticed(tmp_path):
     model, cache, states = _model(tmp_path, num_hidden_layers=4)
     runs = LayerRuns(model, cache, states)
     assert runs.run_end == {0: 3} and runs.spans(1, 0) is not None
+    assert runs.alive()
     model.layers[1].ffn.w_down = model.layers[1].ffn.w_down.clone()
     assert runs.spans(1, 0) is None
+    model.layers[3].ffn.down.w = model.layers[3].ffn.w_down = model.layers[3].ffn.w_down.clone()   # not the recorded layer
+    assert not runs.alive()                                 # the old tensor is gone: the model builds the tables anew
+    fresh = LayerRuns(model, cache, states)
+    moved = model.layers[3].ffn.w_down.data_ptr()
+    assert fresh.alive() and moved in fresh.table[0][3].tolist() and moved not in runs.table[0][3].tolist()
+
+
+def test_the_model_hands_out_runs_after_its_first_forward_and_builds_them_anew_when_a_tensor_is_gone(tmp_path):
+    class Ctx:
+        layer_hook = None
+
+    model, cache, states = _model(tmp_path, num_hidden_layers=5)
+    assert model._runs_for(Ctx(), cache, states) is None          # tensors that parts make at first use may not exist yet
+    model._forwards = 1
+    runs = model._runs_for(Ctx(), cache, states)
+    assert runs is not None and runs.run_end == {0: 4} and model._runs_for(Ctx(), cache, states) is runs
+    other_cache, other_states = make_cache(model, page_size=8, num_pages=12, device="cpu")
+    assert model._runs_for(Ctx(), other_cache, other_states) is not runs       # tables are per cache: the planes differ
+    model.layers[2].mixer_norm.weight = model.layers[2].mixer_norm.weight.clone()
+    again = model._runs_for(Ctx(), cache, states)
+    assert again is not runs and again.alive() and not runs.alive()
+    hooked = Ctx()
+    hooked.layer_hook = lambda *a: None
+    assert model._runs_for(hooked, cache, states) is None          # a hook wants every layer issued from Python
+    model.layer_replay = False
+    assert model._runs_for(Ctx(), cache, states) is None
 
 
 def test_a_layer_that_differs_in_a_constant_or_in_a_part_ends_the_run(tmp_path):

@@ -76,8 +76,11 @@ class LayerRuns:
         self.model_ref = weakref.ref(model)
         order = model.spec.run_order
         sigs, rows = [], []
+        self._held = []     # weak references to the layers' own tensors: one that is gone means the table is stale
         for i in range(len(order)):
             ok, scalars, tensors, view = self._entry(model, cache, i)
+            planes = sum(1 for t in ((view.k, view.v) if view is not None else ()) if t is not None)
+            self._held += [weakref.ref(t) for t in tensors[:len(tensors) - planes]]
             if states is not None and states.tensor(i) is not None:
                 ok = False      # state of its own: one tensor per entry that is not on the layer
             if any(t.data_ptr() < layer_replay._ADDRESS for t in tensors):
@@ -98,6 +101,11 @@ class LayerRuns:
                 self.run_end[a] = b
                 self.table[a] = np.ascontiguousarray(np.asarray(rows[a:b + 1], dtype=np.int64))
             a = b + 1
+
+    def alive(self) -> bool:
+        """Whether every tensor whose address the tables hold still exists. (A part binds its tensors once; one
+        that replaces a tensor later frees the old one, and the tables are then built anew.)"""
+        return all(r() is not None for r in self._held)
 
     @staticmethod
     def _entry(model, cache, i):

@@ -88,7 +88,7 @@ class Model:
         if not self.layer_replay or ctx.layer_hook is not None or self._forwards == 0:
             return None
         runs = self._layer_runs.get(id(cache))
-        if runs is None or (runs.cache_ref() if runs.cache_ref is not None else None) is not cache:
+        if runs is None or (runs.cache_ref() if runs.cache_ref is not None else None) is not cache or not runs.alive():
             if len(self._layer_runs) > 8:
                 self._layer_runs.clear()
             runs = self._layer_runs[id(cache)] = LayerRuns(self, cache, states)
