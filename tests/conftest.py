@@ -19,7 +19,7 @@ import plain_qwen3 as plain  # noqa: E402
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
 
 CONFIGS = {"tiny_a": (plain.TINY_A, 16), "tiny_b": (plain.TINY_B, 8), "tiny_c": (plain.TINY_C, 32),
-           "tiny_d": (plain.TINY_D, 16), "tiny_e": (plain.TINY_E, 16)}
+           "tiny_d": (plain.TINY_D, 16), "tiny_e": (plain.TINY_E, 16), "tiny_b4": (plain.TINY_B4, 8)}
 
 
 def pytest_configure(config):

@@ -6,12 +6,18 @@ sampling parameters and on nothing else, which is what the real step function pr
 every request has "in the cache" and checks what the engine hands it: positions without gaps, pages reserved for
 every position, no page held by two live requests, ids of a step that was queued ahead taken from the step
 before it. Ids are computed when a step runs and handed out by `result()`, like the real runner's.
+
+With state slots (`states`, tensors on the CPU) it also plays a mixer with state of its own: a request's slot counts
+the tokens the request has run, so a slot that was not zeroed when handed out, is shared by two requests or is
+missing shows as a count that differs from where the step starts. `refuse` names prefixes whose row the sampler
+refuses (the kernels' answer to a NaN logit): the id is then UNSAMPLABLE.
 """
 import zlib
 
 from tiny_inference_engine_b200.cache.manager import blocks_for
 
 VOCAB = 1000
+UNSAMPLABLE = -2
 
 
 def next_token(prefix, seed, index):
@@ -42,8 +48,9 @@ class _Pending:
 
 
 class FakeRunner:
-    def __init__(self, cache, max_tokens, max_seqs):
-        self.cache = cache
+    def __init__(self, cache, max_tokens, max_seqs, states=None):
+        self.cache, self.states = cache, states
+        self.refuse = lambda prefix: False
         self.max_tokens, self.max_seqs, self.max_logit_rows = max_tokens, max_seqs, max_seqs
         self.cached = {}          # id(request cache) -> tokens whose keys and values it holds
         self.ids = []             # sampled ids of the last step ("on the device")
@@ -67,11 +74,17 @@ class FakeRunner:
                 assert len(toks) == 1
                 toks = [self.ids[i]]
             elif getattr(e, "device_row", None) is not None:
-                toks[0] = self.ids[e.device_row]
+                toks[0] = max(self.ids[e.device_row], 0)      # a refused row's id is clamped into the vocabulary
             have = self.cached.setdefault(id(e.cache), [])
             assert e.start <= len(have), f"gap: request holds {len(have)} tokens, step starts at {e.start}"
             del have[e.start:]
             have.extend(toks)
+            if self.states is not None and self.states.has_state:
+                slot, count = e.cache.state_slot, self.states.tensor(0)
+                assert slot >= 0, "a request runs without a state slot"
+                assert owners.setdefault(("slot", slot), id(e.cache)) == id(e.cache), "a state slot shared in a step"
+                assert int(count[slot, 0]) == e.start, f"state of {int(count[slot, 0])} tokens at position {e.start}"
+                count[slot, 0] += len(toks)
             for t in e.cache.tables:
                 assert len(t) >= blocks_for(len(have), page), "positions beyond the reserved pages"
                 for b in t.held():
@@ -80,7 +93,8 @@ class FakeRunner:
                 assert 0 <= w < len(toks)
                 if sampling is not None:
                     p, index = sampling[row]
-                    ids.append(next_token(have[:e.start + w + 1], p.seed, index))
+                    prefix = have[:e.start + w + 1]
+                    ids.append(UNSAMPLABLE if self.refuse(prefix) else next_token(prefix, p.seed, index))
                 row += 1
         if sampling is not None:
             assert len(sampling) == row

@@ -1,6 +1,6 @@
-"""The sampler on the host: what the sampling kernels compute, restated with numpy. The engine samples on
-the device (greedy, temperature, top-k and top-p run in kernels inside the step: engine/step.py); this
-function is what tests hold those kernels against, and a way to sample from logits one has on the host.
+"""The sampler on the host: what the sampling kernels compute, restated with numpy in the kernels' own
+precision (float32 weights, sums in double). The engine samples on the device (greedy, temperature, top-k
+and top-p run in kernels inside the step); this function is what the tests hold those kernels against.
 
 It restates the reference's sampler (src/sampling/sampler.cpp:18-81): NaN or empty
 logits and all -inf are errors, a +inf logit is certain, greedy is the first maximum,
@@ -12,9 +12,8 @@ from __future__ import annotations
 
 import numpy as np
 
-from ..errors import InvalidArgument
-from .params import SamplingParams
-from .philox import uniform
+from tiny_inference_engine_b200.errors import InvalidArgument
+from tiny_inference_engine_b200.sampling import SamplingParams, uniform
 
 
 def sample_host(logits: np.ndarray, params: SamplingParams, index: int) -> int:

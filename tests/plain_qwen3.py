@@ -342,6 +342,10 @@ TINY_B = {
     "max_position_embeddings": 1024, "rms_norm_eps": 1e-5, "rope_theta": 1000000.0,
     "tie_word_embeddings": False,
 }
+# Tiny-B with four query heads (q width 128), as the benchmark description states it (same head count as tiny-A;
+# TINY_B above has eight so that the two differ there as well). The reference's own CPU code ran this one:
+# tests/golden/tiny_b4_*.
+TINY_B4 = {**TINY_B, "num_attention_heads": 4, "max_position_embeddings": 256}
 # A third one for the odd corners: as many KV heads as query heads (the num_key_value_heads key
 # is absent), head size 48 (a multiple of 16 that is no power of two, from hidden/heads since
 # the head_dim key is absent too), default theta and untied output. So the three cover

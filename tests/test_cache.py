@@ -89,27 +89,67 @@ def test_window_group_gives_pages_back_as_the_window_passes():
     assert m.num_free(0) == 12 and m.num_free(1) == 12
 
 
-def test_reset_keeps_the_request_and_zeroes_its_place():
+def test_a_state_slot_is_taken_by_the_first_reserve_and_given_back_by_reset_and_release():
     states = StateSlots([None, StateNeed((4,))], max_requests=2)
     m = CacheManager([FULL, None], page_size=4, num_pages=6, state_slots=states)
-    a, b = m.new_request(), m.new_request()
-    assert {a.state_slot, b.state_slot} == {0, 1}
-    with pytest.raises(CapacityError, match="state slots"):
-        m.new_request()
-    m.reserve(a, 10)
-    m.reset(a)
-    assert len(a.tables[0]) == 0 and a.live and a.state_slot >= 0 and m.num_free(0) == 6
-    m.release(a)
-    assert states.num_free == 1
-    c = m.new_request()
-    assert c.state_slot == a.state_slot if a.state_slot >= 0 else True
+    assert m.needs_state_slot
+    waiting = [m.new_request() for _ in range(50)]            # requests that only wait hold nothing
+    assert all(r.state_slot == -1 and not m.holds(r) for r in waiting) and states.num_free == 2
+    a, b, c = waiting[:3]
+    assert m.reserve(a, 10) and m.reserve(b, 3)
+    assert {a.state_slot, b.state_slot} == {0, 1} and m.holds(a)
+    # no slot left: nothing fits, nothing is admitted, and a reserve changes nothing
+    assert m.room(c, 0) == 0 and not m.admits(1, [0]) and not m.reserve(c, 1)
+    assert c.state_slot == -1 and len(c.tables[0]) == 0 and m.num_free(0) == 6 - 3 - 1
+    assert m.room(a, 10) == 4 * (3 + 2) - 10                  # a has its slot: pages alone count
+    m.reset(a)                                                # preemption: pages and slot go back, the request stays
+    assert len(a.tables[0]) == 0 and a.live and a.state_slot == -1 and not m.holds(a) and states.num_free == 1
+    assert m.admits(4, [0]) and m.reserve(c, 4) and c.state_slot >= 0
+    m.truncate(c, 0)                                          # a step that did not run: pages back, the slot stays
+    assert c.state_slot >= 0 and m.holds(c)
+    m.release(c)
+    assert states.num_free == 1 and m.reserve(a, 2) and a.state_slot >= 0
+    with pytest.raises(InvalidArgument, match="released request"):
+        m.reserve(c, 1)
+    # a model without such state never needs a slot
+    plain = CacheManager([FULL], page_size=4, num_pages=6, state_slots=StateSlots([None], max_requests=1))
+    rs = [plain.new_request() for _ in range(3)]
+    assert not plain.needs_state_slot and all(plain.reserve(r, 4) for r in rs) and all(r.state_slot == -1 for r in rs)
+
+
+def test_a_window_group_gets_the_pages_it_can_use_and_the_budget_goes_to_the_rest():
+    full_bytes, win_bytes = 2 * 2 * 8 * 16 * 4, 2 * 1 * 8 * 32 * 4
+    # 4 requests, window 20 and steps of 12 tokens: blocks_for(32, 8) + 2 = 6 pages each
+    m = CacheManager([FULL, WIN], page_size=8, budget_bytes=24 * win_bytes + 100 * full_bytes + 7,
+                     window_requests=4, window_step_tokens=12)
+    assert m.group_pages == [100, 24] and m.num_pages == 100 and m.bytes_per_page == full_bytes
+    assert [p.num_blocks for p in m.pools] == [100, 24]
+    assert m.max_tokens_per_request() == 800                  # the window group bounds no request's length
+    same = CacheManager([FULL, WIN], page_size=8, num_pages=10)
+    assert same.group_pages == [10, 10]                       # not asked for: every group alike
+    capped = CacheManager([FULL, WIN], page_size=8, num_pages=5, window_requests=4, window_step_tokens=12)
+    assert capped.group_pages == [5, 5]                       # never more than the others
+    only = CacheManager([WIN], page_size=8, num_pages=50, window_requests=2)
+    assert only.group_pages == [2 * (3 + 2)] and only.max_tokens_per_request() == 2 ** 31 - 1
+    with pytest.raises(CapacityError, match="beside the window"):
+        CacheManager([FULL, WIN], page_size=8, budget_bytes=24 * win_bytes, window_requests=4, window_step_tokens=12)
+    # a long request runs through a small window group: its pages come back as the window passes them
+    r = m.new_request()
+    for at in range(12, 400, 12):
+        assert m.reserve(r, at)
+        m.advance_window(r, at)
+        assert m.group_pages[1] - m.num_free(1) <= 6
+    m.release(r)
+    assert [p.num_free for p in m.pools] == [100, 24]
 
 
 @pytest.mark.parametrize("seed", range(25))
 def test_no_page_is_lost_held_twice_or_freed_twice_under_random_orders(seed):
     rng = random.Random(seed)
     page = rng.choice([4, 8, 16])
-    m = CacheManager([FULL, WIN, FULL], page_size=page, num_pages=rng.randint(6, 40))
+    states = StateSlots([StateNeed((2,)), None, None], max_requests=rng.randint(2, 6))
+    m = CacheManager([FULL, WIN, FULL], page_size=page, num_pages=rng.randint(6, 40), state_slots=states,
+                     window_requests=rng.choice([None, 2, 6]), window_step_tokens=3 * page)
     live = {}   # request -> tokens covered
     for _ in range(400):
         op = rng.random()
@@ -125,6 +165,8 @@ def test_no_page_is_lost_held_twice_or_freed_twice_under_random_orders(seed):
                 m.advance_window(r, want)
             else:
                 assert [len(t) for t in r.tables] == before
+                if r.state_slot < 0:
+                    assert not m.holds(r)
         elif op < 0.8 and live:
             r, n = rng.choice(list(live.values()))
             cut = rng.randint(0, n)
@@ -147,9 +189,13 @@ def test_no_page_is_lost_held_twice_or_freed_twice_under_random_orders(seed):
             assert all(pool.ref_count(b) == 0 for b in free)
         for r, n in live.values():
             assert len(r.tables[0]) >= blocks_for(n, page)
+        # every state slot has one owner or is free; a request that covers tokens has one
+        owned = [r.state_slot for r, _ in live.values() if r.state_slot >= 0]
+        assert len(owned) == len(set(owned)) and len(owned) + states.num_free == states.max_requests
+        assert all(r.state_slot >= 0 for r, n in live.values() if n > 0)
     for r, _ in list(live.values()):
         m.release(r)
-    assert all(p.num_free == p.num_blocks for p in m.pools)
+    assert all(p.num_free == p.num_blocks for p in m.pools) and states.num_free == states.max_requests
 
 
 def test_state_slots_misuse():

@@ -6,10 +6,12 @@ import random
 
 import pytest
 
+import torch
+
 from fake_runner import VOCAB, FakeRunner, generate_alone
-from tiny_inference_engine_b200.cache import CacheManager
+from tiny_inference_engine_b200.cache import CacheManager, StateSlots
 from tiny_inference_engine_b200.engine import Engine, FinishReason, Scheduler, SchedulerConfig, SeqState, ServingConfig
-from tiny_inference_engine_b200.parts import CacheNeed
+from tiny_inference_engine_b200.parts import CacheNeed, StateNeed
 from tiny_inference_engine_b200.sampling import SamplingParams
 
 PAGE = 4
@@ -24,11 +26,14 @@ class _Model:
     spec = _Spec()
 
 
-def make_engine(pages=64, tokens=16, seqs=4, policy="fcfs", run_ahead=True, stop=()):
-    cache = CacheManager([CacheNeed("full", 1, 8)], page_size=PAGE, num_pages=pages)
+def make_engine(pages=64, tokens=16, seqs=4, policy="fcfs", run_ahead=True, stop=(), slots=None):
+    """With `slots` the stand-in model keeps per-request state (a count of the tokens run) in that many slots."""
+    states = StateSlots([StateNeed((1,), torch.int64)], slots, device="cpu") if slots else None
+    cache = CacheManager([CacheNeed("full", 1, 8)], page_size=PAGE, num_pages=pages, state_slots=states)
     serving = ServingConfig(tokens, seqs, run_ahead=run_ahead)
-    runner = FakeRunner(cache, tokens, seqs)
-    return Engine(_Model(), cache, Scheduler(cache, SchedulerConfig(serving, policy)), serving, stop_tokens=stop, runner=runner)
+    runner = FakeRunner(cache, tokens, seqs, states=states)
+    return Engine(_Model(), cache, Scheduler(cache, SchedulerConfig(serving, policy)), serving, stop_tokens=stop,
+                  states=states, runner=runner)
 
 
 def drain(eng):
@@ -49,6 +54,46 @@ def test_batched_requests_generate_what_each_generates_alone(run_ahead):
     assert eng.stats().decode_tokens == sum(q.max_tokens for q in params) - len(prompts)
 
 
+@pytest.mark.parametrize("slots", [None, 3, 16])
+def test_ten_times_more_requests_than_a_step_holds_wait_at_no_cost_and_all_finish(slots):
+    """A request that waits holds no page and no state slot (src/engine/sequence.h:15-30,
+    src/engine/engine.cpp:51-62: add_request allocates nothing), so the queue is as long as one likes."""
+    rng = random.Random(5)
+    eng = make_engine(pages=24, tokens=16, seqs=4, slots=slots)
+    prompts = [[rng.randrange(VOCAB) for _ in range(rng.randint(1, 20))] for _ in range(40)]
+    params = [SamplingParams(max_tokens=rng.randint(1, 9), seed=i) for i in range(40)]
+    ids = [eng.add_request(p, q) for p, q in zip(prompts, params)]
+    assert eng.cache.num_free() == 24 and (slots is None or eng.states.num_free == slots)
+    drain(eng)
+    assert [eng.sequence(i).tokens[eng.sequence(i).prompt_len:] for i in ids] == \
+        [generate_alone(p, q) for p, q in zip(prompts, params)]
+    assert eng.cache.num_free() == 24 and (slots is None or eng.states.num_free == slots)
+
+
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_a_row_the_sampler_refuses_ends_its_request_with_an_error_and_the_others_go_on(run_ahead):
+    """A NaN among the logits, or nothing finite: the reference's sampler raises and the engine ends that request
+    with FinishReason::Error while the step's other requests get their tokens
+    (src/sampling/sampler.cpp:18-26, src/engine/engine.cpp:157-174)."""
+    from fake_runner import UNSAMPLABLE
+    prompts = [[1, 2, 3], [4, 5, 6, 7, 8, 9, 10, 11, 12], [13], [14, 15]]
+    q = SamplingParams(max_tokens=8, seed=2)
+    want = [generate_alone(p, q) for p in prompts]
+    eng = make_engine(run_ahead=run_ahead)
+    bad = prompts[1] + want[1][:3]                 # request 1's fourth token cannot be sampled
+    eng.runner.refuse = lambda prefix: prefix == bad
+    seen = []
+    eng.set_token_callback(lambda i, t: seen.append(t))
+    ids = [eng.add_request(p, q) for p in prompts]
+    drain(eng)
+    seqs = [eng.sequence(i) for i in ids]
+    assert seqs[1].finish_reason == FinishReason.ERROR and seqs[1].tokens[len(prompts[1]):] == want[1][:3]
+    for i in (0, 2, 3):
+        assert seqs[i].finish_reason == FinishReason.LENGTH and seqs[i].tokens[len(prompts[i]):] == want[i]
+    assert UNSAMPLABLE not in seen and all(t >= 0 for s in seqs for t in s.tokens)
+    assert eng.cache.num_free() == 64
+
+
 @pytest.mark.parametrize("seed", range(120))
 def test_random_workloads_with_small_pools_stop_tokens_and_cancels(seed):
     rng = random.Random(seed)
@@ -61,7 +106,7 @@ def test_random_workloads_with_small_pools_stop_tokens_and_cancels(seed):
     longest = max(len(p) + q.max_tokens for p, q in zip(prompts, params))
     pages = rng.choice([-(-longest // PAGE) + 1, 24, 200])
     eng = make_engine(pages=pages, tokens=rng.choice([8, 16, 64]), seqs=rng.choice([2, 4, 8]), run_ahead=rng.random() < 0.7,
-                      policy=rng.choice(["fcfs", "srpt-aging"]), stop=stop)
+                      policy=rng.choice(["fcfs", "srpt-aging"]), stop=stop, slots=rng.choice([None, None, 2, 5, 16]))
     ids, arrivals = [], sorted(rng.randint(0, 12) for _ in range(n))
     cancel_at = {i: rng.randint(1, 5) for i in range(n) if rng.random() < 0.15}    # request -> after how many of its tokens
     seen = {}
@@ -90,17 +135,20 @@ def test_random_workloads_with_small_pools_stop_tokens_and_cancels(seed):
             assert got == want[i], f"request {i}"
             assert seq.finish_reason == (FinishReason.STOP if got[-1] in stop else FinishReason.LENGTH)
     assert eng.cache.num_free() == pages
+    assert eng.states is None or eng.states.num_free == eng.states.max_requests
 
 
+@pytest.mark.parametrize("slots", [None, 4])
 @pytest.mark.parametrize("run_ahead", [False, True])
 @pytest.mark.parametrize("at_read", [False, True])
 @pytest.mark.parametrize("fail_at", [1, 2, 3, 5, 8, 9, 10, 13])
-def test_a_failed_step_is_rolled_back(run_ahead, fail_at, at_read):
+def test_a_failed_step_is_rolled_back(run_ahead, fail_at, at_read, slots):
     """A step that fails while it is being queued, or whose ids cannot be read (with another step already queued behind
-    it): the engine raises once, and every request still generates what it generates alone."""
+    it): the engine raises once, and every request still generates what it generates alone. Requests with state of
+    fixed size start over instead of being cut back, since that state cannot be cut back."""
     prompts = [list(range(9)), [3] * 20, [200, 100], [9, 8, 7, 6]]
     params = [SamplingParams(max_tokens=7, seed=i) for i in range(4)]
-    eng = make_engine(tokens=8, seqs=4, run_ahead=run_ahead)
+    eng = make_engine(tokens=8, seqs=4, run_ahead=run_ahead, slots=slots)
     if at_read:
         eng.runner.fail_read_at = {fail_at}
     else:

@@ -14,7 +14,7 @@ def engine_for(model_dir, dtype="float32", **kw):
     return load_engine(model_dir, dtype=dtype, **kw)
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e", "tiny_b4"])
 def test_greedy_and_sampled_generation_match_the_plain_implementation(tiny_models, name):
     from tiny_inference_engine_b200 import SamplingParams
     cfg, page, w, d = tiny_models[name]
@@ -161,6 +161,138 @@ def test_a_failed_step_is_rolled_back_and_the_requests_still_finish(tiny_models)
     assert failures == 1
     assert [eng.sequence(i).tokens[eng.sequence(i).prompt_len:] for i in ids] == want
     assert eng.cache.num_free() == 64
+
+
+def test_tiny_a_workload_as_the_reference_engine_ran_it(tmp_path):
+    """tiny-A: prompts of 5, 17 and 33 tokens, greedy, 8 new tokens each, 8 tokens a step, pages of 16, first come
+    first served. The reference's own Engine ran exactly this (tests/golden/make_golden.py); the ids are its ids."""
+    from test_plain import golden_requests, golden_tokens
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig
+    plain.write_model_dir(tmp_path, plain.TINY_A, plain.random_weights(plain.TINY_A, 0))
+    reqs = golden_requests("tiny_a")
+    assert [(len(p), n) for n, p in reqs] == [(5, 8), (17, 8), (33, 8)]
+    for run_ahead in (False, True):
+        eng = engine_for(tmp_path, num_pages=256, page_size=16, serving=ServingConfig(8, 8, run_ahead=run_ahead), policy="fcfs")
+        got = eng.generate_batch([p for _, p in reqs], [SamplingParams(max_tokens=n) for n, _ in reqs])
+        assert got == golden_tokens("tiny_a")
+        assert eng.stats().seqs_scheduled > eng.stats().steps          # really batched
+        assert eng.stats().prefill_tokens == 5 + 17 + 33 and eng.cache.num_free() == 256
+
+
+def test_tiny_b_workload_with_a_pool_that_forces_a_preemption(tmp_path):
+    """tiny-B (4 query heads over one kv head, head 32, q width 128 beside a hidden size of 96, untied output table,
+    theta 1e6, eps 1e-5): prompts of 1, 9, 40 and 64 tokens, 6 new tokens each, 13 tokens a step, pages of 8, and a pool
+    of so few pages that a request is preempted and computed again. Greedy: the ids of the reference's own Engine,
+    which preempted too. Temperature 0.8 with Philox seed 7 (the reference draws from mt19937, so no reference ids):
+    what every request generates alone, and what the plain implementation generates."""
+    from test_plain import GOLDEN, golden_requests, golden_tokens
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig, load_engine
+    cfg = plain.TINY_B4
+    w = plain.random_weights(cfg, 1)
+    plain.write_model_dir(tmp_path, cfg, w)
+    reqs = golden_requests("tiny_b4")
+    assert [(len(p), n) for n, p in reqs] == [(1, 6), (9, 6), (40, 6), (64, 6)]
+    pool = int((GOLDEN / "tiny_b4_small_pool.txt").read_text())
+    prompts = [p for _, p in reqs]
+
+    def small_engine(run_ahead):
+        # as the reference ran it: first come first served, and admission may use the last free page
+        return load_engine(tmp_path, dtype="float32", num_pages=pool, page_size=8, policy="fcfs", watermark_pages=0,
+                           serving=ServingConfig(13, 8, run_ahead=run_ahead))
+
+    for run_ahead in (False, True):
+        eng = small_engine(run_ahead)
+        assert eng.generate_batch(prompts, [SamplingParams(max_tokens=n) for n, _ in reqs]) == golden_tokens("tiny_b4", small=True)
+        assert eng.stats().preemptions >= 1 and eng.cache.num_free() == pool
+        sampled = [SamplingParams(max_tokens=n, temperature=0.8, seed=7) for n, _ in reqs]
+        got = small_engine(run_ahead).generate_batch(prompts, sampled)
+        alone = engine_for(tmp_path, num_pages=64, page_size=8)
+        assert got == [alone.generate(p, q) for p, q in zip(prompts, sampled)]
+        assert got == [plain.generate(w, cfg, p, 6, temperature=0.8, seed=7) for p in prompts]
+
+
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_a_nan_among_the_logits_ends_that_request_with_an_error_and_the_others_go_on(tiny_models, run_ahead):
+    """A layer hook writes a NaN into the rows at position 12, which only the second request reaches: its row of
+    logits cannot be sampled, the kernels say so with the ids, and the engine ends it as the reference does
+    (src/sampling/sampler.cpp:18-26, src/engine/engine.cpp:157-174). The others generate what they generate alone."""
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig
+    from tiny_inference_engine_b200.engine import FinishReason
+    cfg, page, w, d = tiny_models["tiny_a"]
+    prompts = [[5, 6, 7], [30, 31, 32, 33, 34, 35, 36, 37, 38], [200, 100], [9]]
+    params = [SamplingParams(max_tokens=6, temperature=t, seed=4, top_k=k) for t, k in [(0.0, 0), (0.8, 0), (0.8, 5), (0.0, 0)]]
+    alone = engine_for(d, num_pages=64, page_size=page)
+    want = [alone.generate(p, q) for p, q in zip(prompts, params)]
+    eng = engine_for(d, num_pages=64, page_size=page, serving=ServingConfig(16, 4, run_ahead=run_ahead), policy="fcfs")
+    seen = {}
+    eng.runner.fail_hook = lambda ctx: seen.__setitem__("ctx", ctx)      # called with every step's context; never fails
+
+    def poison(layer, x, pending):
+        if layer == 0:
+            ctx = seen["ctx"]
+            x[:ctx.T].masked_fill_((ctx.positions[:ctx.T] == 12)[:, None], float("nan"))
+
+    eng.runner.layer_hook = poison
+    ids = [eng.add_request(p, q) for p, q in zip(prompts, params)]
+    while eng.has_work():
+        eng.step()
+    seqs = [eng.sequence(i) for i in ids]
+    # position 12 is the input of request 1's fifth generated token: four tokens came out
+    assert seqs[1].finish_reason == FinishReason.ERROR and seqs[1].tokens[9:] == want[1][:4]
+    for i in (0, 2, 3):
+        assert seqs[i].finish_reason == FinishReason.LENGTH and seqs[i].tokens[len(prompts[i]):] == want[i]
+    assert eng.cache.num_free() == 64 and all(t >= 0 for q in seqs for t in q.tokens)
+
+
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_a_mixer_with_state_of_its_own_under_the_engine_with_preemption_and_a_failed_step(run_ahead):
+    """The running-mean toy mixer (state in the engine's state slots) under the scheduler: eight requests, three
+    slots and a pool so small that requests are preempted, one step that fails, steps queued ahead or not. A request
+    takes its slot when it is admitted and loses it when it is preempted; after a failed step requests with state
+    start over. Every request generates what the plain restatement generates for it alone."""
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig, StepRunner, make_cache
+    from tiny_inference_engine_b200.engine import Engine, Scheduler, SchedulerConfig
+    from tiny_inference_engine_b200.parts import Model
+    from test_parts_gpu import DictSource
+    from toy_parts import running_mean_model
+    spec, w, cfg, plain_forward = running_mean_model()
+    model = Model(spec, torch.float32).load(DictSource(w))
+    serving = ServingConfig(16, 4, run_ahead=run_ahead)
+    cache, states = make_cache(model, page_size=8, num_pages=6, max_requests=3)
+    assert cache.needs_state_slot and states.bytes_per_slot == 4 * cfg["hidden_size"]
+    runner = StepRunner(model, cache, serving.max_tokens_per_step, serving.max_seqs, serving.max_seqs, states=states)
+    eng = Engine(model, cache, Scheduler(cache, SchedulerConfig(serving, policy="fcfs", watermark_pages=0)), serving,
+                 states=states, runner=runner)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 256, n).tolist() for n in (5, 17, 9, 1, 12, 3, 20, 7)]
+    new = [10, 6, 12, 9, 5, 11, 4, 8]
+
+    def plain_generate(prompt, n):
+        toks = list(prompt)
+        for _ in range(n):
+            toks.append(int(plain_forward(toks)[-1].argmax()))
+        return toks[len(prompt):]
+
+    want = [plain_generate(p, n) for p, n in zip(prompts, new)]
+    calls = {"n": 0}
+
+    def fail_sixth(ctx):
+        calls["n"] += 1
+        if calls["n"] == 6:
+            raise RuntimeError("injected")
+
+    runner.fail_hook = fail_sixth
+    ids = [eng.add_request(p, SamplingParams(max_tokens=n)) for p, n in zip(prompts, new)]
+    assert states.num_free == 3                        # eight requests wait; none holds a slot
+    failures = 0
+    while eng.has_work():
+        try:
+            eng.step()
+        except RuntimeError:
+            failures += 1
+    assert failures == 1 and eng.stats().preemptions >= 1
+    assert [eng.sequence(i).tokens[len(p):] for i, p in zip(ids, prompts)] == want
+    assert states.num_free == 3 and cache.num_free() == 6
 
 
 def test_capacity_errors_cancel_and_callbacks(tiny_models):

@@ -317,7 +317,7 @@ def test_sampling_kernel_frequencies(ops):
 def _filtered_case(ops, z, rows, counter, one_cta=False):
     """rows: (temperature, top_k, top_p, seed) for each row of z; the kernels against the sampler on the host."""
     from tiny_inference_engine_b200.sampling import SamplingParams
-    from tiny_inference_engine_b200.sampling.sampler import sample_host
+    from host_sampler import sample_host
     R = len(rows)
     params = [SamplingParams(temperature=t, top_k=k, top_p=p, seed=s) for t, k, p, s in rows]
     inv = np.array([q.inv_temperature() for q in params], dtype=np.float32)
@@ -362,6 +362,42 @@ def test_sampling_kernel_filters_over_a_large_vocabulary(ops):
     for counter in (0, 1, 2):
         _filtered_case(ops, z, rows, counter)
     _filtered_case(ops, z, rows, 3, one_cta=True)
+
+
+@pytest.mark.parametrize("one_cta", [False, True])
+def test_sampling_kernels_refuse_rows_with_a_nan_or_nothing_finite(ops, one_cta):
+    """The reference's sampler raises for a NaN logit and for a row of -inf (src/sampling/sampler.cpp:18-26). The
+    kernels answer -2 for such a row, with or without filters, and sample the rows beside it as ever."""
+    from host_sampler import sample_host
+    from tiny_inference_engine_b200.errors import InvalidArgument
+    from tiny_inference_engine_b200.sampling import SamplingParams
+    rng = np.random.default_rng(21)
+    V = 3001
+    params = [SamplingParams(temperature=t, top_k=k, top_p=p, seed=7 + i) for i, (t, k, p) in enumerate(
+        [(0.0, 0, 1.0), (0.0, 0, 1.0), (0.8, 0, 1.0), (0.8, 0, 1.0), (0.8, 20, 0.9), (0.8, 20, 0.9), (0.8, 20, 0.9),
+         (1.0, 0, 0.5), (1.0, 0, 0.5), (0.0, 0, 1.0), (0.7, 5, 1.0)])]
+    R = len(params)
+    z = (rng.standard_normal((R, V)) * 2).astype(np.float32)
+    z[1, 2999] = np.nan          # greedy, a NaN at the far end of the row
+    z[3, 0] = np.nan             # temperature, a NaN at the start
+    z[5, 1500] = np.nan          # filtered, a NaN in the middle (and a +inf, which does not save the row)
+    z[5, 7] = np.inf
+    z[6] = -np.inf               # filtered, nothing finite
+    z[8] = np.nan                # every logit a NaN
+    z[9] = -np.inf               # greedy, nothing finite
+    z[10, 5:] = -np.inf          # five finite values left: this row is fine
+    refused = {1, 3, 5, 6, 8, 9}
+    for r in range(R):
+        if r in refused:
+            with pytest.raises(InvalidArgument):
+                sample_host(z[r], params[r], 3)
+    out = torch.full((R,), 77, dtype=torch.int32, device="cuda")
+    seeds = np.array([q.seed for q in params], dtype=np.int64)
+    ops.sample(dev(z), out, dev(np.array([q.inv_temperature() for q in params], dtype=np.float32)), dev(seeds, torch.int64),
+               dev(np.full(R, 3), torch.int64), dev(np.array([q.top_k for q in params]), torch.int32),
+               dev(np.array([q.top_p for q in params], dtype=np.float32)), one_cta=one_cta)
+    got = out.tolist()
+    assert got == [-2 if r in refused else sample_host(z[r], params[r], 3) for r in range(R)]
 
 
 def test_refusals_are_clear(ops):

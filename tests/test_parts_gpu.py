@@ -240,57 +240,9 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
     registered from here, built by the same Model and stepped by the same step function, cut
     anywhere and beside other requests."""
     from tiny_inference_engine_b200 import StepEntry
-    from tiny_inference_engine_b200.config import LayerSpec, ModelSpec, PartSpec
-    from tiny_inference_engine_b200.parts import Mixer, StateNeed, register_part
-    from tiny_inference_engine_b200.weights import TensorNeed
-
-    class RunningMean(Mixer):
-        def __init__(self, spec, dtype, prefix=""):
-            self.name, self.d, self.dtype = spec["name"], spec["hidden_size"], dtype
-
-        def needs(self):
-            return {self.name: TensorNeed((self.d, self.d))}
-
-        def bind(self, get):
-            self.w = get(self.name).float()
-
-        def state_need(self):
-            return StateNeed((self.d,), torch.float32)
-
-        def forward(self, h, ctx, cache, state):
-            out = torch.empty_like(h)
-            qs = ctx.host.query_start
-            for s in range(ctx.S):                 # a toy: plain torch, one request at a time
-                slot = int(ctx.host.state_slots[s])
-                rows = h[qs[s]:qs[s + 1]].float()
-                sums = state[slot] + torch.cumsum(rows, 0)
-                state[slot] = sums[-1]
-                counts = torch.arange(ctx.host.starts[s] + 1, ctx.host.starts[s] + 1 + rows.shape[0], device=h.device)
-                out[qs[s]:qs[s + 1]] = ((sums / counts[:, None]) @ self.w.T).to(h.dtype)
-            return out
-
-    register_part("mixer", "running_mean", RunningMean, replace=True)
-    cfg = plain.normalise_config(plain.TINY_A)
-    w = plain.random_weights(cfg, 7, std=0.1)
+    from toy_parts import running_mean_model
+    spec, w, cfg, plain_forward = running_mean_model()
     D = cfg["hidden_size"]
-    w["model.layers.1.toy.weight"] = (np.random.default_rng(0).standard_normal((D, D)) * 0.1).astype(np.float32)
-    for k in [k for k in w if k.startswith("model.layers.1.self_attn")]:
-        del w[k]
-    base = qwen_spec(cfg)
-    l1 = base.layers[1]
-    toy = LayerSpec(l1.prefix, l1.block, PartSpec("running_mean", {"name": "model.layers.1.toy.weight", "hidden_size": D}),
-                    l1.mixer_norm, l1.ffn, l1.ffn_norm)
-    spec = ModelSpec(**{**base.__dict__, "layers": (base.layers[0], toy)})
-
-    def plain_forward(toks):
-        T, pos = len(toks), np.arange(len(toks))
-        x = plain.embed(w["model.embed_tokens.weight"], toks)
-        x = plain.decoder_layer(x, w, 0, cfg, pos)
-        p = "model.layers.1."
-        h = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
-        x = x + (np.cumsum(h, 0) / (pos + 1)[:, None]) @ w[p + "toy.weight"].astype(np.float64).T
-        x = x + plain.mlp_block(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]), w, p)
-        return plain.linear(plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), w["model.embed_tokens.weight"])
 
     model, cache, runner = build(spec, w, "float32", page=8, pages=32)
     assert model.cache_needs()[1] is None and model.state_needs()[1].shape == (D,)
@@ -298,7 +250,9 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
     rng = np.random.default_rng(8)
     a, b = rng.integers(0, 256, 40).tolist(), rng.integers(0, 256, 25).tolist()
     ra, rb = cache.new_request(), cache.new_request()
-    assert ra.state_slot != rb.state_slot
+    assert ra.state_slot == rb.state_slot == -1          # a slot is taken by the first reserve, not before
+    with pytest.raises(Exception, match="without a state slot"):
+        runner.run([StepEntry(ra, a[:1], 0, [0])])
     got_a, got_b, pa, pb = [], [], 0, 0
     for na, nb in [(7, 0), (2, 11), (1, 1), (20, 13), (10, 0)]:
         entries = []
@@ -311,6 +265,7 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
         out = runner.run(entries).float().cpu().numpy()
         got_a.append(out[:na]), got_b.append(out[na:])
         pa, pb = pa + na, pb + nb
+    assert ra.state_slot >= 0 and rb.state_slot >= 0 and ra.state_slot != rb.state_slot
     assert_logits_close(np.concatenate(got_a), plain_forward(a), "float32", "toy mixer, request a")
     assert_logits_close(np.concatenate(got_b), plain_forward(b), "float32", "toy mixer, request b")
     # a slot handed out again starts from zero
@@ -431,6 +386,114 @@ def test_a_toy_feed_forward_with_routing_and_another_position_encoding():
         pa, pb = pa + na, pb + nb
     assert_logits_close(np.concatenate(got_a), want_a, "float32", "toy parts, request a beside b")
     assert_logits_close(np.concatenate(got_b), want_b, "float32", "toy parts, request b beside a")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_embedding_output_head_norm_and_a_rotation_with_a_score_scale(dtype):
+    """Four more parts the framework has never seen, registered from here, each chosen by the model description
+    alone: an embedding scaled by sqrt(hidden), an output head with a soft cap on the logits, a head norm with
+    another formula (x^ * (1 + w), its weight under the usual name: the fused q/k kernel must not stand in for
+    it), and a rotation with stretched frequencies that asks for a factor on the attention scores."""
+    import dataclasses
+    from tiny_inference_engine_b200.config import ModelSpec, PartSpec
+    from tiny_inference_engine_b200.parts import (LMHead, Norm, RotaryEncoding, TokenEmbedding, register_part)
+    from tiny_inference_engine_b200.weights import TensorNeed
+    CAP, STRETCH, FACTOR = 5.0, 4.0, 1.21
+
+    class ScaledEmbedding(TokenEmbedding):
+        def forward(self, tokens, x):
+            super().forward(tokens, x)
+            x.mul_(float(np.sqrt(np.float32(self.hidden))))
+
+    class SoftCapHead(LMHead):
+        def forward(self, last, logits):
+            super().forward(last, logits)
+            logits.copy_(CAP * torch.tanh(logits / CAP))
+
+    class OnePlusNorm(Norm):
+        def __init__(self, spec, dtype, prefix=""):
+            self.name, self.size, self.eps = prefix + spec["name"], spec["size"], spec["eps"]
+
+        def needs(self):
+            return {self.name: TensorNeed((self.size,), "norm")}
+
+        def bind(self, get):
+            self.weight = get(self.name).float()
+
+        def rows(self, x, out):
+            v = x.float()
+            out.copy_((v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps) * (1.0 + self.weight)).to(out.dtype))
+
+    class StretchedRope(RotaryEncoding):
+        def __init__(self, spec, dtype, prefix=""):
+            super().__init__(spec, dtype, prefix)
+            self.inv_freq_host = (self.inv_freq_host / np.float32(STRETCH)).astype(np.float32)
+
+        def score_scale(self):
+            return FACTOR
+
+    register_part("embedding", "scaled_embedding", ScaledEmbedding, replace=True)
+    register_part("head", "soft_cap_head", SoftCapHead, replace=True)
+    register_part("norm", "one_plus_norm", OnePlusNorm, replace=True)
+    register_part("position", "stretched_rope", StretchedRope, replace=True)
+
+    cfg = plain.normalise_config(plain.TINY_D)
+    w = sharp_weights(cfg, 31)
+    base = qwen_spec(cfg)
+    l0, l1 = base.layers
+    p0 = dict(l0.mixer.params)
+    p0["q_norm"] = PartSpec("one_plus_norm", dict(p0["q_norm"].params))
+    p1 = dict(l1.mixer.params)
+    p1["position"] = PartSpec("stretched_rope", dict(p1["position"].params))
+    spec = ModelSpec(**{**base.__dict__, "embedding": PartSpec("scaled_embedding", dict(base.embedding.params)),
+                        "head": PartSpec("soft_cap_head", dict(base.head.params)),
+                        "layers": (dataclasses.replace(l0, mixer=PartSpec(l0.mixer.kind, p0)),
+                                   dataclasses.replace(l1, mixer=PartSpec(l1.mixer.kind, p1)))})
+    Hq, Hkv, Dh, eps, theta = (cfg[k] for k in ("num_attention_heads", "num_key_value_heads", "head_dim", "rms_norm_eps", "rope_theta"))
+    ws = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()} if dtype == "bfloat16" else w
+    st = lambda a: plain.round_bf16(a) if dtype == "bfloat16" else a       # what the engine stores between kernels
+
+    def rotate(x, pos, heads, stretch):
+        T, half = x.shape[0], Dh // 2
+        inv = (plain.rope_inv_freq(theta, Dh) / np.float32(stretch)).astype(np.float32)
+        ang = (pos.astype(np.float32)[:, None] * inv[None, :]).astype(np.float32).astype(np.float64)
+        c, s_ = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+        v = x.reshape(T, heads, Dh)
+        return np.concatenate([v[..., :half] * c - v[..., half:] * s_, v[..., half:] * c + v[..., :half] * s_], -1).reshape(T, -1)
+
+    def layer(x, i, pos, one_plus, stretch, factor):
+        p, T = f"model.layers.{i}.", x.shape[0]
+        h = st(plain.rms_norm(x, ws[p + "input_layernorm.weight"], eps))
+        q, k, v = (st(plain.linear(h, ws[p + f"self_attn.{n}_proj.weight"])) for n in "qkv")
+        qw = ws[p + "self_attn.q_norm.weight"]
+        if one_plus:
+            qr = q.reshape(T * Hq, Dh).astype(np.float64)
+            q = st(qr / np.sqrt((qr ** 2).mean(-1, keepdims=True) + eps) * (1.0 + qw.astype(np.float64))).reshape(T, -1)
+        else:
+            q = plain.rms_norm(q.reshape(T * Hq, Dh), qw, eps).reshape(T, -1)
+        k = plain.rms_norm(k.reshape(T * Hkv, Dh), ws[p + "self_attn.k_norm.weight"], eps).reshape(T, -1)
+        q, k = st(rotate(q, pos, Hq, stretch)), st(rotate(k, pos, Hkv, stretch))
+        a = st(plain.causal_attention(q * factor, k, v, Hq, Hkv, Dh))      # a factor on every score
+        x = x + st(plain.linear(a, ws[p + "self_attn.o_proj.weight"]))
+        h = st(plain.rms_norm(x, ws[p + "post_attention_layernorm.weight"], eps))
+        return x + plain.mlp_block(h, ws, p, dtype)
+
+    def plain_forward(toks):
+        pos = np.arange(len(toks))
+        x = plain.embed(ws["model.embed_tokens.weight"], toks) * np.float64(np.sqrt(np.float32(cfg["hidden_size"])))
+        x = layer(x, 0, pos, True, 1.0, 1.0)
+        x = layer(x, 1, pos, False, STRETCH, FACTOR)
+        logits = plain.linear(st(plain.rms_norm(x, ws["model.norm.weight"], eps)), ws["lm_head.weight"])
+        return CAP * np.tanh(logits / CAP)
+
+    model, cache, runner = build(spec, w, dtype, page=16, pages=32)
+    assert type(model.embedding).__name__ == "ScaledEmbedding" and type(model.head).__name__ == "SoftCapHead"
+    assert not model.layers[0].mixer.q_norm.fusable_rms and model.layers[0].mixer.k_norm.fusable_rms
+    toks = np.random.default_rng(4).integers(0, cfg["vocab_size"], 90).tolist()
+    want = plain_forward(toks)
+    assert np.abs(want).max() > 0.5 * CAP                       # the cap bites
+    assert_logits_close(run_whole(runner, cache, toks), want, dtype, "toy embedding, head, norm, rotation: whole")
+    assert_logits_close(run_whole(runner, cache, toks, cuts=[50, 2, 1, 1, 36]), want, dtype, "the same in portions")
 
 
 @pytest.mark.timeout(600)

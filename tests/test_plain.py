@@ -2,37 +2,60 @@
 from pathlib import Path
 
 import numpy as np
+import pytest
 
 import plain_qwen3 as plain
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-def _requests():
+# model of tests/golden -> (configuration, seed of its weights)
+MODELS = {"tiny_a": (plain.TINY_A, 0), "tiny_b4": (plain.TINY_B4, 1)}
+
+
+def golden_requests(name):
+    """[(tokens to generate, prompt)] of a golden workload."""
     out = []
-    for line in (GOLDEN / "tiny_a_requests.txt").read_text().splitlines():
+    for line in (GOLDEN / f"{name}_requests.txt").read_text().splitlines():
         f = [int(x) for x in line.split()]
         out.append((f[0], f[1:]))
     return out
 
 
-def test_logits_and_hidden_states_match_the_reference():
-    cfg, w = plain.TINY_A, plain.random_weights(plain.TINY_A, 0)
-    for i, (_, ids) in enumerate(_requests()):
+def golden_tokens(name, small=False):
+    lines = (GOLDEN / f"{name}_greedy{'_small' if small else ''}.txt").read_text().splitlines()
+    return [[int(x) for x in l.split()] for l in lines if not l.startswith("#")]
+
+
+@pytest.mark.parametrize("name", list(MODELS))
+def test_logits_and_hidden_states_match_the_reference(name):
+    cfg, seed = MODELS[name]
+    w = plain.random_weights(cfg, seed)
+    for i, (_, ids) in enumerate(golden_requests(name)):
         hidden = []
         logits = plain.forward(w, cfg, ids, hidden_out=hidden)
-        ref = np.fromfile(GOLDEN / f"tiny_a_logits_{i}.f32", dtype="<f4").reshape(len(ids), -1)
-        ref_h = np.fromfile(GOLDEN / f"tiny_a_hidden_{i}.f32", dtype="<f4").reshape(cfg["num_hidden_layers"], len(ids), -1)
+        ref = np.fromfile(GOLDEN / f"{name}_logits_{i}.f32", dtype="<f4").reshape(len(ids), -1)
+        ref_h = np.fromfile(GOLDEN / f"{name}_hidden_{i}.f32", dtype="<f4").reshape(cfg["num_hidden_layers"], len(ids), -1)
+        assert ref.shape[1] == cfg["vocab_size"] and ref_h.shape[2] == cfg["hidden_size"]
         assert np.abs(logits - ref).max() <= 2e-6 * np.abs(ref).max()
         assert np.abs(np.stack(hidden) - ref_h).max() <= 2e-6 * np.abs(ref_h).max()
         assert (logits.argmax(-1) == ref.argmax(-1)).all()
 
 
-def test_greedy_tokens_match_the_reference_engine():
-    cfg, w = plain.TINY_A, plain.random_weights(plain.TINY_A, 0)
-    want = [[int(x) for x in l.split()] for l in (GOLDEN / "tiny_a_greedy.txt").read_text().splitlines()]
-    for (n_new, ids), ref in zip(_requests(), want):
+@pytest.mark.parametrize("name", list(MODELS))
+def test_greedy_tokens_match_the_reference_engine(name):
+    cfg, seed = MODELS[name]
+    w = plain.random_weights(cfg, seed)
+    for (n_new, ids), ref in zip(golden_requests(name), golden_tokens(name)):
         assert plain.generate(w, cfg, ids, n_new) == ref
+
+
+def test_the_reference_engine_generates_the_same_tokens_when_it_preempts():
+    """tiny-B's workload from a pool of so few pages that the reference's scheduler preempts a request
+    (tests/engine/test_engine_batching.cpp:58-75): the tokens are those of the roomy run."""
+    header = (GOLDEN / "tiny_b4_greedy_small.txt").read_text().splitlines()[0]
+    assert header.startswith("# preemptions ") and int(header.split()[2]) >= 1
+    assert golden_tokens("tiny_b4", small=True) == golden_tokens("tiny_b4")
 
 
 def test_rope_position_zero_is_identity_and_scores_depend_on_distance_only():

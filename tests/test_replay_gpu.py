@@ -58,7 +58,7 @@ def cuts_of(n, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e", "tiny_b4"])
 def test_replay(tiny_models, tmp_path, name, dtype):
     cfg, page, w, model_dir = tiny_models[name]
     V = cfg["vocab_size"]

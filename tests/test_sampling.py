@@ -4,7 +4,8 @@ import pytest
 
 import plain_qwen3 as plain
 from tiny_inference_engine_b200.errors import InvalidArgument
-from tiny_inference_engine_b200.sampling import SamplingParams, philox4x32, sample_host, uniform
+from host_sampler import sample_host
+from tiny_inference_engine_b200.sampling import SamplingParams, philox4x32, uniform
 
 
 def test_params_are_checked():

@@ -7,11 +7,11 @@ import random
 
 import pytest
 
-from tiny_inference_engine_b200.cache import CacheManager, blocks_for
+from tiny_inference_engine_b200.cache import CacheManager, StateSlots, blocks_for
 from tiny_inference_engine_b200.engine import Scheduler, SchedulerConfig, ServingConfig
 from tiny_inference_engine_b200.engine.sequence import SeqState, Sequence
 from tiny_inference_engine_b200.errors import InvalidArgument
-from tiny_inference_engine_b200.parts import CacheNeed
+from tiny_inference_engine_b200.parts import CacheNeed, StateNeed
 from tiny_inference_engine_b200.sampling import SamplingParams
 
 PAGE = 4
@@ -20,8 +20,12 @@ PAGE = 4
 class Rig:
     """Scheduler + cache, and the engine's bookkeeping around them."""
 
-    def __init__(self, pages=64, tokens=16, seqs=4, policy="fcfs", aging=16, watermark=-1, needs=None):
-        self.cache = CacheManager(needs or [CacheNeed("full", 1, 8)], page_size=PAGE, num_pages=pages)
+    def __init__(self, pages=64, tokens=16, seqs=4, policy="fcfs", aging=16, watermark=-1, needs=None, slots=None,
+                 window_requests=None):
+        needs = needs or [CacheNeed("full", 1, 8)]
+        self.states = StateSlots([StateNeed((2,))] + [None] * (len(needs) - 1), slots) if slots else None
+        self.cache = CacheManager(needs, page_size=PAGE, num_pages=pages, state_slots=self.states,
+                                  window_requests=window_requests, window_step_tokens=tokens)
         self.s = Scheduler(self.cache, SchedulerConfig(ServingConfig(tokens, seqs), policy, aging, watermark))
         self.seqs, self.next = [], 0
 
@@ -189,13 +193,43 @@ def test_cancel_while_waiting_running_or_preempted():
     assert a.num_generated == 6 and r.cache.num_free() == 4
 
 
-@pytest.mark.parametrize("seed", range(60))
+def test_state_slots_are_taken_at_admission_and_admission_stops_when_none_is_left():
+    """Requests that wait hold nothing, however many there are; a request gets its slot when it is admitted and
+    loses it when it is preempted or ends; with no slot free admission stops (it does not raise)."""
+    r = Rig(pages=64, tokens=32, seqs=4, slots=2)
+    qs = [r.add(3, max_tokens=3) for _ in range(40)]
+    assert r.states.num_free == 2 and all(q.cache.state_slot == -1 for q in qs)
+    assert r.step() == [(0, 3), (1, 3)]                   # two slots: two requests run, although four are allowed
+    assert r.states.num_free == 0 and {qs[0].cache.state_slot, qs[1].cache.state_slot} == {0, 1}
+    assert r.step() == [(0, 1), (1, 1)]
+    assert r.step() == [(0, 1), (1, 1)]                   # both end here and give their slots back
+    assert r.states.num_free == 2
+    assert r.step() == [(2, 3), (3, 3)]
+    while r.s.has_work():
+        r.step()
+    assert all(q.num_generated == 3 for q in qs) and r.states.num_free == 2 and r.cache.num_free() == 64
+
+
+def test_a_preempted_request_gives_its_state_slot_back():
+    r = Rig(pages=4, tokens=16, seqs=4, watermark=0, slots=3)
+    a, b = r.add(7, 6), r.add(7, 6)
+    r.step(), r.step()
+    assert r.states.num_free == 1
+    assert r.step() == [(0, 1)] and b.state == SeqState.WAITING and b.cache.state_slot == -1
+    assert r.states.num_free == 2
+    while r.s.has_work():
+        r.step()
+    assert a.num_generated == b.num_generated == 6 and r.states.num_free == 3
+
+
+@pytest.mark.parametrize("seed", range(300))
 def test_randomized_simulation_keeps_the_invariants(seed):
     rng = random.Random(seed)
     needs = [CacheNeed("full", 1, 8)] + ([CacheNeed("window", 1, 8, window=rng.choice([6, 13]))] if seed % 3 == 0 else [])
     pages, tokens, seqs = rng.randint(6, 40), rng.choice([4, 8, 16, 32]), rng.randint(1, 4)
     r = Rig(pages=pages, tokens=max(tokens, seqs), seqs=seqs, policy=rng.choice(["fcfs", "srpt-aging"]),
-            aging=rng.choice([0, 4, 16]), needs=needs)
+            aging=rng.choice([0, 4, 16]), needs=needs, slots=rng.choice([None, 1, 2, 5]),
+            window_requests=rng.choice([None, seqs]) if len(needs) > 1 else None)
     cap = pages * PAGE
     pending_adds = rng.randint(3, 12)
     empty_in_a_row = 0
@@ -233,9 +267,16 @@ def test_randomized_simulation_keeps_the_invariants(seed):
             assert len(held) == len(set(held)) and len(held) + pool.num_free == pool.num_blocks
         for q in live:
             assert len(q.cache.tables[0]) == blocks_for(q.num_computed, PAGE)
+        if r.states is not None:
+            # a slot has one owner, who runs; whoever waits holds none
+            owned = [q.cache.state_slot for q in live if q.cache.state_slot >= 0]
+            assert len(owned) == len(set(owned)) and len(owned) + r.states.num_free == r.states.max_requests
+            assert all(q.cache.state_slot >= 0 for q in r.s.running if q.num_computed > 0)
+            assert all(q.cache.state_slot == -1 for q in r.s.waiting)
     assert not r.s.has_work(), "not every request finished"
     assert all(q.state == SeqState.FINISHED for q in r.seqs)
     assert all(p.num_free == p.num_blocks for p in r.cache.pools)
+    assert r.states is None or r.states.num_free == r.states.max_requests
 
 
 def test_a_batch_that_is_neither_complete_nor_abandoned_keeps_its_requests_out_and_requeue_starts_one_over():

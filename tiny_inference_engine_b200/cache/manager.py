@@ -12,6 +12,15 @@ Pages go back to the pool when a request is released (finished, cancelled or pre
 when a table is truncated after a failed step, and, in a window group, when the window has
 passed them: their table entry becomes -1 and no later query reads below the window.
 `reserve` is all-or-nothing over all groups (src/kv/paged_kv_cache.cpp:41-49).
+
+A request that only waits holds nothing (src/engine/sequence.h:15-30: an empty block table):
+pages and, for models whose mixers keep state of fixed size, the state slot are taken by
+`reserve`, that is when the scheduler admits the request, and go back on `reset`
+(preemption) and `release`.
+
+Groups may differ in size. A window group never holds more than the pages of a window plus
+one step per request, so with `window_requests` and `window_step_tokens` given it gets only
+that many pages and the byte budget goes to the groups that keep every key.
 """
 from __future__ import annotations
 
@@ -76,7 +85,11 @@ class CacheManager:
     storage is allocated (host-side tests and the scheduler's arithmetic)."""
 
     def __init__(self, needs, page_size: int, num_pages: int | None = None, budget_bytes: int | None = None,
-                 dtype=None, device=None, state_slots=None):
+                 dtype=None, device=None, state_slots=None, window_requests: int | None = None,
+                 window_step_tokens: int = 0):
+        """`num_pages` (or what `budget_bytes` buys) is the page count of the groups that keep every key.
+        With `window_requests` a window group holds only what that many requests can use at once:
+        the pages of `window + window_step_tokens` tokens, and two more for the edges, per request."""
         if page_size <= 0:
             raise InvalidArgument(f"page size must be positive, got {page_size}")
         self.page_size = page_size
@@ -94,31 +107,50 @@ class CacheManager:
         self._entry_group = {e: gi for gi, g in enumerate(self.groups) for e in g.entries}
         self._entry_plane = {e: pi for g in self.groups for pi, e in enumerate(g.entries)}
         elem = 4 if dtype is None else _elem_size(dtype)
-        self.bytes_per_page = sum(2 * len(g.entries) * g.kv_heads * page_size * g.head_dim * elem for g in self.groups)
+        group_bytes = [2 * len(g.entries) * g.kv_heads * page_size * g.head_dim * elem for g in self.groups]
+        # what a window group can ever use (None: as many pages as the other groups)
+        bounded = [None] * len(self.groups)
+        if window_requests is not None:
+            if window_requests <= 0 or window_step_tokens < 0:
+                raise InvalidArgument(f"bad window sizing: {window_requests} requests, {window_step_tokens} tokens a step")
+            for gi, g in enumerate(self.groups):
+                if g.kind == "window":
+                    bounded[gi] = window_requests * (blocks_for(g.window + window_step_tokens, page_size) + 2)
+        self.bytes_per_page = sum(b for b, fixed in zip(group_bytes, bounded) if fixed is None) or sum(group_bytes)
         if num_pages is None:
             if budget_bytes is None:
                 raise InvalidArgument("give num_pages or budget_bytes")
-            num_pages = budget_bytes // max(1, self.bytes_per_page)
-            if num_pages == 0:
-                raise CapacityError(f"KV budget of {budget_bytes} bytes is smaller than one {self.bytes_per_page}-byte page")
+            left = budget_bytes - sum(b * fixed for b, fixed in zip(group_bytes, bounded) if fixed is not None)
+            if all(fixed is not None for fixed in bounded) and bounded:
+                left = budget_bytes       # window groups only: the budget caps them all alike
+            num_pages = left // max(1, self.bytes_per_page)
+            if num_pages <= 0:
+                raise CapacityError(f"KV budget of {budget_bytes} bytes is smaller than one {self.bytes_per_page}-byte page"
+                                    + (" beside the window groups' pages" if any(f is not None for f in bounded) else ""))
         num_pages = int(min(num_pages, (2 ** 31 - 1) // page_size))  # slots are 32-bit
         if num_pages <= 0:
             raise InvalidArgument(f"the cache needs at least one page, got {num_pages}")
         self.num_pages = num_pages
-        self.pools = [BlockPool(num_pages) for _ in self.groups]
+        self.group_pages = [num_pages if fixed is None else int(min(fixed, num_pages)) for fixed in bounded]
+        self.pools = [BlockPool(n) for n in self.group_pages]
         self.storage = []
         if device is not None:
             import torch
-            for g in self.groups:
-                self.storage.append(torch.zeros((len(g.entries), 2, num_pages, g.kv_heads, page_size, g.head_dim),
+            for g, n in zip(self.groups, self.group_pages):
+                self.storage.append(torch.zeros((len(g.entries), 2, n, g.kv_heads, page_size, g.head_dim),
                                                 dtype=dtype, device=device))
         self.state_slots = state_slots
         self._live: set[int] = set()
 
+    @property
+    def needs_state_slot(self) -> bool:
+        """True when some mixer of the model keeps per-request state: a request then runs only with a slot."""
+        return self.state_slots is not None and self.state_slots.has_state
+
     # -- requests
     def new_request(self) -> RequestCache:
-        slot = self.state_slots.allocate() if self.state_slots is not None else -1
-        req = RequestCache([BlockTable() for _ in self.groups], slot)
+        """A request that holds nothing yet: empty tables, no state slot."""
+        req = RequestCache([BlockTable() for _ in self.groups], -1)
         self._live.add(id(req))
         return req
 
@@ -132,20 +164,45 @@ class CacheManager:
         want = blocks_for(new_len, self.page_size)
         return [max(0, want - len(t)) for t in req.tables]
 
+    def _lacks_slot(self, req: RequestCache) -> bool:
+        return self.needs_state_slot and req.state_slot < 0
+
+    def holds(self, req: RequestCache) -> bool:
+        """Whether preempting the request would give anything back: a page or a state slot."""
+        return req.state_slot >= 0 or any(len(t) > t.released for t in req.tables)
+
     def room(self, req: RequestCache, computed: int) -> int:
         """How many more tokens `req` could hold with its pages plus all free ones
-        (src/engine/batch_scheduler.cpp:42-48, the minimum over groups)."""
+        (src/engine/batch_scheduler.cpp:42-48, the minimum over groups); none if it needs a state slot,
+        has none and none is free."""
+        if self._lacks_slot(req) and self.state_slots.num_free == 0:
+            return 0
         if not self.groups:
             return 2 ** 31
         return min((len(t) + p.num_free) * self.page_size - computed for t, p in zip(req.tables, self.pools))
 
+    def admits(self, tokens: int, keep_free) -> bool:
+        """Whether a request that holds nothing can take `tokens` tokens and leave `keep_free[g]` pages of
+        every group free (a state slot, where the model needs one, must be free too)."""
+        if self.needs_state_slot and self.state_slots.num_free == 0:
+            return False
+        pages = blocks_for(tokens, self.page_size)
+        return all(p.num_free - pages >= keep for p, keep in zip(self.pools, keep_free))
+
     def reserve(self, req: RequestCache, new_len: int) -> bool:
-        """Grows every table to cover new_len tokens, or changes nothing and returns False."""
+        """Grows every table to cover new_len tokens and takes a state slot (zeroed) if the request needs one
+        and has none; or changes nothing and returns False."""
         if new_len < 0:
             raise InvalidArgument(f"cannot reserve pages for {new_len} tokens")
+        if not req.live:
+            raise InvalidArgument("cannot reserve for a released request")
         need = self.pages_needed(req, new_len)
         if any(n > p.num_free for n, p in zip(need, self.pools)):
             return False
+        if self._lacks_slot(req):
+            if self.state_slots.num_free == 0:
+                return False
+            req.state_slot = self.state_slots.allocate()
         for n, t, p in zip(need, req.tables, self.pools):
             for _ in range(n):
                 t.append(p.allocate())
@@ -204,14 +261,16 @@ class CacheManager:
         self._live.discard(id(req))
 
     def reset(self, req: RequestCache) -> None:
-        """Preemption: pages go back, the request stays and starts again from token 0 with a zeroed state."""
+        """Preemption: pages and state slot go back, the request stays; its next `reserve` starts it again
+        from token 0 with a slot handed out zeroed."""
         for t, p in zip(req.tables, self.pools):
             for b in t.held():
                 p.release(b)
             t.n = 0
             t.released = 0
         if self.state_slots is not None and req.state_slot >= 0:
-            self.state_slots.zero(req.state_slot)
+            self.state_slots.release(req.state_slot)
+        req.state_slot = -1
 
     # -- what the model sees
     def group_of(self, entry: int) -> int:
@@ -229,7 +288,10 @@ class CacheManager:
         return LayerCache(st[pi, 0], st[pi, 1], gi, writes)
 
     def max_tokens_per_request(self) -> int:
-        return self.num_pages * self.page_size
+        """The longest a lone request can get: what the groups that keep every key can hold (a window
+        group gives pages back as it goes and bounds nothing)."""
+        full = [n for g, n in zip(self.groups, self.group_pages) if g.kind == "full"]
+        return min(full) * self.page_size if full else 2 ** 31 - 1
 
 
 def _elem_size(dtype) -> int:

@@ -1,9 +1,10 @@
 """Slots of per-request state of fixed size, beside the paged cache.
 
 A mixer that carries state across steps (a recurrence, a running sum) declares a shape; every
-admitted request owns one slot index, the same in every such layer. A slot is zeroed when
-it is handed out and when its request is preempted: state is recomputed from token 0 like
-the keys and values. The reference has no such state (src/engine/sequence.h:15-30); with
+admitted request owns one slot index, the same in every such layer. A slot is taken when a
+request is admitted (its first `CacheManager.reserve`), zeroed as it is handed out, and given
+back when the request ends or is preempted: state is recomputed from token 0 like the keys
+and values. A request that waits holds none. The reference has no such state (src/engine/sequence.h:15-30); with
 no stateful mixer in the model the pool holds indices only and no memory.
 """
 from __future__ import annotations
@@ -20,6 +21,7 @@ class StateSlots:
         self._free = list(range(max_requests - 1, -1, -1))
         self._used = [False] * max_requests
         self._tensors = {}
+        self.has_state = any(need is not None for need in needs)
         if device is not None:
             import torch
             for i, need in enumerate(needs):

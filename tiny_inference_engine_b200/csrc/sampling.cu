@@ -74,9 +74,12 @@ __device__ __forceinline__ void block_argmax(float& v, int& i, float* sv, int* s
   i = si[0];
 }
 
-// out[r] = sampled id of row r. inv_temperature[r] == 0 means greedy. A NaN logit never
-// compares greater, so it is never chosen; rows are checked for NaN on the host only when the
-// caller asks for the host sampler.
+// What the kernels answer for a row that cannot be sampled: one with a NaN among its logits, or with
+// no value above -inf. The reference's sampler raises for both (src/sampling/sampler.cpp:18-26); here the
+// refusal travels with the ids, and whoever reads them ends that request (the rows beside it are sampled).
+constexpr int kUnsamplable = -2;
+
+// out[r] = sampled id of row r, or kUnsamplable. inv_temperature[r] == 0 means greedy.
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* __restrict__ logits, long long row_stride,
                                                                 int vocab, const float* __restrict__ inv_temperature,
                                                                 const unsigned long long* __restrict__ seeds,
@@ -94,6 +97,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* __r
 
   float best = -INFINITY;
   int best_i = 0x7fffffff;
+  int nan_seen = 0;
   // eight loads in flight per thread: one block reads the row, so what bounds it is the latency of its loads
   for (int i0 = tid; i0 < vocab; i0 += 8 * kSampleThreads) {
     float v[8];
@@ -105,10 +109,15 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const float* __r
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int i = i0 + j * kSampleThreads;
+      nan_seen |= v[j] != v[j];
       if (i < vocab) arg_better(best, best_i, v[j], i);
     }
   }
   block_argmax(best, best_i, sv, si);
+  if (__syncthreads_or(nan_seen) || best == -INFINITY) {   // a NaN somewhere, or nothing finite to choose from
+    if (tid == 0) out[r] = kUnsamplable;
+    return;
+  }
   const float inv_t = inv_temperature ? inv_temperature[r] : 0.0f;
   if (!(inv_t > 0.0f) || isinf(inv_t) || best == INFINITY) {  // greedy, or a certain token
     if (tid == 0) out[r] = best_i;
@@ -375,7 +384,8 @@ __device__ void filter_select(const float* __restrict__ z, int vocab, float best
 __device__ __forceinline__ double warp_shfl_up_double(double v, int o) { return __shfl_up_sync(0xffffffffu, v, o); }
 
 // Rows with top_k[r] in (0, vocab) or top_p[r] < 1 and a temperature: out[r] is overwritten with
-// the filtered draw (the plain kernel has written the unfiltered one). Other rows are left alone.
+// the filtered draw (the plain kernel has written the unfiltered one). Other rows are left alone,
+// and so are rows that the plain kernel refused (kUnsamplable).
 __global__ void __launch_bounds__(kFilterThreads) sample_filtered_kernel(const float* __restrict__ logits, long long row_stride,
                                                                          int vocab, const float* __restrict__ inv_temperature,
                                                                          const int* __restrict__ top_k,
@@ -392,6 +402,7 @@ __global__ void __launch_bounds__(kFilterThreads) sample_filtered_kernel(const f
   const float p = top_p[r];
   const bool by_k = k > 0 && k < vocab, by_p = p < 1.0f;
   if (!(inv_t > 0.0f) || isinf(inv_t) || (!by_k && !by_p)) return;   // greedy or unfiltered: the plain kernel's id stands
+  if (out[r] == kUnsamplable) return;                                 // the plain kernel refused the row: so does this one
   const float* z = logits + static_cast<long long>(r) * row_stride;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -598,6 +609,7 @@ __global__ void __launch_bounds__(kFilterThreads, 1) sample_filtered_cluster_ker
   const float p = top_p[r];
   const bool by_k = k > 0 && k < vocab, by_p = p < 1.0f;
   if (!(inv_t > 0.0f) || isinf(inv_t) || (!by_k && !by_p)) return;   // the whole cluster: the plain kernel's id stands
+  if (out[r] == kUnsamplable) return;                                 // the plain kernel refused the row (every CTA reads the same word)
   const float* z = logits + static_cast<long long>(r) * row_stride;
 
   // the row's maximum: each CTA over its ids, then the eight results in rank order

@@ -31,6 +31,7 @@ class EngineStats:
 
 
 PLACEHOLDER = -1      # stands in a request's tokens for the one that a step in flight is sampling
+UNSAMPLABLE = -2      # what the sampling kernels answer for a row with a NaN or with nothing finite (csrc/sampling.cu)
 
 
 @dataclass
@@ -83,14 +84,15 @@ class Engine:
                 raise InvalidArgument(f"prompt token {t} outside vocabulary of {vocab}")
         page = self.cache.page_size
         context_cap = self.model.spec.max_positions
-        pool_cap = self.cache.num_pages * page
+        pool_cap = self.cache.max_tokens_per_request()
         n = len(prompt)
         if n >= context_cap:
             raise CapacityError(f"prompt of {n} tokens leaves no room to generate in the model context of {context_cap}")
         if n >= pool_cap:
             raise CapacityError(f"prompt of {n} tokens plus one generated token needs {blocks_for(n + 1, page)} KV pages "
-                                f"but the cache holds {self.cache.num_pages}; raise --kv-mem")
+                                f"but the cache holds {pool_cap // page}; raise --kv-mem")
         params.max_tokens = min(params.max_tokens, min(context_cap, pool_cap) - n)
+        # A waiting request holds no page and no state slot: both are taken when the scheduler admits it.
         seq = Sequence(id=self._next_id, tokens=prompt, prompt_len=n, params=params, cache=self.cache.new_request())
         self._next_id += 1
         self.scheduler.add(seq)
@@ -237,7 +239,7 @@ class Engine:
         for seq, _ in batch.seqs:
             if seq.state == SeqState.FINISHED:
                 continue
-            if self.states is not None and self.states.bytes_per_slot > 0:
+            if self.cache.needs_state_slot:
                 self.cache.reset(seq.cache)
                 seq.num_computed = 0
             else:
@@ -296,6 +298,11 @@ class Engine:
             if seq.state == SeqState.FINISHED:
                 continue  # cancelled by an earlier token callback of this step, or ended a step ago
             token = tokens[i]
+            if token < 0:
+                # The sampler refused the row (src/sampling/sampler.cpp:18-26): this request ends with an error,
+                # the step's other requests go on (src/engine/engine.cpp:157-174).
+                self._finish(seq, FinishReason.ERROR)
+                continue
             try:
                 if pending.advanced:
                     seq.tokens[pending.token_at[seq.id]] = token

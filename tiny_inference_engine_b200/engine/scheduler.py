@@ -1,7 +1,9 @@
 """Continuous batching: which requests run in a step and how many of their pending tokens.
 
-The decisions are the reference's BatchScheduler (src/engine/batch_scheduler.cpp:78-174),
-restated over this engine's cache manager (several page groups, state slots):
+The rules are those of the reference's BatchScheduler (src/engine/batch_scheduler.cpp:78-174); the
+code is built around what this engine schedules over: a cache manager with several page groups of
+different sizes, state slots that are a resource like pages, and steps decided while the one before
+is still on the GPU. A decision is a `_Draft` that four passes fill in turn:
 
   1. every running request with exactly one pending token decodes, oldest first; one that
      needs a page when none is free preempts the NEWEST request admitted after it that is
@@ -15,9 +17,11 @@ restated over this engine's cache manager (several page groups, state slots):
   4. if nothing could run, the oldest running request preempts newer ones until it can
      take a portion (the engine never stalls).
 
-When pages run out, a request is preempted BY RECOMPUTE: its pages and state go back, its
-tokens (prompt and generated) stay, and it is prefilled again later
-(src/engine/batch_scheduler.cpp:67-76). An older request is never preempted for a newer one.
+When pages (or state slots) run out, a request is preempted BY RECOMPUTE: its pages and state slot
+go back, its tokens (prompt and generated) stay, and it is prefilled again later
+(src/engine/batch_scheduler.cpp:67-76). A waiting request holds neither pages nor a slot; both are
+taken when it is admitted, by the same all-or-nothing `CacheManager.reserve`. An older request is
+never preempted for a newer one.
 The scheduler owns pages while requests run: every (request, n) it returns already has
 pages reserved for num_computed + n tokens. Deciding a step (`schedule`) is separate from
 finishing it (`complete` / `abandon`); requests of a batch that is neither are skipped by the next
@@ -28,7 +32,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-from ..cache.manager import CacheManager, blocks_for
+from ..cache.manager import CacheManager
 from ..errors import InvalidArgument
 from .sequence import SeqState, Sequence
 
@@ -71,6 +75,20 @@ class ScheduledBatch:
         return not self.seqs
 
 
+class _Draft:
+    """A step while it is being decided: what has been granted and what is left of the step's limits."""
+
+    def __init__(self, number: int, tokens: int, seqs: int):
+        self.batch = ScheduledBatch(id=number)
+        self.tokens_left = tokens
+        self.seq_limit = seqs
+        self.evicted: set[int] = set()      # requests preempted while this step was decided
+
+    @property
+    def closed(self) -> bool:
+        return self.tokens_left == 0 or len(self.batch.seqs) == self.seq_limit
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, config: SchedulerConfig | None = None):
         self.cache = cache
@@ -81,8 +99,11 @@ class Scheduler:
         if self.config.aging < 0:
             raise InvalidArgument(f"aging must be non-negative, got {self.config.aging}")
         wm = self.config.watermark_pages
-        if wm < -1 or wm >= cache.num_pages:
-            raise InvalidArgument(f"watermark of {wm} pages must be -1 (auto) or below the pool's {cache.num_pages} pages")
+        smallest = min((p.num_blocks for p in cache.pools), default=cache.num_pages)
+        if wm < -1 or wm >= smallest:
+            raise InvalidArgument(f"watermark of {wm} pages must be -1 (auto) or below the pool's {smallest} pages")
+        # pages that admission leaves free, per group (src/engine/batch_scheduler.cpp:15-23: 1 % of the pool)
+        self._margins = [wm if wm >= 0 else max(1, p.num_blocks // 100) for p in cache.pools]
         self.watermark = wm if wm >= 0 else max(1, cache.num_pages // 100)
         self.waiting: list[Sequence] = []
         self.running: list[Sequence] = []     # admission order, oldest first
@@ -103,131 +124,108 @@ class Scheduler:
     def _busy(self, seq: Sequence) -> bool:
         return seq.id in self._in_flight
 
-    def _order_key(self, s: Sequence):
-        if self.config.policy == "srpt-aging":
-            return (s.num_pending - self.config.aging * (self.step_no - s.waiting_since_step), s.waiting_since_step, s.id)
-        return (0, s.waiting_since_step, s.id)
+    def _priority(self, s: Sequence):
+        """Admission order (src/engine/batch_scheduler.cpp:31-40): arrival, or least pending work made
+        smaller by `aging` for every step waited; ties by arrival, then id."""
+        waited = self.step_no - s.waiting_since_step
+        score = s.num_pending - self.config.aging * waited if self.config.policy == "srpt-aging" else 0
+        return (score, s.waiting_since_step, s.id)
 
-    def _fit(self, seq: Sequence, want: int) -> int:
-        """The most of `want` tokens `seq` can run next with the pages it holds plus the free ones."""
+    def _room(self, seq: Sequence, want: int) -> int:
+        """How many of `want` tokens `seq` can run next with what it holds plus what is free."""
         return max(0, min(want, self.cache.room(seq.cache, seq.num_computed)))
 
-    def _holds_pages(self, seq: Sequence) -> bool:
-        return any(len(t) > t.released for t in seq.cache.tables)
-
-    def _newest_after(self, index: int):
-        for j in range(len(self.running) - 1, index, -1):
-            s = self.running[j]
-            if not self._busy(s) and self._holds_pages(s):
-                return s
-        return None
-
-    def _newer_busy(self, index: int) -> bool:
-        return any(self._busy(s) for s in self.running[index + 1:])
-
-    def _preempt(self, seq: Sequence) -> None:
+    def _evict(self, seq: Sequence, draft: _Draft) -> None:
         self.cache.reset(seq.cache)
         seq.num_computed = 0
-        seq.state = SeqState.WAITING
-        seq.waiting_since_step = self.step_no
         seq.num_preemptions += 1
         self.num_preemptions += 1
         self.running.remove(seq)
-        self.waiting.append(seq)
+        self.add(seq)
+        draft.evicted.add(seq.id)
+
+    def _make_room(self, seq: Sequence, want: int, draft: _Draft) -> int:
+        """Preempts, newest first, idle requests admitted after `seq` that hold a page or a state slot, until
+        some of `want` tokens of `seq` fit or no such request is left. Returns how many fit."""
+        fit = self._room(seq, want)
+        while fit == 0:
+            behind = self.running[self.running.index(seq) + 1:]
+            victim = next((s for s in reversed(behind) if not self._busy(s) and self.cache.holds(s.cache)), None)
+            if victim is None:
+                break
+            self._evict(victim, draft)
+            fit = self._room(seq, want)
+        return fit
+
+    def _grant(self, draft: _Draft, seq: Sequence, n: int) -> None:
+        if not self.cache.reserve(seq.cache, seq.num_computed + n):
+            raise InvalidArgument(f"sequence {seq.id}: {n} more tokens were counted as fitting, "
+                                  f"but their pages could not be reserved")
+        draft.batch.seqs.append((seq, n))
+        draft.tokens_left -= n
 
     # -- one decision
     def schedule(self) -> ScheduledBatch:
         self.step_no += 1
-        batch = ScheduledBatch(id=self._next_batch)
+        draft = _Draft(self._next_batch, self.config.serving.max_tokens_per_step, self.config.serving.max_seqs)
         self._next_batch += 1
-        budget = self.config.serving.max_tokens_per_step
-        max_seqs = self.config.serving.max_seqs
-        page = self.cache.page_size
+        self._decode_pass(draft)
+        self._prompt_pass(draft)
+        self._admission_pass(draft)
+        if draft.batch.empty():
+            self._rescue_pass(draft)
+        self._in_flight.update(seq.id for seq, _ in draft.batch.seqs)
+        return draft.batch
 
-        def full() -> bool:
-            return budget == 0 or len(batch.seqs) == max_seqs
-
-        def take(seq: Sequence, n: int) -> None:
-            nonlocal budget
-            if not self.cache.reserve(seq.cache, seq.num_computed + n):
-                raise InvalidArgument(f"scheduler bug: {n} tokens of sequence {seq.id} do not fit the pages it counted")
-            batch.seqs.append((seq, n))
-            budget -= n
-
-        # 1. decodes, oldest first
-        i = 0
-        while i < len(self.running) and not full():
-            seq = self.running[i]
-            if self._busy(seq) or seq.num_pending != 1:
-                i += 1
+    def _decode_pass(self, draft: _Draft) -> None:
+        """Rule 1. The candidates are fixed up front; one that an older candidate preempted is passed over."""
+        for seq in [s for s in self.running if s.num_pending == 1 and not self._busy(s)]:
+            if draft.closed:
+                return
+            if seq.id in draft.evicted:
                 continue
-            preempted_self = deferred = False
-            while self._fit(seq, 1) == 0:
-                victim = self._newest_after(i)
-                if victim is None and self._newer_busy(i):
-                    deferred = True
-                    break
-                self._preempt(victim if victim is not None else seq)
-                if victim is None:
-                    preempted_self = True
-                    break
-            if deferred:
-                i += 1
-                continue
-            if preempted_self:
-                continue  # running[i] is now the next sequence
-            take(seq, 1)
-            i += 1
+            if self._make_room(seq, 1, draft):
+                self._grant(draft, seq, 1)
+            elif any(self._busy(s) for s in self.running[self.running.index(seq) + 1:]):
+                pass        # a newer request is on the GPU: what it holds can be had in the next decision
+            else:
+                self._evict(seq, draft)
 
-        # 2. prompts in progress
+    def _prompt_pass(self, draft: _Draft) -> None:
+        """Rule 2."""
         for seq in self.running:
-            if full():
-                break
-            if self._busy(seq) or seq.num_pending <= 1:
-                continue
-            n = self._fit(seq, min(seq.num_pending, budget))
-            if n > 0:
-                take(seq, n)
+            if draft.closed:
+                return
+            if seq.num_pending > 1 and not self._busy(seq):
+                n = self._room(seq, min(seq.num_pending, draft.tokens_left))
+                if n:
+                    self._grant(draft, seq, n)
 
-        # 3. admission in policy order
-        self.waiting.sort(key=self._order_key)
-        admitted = []
-        for seq in self.waiting:
-            if full() or len(self.running) >= max_seqs:
-                break
-            if seq.num_preemptions > 0 and seq.waiting_since_step == self.step_no:
+    def _admission_pass(self, draft: _Draft) -> None:
+        """Rule 3. Whether a portion fits is asked of every page group and of the state slots at once."""
+        self.waiting.sort(key=self._priority)
+        nothing_kept = [0] * len(self._margins)
+        for seq in list(self.waiting):
+            if draft.closed or len(self.running) >= draft.seq_limit:
+                return
+            if seq.id in draft.evicted:
                 continue
-            n = min(seq.num_pending, budget)
-            keep_free = self.watermark if self.running else 0
-            if self.cache.min_free() - blocks_for(n, page) < keep_free:
-                break
-            seq.state = SeqState.PREFILLING
+            n = min(seq.num_pending, draft.tokens_left)
+            if not self.cache.admits(n, self._margins if self.running else nothing_kept):
+                return
+            self.waiting.remove(seq)
             self.running.append(seq)
-            take(seq, n)
-            admitted.append(seq)
-        if admitted:
-            ids = {s.id for s in admitted}
-            self.waiting = [s for s in self.waiting if s.id not in ids]
+            seq.state = SeqState.PREFILLING
+            self._grant(draft, seq, n)
 
-        # 4. never stall
-        if batch.empty():
-            for i, seq in enumerate(self.running):
-                if self._busy(seq):
-                    continue
-                want = min(seq.num_pending, budget)
-                while self._fit(seq, want) == 0:
-                    victim = self._newest_after(i)
-                    if victim is None:
-                        break
-                    self._preempt(victim)
-                n = self._fit(seq, want)
-                if n > 0:
-                    take(seq, n)
-                break
-
-        for seq, _ in batch.seqs:
-            self._in_flight.add(seq.id)
-        return batch
+    def _rescue_pass(self, draft: _Draft) -> None:
+        """Rule 4: the oldest request that is not on the GPU takes what it can, at the cost of newer ones."""
+        seq = next((s for s in self.running if not self._busy(s)), None)
+        if seq is None:
+            return
+        n = self._make_room(seq, min(seq.num_pending, draft.tokens_left), draft)
+        if n:
+            self._grant(draft, seq, n)
 
     def complete(self, batch: ScheduledBatch) -> None:
         """The engine advanced num_computed of every sequence of the batch (when the step's tokens are back, or,

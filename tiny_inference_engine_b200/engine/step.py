@@ -150,7 +150,7 @@ class StepRunner:
         self._staging_turn = 0
         # The device copy of the index arrays never moves: captured graphs read it at fixed offsets.
         G = len(cache.groups)
-        mb = _round_up(blocks_for(self.max_positions, cache.page_size), 4)
+        mb = self._table_cap = _round_up(blocks_for(self.max_positions, cache.page_size), 4)
         words = 4 * max_tokens + 6 * self.max_seqs + 6 * self.max_logit_rows + G * (max_tokens + self.max_seqs * mb) + 64 * (8 + 2 * G)
         self._dev = torch.zeros(words, dtype=torch.int32, device=device)
         self._ids = torch.zeros(self.max_logit_rows, dtype=torch.int32, device=device)
@@ -251,7 +251,9 @@ class StepRunner:
         sb = _bucket(S, self.max_seqs)
         if sb > self.max_logit_rows or sb > self.max_tokens:
             return None
-        mb = max(16, _bucket(need, 1 << 30))
+        # table lengths come in powers of two, but never longer than the longest table a request can have:
+        # the index buffer is sized for that
+        mb = min(max(16, _bucket(need, 1 << 30)), max(self._table_cap, need))
         filtered = sampling is not None and any(p.filters for p, _ in sampling)   # one more kernel in the graph
         return (sb, mb, sampling is not None, filtered)
 
@@ -314,6 +316,8 @@ class StepRunner:
             seen.add(id(e.cache))
             if not e.cache.live:
                 raise InvalidArgument("a step entry names a released request")
+            if self.cache.needs_state_slot and e.cache.state_slot < 0:
+                raise InvalidArgument("a step entry names a request without a state slot (nothing was reserved for it)")
             end = e.start + len(e.tokens)
             if e.start < 0 or end > self.max_positions:
                 raise CapacityError(f"positions [{e.start}, {end}) do not fit the model's {self.max_positions}")

@@ -47,6 +47,7 @@ class GQAttention(Mixer):
         self.q_norm = build_part("norm", p["q_norm"], dtype, prefix=self.prefix) if p.get("q_norm") else None
         self.k_norm = build_part("norm", p["k_norm"], dtype, prefix=self.prefix) if p.get("k_norm") else None
         self.position = build_part("position", p["position"], dtype, prefix=self.prefix)
+        self.scale *= float(self.position.score_scale())
         self.q_dim, self.kv_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
         self.w_qkv = self.w_o = None
 
@@ -83,14 +84,17 @@ class GQAttention(Mixer):
         T = h.shape[0]
         Hq, Hkv, Dh = self.heads, self.kv_heads, self.head_dim
         g = ctx.groups[cache.group]
+        # One kernel does the head norms, the rotation and the cache append when the parts say it may: a norm
+        # that is exactly an RMSNorm (`fusable_rms`), an encoding that is a rotation by a frequency table or
+        # leaves q and k alone. Anything else is called through its own interface below.
         table = self.position.fused_table()
-        fused = table is not None or type(self.position).__name__ == "NoPositionEncoding"
-        qw = self.q_norm.weight if self.q_norm is not None else None
-        kw = self.k_norm.weight if self.k_norm is not None else None
-        q_eps = self.q_norm.eps if self.q_norm is not None else 0.0
-        k_eps = self.k_norm.eps if self.k_norm is not None else 0.0
-        fused = fused and all(n is None or hasattr(n, "weight") for n in (self.q_norm, self.k_norm))
+        fused = (table is not None or self.position.is_identity) and \
+            all(n is None or n.fusable_rms for n in (self.q_norm, self.k_norm))
         if fused:
+            qw = self.q_norm.weight if self.q_norm is not None else None
+            kw = self.k_norm.weight if self.k_norm is not None else None
+            q_eps = self.q_norm.eps if self.q_norm is not None else 0.0
+            k_eps = self.k_norm.eps if self.k_norm is not None else 0.0
             width = self.q_dim + (2 * self.kv_dim if cache.writes else 0)
             qkv = ctx.ws.rows("attn.qkv", T, self.q_dim + 2 * self.kv_dim, self.dtype)[:, :width]
             if self._capacity is None:
@@ -107,7 +111,8 @@ class GQAttention(Mixer):
             self.gemm_q(h, q)
             if self.q_norm is not None:
                 self.q_norm.rows(q.view(T * Hq, Dh), q.view(T * Hq, Dh))
-            self.position.apply(q, ctx.positions, Hq, Dh)
+            if not self.position.is_identity:
+                self.position.apply(q, ctx.positions, Hq, Dh)
             if cache.writes:
                 k = ctx.ws.rows("attn.k", T, self.kv_dim, self.dtype)
                 v = ctx.ws.rows("attn.v", T, self.kv_dim, self.dtype)
@@ -115,7 +120,8 @@ class GQAttention(Mixer):
                 self.gemm_v(h, v)
                 if self.k_norm is not None:
                     self.k_norm.rows(k.view(T * Hkv, Dh), k.view(T * Hkv, Dh))
-                self.position.apply(k, ctx.positions, Hkv, Dh)
+                if not self.position.is_identity:
+                    self.position.apply(k, ctx.positions, Hkv, Dh)
                 ops.kv_append(k, v, g.slots, cache.k, cache.v)
         attn = ctx.ws.rows("attn.out", T, self.q_dim, self.dtype)
         self.attend(q, attn, ctx, g, cache)

@@ -3,8 +3,8 @@
 A part is built from a `PartSpec` (its kind and its sizes and constants) and the compute
 dtype; it says which checkpoint tensors it needs, binds them, and runs on the rows of one
 step. No part knows which model it is in. Kinds are registered by name, so a test or a
-user can add a mixer, a feed-forward, a norm, a position encoding or a block arrangement
-without touching this package.
+user can add a mixer, a feed-forward, a norm, a position encoding, a block arrangement, a
+token embedding or an output head without touching this package.
 """
 from __future__ import annotations
 
@@ -54,6 +54,11 @@ class Part:
 
 
 class Norm(Part):
+    # True only for a norm that computes out = (x / sqrt(mean(x^2) + eps)) * weight with a float32 `weight`
+    # and an `eps` of its own: kernels that fuse that formula into other work (the q/k norm with the rotation
+    # and the cache append) may then stand in for `rows`. Any other formula leaves it False and is called.
+    fusable_rms = False
+
     def add_norm(self, x: torch.Tensor, delta, out: torch.Tensor, rows=None) -> None:
         """x (float32 residual stream) += delta when given; out = norm(x). With rows: only those rows, x untouched."""
         raise NotImplementedError
@@ -64,10 +69,18 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    # True for an encoding that leaves q and k as they are: the mixer then need not call it at all.
+    is_identity = False
+
     def fused_table(self):
         """float32 inverse frequencies [rotary_dim / 2] if the encoding is a rotation the fused
         kernel can apply, else None (then `apply` is called on q and k)."""
         return None
+
+    def score_scale(self) -> float:
+        """A factor on the attention scores that the encoding asks for (a rotation stretched to longer
+        contexts may come with one); the mixer multiplies its softmax scale by it."""
+        return 1.0
 
     def apply(self, x: torch.Tensor, positions: torch.Tensor, heads: int, head_dim: int) -> None:
         raise NotImplementedError
@@ -91,6 +104,23 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids to the float32 residual stream."""
+
+    def forward(self, tokens: torch.Tensor, x: torch.Tensor) -> None:
+        """tokens int32 [T] -> x float32 [T, D] (written in place)."""
+        raise NotImplementedError
+
+
+class OutputHead(Part):
+    """The rows that reached the final norm to float32 logits. Built with `embedding=` the model's embedding
+    part, for heads that share its table."""
+
+    def forward(self, last: torch.Tensor, logits: torch.Tensor) -> None:
+        """last [R, D] in the compute dtype -> logits float32 [R, V] (written in place)."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """The arrangement of mixer, feed-forward and their norms in one layer."""
 
@@ -105,12 +135,16 @@ FEED_FORWARDS: dict[str, Callable] = {}
 NORMS: dict[str, Callable] = {}
 POSITION_ENCODINGS: dict[str, Callable] = {}
 BLOCKS: dict[str, Callable] = {}
+EMBEDDINGS: dict[str, Callable] = {}
+HEADS: dict[str, Callable] = {}
 _REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITION_ENCODINGS,
-               "block": BLOCKS}
+               "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS}
 
 
 def register_part(family: str, kind: str, factory: Callable, replace: bool = False) -> None:
-    """family: mixer | feed_forward | norm | position | block. factory(spec, dtype, prefix="") -> part."""
+    """family: mixer | feed_forward | norm | position | block | embedding | head.
+    factory(spec, dtype, prefix="") -> part; a block's factory takes (layer_spec, dtype), a head's
+    (spec, dtype, embedding=the model's embedding part)."""
     reg = _REGISTRIES[family]
     if kind in reg and not replace:
         raise ValueError(f"{family} '{kind}' is already registered")

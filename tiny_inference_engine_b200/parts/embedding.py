@@ -5,12 +5,13 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..errors import InvalidArgument
 from ..weights.loader import TensorNeed
-from .base import Part, to_compute
+from .base import Embedding, OutputHead, register_part, to_compute
 
 
-class TokenEmbedding(Part):
-    def __init__(self, spec, dtype):
+class TokenEmbedding(Embedding):
+    def __init__(self, spec, dtype, prefix: str = ""):
         self.name = spec["name"]
         self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
         self.dtype = dtype
@@ -26,8 +27,8 @@ class TokenEmbedding(Part):
         ops.embed(self.table, tokens, x)
 
 
-class LMHead(Part):
-    def __init__(self, spec, dtype, embedding: TokenEmbedding):
+class LMHead(OutputHead):
+    def __init__(self, spec, dtype, embedding: TokenEmbedding | None = None, prefix: str = ""):
         self.name = spec["name"]
         self.tied = bool(spec["tied"])
         self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
@@ -40,8 +41,14 @@ class LMHead(Part):
         return {self.name: TensorNeed((self.vocab, self.hidden), optional=self.tied)}
 
     def bind(self, get):
+        if self.tied and getattr(self.embedding, "table", None) is None:
+            raise InvalidArgument("a tied output head needs an embedding part that holds its `table`")
         self.weight = self.embedding.table if self.tied else to_compute(get(self.name), self.dtype).contiguous()
         self.product = ops.bound_gemm(self.weight)
 
     def forward(self, last, logits):
         self.product(last, logits)
+
+
+register_part("embedding", "token_embedding", TokenEmbedding, replace=True)
+register_part("head", "lm_head", LMHead, replace=True)

@@ -11,7 +11,6 @@ from ..errors import InvalidArgument, UnsupportedError
 from ..ops import replay as layer_replay
 from ..weights.loader import TensorNeed, TensorSource, bind_check
 from .base import BLOCKS, CacheNeed, StateNeed, build_part
-from .embedding import LMHead, TokenEmbedding
 from .layer_runs import LayerRuns, same_handoff
 
 
@@ -37,10 +36,10 @@ class Model:
             raise InvalidArgument(f"compute dtype must be float32 or bfloat16, got {dtype}")
         spec.validate()
         self.spec, self.dtype = spec, dtype
-        self.embedding = TokenEmbedding(spec.embedding, dtype)
+        self.embedding = build_part("embedding", spec.embedding, dtype)
         self.layers = [_build_block(l, dtype) for l in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, dtype)
-        self.head = LMHead(spec.head, dtype, self.embedding)
+        self.head = build_part("head", spec.head, dtype, embedding=self.embedding)
         self.loaded = False
         # Layers built alike are issued by one call after the first two of their run (ops/replay.py);
         # TIE_NO_LAYER_REPLAY=1 issues every layer from Python.

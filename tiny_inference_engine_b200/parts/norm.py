@@ -13,6 +13,7 @@ from .base import Norm, register_part
 class RMSNorm(Norm):
     launches_only = True
     takes_split_sum = True      # add_norm adds the partial sums of a split product itself
+    fusable_rms = True          # exactly the formula above, with `weight` (float32) and `eps`
 
     def __init__(self, spec, dtype, prefix: str = ""):
         self.name = prefix + spec["name"]

@@ -39,6 +39,7 @@ class NoPositionEncoding(PositionEncoding):
     """Leaves q and k as they are."""
 
     launches_only = True
+    is_identity = True
 
     def __init__(self, spec=None, dtype=None, prefix: str = ""):
         pass

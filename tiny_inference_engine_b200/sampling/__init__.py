@@ -1,6 +1,5 @@
-"""Sampling parameters, the Philox generator, and the samplers."""
+"""Sampling parameters and the Philox generator; the samplers themselves are kernels (csrc/sampling.cu)."""
 from .params import SamplingParams
 from .philox import philox4x32, uniform
-from .sampler import sample_host
 
-__all__ = ["SamplingParams", "philox4x32", "uniform", "sample_host"]
+__all__ = ["SamplingParams", "philox4x32", "uniform"]
