@@ -27,14 +27,14 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE.json configs[2]: the Qwen3-8B shape.
+# The Qwen3-8B shape: the headline configuration.
 QWEN3_8B = {
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 151936, "hidden_size": 4096,
     "intermediate_size": 12288, "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8,
     "head_dim": 128, "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
     "tie_word_embeddings": False,
 }
-# BASELINE.json configs[3]: the Qwen3-4B shape of the serving mix (`--workload serving`).
+# The Qwen3-4B shape of the serving mix (`--workload serving`).
 QWEN3_4B = dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True)
 # A larger shape of the same architecture (`--shape 32b`): 64 layers, 64 query heads over 8 kv heads.
 QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64)

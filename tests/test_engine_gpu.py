@@ -34,16 +34,21 @@ def test_bfloat16_generation_follows_the_plain_one_where_the_choice_is_clear(tin
     from tiny_inference_engine_b200 import SamplingParams
     cfg, page, w, d = tiny_models["tiny_b"]
     eng = engine_for(d, dtype="bfloat16", num_pages=64, page_size=page)
-    prompt = np.random.default_rng(3).integers(0, cfg["vocab_size"], 20).tolist()
-    got = eng.generate(prompt, SamplingParams(max_tokens=12))
     wq = {k: (plain.round_bf16(v) if v.ndim == 2 else v) for k, v in w.items()}
-    tokens = list(prompt)
-    for t in got:                                   # teacher-forced: each step's choice is checked on its own
-        logits = plain.forward(wq, cfg, tokens)[-1]
-        top = np.sort(logits)[-2:]
-        if top[1] - top[0] > 0.04 * np.abs(logits).max():
-            assert t == int(np.argmax(logits))
-        tokens.append(t)
+    checked = steps = 0
+    for seed in (3, 4, 5):
+        prompt = np.random.default_rng(seed).integers(0, cfg["vocab_size"], 20).tolist()
+        got = eng.generate(prompt, SamplingParams(max_tokens=12))
+        tokens = list(prompt)
+        for t in got:                               # teacher-forced: each step's choice is checked on its own
+            logits = plain.forward(wq, cfg, tokens)[-1]
+            top = np.sort(logits)[-2:]
+            steps += 1
+            if top[1] - top[0] > 0.04 * np.abs(logits).max():
+                assert t == int(np.argmax(logits))
+                checked += 1
+            tokens.append(t)
+    assert checked >= steps // 2, f"only {checked} of {steps} steps had a clear choice: the test shows too little"
 
 
 @pytest.mark.parametrize("pages", [256, 7])

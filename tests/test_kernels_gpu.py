@@ -695,6 +695,39 @@ def test_decode_attention_over_long_contexts_with_the_longest_splits(ops, page, 
     assert rel_err(host(out), want) < TOL["bfloat16"] and not counters.any()
 
 
+def test_a_context_beyond_the_splits_a_call_allows_costs_time_or_is_refused_but_never_keys(ops):
+    """A caller of the exported kernels who sizes max_splits from something else than the longest context: the
+    CUDA-core and cp.async kernels let the last split take the rest (the merge reads no more splits than there
+    are), the TMA kernel, whose splits are bounded by its page table in shared memory, says so in the status word."""
+    from tiny_inference_engine_b200.errors import TieError
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(77)
+    Hq, Hkv, Dh, page = 4, 2, 64, 16
+    ctx = [700, 130, 64, 1]                      # 700 keys need 6 splits of 128; the call allows 2
+    split_keys, max_splits, S = 128, 2, len(ctx)
+    for dtype in ("float32", "bfloat16"):
+        kc, vc, bt, ks, vs = paged_cache(rng, dtype, ctx, Hkv, Dh, page, sum(-(-c // page) for c in ctx) + 3)
+        q = as_stored(rng.standard_normal((S, Hq * Dh)), dtype)
+        want = np.concatenate([dense_reference(q[i:i + 1], ks[i], vs[i], Hq, Hkv, Dh, 1) for i in range(S)])
+        args = (dev(np.arange(S + 1), torch.int32), dev(np.array(ctx), torch.int32), dev(bt, torch.int32), Hq, Hkv, Dh,
+                1 / np.sqrt(Dh), dev(np.arange(S), torch.int32), S, split_keys, max_splits)
+        fns = [ops.attention_split] + ([ops.attention_decode_tc] if dtype == "bfloat16" else [])
+        for fn in fns:
+            out = torch.full((S, Hq * Dh), float("nan"), device="cuda", dtype=DT[dtype])
+            scratch = torch.full((ops.attention_split_scratch_floats(S, Hq, Dh, max_splits),), float("nan"), device="cuda")
+            fn(dev(q, DT[dtype]), dev(kc, DT[dtype]), dev(vc, DT[dtype]), out, *args, scratch)
+            torch.cuda.synchronize()
+            assert rel_err(host(out), want) < TOL[dtype], fn.__name__
+    out = torch.full((S, Hq * Dh), float("nan"), device="cuda", dtype=torch.bfloat16)
+    counters = torch.zeros(S * Hkv, dtype=torch.int32, device="cuda")
+    ops.attention_decode_tma(dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *args, scratch, counters)
+    torch.cuda.synchronize()
+    with pytest.raises(TieError, match="fewer splits"):
+        gemm_select.check_status()
+    assert torch.isnan(out[0].float()).all() and rel_err(host(out)[1:], want[1:]) < TOL["bfloat16"]
+    gemm_select.check_status()                   # read and cleared
+
+
 def test_tensor_core_attention_refuses_other_sizes(ops):
     q = torch.zeros(4, 2 * 48, device="cuda", dtype=torch.bfloat16)
     assert not ops.attention_tc_takes(q, 2, 1, 48)

@@ -398,7 +398,7 @@ def test_toy_embedding_output_head_norm_and_a_rotation_with_a_score_scale(dtype)
     from tiny_inference_engine_b200.config import ModelSpec, PartSpec
     from tiny_inference_engine_b200.parts import (LMHead, Norm, RotaryEncoding, TokenEmbedding, register_part)
     from tiny_inference_engine_b200.weights import TensorNeed
-    CAP, STRETCH, FACTOR = 5.0, 4.0, 1.21
+    CAP, STRETCH, FACTOR = 0.5, 4.0, 1.21
 
     class ScaledEmbedding(TokenEmbedding):
         def forward(self, tokens, x):

@@ -10,7 +10,7 @@ import plain_qwen3 as plain
 from tiny_inference_engine_b200.config import parse_qwen3_config, qwen3_spec
 from tiny_inference_engine_b200.errors import LoadError
 from tiny_inference_engine_b200.parts import expected_tensors
-from tiny_inference_engine_b200.weights import (RandomSource, SafetensorsFile, SafetensorsSource, bind_check,
+from tiny_inference_engine_b200.weights import (RandomSource, SafetensorsFile, SafetensorsSource, TensorNeed, bind_check,
                                                 write_random_model, write_safetensors)
 
 
@@ -127,3 +127,37 @@ def test_random_source_is_per_tensor():
     fewer = {k: v for k, v in needs.items() if "layers.0" not in k}
     b = RandomSource(needs, 1, torch.float32).get("model.layers.1.mlp.up_proj.weight")
     assert torch.equal(a, b) and len(fewer) < len(needs)
+
+
+def test_counter_based_normal_values_are_a_function_of_seed_tensor_and_element():
+    """Philox against the scalar generator of the sampling code, any slice equal to the same slice of the whole,
+    streams that differ by seed and by tensor, and the statistics of a standard normal."""
+    from tiny_inference_engine_b200.sampling import philox4x32
+    from tiny_inference_engine_b200.weights.counter_random import _philox4x32_10, standard_normal
+    c = torch.tensor([0, 1, 2 ** 33 + 5, 12345678901], dtype=torch.int64)
+    words = _philox4x32_10(c, 0xDEADBEEF, 0x12345678)
+    for i, ci in enumerate(c.tolist()):
+        assert tuple(int(x[i]) for x in words) == tuple(philox4x32((ci & 0xFFFFFFFF, ci >> 32, 0, 0), (0xDEADBEEF, 0x12345678)))
+    z = standard_normal(3, 7, 0, 400_000)
+    for start, count in [(0, 1), (1, 6), (1001, 5000), (399_997, 3)]:
+        assert torch.equal(standard_normal(3, 7, start, count), z[start:start + count])
+    assert not torch.equal(standard_normal(4, 7, 0, 64), z[:64]) and not torch.equal(standard_normal(3, 8, 0, 64), z[:64])
+    assert abs(z.mean()) < 5e-3 and abs(z.std() - 1) < 5e-3 and abs((z.abs() > 2).double().mean() - 0.0455) < 2e-3
+    assert abs((z ** 3).mean()) < 0.02 and abs((z ** 4).mean() - 3) < 0.05 and z.abs().max() < 6.5
+    lag = (z[:-1] * z[1:]).mean()                 # neighbours come from one Philox call: still uncorrelated
+    assert abs(lag) < 5e-3
+
+
+@pytest.mark.gpu
+def test_random_weights_drawn_on_the_gpu_are_those_of_the_written_folder(tmp_path):
+    """`--random-weights` (drawn on the device) and `tie make-random` (drawn on the CPU, written to a folder) name the
+    same model by configuration and seed: every tensor bit for bit, in both dtypes."""
+    for dtype in (torch.bfloat16, torch.float32):
+        d = write_random_model(tmp_path / str(dtype), plain.TINY_D, seed=9, dtype=dtype)
+        folder = SafetensorsSource(d)
+        on_gpu = RandomSource(needs_of(plain.TINY_D), 9, dtype, device="cuda")
+        for name in folder.shapes():
+            a, b = folder.get(name), on_gpu.get(name).cpu()
+            assert a.dtype == b.dtype and torch.equal(a, b), name
+    big = RandomSource({"w": TensorNeed((5000, 4099))}, 2, torch.bfloat16, device="cuda").get("w")   # more than one piece
+    assert torch.equal(big.cpu()[-3:], RandomSource({"w": TensorNeed((5000, 4099))}, 2, torch.bfloat16).get("w")[-3:])

@@ -17,7 +17,7 @@ import sys
 import time
 
 USAGE = """usage: tie generate -m <model_dir> (-p "<ids>" | --prompt-len N) [options]
-       tie make-random -o <model_dir> --config <config.json> [--seed S] [--dtype bfloat16|float32]
+       tie make-random -o <model_dir> --config <config.json> [--seed S] [--dtype bfloat16|float32] [--device cpu|cuda]
 
 generate options:
   -m, --model PATH      model directory (config.json + model.safetensors)
@@ -149,6 +149,7 @@ def run_make_random(argv) -> int:
     ap.add_argument("--config")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--device", default="cpu")
     try:
         o = ap.parse_args(argv)
     except SystemExit:
@@ -157,7 +158,7 @@ def run_make_random(argv) -> int:
         raise InvalidArgument("--out and --config are required")
     with open(o.config) as f:
         cfg = json.load(f)
-    d = write_random_model(o.out, cfg, o.seed, parse_dtype(o.dtype))
+    d = write_random_model(o.out, cfg, o.seed, parse_dtype(o.dtype), device=o.device)
     print(f"[tie] wrote {d}/config.json and {d}/model.safetensors", file=sys.stderr)
     return 0
 

@@ -84,6 +84,10 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   if (lo > pos) return;
   const int hi = min(pos, lo + a.split_keys - 1);
   const int n_splits = (pos - lo0) / a.split_keys + 1;
+  if (n_splits > a.max_splits) {   // the caller sized max_splits for shorter contexts: say so, write nothing
+    if (threadIdx.x == 0 && split == 0) *reinterpret_cast<volatile int*>(a.status) = 13;
+    return;
+  }
   const int kt_first = lo / kKeysPerTile, kt_last = hi / kKeysPerTile;
   const int n_tiles = kt_last - kt_first + 1;
   const int box_rows = min(a.page_size, kKeysPerTile);

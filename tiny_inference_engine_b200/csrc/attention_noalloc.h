@@ -17,6 +17,9 @@
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress) and remembers it. Make that first call outside of any stream
 //     capture; later calls on that device only launch kernels.
+//   * A sequence is cut into at most max_splits splits of split_keys keys; if its context is longer than
+//     max_splits * split_keys the last split takes the rest (slower, still right). Size max_splits as
+//     ceil(longest context / split_keys) to keep the splits even.
 //   * It calls no cudaMalloc, cudaFree or any allocating routine, on any call.
 //   * All calls share the one array and it keeps what the last call left. Nothing in it has to
 //     start at zero: the split kernel writes every entry that the merge kernel reads. But two

@@ -141,7 +141,9 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   const int lo = lo0 + split * split_keys;
   if (lo > pos) return;  // this sequence has fewer splits
-  const int hi = min(pos, lo + split_keys - 1);
+  // The last split takes whatever is left, so that a context longer than max_splits * split_keys (a caller
+  // who sized max_splits from something else than the longest context) costs time, never keys.
+  const int hi = split == max_splits - 1 ? pos : min(pos, lo + split_keys - 1);
   const int kvh = h / (a.q_heads / a.kv_heads);
 
   float* qs = smem + warp * a.head_dim;
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(kMergeThreads) attention_merge_kernel(AttnArgs
     return;
   }
   const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int splits = (pos - lo0) / split_keys + 1;
+  const int splits = min((pos - lo0) / split_keys + 1, max_splits);   // the last one took the rest (split kernels)
   const int stride = a.head_dim + 2;
   const float* src = scratch + (static_cast<long long>(li) * a.q_heads + h) * max_splits * stride;
   if (threadIdx.x < 32) {

@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_tc_kernel(AttnTcArgs
   const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   const int lo = lo0 + split * a.split_keys;
   if (lo > pos) return;
-  const int hi = min(pos, lo + a.split_keys - 1);
+  const int hi = split == a.max_splits - 1 ? pos : min(pos, lo + a.split_keys - 1);   // the last split takes the rest
   const int* table = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
 
   constexpr int CPR = DH / 8;

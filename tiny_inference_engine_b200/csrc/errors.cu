@@ -67,7 +67,8 @@ int* status_word() {
 
 // 0 when no kernel gave up a bounded wait since the last call; else where the first... the last one did:
 // 1 = a matrix product's TMA producer on a free stage, 2 = its MMA issuer on landed bytes, 3 = its
-// epilogue on the accumulator; 11 = an attention kernel's producer, 12 = its consumers.
+// epilogue on the accumulator, 4 = a CTA of a pair on its partner at the end; 11 = an attention kernel's
+// producer, 12 = its consumers, 13 = a context that needs more splits than the call allowed (nothing written for it).
 // Reading clears it. Call after the stream has been synchronized.
 TIE_API int tie_kernel_status() {
   if (tie::g_status_host == nullptr) return 0;

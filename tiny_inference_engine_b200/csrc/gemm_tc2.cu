@@ -12,15 +12,24 @@
 // empty[s] and acc_full[b] exist in both CTAs and are signalled by tcgen05.commit with a
 // cluster multicast mask; acc_empty[b] lives in the leader and collects the eight epilogue
 // warps of the pair. A pair walks the tiles pair, pair + pairs, ...; two accumulators let a
-// tile's epilogue overlap the next tile's MMAs. Every wait is bounded (status word as in
-// gemm_tc.cu). No TMA multicast: every CTA fetches its own operands.
+// tile's epilogue overlap the next tile's MMAs. No TMA multicast: every CTA fetches its own operands.
+//
+// Waits. Every mbarrier wait is bounded (status word as in gemm_tc.cu), and so is the handshake of the pair
+// before it frees its tensor memory (`peer_done`: a remote arrive and a bounded wait, code 4). Three waits have
+// no limit, because the instruction set gives them none: tcgen05.alloc (returns once 512 columns are free on both
+// SMs; this kernel never shares an SM with another holder of tensor memory, since its 225 KB of shared memory
+// exclude every kernel of this library that allocates some), the barrier.cluster right behind it (it waits for
+// the partner CTA, which the hardware schedules together with this one and which has nothing ahead of it but the
+// same allocation), and griddepcontrol.wait (never executed by this kernel as it is launched, see below).
 //
 // Programmatic dependent launch: the kernel behind this one may start while it runs (launch_dependents at the
 // top), but this kernel itself is launched without the attribute and so starts only when the kernel ahead of it
 // has finished. Started early, steps of 512 tokens that mixed two prompt portions with decoded tokens (Qwen3-8B
-// shapes: 48 pairs of CTAs for the q/k/v product) hung about once in five runs with no bounded wait expired; as
-// it is, hundreds of runs of the same steps are clean. The prologue this gives up is a few microseconds of a
-// product that takes hundreds.
+// shapes: 48 pairs of CTAs for the q/k/v product) hung about once in five runs with no bounded wait expired, so
+// in one of the waits named above or in the cluster barrier that used to stand at the end; as it is, hundreds of
+// runs of the same steps are clean. The prologue this gives up is a few microseconds of a product that takes
+// hundreds. The pdl_wait() calls below stay (they return at once for a kernel launched this way) so that the
+// order of loads and stores against the kernel ahead does not rest on the launch mode.
 #include "umma.cuh"
 #include "launchers.h"
 
@@ -84,7 +93,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint64_t* empty = full + k2Stages;                                         // both CTAs
   uint64_t* acc_full = empty + k2Stages;                                     // [2], both CTAs
   uint64_t* acc_empty = acc_full + 2;                                        // [2], used in the leader
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* peer_done = acc_empty + 2;                                       // both CTAs: the partner is through
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(peer_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,6 +110,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       mbar_init(acc_full + b, 1);
       mbar_init(acc_empty + b, 8);     // four epilogue warps of each CTA of the pair
     }
+    mbar_init(peer_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -274,7 +285,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     while (clock64() - t0 < 4000000ull) {
     }
   }
-  cluster_sync();      // neither CTA leaves while its partner may still touch its shared or tensor memory
+  // Neither CTA leaves, or frees tensor memory, while its partner may still touch its shared or tensor memory:
+  // each tells the other that it is through and waits (with the limit of every other wait) to be told. The
+  // partner's arrive is its last access to this CTA's memory, and it comes before this wait can return.
+  // A CTA that gave up a wait still waits here for its partner, which may need a limit of its own to get
+  // here, so this limit is twice the usual one and does not look at the abort flag.
+  if (threadIdx.x == 0) {
+    remote_arrive(map_to_cta(peer_done, rank ^ 1u));
+    const unsigned long long t0 = clock64();
+    while (!mbar_try_wait(peer_done, 0)) {
+      if (clock64() - t0 > 2 * kWaitCycles) {
+        *reinterpret_cast<volatile int*>(status) = 4;
+        break;
+      }
+    }
+  }
+  __syncthreads();
   if (warp == 4) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(k2TmemCols) : "memory");
   }
@@ -296,19 +322,17 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, i
   cfg.blockDim = dim3(k2Threads);
   cfg.dynamicSmemBytes = k2Smem;
   cfg.stream = s;
-  cudaLaunchAttribute attrs[2];
+  cudaLaunchAttribute attrs[1];     // the cluster shape and nothing else: no early start (see the top of this file)
   attrs[0].id = cudaLaunchAttributeClusterDimension;
   attrs[0].val.clusterDim.x = 2;
   attrs[0].val.clusterDim.y = 1;
   attrs[0].val.clusterDim.z = 1;
-  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attrs[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;
+  cfg.numAttrs = 1;
   // pairs that can be resident at once (SMs pair up inside a GPC, so it may be fewer than half the SMs)
   static int resident_pairs = 0;
   if (resident_pairs == 0) {
     cfg.gridDim = dim3(2 * 74);
-    cfg.numAttrs = 1;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<OutT>, &cfg) != cudaSuccess || n < 1) {
       set_error("gemm_tc2: no pair of SMs can hold the kernel (%s)", cudaGetErrorString(cudaGetLastError()));
@@ -318,7 +342,6 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, i
   }
   const int pairs = n_tiles < resident_pairs ? n_tiles : resident_pairs;
   cfg.gridDim = dim3(2 * pairs);
-  cfg.numAttrs = 1;   // clusters only, no early start: see the note at the top of this file
   cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<OutT>, ma, mw, static_cast<OutT*>(out), M, N, ceil_div(K, k2BK), ldo, silu, tiles_m,
                      n_tiles, status_word());
   return kOk;

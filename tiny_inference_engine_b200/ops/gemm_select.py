@@ -171,8 +171,11 @@ def check_status() -> None:
     if code:
         where = {1: "a matrix product's TMA producer waiting for a free stage", 2: "a matrix product's MMA issuer waiting "
                  "for operands", 3: "a matrix product's epilogue waiting for the accumulator",
+                 4: "a CTA of a pair waiting for its partner before it frees its tensor memory",
                  11: "an attention kernel's TMA producer waiting for a free stage",
                  12: "an attention kernel waiting for keys and values"}.get(code, f"code {code}")
+        if code == 13:
+            raise TieError("decode attention was given fewer splits than a context needs; that sequence's output was not written")
         raise TieError(f"a kernel gave up after its wait limit ({where}); its output is invalid")
 
 

@@ -67,8 +67,10 @@ class SafetensorsSource(TensorSource):
 
 class RandomSource(TensorSource):
     """Random values for exactly the tensors a model needs: matrices N(0, std), norm weights
-    1 + N(0, norm_std), each tensor from its own generator seeded by (seed, ordinal of the
-    name), so a tensor's values do not depend on which others exist."""
+    1 + N(0, norm_std). Element i of a tensor is a function of (seed, ordinal of the tensor's name among
+    the sorted names, i) alone (weights/counter_random.py): the same bits whether drawn on the CPU or on
+    the GPU, in one piece or in several, so that a random model can be named by its configuration and its
+    seed across tools (`--random-weights`, `tie make-random`, bench.py)."""
 
     def __init__(self, needs: dict[str, TensorNeed], seed: int, dtype: torch.dtype = torch.bfloat16, std: float = 0.02,
                  norm_std: float = 0.01, device: str = "cpu"):
@@ -80,21 +82,23 @@ class RandomSource(TensorSource):
         return {n: (t.shape, torch.float32 if t.role == "norm" else self.dtype) for n, t in self.needs.items()}
 
     def get(self, name):
+        from .counter_random import standard_normal
         need = self.needs[name]
-        g = torch.Generator(device=self.device)
-        g.manual_seed((self.seed * 1_000_003 + self._ordinal[name]) & 0x7FFFFFFFFFFFFFFF)
-        if need.role == "norm":
-            t = torch.randn(need.shape, generator=g, device=self.device, dtype=torch.float32)
-            return t.mul_(self.norm_std).add_(1.0)
+        ordinal = self._ordinal[name]
         if need.role == "table":
             return torch.zeros(need.shape, dtype=torch.int32, device=self.device)
-        rows = need.shape[0]
-        out = torch.empty(need.shape, dtype=self.dtype, device=self.device)
-        step = max(1, (1 << 26) // max(1, out[0].numel()))  # bounded float32 scratch for large tables
-        for r in range(0, rows, step):
-            chunk = torch.randn(out[r:r + step].shape, generator=g, device=self.device, dtype=torch.float32)
-            out[r:r + step] = chunk.mul_(self.std).to(self.dtype)
-        return out
+        numel = 1
+        for n in need.shape:
+            numel *= n
+        if need.role == "norm":
+            z = standard_normal(self.seed, ordinal, 0, numel, self.device)
+            return (z * self.norm_std + 1.0).to(torch.float32).reshape(need.shape)
+        out = torch.empty(numel, dtype=self.dtype, device=self.device)
+        step = 1 << 24                              # bounded float64 scratch for large tables
+        for at in range(0, numel, step):
+            n = min(step, numel - at)
+            out[at:at + n] = (standard_normal(self.seed, ordinal, at, n, self.device) * self.std).to(torch.float32).to(self.dtype)
+        return out.reshape(need.shape)
 
 
 def bind_check(needs: dict[str, TensorNeed], source: TensorSource, what: str = "the model") -> None:
