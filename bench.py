@@ -11,8 +11,11 @@ ids in, sampled ids out, every step). `prefill` is one 2,048-token prompt in one
 (timed first, as a burst); `roofline` is the bytes a decode step has to read (every weight
 it uses once, and the cache of the live requests) over its time, against the measured copy
 bandwidth (`frac_b1`, `frac_b64`: the same for the two points); `points` holds decode at
-batch 1 and 64. Weights are 16 GB and the caches gigabytes, far more than the
-126 MB L2, so no flush is needed between steps.
+batch 1 and 64, decode at batch 8 with contexts of 16,384 and 32,768 tokens (`frac_ctx...` beside them: there the
+cache is the larger stream), the Qwen3-4B serving mix (`serving_4b`: the figures of `--workload serving`) and
+the Qwen3-32B shape at batch 8 ending at context 8,192 (`decode_32b_b8_ctx8192`); `--no-extra` leaves the
+last four out. Weights are 16 GB and the caches gigabytes, far more than the 126 MB L2, so no flush is
+needed between steps.
 """
 import argparse
 import json
@@ -109,7 +112,7 @@ def prefill_flops(cfg, layers, T):
     return gemm + attn
 
 
-def serving_mix(args) -> int:
+def serving_mix(args) -> dict:
     """The serving workload of the reference's own bench (bench/workload.cpp, bench/report.h:29-36) on the
     Qwen3-4B shape: `--requests` requests at once, prompt lengths uniform in [128, 4096] of uniform random ids,
     256 new tokens each at temperature 0.7, continuous batching with 512 tokens a step. One JSON line: generated
@@ -161,7 +164,9 @@ def serving_mix(args) -> int:
         return {"p50": round(float(np.percentile(a, 50)), 2), "p90": round(float(np.percentile(a, 90)), 2),
                 "p99": round(float(np.percentile(a, 99)), 2)}
 
-    print(json.dumps({
+    del engine, runner, cache, states, model
+    torch.cuda.empty_cache()
+    return {
         "metric": "generated tok/s, serving mix (Qwen3-4B bf16, 1 B200)", "value": round(generated / total, 1), "unit": "tokens/s",
         "requests": n, "prompt_tokens": int(lengths.sum()), "generated_tokens": generated, "seconds": round(total, 3),
         "total_tok_s": round((int(lengths.sum()) + generated) / total, 1), "ttft_ms": pct(ttft), "itl_ms": pct(itl), "e2e_s": pct(e2e),
@@ -169,8 +174,7 @@ def serving_mix(args) -> int:
         "preemptions": st1.preemptions - st0.preemptions, "steps_queued_ahead": st1.steps_ahead - st0.steps_ahead,
         "config": {"model": "Qwen3-4B shape", "layers": args.layers, "max_tokens_per_step": budget, "max_seqs": serving.max_seqs,
                    "kv_pages": pages, "page_size": PAGE, "temperature": 0.7, "new_tokens": new_tokens},
-        "data": "synthetic (random weights N(0,0.02), uniform random token ids, all requests at time 0)"}))
-    return 0
+        "data": "synthetic (random weights N(0,0.02), uniform random token ids, all requests at time 0)"}
 
 
 def main() -> int:
@@ -184,7 +188,8 @@ def main() -> int:
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: the contract line is the default, 8b")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (reported in config)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 (and the extra points)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the long contexts, the serving mix and the 32B shape")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
                     help="decode: the contract line (default); serving: the Qwen3-4B serving mix, its own line")
     ap.add_argument("--requests", type=int, default=64, help="serving mix: concurrent requests")
@@ -204,7 +209,10 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
     if args.workload == "serving":
-        return serving_mix(args)
+        print(json.dumps(serving_mix(args)))
+        return 0
+
+    import gc
 
     import numpy as np
     import torch
@@ -221,41 +229,54 @@ def main() -> int:
     rng = np.random.default_rng(0)
     clocks = ClockSampler()
 
-    with tempfile.TemporaryDirectory() as d:
-        (Path(d) / "config.json").write_text(json.dumps(cfg))
-        t0 = time.time()
-        model = load_model(d, "bfloat16", random_weights=True, seed=0)
-        torch.cuda.synchronize()
-        print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    def build(config):
+        with tempfile.TemporaryDirectory() as d:
+            (Path(d) / "config.json").write_text(json.dumps(config))
+            t0 = time.time()
+            m = load_model(d, "bfloat16", random_weights=True, seed=0)
+            torch.cuda.synchronize()
+            print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+        return m
 
+    model = build(cfg)
     V = cfg["vocab_size"]
+    extra = not (args.no_points or args.no_extra or args.profile is not None)
+    long_contexts = (16384, 32768) if extra else ()
     max_batch = B if args.no_points else max(B, 64)
     if args.profile == "mixed":
         max_batch = 32
     pages_per_seq = (CTX + PAGE - 1) // PAGE + 1
-    cache, states = make_cache(model, page_size=PAGE, num_pages=max_batch * pages_per_seq + 8, max_requests=max_batch * 2)
+    num_pages = max([max_batch * pages_per_seq] + [B * (c // PAGE + 1) for c in long_contexts]) + 8
+    cache, states = make_cache(model, page_size=PAGE, num_pages=num_pages, max_requests=max_batch * 2)
     chunk = max(args.prefill_tokens, 2048)
     runner = StepRunner(model, cache, max_tokens=chunk, max_seqs=max_batch, max_logit_rows=max_batch, states=states,
                         use_graphs=args.profile is None)
 
-    def fill(batch, length):
-        """`batch` requests with `length` random tokens each in the cache, by real prefill in portions."""
+    def fill(run, pool, batch, length, reserve, random_fill=False):
+        """`batch` requests with `length` tokens each in the cache: by real prefill in portions, or (the long contexts,
+        where prefill would take longer than everything else together) by pages of random keys and values: what a
+        decode step costs does not depend on what the keys are."""
         reqs = []
+        if random_fill:
+            for st in pool.storage:
+                st.normal_(0.0, 1.0)
         for _ in range(batch):
-            req = cache.new_request()
-            assert cache.reserve(req, CTX)
-            toks = rng.integers(0, V, length)
-            for at in range(0, length, chunk):
-                runner.run([StepEntry(req, toks[at:at + chunk], at, [])])
+            req = pool.new_request()
+            assert pool.reserve(req, reserve)
+            if not random_fill:
+                toks = rng.integers(0, V, length)
+                for at in range(0, length, chunk):
+                    run.run([StepEntry(req, toks[at:at + chunk], at, [])])
             reqs.append(req)
         torch.cuda.synchronize()
-        runner.check()
+        run.check()
         return reqs
 
-    def decode_device(batch, steps, warmup):
-        """Device time of `steps` decode steps of `batch` requests whose context ends at CTX."""
-        start = CTX - steps - warmup
-        reqs = fill(batch, start)
+    def decode_device(batch, steps, warmup, ctx=CTX, run=None, pool=None, random_fill=False):
+        """Device time of `steps` decode steps of `batch` requests whose context ends at `ctx`."""
+        run, pool = run or runner, pool or cache
+        start = ctx - steps - warmup
+        reqs = fill(run, pool, batch, start, ctx, random_fill)
         toks = rng.integers(0, V, (steps + warmup, batch))
         greedy = [(SamplingParams(), 0)] * batch
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -263,27 +284,33 @@ def main() -> int:
         for i in range(steps + warmup):
             if i == warmup:
                 torch.cuda.synchronize()
-                launches0, replays0 = kernel_library.launch_count(), runner.graph_replays
+                launches0, replays0 = kernel_library.launch_count(), run.graph_replays
                 e0.record()
-            runner.run([StepEntry(r, [int(toks[i, j])], start + i, [0]) for j, r in enumerate(reqs)], greedy)
+            run.run([StepEntry(r, [int(toks[i, j])], start + i, [0]) for j, r in enumerate(reqs)], greedy)
         e1.record()
         torch.cuda.synchronize()
-        runner.check()
+        run.check()
         ms = e0.elapsed_time(e1)
-        per_graph = max(runner.kernels_in_graph.values(), default=0)
-        launches = (kernel_library.launch_count() - launches0) + (runner.graph_replays - replays0) * per_graph
+        per_graph = max(run.kernels_in_graph.values(), default=0)
+        launches = (kernel_library.launch_count() - launches0) + (run.graph_replays - replays0) * per_graph
         for r in reqs:
-            cache.release(r)
+            pool.release(r)
         return ms / steps, launches
+
+    def hbm_frac(config, layers, batch, ctx, steps, ms):
+        """Bytes a decode step has to read (weights once, the live requests' cache at the mean context of the
+        timed steps) over its time, as a fraction of the copy bandwidth."""
+        nbytes = weight_bytes_per_decode_step(config, layers) + batch * (ctx - steps / 2) * kv_bytes_per_token(config, layers)
+        return round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
 
     if args.profile is not None:
         greedy = [(SamplingParams(), 0)] * B
         if args.profile == "decode":
-            reqs = fill(B, CTX - 4)
+            reqs = fill(runner, cache, B, CTX - 4, CTX)
             steps = [[StepEntry(r, [int(rng.integers(0, V))], CTX - 4 + i, [0]) for r in reqs] for i in range(3)]
         elif args.profile == "mixed":
-            reqs = fill(30, 2048)
-            prompt = fill(1, 1024)[0]
+            reqs = fill(runner, cache, 30, 2048, CTX)
+            prompt = fill(runner, cache, 1, 1024, CTX)[0]
             greedy = [(SamplingParams(), 0)] * 30
             steps = [[StepEntry(r, [int(rng.integers(0, V))], 2048 + i, [0]) for r in reqs] +
                      [StepEntry(prompt, rng.integers(0, V, 482), 1024 + 482 * i, [])] for i in range(3)]
@@ -333,8 +360,12 @@ def main() -> int:
             steps_b = max(16, K // 4)
             ms_b, _ = decode_device(b, steps_b, W)
             points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
-            bytes_b = weight_bytes_per_decode_step(cfg, args.layers) + b * (CTX - steps_b / 2) * kv_bytes_per_token(cfg, args.layers)
-            point_fracs[f"frac_b{b}"] = round(bytes_b / (ms_b / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+            point_fracs[f"frac_b{b}"] = hbm_frac(cfg, args.layers, b, CTX, steps_b, ms_b)
+        for ctx in long_contexts:          # the cache is the larger stream here: decode attention sets the pace
+            steps_c = 24
+            ms_c, _ = decode_device(B, steps_c, W, ctx=ctx, random_fill=True)
+            points[f"decode_b{B}_ctx{ctx}"] = round(B / (ms_c / 1e3), 1)
+            point_fracs[f"frac_ctx{ctx}"] = hbm_frac(cfg, args.layers, B, ctx, steps_c, ms_c)
 
     # end to end through the Python entry point: host token ids in, sampled ids out, every step
     serving = ServingConfig(max_tokens_per_step=chunk, max_seqs=B)
@@ -364,6 +395,25 @@ def main() -> int:
     h2d = runner.last_h2d_bytes          # the index arrays of a timed step: one copy from pinned memory
     while engine.has_work():
         engine.step()
+
+    if extra:
+        # the other two workloads, each with a model of its own: this one goes first
+        del engine, runner, cache, states, model
+        gc.collect()
+        torch.cuda.empty_cache()
+        mix = serving_mix(argparse.Namespace(layers=0, requests=64, kv_pages=0))
+        points["serving_4b"] = {k: mix[k] for k in ("value", "total_tok_s", "ttft_ms", "itl_ms", "preemptions", "mean_seqs_per_step")}
+        gc.collect()
+        torch.cuda.empty_cache()
+        big_name, big = SHAPES["32b"]
+        big_model = build(big)
+        b32, ctx32, steps32 = 8, 8192, 16
+        big_cache, big_states = make_cache(big_model, page_size=PAGE, num_pages=b32 * (ctx32 // PAGE + 1) + 8, max_requests=2 * b32)
+        big_runner = StepRunner(big_model, big_cache, max_tokens=64, max_seqs=b32, max_logit_rows=b32, states=big_states)
+        ms32, _ = decode_device(b32, steps32, W, ctx=ctx32, run=big_runner, pool=big_cache, random_fill=True)
+        points["decode_32b_b8_ctx8192"] = {"value": round(b32 / (ms32 / 1e3), 1), "ms_per_step": round(ms32, 3),
+                                           "frac": hbm_frac(big, big["num_hidden_layers"], b32, ctx32, steps32, ms32)}
+        del big_runner, big_cache, big_states, big_model
     clk = clocks.stop()
 
     step_bytes = weight_bytes_per_decode_step(cfg, args.layers) + B * (CTX - K / 2) * kv_bytes_per_token(cfg, args.layers)
