@@ -434,6 +434,77 @@ def test_gemm_tensor_cores(ops, out_dtype, M, N, K):
     assert rel_err(host(out), plain.linear(a, w)) < (TOL["bfloat16"] if out_dtype == "bfloat16" else 2e-5)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 503, 96), (8, 1000, 520), (16, 72, 200), (77, 130, 1000), (128, 256, 512), (200, 96, 72),
+                                   (300, 503, 96), (700, 311, 136), (1100, 2560, 520)])
+def test_products_with_the_weight_kept_in_k_blocks(ops, M, N, K):
+    """A bound product keeps its weight as [ceil(K / 64), N, 64] (every box a stage loads is one piece of memory) and
+    gives the plain product at every token count: the transposed tiling, the 128-token row tiles, the kernel on pairs
+    of SMs (the last case), widths and depths that end inside a tile (rows of the next k-block come in with the
+    last boxes; they reach no output), a depth that is no multiple of 64 (zeros); and a slice of its rows
+    (the k rows of a stacked q/k/v weight) without a copy."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(M * N + K)
+    a, w = as_stored(rng.standard_normal((M, K)), "bfloat16"), as_stored(rng.standard_normal((N, K)), "bfloat16")
+    g = ops.bound_gemm(dev(w, torch.bfloat16))
+    assert g.packed_rows == N and tuple(g.w.shape) == (-(-K // 64), N, 64) and (g.N, g.K) == (N, K)
+    assert torch.equal(g.row_major().cpu(), dev(w, torch.bfloat16).cpu())
+    want = plain.linear(a, w)
+    for out_dtype in ("bfloat16", "float32"):
+        out = torch.full((M, N), float("nan"), device="cuda", dtype=DT[out_dtype])
+        got = g(dev(a, torch.bfloat16), out)
+        torch.cuda.synchronize()
+        gemm_select.check_status()
+        assert got is out and rel_err(host(out), want) < (TOL["bfloat16"] if out_dtype == "bfloat16" else 2e-5), out_dtype
+    lo, hi = N // 3, N // 3 + max(8, N // 2)
+    part = g.rows(lo, hi)
+    assert part.w.data_ptr() == g.w.data_ptr() and (part.N, part.row0) == (hi - lo, lo)
+    wide = torch.full((M, hi - lo + 16), 7.0, device="cuda", dtype=torch.float32)
+    part(dev(a, torch.bfloat16), wide[:, 8:8 + hi - lo])
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(wide[:, 8:8 + hi - lo]), want[:, lo:hi]) < 2e-5
+    assert (wide[:, :8] == 7).all() and (wide[:, 8 + hi - lo:] == 7).all()
+
+
+@pytest.mark.parametrize("M", [5, 300, 640])
+def test_silu_product_and_split_sums_with_the_weight_in_k_blocks(ops, M):
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(M)
+    I, K = 352, 264
+    a = as_stored(rng.standard_normal((M, K)), "bfloat16")
+    gate, up = as_stored(rng.standard_normal((I, K)) * 0.3, "bfloat16"), as_stored(rng.standard_normal((I, K)) * 0.3, "bfloat16")
+    g = ops.bound_gemm(ops.interleave_gate_up(dev(gate, torch.bfloat16), dev(up, torch.bfloat16)), silu=True)
+    assert g.packed_rows == 2 * I
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    g(dev(a, torch.bfloat16), out)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(out), plain.swiglu(plain.linear(a, gate), plain.linear(a, up))) < TOL["bfloat16"]
+    # a split product leaves its partial sums for the consumer, as with a row-major weight
+    D, K2 = 520, 4096
+    a2, w2 = as_stored(rng.standard_normal((M, K2)), "bfloat16"), as_stored(rng.standard_normal((D, K2)) * 0.05, "bfloat16")
+    buf = {}
+    got = ops.bound_gemm(dev(w2, torch.bfloat16))(dev(a2, torch.bfloat16), torch.empty(M, D, device="cuda", dtype=torch.bfloat16),
+                                                  partial_scratch=lambda n: buf.setdefault("p", torch.full((n,), float("nan"), device="cuda")))
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    if isinstance(got, ops.SplitSum):
+        got = got.materialize(torch.empty(M, D, device="cuda", dtype=torch.float32))
+    assert rel_err(host(got), plain.linear(a2, w2)) < TOL["bfloat16"]
+
+
+def test_embedding_rows_from_a_table_in_k_blocks(ops):
+    rng = np.random.default_rng(3)
+    V, D = 503, 200                                      # the depth ends inside a k-block
+    table = as_stored(rng.standard_normal((V, D)), "bfloat16")
+    ids = np.array([0, 502, 17, 17, 256], dtype=np.int32)
+    packed = ops.pack_k_blocks(dev(table, torch.bfloat16))
+    assert tuple(packed.shape) == (4, V, 64) and torch.equal(ops.unpack_k_blocks(packed, D).cpu(), dev(table, torch.bfloat16).cpu())
+    out = torch.full((5, D), float("nan"), device="cuda")
+    ops.embed(packed, dev(ids, torch.int32), out)
+    assert np.array_equal(host(out), table[ids])
+
+
 @pytest.mark.parametrize("transposed,bn,splits", [(0, 16, 1), (0, 64, 1), (0, 256, 1), (1, 128, 1), (1, 256, 1), (1, 128, 3),
                                                   (1, 256, 5), (0, 128, 2)])
 def test_gemm_tensor_cores_every_tiling(ops, transposed, bn, splits):

@@ -13,15 +13,25 @@ namespace tie {
 
 // ---------------------------------------------------------------------------------------------
 // x[t, :] = float(table[ids[t], :]). The residual stream is float in both paths.
+// With k_block_rows > 0 the table is stored in k-blocks, [ceil(dim / 64)][k_block_rows][64] (the layout the
+// matrix products stream best, gemm_tc.cu; a tied output table is this very tensor): element i of row id is at
+// ((i / 64) * k_block_rows + id) * 64 + i % 64.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
-                             int dim, int vocab) {
+                             int dim, int vocab, int k_block_rows) {
   pdl_sync();
   const int t = blockIdx.x;
   int id = ids[t];
-  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; never read outside the table
-  const T* row = table + static_cast<size_t>(id) * dim;
+  // ids are validated on the host (an id that a step ahead could not sample arrives negative: its request ends
+  // anyway); never read outside the table
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
   float* out = x + static_cast<size_t>(t) * dim;
+  if (k_block_rows > 0) {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+      out[i] = ld(table + (static_cast<size_t>(i >> 6) * k_block_rows + id) * 64 + (i & 63));
+    return;
+  }
+  const T* row = table + static_cast<size_t>(id) * dim;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = ld(row + i);
 }
 
@@ -582,9 +592,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_rows_kernel(T* __rest
 
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-int launch_embed(const void* table, const int* ids, float* x, int tokens, int dim, int vocab, cudaStream_t s) {
+int launch_embed(const void* table, const int* ids, float* x, int tokens, int dim, int vocab, int k_block_rows, cudaStream_t s) {
   if (tokens == 0) return kOk;
-  TIE_LAUNCH((embed_kernel<T>), tokens, dim >= 1024 ? 256 : 128, 0, s, static_cast<const T*>(table), ids, x, dim, vocab);
+  TIE_LAUNCH((embed_kernel<T>), tokens, dim >= 1024 ? 256 : 128, 0, s, static_cast<const T*>(table), ids, x, dim, vocab, k_block_rows);
   TIE_RETURN_LAUNCH("embed");
 }
 
@@ -725,11 +735,13 @@ using namespace tie;
     return kBadArgument;                                               \
   } while (0)
 
+// k_block_rows > 0: the table is stored in k-blocks of 64 columns, k_block_rows rows each (see embed_kernel).
 TIE_API int tie_embed(int dtype, const void* table, const int* ids, float* x, int tokens, int dim, int vocab,
-                      cudaStream_t s) {
-  TIE_REQUIRE(tokens >= 0 && dim > 0 && vocab > 0, "embed: bad sizes tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
-  TIE_DISPATCH(dtype, launch_embed<float>(table, ids, x, tokens, dim, vocab, s),
-               launch_embed<__nv_bfloat16>(table, ids, x, tokens, dim, vocab, s));
+                      int k_block_rows, cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && dim > 0 && vocab > 0 && (k_block_rows == 0 || k_block_rows >= vocab),
+              "embed: bad sizes tokens=%d dim=%d vocab=%d (k-blocks of %d rows)", tokens, dim, vocab, k_block_rows);
+  TIE_DISPATCH(dtype, launch_embed<float>(table, ids, x, tokens, dim, vocab, k_block_rows, s),
+               launch_embed<__nv_bfloat16>(table, ids, x, tokens, dim, vocab, k_block_rows, s));
 }
 
 TIE_API int tie_scatter_ids(int* tokens, const int* dst, const int* src, const int* ids, int n, cudaStream_t s) {

@@ -85,7 +85,7 @@ __device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
 template <typename OutT>
 __global__ void __launch_bounds__(k2Threads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
-                int M, int N, int k_blocks, long long ldo, int silu, int tiles_m, int n_tiles, int* status) {
+                int M, int N, int k_blocks, long long ldo, int silu, int tiles_m, int n_tiles, int* status, int w_rows, int w_row0) {
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -144,7 +144,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           uint8_t* sa = smem + s * k2Stage;
           if (elect_one()) {
             if (rank == 0) mbar_expect_tx(full + s, 2 * k2Stage);
-            tma_load_2d_pair(sa + k2StageA, &map_w, kb * k2BK, row_w, bar);      // weights never change: before the wait
+            // weights never change: before the wait. Stored in k-blocks (w_rows > 0) a box is 16 KB in one piece.
+            if (w_rows > 0) tma_load_2d_pair(sa + k2StageA, &map_w, 0, kb * w_rows + w_row0 + row_w, bar);
+            else tma_load_2d_pair(sa + k2StageA, &map_w, kb * k2BK, row_w, bar);
           }
           __syncwarp();
           if (first) {
@@ -308,7 +310,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 template <typename OutT>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int silu,
-                      cudaStream_t s) {
+                      int w_rows, int w_row0, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc2_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2Smem)) != cudaSuccess) {
@@ -343,7 +345,7 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, i
   const int pairs = n_tiles < resident_pairs ? n_tiles : resident_pairs;
   cfg.gridDim = dim3(2 * pairs);
   cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<OutT>, ma, mw, static_cast<OutT*>(out), M, N, ceil_div(K, k2BK), ldo, silu, tiles_m,
-                     n_tiles, status_word());
+                     n_tiles, status_word(), w_rows, w_row0);
   return kOk;
 }
 
@@ -352,21 +354,24 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, i
 using namespace tie;
 
 // out[M, N] (or, with silu, out[M, N / 2] = silu(gate) * up for w in blocks of 16 gate + 16 up rows)
-// = a[M, K] . w[N, K]^T on pairs of SMs. a, w bfloat16 with K and row strides multiples of 8.
+// = a[M, K] . w[N, K]^T on pairs of SMs. a, w bfloat16 with K and row strides multiples of 8. w_rows > 0: w is
+// stored in k-blocks, [ceil(K / 64)][w_rows][64], and the product uses its rows w_row0 .. w_row0 + N - 1 (gemm_tc.cu).
 TIE_API int tie_gemm_tc2(int out_dtype, const void* a, const void* w, void* out, int M, int N, int K, long long lda,
-                         long long ldw, long long ldo, int silu, cudaStream_t s) {
+                         long long ldw, long long ldo, int silu, int w_rows, int w_row0, cudaStream_t s) {
   TIE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc2: bad sizes M=%d N=%d K=%d", M, N, K);
-  TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tc2: K=%d and the row strides must be multiples of 8", K);
+  TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && (w_rows > 0 || ldw % 8 == 0), "gemm_tc2: K=%d and the row strides must be multiples of 8", K);
+  TIE_REQUIRE(w_rows == 0 || (w_row0 >= 0 && w_row0 + N <= w_rows), "gemm_tc2: rows %d..%d of a weight of %d rows", w_row0, w_row0 + N, w_rows);
   TIE_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0,
               "gemm_tc2: operands must be 16-byte aligned");
   TIE_REQUIRE(out_dtype == TIE_BF16 || out_dtype == TIE_F32, "gemm_tc2: output dtype code %d", out_dtype);
   TIE_REQUIRE(!silu || N % 32 == 0, "gemm_tc2: the SiLU epilogue needs weight rows in blocks of 16 gate + 16 up (N=%d)", N);
   TIE_REQUIRE(status_word() != nullptr, "gemm_tc2: cannot allocate the status word");
   CUtensorMap ma, mw;
-  TIE_REQUIRE(make_map_bf16(&ma, a, M, K, lda, k2BK, 128) && make_map_bf16(&mw, w, N, K, ldw, k2BK, 128),
-              "gemm_tc2: cuTensorMapEncodeTiled failed (M %d, N %d, K %d)", M, N, K);
-  const int st = out_dtype == TIE_BF16 ? launch_tc2<__nv_bfloat16>(ma, mw, out, M, N, K, ldo, silu, s)
-                                       : launch_tc2<float>(ma, mw, out, M, N, K, ldo, silu, s);
+  const bool w_ok = w_rows > 0 ? make_map_bf16(&mw, w, static_cast<long long>(ceil_div(K, k2BK)) * w_rows, k2BK, k2BK, k2BK, 128)
+                               : make_map_bf16(&mw, w, N, K, ldw, k2BK, 128);
+  TIE_REQUIRE(make_map_bf16(&ma, a, M, K, lda, k2BK, 128) && w_ok, "gemm_tc2: cuTensorMapEncodeTiled failed (M %d, N %d, K %d)", M, N, K);
+  const int st = out_dtype == TIE_BF16 ? launch_tc2<__nv_bfloat16>(ma, mw, out, M, N, K, ldo, silu, w_rows, w_row0, s)
+                                       : launch_tc2<float>(ma, mw, out, M, N, K, ldo, silu, w_rows, w_row0, s);
   if (st != kOk) return st;
   TIE_RETURN_LAUNCH("gemm_tc2");
 }

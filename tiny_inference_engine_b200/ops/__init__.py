@@ -73,13 +73,35 @@ class SplitSum:
 
 
 def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = float(table[ids[t]]); out is the float32 residual stream [T, D]."""
+    """out[t] = float(table[ids[t]]); out is the float32 residual stream [T, D]. The table is [V, D], or the
+    same in k-blocks, [ceil(D / 64), V, 64] (`pack_k_blocks`: what a tied output table is stored as)."""
     _dev(table, ids, out)
     T, D = out.shape
-    _need(table.dim() == 2 and table.shape[1] == D and table.is_contiguous(), "embed: table must be [V, D] contiguous")
+    packed = table.dim() == 3
+    _need(table.is_contiguous() and ((not packed and table.dim() == 2 and table.shape[1] == D) or
+                                     (packed and table.shape[2] == 64 and table.shape[0] == (D + 63) // 64)),
+          "embed: table must be [V, D] or [ceil(D / 64), V, 64], contiguous")
     _need(ids.dtype == torch.int32 and ids.numel() == T and ids.is_contiguous(), "embed: ids must be int32 [T]")
     _need(out.dtype == torch.float32 and out.is_contiguous(), "embed: output must be float32 contiguous")
-    call("tie_embed", dtype_code(table), table.data_ptr(), ids.data_ptr(), out.data_ptr(), T, D, table.shape[0], _stream())
+    V = table.shape[1] if packed else table.shape[0]
+    call("tie_embed", dtype_code(table), table.data_ptr(), ids.data_ptr(), out.data_ptr(), T, D, V, V if packed else 0, _stream())
+
+
+def pack_k_blocks(w: torch.Tensor) -> torch.Tensor:
+    """[N, K] -> [ceil(K / 64), N, 64]: the rows' first 64 columns, then their next 64, and so on (zeros beyond K).
+    The tensor-core products load a weight in boxes of 128 rows x 64 columns; stored like this a box is one piece
+    of 16 KB instead of 128 pieces of 128 bytes a row apart, which is what the memory streams fastest."""
+    N, K = w.shape
+    kb = (K + 63) // 64
+    if K % 64:
+        w = torch.nn.functional.pad(w, (0, kb * 64 - K))
+    return w.view(N, kb, 64).permute(1, 0, 2).contiguous()
+
+
+def unpack_k_blocks(packed: torch.Tensor, K: int) -> torch.Tensor:
+    """The inverse of pack_k_blocks: [ceil(K / 64), N, 64] -> [N, K] (a copy)."""
+    kb, N, _ = packed.shape
+    return packed.permute(1, 0, 2).reshape(N, kb * 64)[:, :K].contiguous()
 
 
 def scatter_ids(tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, ids: torch.Tensor, n: int) -> None:
@@ -386,11 +408,14 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, partial_scratch=No
     return gemm_select.gemm(a, w, out, partial_scratch)
 
 
-def bound_gemm(w: torch.Tensor, silu: bool = False, split_many: bool = True):
+def bound_gemm(w: torch.Tensor, silu: bool = False, split_many: bool = True, pack: bool = True):
     """A matrix product bound to one weight (gemm_select.BoundGemm): checked once, called every step.
-    `split_many` False: above 128 tokens k is never split (the consumer wants the finished product)."""
+    `split_many` False: above 128 tokens k is never split (the consumer wants the finished product). With `pack`
+    a weight that the tensor-core kernels take is stored in k-blocks (pack_k_blocks) from here on: the product
+    keeps that copy (`.w`) and the caller lets go of its own. `.rows(a, b)` is the product with rows a..b-1 of
+    the same weight, without a copy."""
     from . import gemm_select
-    return gemm_select.BoundGemm(w, silu, split_many)
+    return gemm_select.BoundGemm(w, silu, split_many, pack)
 
 
 def partial_capacity(max_rows: int, N: int, K: int, split_many: bool = True) -> int:

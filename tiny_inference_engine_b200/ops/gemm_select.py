@@ -142,7 +142,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None
         pair = transposed is None and bn is None and splits is None and pair_takes(M, N)
     if pair:
         _call("tie_gemm_tc2", dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
-              w.stride(0), out.stride(0), 1 if silu else 0, _stream())
+              w.stride(0), out.stride(0), 1 if silu else 0, 0, 0, _stream())
         return out
     t, b, s = plan(M, N, K)
     transposed = t if transposed is None else int(transposed)
@@ -159,7 +159,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None
         scratch = _scratch_for(splits * M * N, a.device)
     _call("tie_gemm_tc", dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
           w.stride(0), out.stride(0), transposed, bn, splits, scratch.data_ptr() if splits > 1 else 0, 1 if silu else 0,
-          0 if leave else 1, int(deep if deep is not None else (not transposed or bn >= 128)), _stream())
+          0 if leave else 1, int(deep if deep is not None else (not transposed or bn >= 128)), 0, 0, _stream())
     if leave:
         return SplitSum(scratch, _library().tie_gemm_tc_real_splits(K, splits), M, N)
     return out
@@ -203,15 +203,44 @@ class BoundGemm:
     The weight's address, sizes and kernel family are fixed when the part binds its tensors; a call looks up
     the tiling of its token count (computed once per count) and goes straight to the launcher. `a` and `out`
     come from the step's workspace: rows contiguous, 16-byte aligned, the compute dtype (the parts' contract);
-    anything the tensor-core kernels do not take falls back to `gemm` with its full checks."""
+    anything the tensor-core kernels do not take falls back to `gemm` with its full checks.
 
-    def __init__(self, w: torch.Tensor, silu: bool = False, split_many: bool = True):
-        self.w, self.silu, self.split_many = w, silu, split_many
-        self.N, self.K = w.shape
-        self.fast = (w.dtype == torch.bfloat16 and w.stride(1) == 1 and self.K % 8 == 0 and w.stride(0) % 8 == 0
-                     and w.data_ptr() % 16 == 0 and (not silu or self.N % 32 == 0))
-        self.w_ptr, self.ldw = w.data_ptr(), w.stride(0)
+    A weight that the tensor-core kernels take is kept in k-blocks (`ops.pack_k_blocks`, with `pack`): `.w` is then
+    [ceil(K / 64), rows, 64] and `packed_rows` its number of rows; `.rows(a, b)` gives the product with a slice of
+    its rows (the q rows of a stacked q/k/v weight) over the same memory."""
+
+    def __init__(self, w: torch.Tensor, silu: bool = False, split_many: bool = True, pack: bool = True, _slice=None):
+        self.silu, self.split_many = silu, split_many
+        if _slice is not None:              # rows [row0, row0 + N) of a packed weight
+            parent, row0, n = _slice
+            self.w, self.N, self.K, self.packed_rows, self.row0, self.fast = parent.w, n, parent.K, parent.packed_rows, row0, True
+        else:
+            self.N, self.K = w.shape
+            self.fast = (w.dtype == torch.bfloat16 and w.stride(1) == 1 and self.K % 8 == 0 and w.stride(0) % 8 == 0
+                         and w.data_ptr() % 16 == 0 and (not silu or self.N % 32 == 0))
+            self.packed_rows = self.row0 = 0
+            if pack and self.fast and w.is_cuda:
+                from . import pack_k_blocks
+                w = pack_k_blocks(w)
+                self.packed_rows = self.N
+            self.w = w
+        self.w_ptr, self.ldw = self.w.data_ptr(), (64 if self.packed_rows else self.w.stride(0))
         self._plans: dict[int, tuple] = {}
+
+    def rows(self, begin: int, end: int) -> "BoundGemm":
+        """The product with rows begin..end-1 of this weight (no SiLU epilogue)."""
+        if not 0 <= begin < end <= self.N:
+            raise ValueError(f"rows {begin}..{end} of a weight of {self.N} rows")
+        if self.packed_rows:
+            return BoundGemm(None, False, self.split_many, _slice=(self, self.row0 + begin, end - begin))
+        return BoundGemm(self.w[begin:end], False, self.split_many, pack=False)
+
+    def row_major(self) -> torch.Tensor:
+        """The weight as [N, K] (a copy if it is kept in k-blocks): for callers that need it the plain way."""
+        if not self.packed_rows:
+            return self.w
+        from . import unpack_k_blocks
+        return unpack_k_blocks(self.w, self.K)[self.row0:self.row0 + self.N]
 
     def _plan(self, M: int):
         pair = pair_takes(M, self.N)
@@ -232,10 +261,11 @@ class BoundGemm:
         if not (self.fast and a.dtype == torch.bfloat16 and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
                 and out.stride(1) == 1 and a.shape[1] == self.K and out.shape[1] == (self.N // 2 if self.silu else self.N)
                 and out.shape[0] == M and out.dtype in (torch.bfloat16, torch.float32)):
+            w = self.row_major()
             if self.silu:
-                gemm_silu(a, self.w, out)
+                gemm_silu(a, w, out)
                 return out
-            return gemm(a, self.w, out, partial_scratch)
+            return gemm(a, w, out, partial_scratch)
         global _ops
         if _ops is None:
             from . import SplitSum, _need, _stream, dtype_code
@@ -245,7 +275,7 @@ class BoundGemm:
         code = 1 if out.dtype == torch.bfloat16 else 0
         if pair:
             _call("tie_gemm_tc2", code, a.data_ptr(), self.w_ptr, out.data_ptr(), M, self.N, self.K, a.stride(0), self.ldw,
-                  out.stride(0), 1 if self.silu else 0, _stream())
+                  out.stride(0), 1 if self.silu else 0, self.packed_rows, self.row0, _stream())
             return out
         leave = splits > 1 and partial_scratch is not None
         scratch = 0
@@ -256,7 +286,7 @@ class BoundGemm:
             buf = _scratch_for(splits * M * self.N, a.device)
             scratch = buf.data_ptr()
         _call("tie_gemm_tc", code, a.data_ptr(), self.w_ptr, out.data_ptr(), M, self.N, self.K, a.stride(0), self.ldw, out.stride(0),
-              t, bn, splits, scratch, 1 if self.silu else 0, 0 if leave else 1, deep, _stream())
+              t, bn, splits, scratch, 1 if self.silu else 0, 0 if leave else 1, deep, self.packed_rows, self.row0, _stream())
         if leave:
             return SplitSum(buf, real, M, self.N)
         return out

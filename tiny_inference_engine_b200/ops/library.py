@@ -16,7 +16,7 @@ _LIB = None
 P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 _SIGNATURES = {
-    "tie_embed": [I, P, P, P, I, I, I, P],
+    "tie_embed": [I, P, P, P, I, I, I, I, P],
     "tie_scatter_ids": [P, P, P, P, I, P],
     "tie_add_rmsnorm": [I, P, P, P, L, I, P, P, F, P, I, I, P],
     "tie_rmsnorm_rows": [I, P, L, P, F, P, L, I, L, P],
@@ -29,8 +29,8 @@ _SIGNATURES = {
     "tie_attention_split": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_sample": [P, L, I, I, P, P, P, P, P],
     "tie_sample_filtered": [P, L, I, I, P, P, P, P, P, P, I, P],
-    "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, I, I, I, P],
-    "tie_gemm_tc2": [I, P, P, P, I, I, I, L, L, L, I, P],
+    "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, I, I, I, I, I, P],
+    "tie_gemm_tc2": [I, P, P, P, I, I, I, L, L, L, I, I, I, P],
     "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_decode_tc": [P, L, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_attention_decode_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P, P],

@@ -64,13 +64,18 @@ class GQAttention(Mixer):
 
     def bind(self, get):
         w = [to_compute(get(self.prefix + f"{n}_proj.weight"), self.dtype) for n in "qkv"]
-        self.w_qkv = torch.cat(w, dim=0).contiguous()
-        self.w_q = self.w_qkv[:self.q_dim]
-        self.w_k = self.w_qkv[self.q_dim:self.q_dim + self.kv_dim]
-        self.w_v = self.w_qkv[self.q_dim + self.kv_dim:]
-        self.w_o = to_compute(get(self.prefix + "o_proj.weight"), self.dtype).contiguous()
-        self.gemm_qkv, self.gemm_q, self.gemm_k, self.gemm_v, self.gemm_o = (
-            ops.bound_gemm(w, split_many=w is self.w_o) for w in (self.w_qkv, self.w_q, self.w_k, self.w_v, self.w_o))
+        # One stacked weight, so that one product reads the activations once; the products bound to it keep it in the
+        # layout they stream best, and q, k and v alone (layers that read another layer's cache, norms and position
+        # encodings that the fused kernel does not know) are row slices of the same memory.
+        self.gemm_qkv = ops.bound_gemm(torch.cat(w, dim=0).contiguous(), split_many=False)
+        del w
+        self.w_qkv = self.gemm_qkv.w
+        self.gemm_q = self.gemm_qkv.rows(0, self.q_dim)
+        self.gemm_k = self.gemm_qkv.rows(self.q_dim, self.q_dim + self.kv_dim)
+        self.gemm_v = self.gemm_qkv.rows(self.q_dim + self.kv_dim, self.q_dim + 2 * self.kv_dim)
+        self.w_q, self.w_k, self.w_v = self.gemm_q.w, self.gemm_k.w, self.gemm_v.w
+        self.gemm_o = ops.bound_gemm(to_compute(get(self.prefix + "o_proj.weight"), self.dtype).contiguous(), split_many=True)
+        self.w_o = self.gemm_o.w
         self._capacity = None       # (q/k/v product, output product): the most partial sums a step can leave
         for part in (self.q_norm, self.k_norm, self.position):
             if part is not None:
@@ -98,8 +103,8 @@ class GQAttention(Mixer):
             width = self.q_dim + (2 * self.kv_dim if cache.writes else 0)
             qkv = ctx.ws.rows("attn.qkv", T, self.q_dim + 2 * self.kv_dim, self.dtype)[:, :width]
             if self._capacity is None:
-                self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape, split_many=False),
-                                  ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape))
+                self._capacity = (ops.partial_capacity(ctx.ws.max_rows, self.gemm_qkv.N, self.gemm_qkv.K, split_many=False),
+                                  ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K))
             got = (self.gemm_qkv if cache.writes else self.gemm_q)(
                 h, qkv, lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32, self._capacity[0]))
             ops.qk_norm_rope_append(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, g.slots, cache.k, cache.v, Hq, Hkv,
@@ -127,8 +132,8 @@ class GQAttention(Mixer):
         self.attend(q, attn, ctx, g, cache)
         out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
         if self._capacity is None:
-            self._capacity = (ops.partial_capacity(ctx.ws.max_rows, *self.w_qkv.shape, split_many=False),
-                              ops.partial_capacity(ctx.ws.max_rows, *self.w_o.shape))
+            self._capacity = (ops.partial_capacity(ctx.ws.max_rows, self.gemm_qkv.N, self.gemm_qkv.K, split_many=False),
+                              ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K))
         return self.gemm_o(attn, out, lambda n: ctx.ws.flat("mixer.out.partial", n, torch.float32, self._capacity[1]))
 
     def attend(self, q, attn, ctx, g, cache):

@@ -21,7 +21,10 @@ class TokenEmbedding(Embedding):
         return {self.name: TensorNeed((self.vocab, self.hidden))}
 
     def bind(self, get):
-        self.table = to_compute(get(self.name), self.dtype).contiguous()
+        # Kept the way a matrix product streams it best (in k-blocks, for the tensor-core kernels): an output head
+        # that shares the table multiplies by this very tensor (`product`), and a row of it is as cheap to gather.
+        self.product = ops.bound_gemm(to_compute(get(self.name), self.dtype).contiguous())
+        self.table = self.product.w
 
     def forward(self, tokens, x):
         ops.embed(self.table, tokens, x)
@@ -41,10 +44,13 @@ class LMHead(OutputHead):
         return {self.name: TensorNeed((self.vocab, self.hidden), optional=self.tied)}
 
     def bind(self, get):
-        if self.tied and getattr(self.embedding, "table", None) is None:
-            raise InvalidArgument("a tied output head needs an embedding part that holds its `table`")
-        self.weight = self.embedding.table if self.tied else to_compute(get(self.name), self.dtype).contiguous()
-        self.product = ops.bound_gemm(self.weight)
+        if self.tied:
+            if getattr(self.embedding, "product", None) is None:
+                raise InvalidArgument("a tied output head needs an embedding part that offers the `product` with its table")
+            self.product = self.embedding.product
+        else:
+            self.product = ops.bound_gemm(to_compute(get(self.name), self.dtype).contiguous())
+        self.weight = self.product.w
 
     def forward(self, last, logits):
         self.product(last, logits)

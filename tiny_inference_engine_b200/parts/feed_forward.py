@@ -32,9 +32,11 @@ class SwiGLU(FeedForward):
         # On the tensor-core path gate and up rows are interleaved in blocks of 16 and SiLU * up
         # happens in the product's epilogue; else they are stacked and a kernel of its own does it.
         self.fused = self.dtype == torch.bfloat16 and self.inter % 16 == 0 and self.hidden % 8 == 0
-        self.w_gate_up = ops.interleave_gate_up(gate, up) if self.fused else torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = to_compute(get(self.prefix + "down_proj.weight"), self.dtype).contiguous()
-        self.gate_up, self.down = ops.bound_gemm(self.w_gate_up, silu=self.fused), ops.bound_gemm(self.w_down)
+        self.gate_up = ops.bound_gemm(ops.interleave_gate_up(gate, up) if self.fused else torch.cat([gate, up], dim=0).contiguous(),
+                                      silu=self.fused)
+        del gate, up
+        self.down = ops.bound_gemm(to_compute(get(self.prefix + "down_proj.weight"), self.dtype).contiguous())
+        self.w_gate_up, self.w_down = self.gate_up.w, self.down.w      # as the products keep them (in k-blocks when they stream them)
         self._partial_capacity = None
 
     def forward(self, h, ctx):
@@ -48,7 +50,7 @@ class SwiGLU(FeedForward):
             ops.silu_mul(gu, act)
         out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
         if self._partial_capacity is None:
-            self._partial_capacity = ops.partial_capacity(ctx.ws.max_rows, *self.w_down.shape)
+            self._partial_capacity = ops.partial_capacity(ctx.ws.max_rows, self.down.N, self.down.K)
         return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
 
 
