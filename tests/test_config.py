@@ -161,3 +161,17 @@ def test_matrix_product_plans_are_ones_the_kernel_takes():
     # the shapes the cost estimate was fitted on: the measured best, or close to it
     assert gs.plan(512, 2560, 9728)[1:] == (256, 3) and gs.plan(384, 4096, 12288)[1:] == (256, 3)
     assert gs.plan(2048, 24576, 4096)[2] == 1
+
+
+def test_pair_kernel_tile_widths_follow_the_waves():
+    """The width of the pair kernel's tiles: the full 256 where narrower tiles save no wave (2,048 tokens of Qwen3-8B's
+    products), narrower where the tiles of a short portion leave most pairs of SMs idle or a wave nearly empty."""
+    from tiny_inference_engine_b200.ops import gemm_select as gs
+    for N, K in ((6144, 4096), (4096, 4096), (4096, 12288)):
+        assert gs.pair_width(2048, N, K, 74) == 256
+    assert gs.pair_width(2048, 24576, 4096, 74) in (224, 256)
+    assert gs.pair_width(512, 6144, 4096, 74) == 192          # 64 tiles in one wave instead of 48 wider ones
+    assert gs.pair_width(512, 24576, 4096, 74) == 224         # 220 tiles: three waves, as 192 of full width, each shorter
+    for M in (512, 700, 1024, 2048, 4096):
+        for N in (256, 2560, 4096, 9728, 151936):
+            assert gs.pair_width(M, N, 4096, 74) in gs.PAIR_WIDTHS

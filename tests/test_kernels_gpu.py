@@ -466,6 +466,30 @@ def test_products_with_the_weight_kept_in_k_blocks(ops, M, N, K):
     assert (wide[:, :8] == 7).all() and (wide[:, 8 + hi - lo:] == 7).all()
 
 
+@pytest.mark.parametrize("bn", [128, 160, 192, 224, 256])
+def test_pair_kernel_at_every_tile_width(ops, bn):
+    """The product on pairs of SMs with tiles of 256 rows by 128 to 256 columns, plain and with the SiLU epilogue,
+    at sizes that end inside a tile; the width changes which CTA computes what, not what is computed."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(bn)
+    M, N, K = 600, 1000, 264
+    a, w = as_stored(rng.standard_normal((M, K)), "bfloat16"), as_stored(rng.standard_normal((N, K)), "bfloat16")
+    wide = torch.full((M, N + 16), 7.0, device="cuda", dtype=torch.float32)
+    gemm_select.gemm_tc(dev(a, torch.bfloat16), dev(w, torch.bfloat16), wide[:, 8:8 + N], pair=True, bn=bn)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(wide[:, 8:8 + N]), plain.linear(a, w)) < 2e-5
+    assert (wide[:, :8] == 7).all() and (wide[:, 8 + N:] == 7).all()
+    I = 352
+    gate, up = as_stored(rng.standard_normal((I, K)) * 0.3, "bfloat16"), as_stored(rng.standard_normal((I, K)) * 0.3, "bfloat16")
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm_select.gemm_tc(dev(a, torch.bfloat16), ops.interleave_gate_up(dev(gate, torch.bfloat16), dev(up, torch.bfloat16)), out,
+                        silu=True, pair=True, bn=bn)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert rel_err(host(out), plain.swiglu(plain.linear(a, gate), plain.linear(a, up))) < TOL["bfloat16"]
+
+
 @pytest.mark.parametrize("M", [5, 300, 640])
 def test_silu_product_and_split_sums_with_the_weight_in_k_blocks(ops, M):
     from tiny_inference_engine_b200.ops import gemm_select

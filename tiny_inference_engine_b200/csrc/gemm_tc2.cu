@@ -1,10 +1,12 @@
 // bfloat16 matrix products for many rows (prompt portions) on pairs of SMs: tcgen05.mma with
-// cta_group::2. Two CTAs of a cluster compute one 256 x 256 tile of out[M, N] = a[M, K] . w[N, K]^T:
-// each CTA stages its own 128 rows of a and its own 128 of the 256 rows of w (32 KB per 64-deep
-// k-block instead of the 48 KB a lone CTA needs for 128 x 256), one thread of the leader CTA
-// issues the MMAs for both, and each CTA's tensor memory receives its 128 x 256 float
+// cta_group::2. Two CTAs of a cluster compute one 256 x BN tile of out[M, N] = a[M, K] . w[N, K]^T:
+// each CTA stages its own 128 rows of a and its own half of the BN rows of w (32 KB per 64-deep
+// k-block at BN = 256 instead of the 48 KB a lone CTA needs for 128 x 256), one thread of the leader CTA
+// issues the MMAs for both, and each CTA's tensor memory receives its 128 x BN float
 // accumulator. A third less operand traffic from L2 per flop is what this buys; the 1-CTA
-// kernel in gemm_tc.cu is limited by exactly that feed.
+// kernel in gemm_tc.cu is limited by exactly that feed. BN is 256, or narrower (multiples of 32 from 128 up)
+// where that fills the last wave of tiles better: 128 tiles of 256 x 256 are 1.73 waves on 74 pairs and take
+// two; 208 tiles of 256 x 160 take three waves of 0.625 each (the host picks, ops/gemm_select.py).
 //
 // Per CTA: warps 0-3 epilogue (tcgen05.ld, optional SiLU * up, stores), warp 4 TMA producer,
 // warp 5 (leader CTA only) MMA issuer. Barriers: full[s] lives in the leader and counts the
@@ -39,9 +41,9 @@ constexpr int k2Threads = 192;
 constexpr int k2BK = 64;
 constexpr int k2Stages = 7;
 constexpr int k2StageA = 128 * k2BK * 2;      // this CTA's 128 rows of a
-constexpr int k2StageB = 128 * k2BK * 2;      // this CTA's 128 of the tile's 256 rows of w
-constexpr int k2Stage = k2StageA + k2StageB;
-constexpr int k2TmemCols = 512;               // two 256-column accumulators
+constexpr int k2StageB = 128 * k2BK * 2;      // this CTA's half of the tile's rows of w (128 at most: BN = 256)
+constexpr int k2Stage = k2StageA + k2StageB;  // stages are as large for every BN: narrower tiles leave part of them unused
+constexpr int k2TmemCols = 512;               // two accumulators of up to 256 columns
 constexpr size_t k2Smem = static_cast<size_t>(k2Stages) * k2Stage + 1024 + 256;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -82,7 +84,7 @@ __device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-template <typename OutT>
+template <typename OutT, int BN>
 __global__ void __launch_bounds__(k2Threads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ out,
                 int M, int N, int k_blocks, long long ldo, int silu, int tiles_m, int n_tiles, int* status, int w_rows, int w_row0) {
@@ -134,7 +136,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool first = true, ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += pairs) {
         const int row_a = (tile % tiles_m) * 256 + static_cast<int>(rank) * 128;
-        const int row_w = (tile / tiles_m) * 256 + static_cast<int>(rank) * 128;
+        const int row_w = (tile / tiles_m) * BN + static_cast<int>(rank) * (BN / 2);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(empty + s, parity, abort_flag, status, 1) ? 1 : 0)) {
             ok = false;
@@ -143,7 +145,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t bar = map_to_cta(full + s, 0);
           uint8_t* sa = smem + s * k2Stage;
           if (elect_one()) {
-            if (rank == 0) mbar_expect_tx(full + s, 2 * k2Stage);
+            if (rank == 0) mbar_expect_tx(full + s, 2 * (k2StageA + (BN / 2) * k2BK * 2));
             // weights never change: before the wait. Stored in k-blocks (w_rows > 0) a box is 16 KB in one piece.
             if (w_rows > 0) tma_load_2d_pair(sa + k2StageA, &map_w, 0, kb * w_rows + w_row0 + row_w, bar);
             else tma_load_2d_pair(sa + k2StageA, &map_w, kb * k2BK, row_w, bar);
@@ -166,7 +168,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 5) {
     // ---- MMA issuer: a warp of the leader CTA walks the loop (uniform), one elected lane drives both CTAs' tensor cores
     if (rank == 0) {
-      constexpr uint32_t idesc = instr_desc(256, 256);
+      constexpr uint32_t idesc = instr_desc(BN, 256);
       const uint32_t ring_lo = desc_lo_sw128(smem_u32(smem));   // descriptors as (low word, constant high word)
       int s = 0, local = 0;
       uint32_t parity = 0;
@@ -175,7 +177,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int buf = local & 1;
         if (!__all_sync(0xffffffffu, mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1, abort_flag, status, 2) ? 1 : 0)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_acc = tmem_base + buf * 256;
+        const uint32_t tmem_acc = tmem_base + buf * 256;      // the second accumulator at column 256 whatever BN
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(full + s, parity, abort_flag, status, 2) ? 1 : 0)) {
             ok = false;
@@ -207,7 +209,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int local = 0;
     for (int tile = pair; tile < n_tiles; tile += pairs, ++local) {
       const int buf = local & 1;
-      const int i0 = (tile % tiles_m) * 256 + static_cast<int>(rank) * 128, j0 = (tile / tiles_m) * 256;
+      const int i0 = (tile % tiles_m) * 256 + static_cast<int>(rank) * 128, j0 = (tile / tiles_m) * BN;
       if (!mbar_wait(acc_full + buf, (local >> 1) & 1, abort_flag, status, 3)) break;
       if (local == 0) pdl_wait();
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -215,7 +217,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int i = i0 + warp * 32 + lane;
       if (silu) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < 256; c0 += 32) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
           if (j0 + c0 >= N) break;
           uint32_t g[16], u[16];
           tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, g);
@@ -246,7 +248,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
       } else {
 #pragma unroll 1
-        for (int c0 = 0; c0 < 256; c0 += 16) {
+        for (int c0 = 0; c0 < BN; c0 += 16) {
           if (j0 + c0 >= N) break;
           uint32_t r[16];
           tmem_ld16(tmem_acc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
@@ -308,18 +310,44 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
-template <typename OutT>
+// Pairs of SMs that can hold the kernel at once (SMs pair up inside a GPC, so it may be fewer than half the SMs);
+// 0 if the query fails. The same for every instantiation: they differ in neither threads nor shared memory.
+static int resident_pairs() {
+  static int pairs = -1;
+  if (pairs < 0) {
+    pairs = 0;
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<__nv_bfloat16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2Smem)) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.blockDim = dim3(k2Threads);
+      cfg.dynamicSmemBytes = k2Smem;
+      cfg.gridDim = dim3(2 * 74);
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<__nv_bfloat16, 256>, &cfg) == cudaSuccess && n >= 1) pairs = n;
+      else cudaGetLastError();
+    }
+  }
+  return pairs;
+}
+
+template <typename OutT, int BN>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int silu,
                       int w_rows, int w_row0, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc2_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2Smem)) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc2_kernel<OutT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(k2Smem)) != cudaSuccess) {
       set_error("gemm_tc2: cannot reserve %zu bytes of shared memory", k2Smem);
       return kCudaError;
     }
     configured = true;
   }
-  const int tiles_m = ceil_div(M, 256), n_tiles = tiles_m * ceil_div(N, 256);
+  const int tiles_m = ceil_div(M, 256), n_tiles = tiles_m * ceil_div(N, BN);
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(k2Threads);
   cfg.dynamicSmemBytes = k2Smem;
@@ -331,20 +359,14 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mw, void* out, i
   attrs[0].val.clusterDim.z = 1;
   cfg.attrs = attrs;
   cfg.numAttrs = 1;
-  // pairs that can be resident at once (SMs pair up inside a GPC, so it may be fewer than half the SMs)
-  static int resident_pairs = 0;
-  if (resident_pairs == 0) {
-    cfg.gridDim = dim3(2 * 74);
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<OutT>, &cfg) != cudaSuccess || n < 1) {
-      set_error("gemm_tc2: no pair of SMs can hold the kernel (%s)", cudaGetErrorString(cudaGetLastError()));
-      return kCudaError;
-    }
-    resident_pairs = n;
+  const int resident = resident_pairs();
+  if (resident < 1) {
+    set_error("gemm_tc2: no pair of SMs can hold the kernel");
+    return kCudaError;
   }
-  const int pairs = n_tiles < resident_pairs ? n_tiles : resident_pairs;
+  const int pairs = n_tiles < resident ? n_tiles : resident;
   cfg.gridDim = dim3(2 * pairs);
-  cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<OutT>, ma, mw, static_cast<OutT*>(out), M, N, ceil_div(K, k2BK), ldo, silu, tiles_m,
+  cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<OutT, BN>, ma, mw, static_cast<OutT*>(out), M, N, ceil_div(K, k2BK), ldo, silu, tiles_m,
                      n_tiles, status_word(), w_rows, w_row0);
   return kOk;
 }
@@ -356,8 +378,14 @@ using namespace tie;
 // out[M, N] (or, with silu, out[M, N / 2] = silu(gate) * up for w in blocks of 16 gate + 16 up rows)
 // = a[M, K] . w[N, K]^T on pairs of SMs. a, w bfloat16 with K and row strides multiples of 8. w_rows > 0: w is
 // stored in k-blocks, [ceil(K / 64)][w_rows][64], and the product uses its rows w_row0 .. w_row0 + N - 1 (gemm_tc.cu).
+// How many pairs of SMs hold the kernel at once: what the host counts waves of tiles with.
+TIE_API int tie_gemm_tc2_pairs() { return resident_pairs(); }
+
+// bn: the tile width, 128, 160, 192, 224 or 256 (0: 256).
 TIE_API int tie_gemm_tc2(int out_dtype, const void* a, const void* w, void* out, int M, int N, int K, long long lda,
-                         long long ldw, long long ldo, int silu, int w_rows, int w_row0, cudaStream_t s) {
+                         long long ldw, long long ldo, int silu, int w_rows, int w_row0, int bn, cudaStream_t s) {
+  if (bn == 0) bn = 256;
+  TIE_REQUIRE(bn == 128 || bn == 160 || bn == 192 || bn == 224 || bn == 256, "gemm_tc2: tile width %d", bn);
   TIE_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc2: bad sizes M=%d N=%d K=%d", M, N, K);
   TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && (w_rows > 0 || ldw % 8 == 0), "gemm_tc2: K=%d and the row strides must be multiples of 8", K);
   TIE_REQUIRE(w_rows == 0 || (w_row0 >= 0 && w_row0 + N <= w_rows), "gemm_tc2: rows %d..%d of a weight of %d rows", w_row0, w_row0 + N, w_rows);
@@ -367,11 +395,23 @@ TIE_API int tie_gemm_tc2(int out_dtype, const void* a, const void* w, void* out,
   TIE_REQUIRE(!silu || N % 32 == 0, "gemm_tc2: the SiLU epilogue needs weight rows in blocks of 16 gate + 16 up (N=%d)", N);
   TIE_REQUIRE(status_word() != nullptr, "gemm_tc2: cannot allocate the status word");
   CUtensorMap ma, mw;
-  const bool w_ok = w_rows > 0 ? make_map_bf16(&mw, w, static_cast<long long>(ceil_div(K, k2BK)) * w_rows, k2BK, k2BK, k2BK, 128)
-                               : make_map_bf16(&mw, w, N, K, ldw, k2BK, 128);
+  const bool w_ok = w_rows > 0 ? make_map_bf16(&mw, w, static_cast<long long>(ceil_div(K, k2BK)) * w_rows, k2BK, k2BK, k2BK, bn / 2)
+                               : make_map_bf16(&mw, w, N, K, ldw, k2BK, bn / 2);
   TIE_REQUIRE(make_map_bf16(&ma, a, M, K, lda, k2BK, 128) && w_ok, "gemm_tc2: cuTensorMapEncodeTiled failed (M %d, N %d, K %d)", M, N, K);
-  const int st = out_dtype == TIE_BF16 ? launch_tc2<__nv_bfloat16>(ma, mw, out, M, N, K, ldo, silu, w_rows, w_row0, s)
-                                       : launch_tc2<float>(ma, mw, out, M, N, K, ldo, silu, w_rows, w_row0, s);
+  int st = kOk;
+#define TIE_TC2_CASE(B)                                                                                                  \
+  case B:                                                                                                                \
+    st = out_dtype == TIE_BF16 ? launch_tc2<__nv_bfloat16, B>(ma, mw, out, M, N, K, ldo, silu, w_rows, w_row0, s)         \
+                               : launch_tc2<float, B>(ma, mw, out, M, N, K, ldo, silu, w_rows, w_row0, s);                \
+    break;
+  switch (bn) {
+    TIE_TC2_CASE(128)
+    TIE_TC2_CASE(160)
+    TIE_TC2_CASE(192)
+    TIE_TC2_CASE(224)
+    TIE_TC2_CASE(256)
+  }
+#undef TIE_TC2_CASE
   if (st != kOk) return st;
   TIE_RETURN_LAUNCH("gemm_tc2");
 }

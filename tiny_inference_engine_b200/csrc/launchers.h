@@ -30,7 +30,7 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
                         long long ldw, long long ldo, int transposed, int bn, int splits, float* scratch, int silu,
                         int reduce, int deep, int w_rows, int w_row0, cudaStream_t s);
 TIE_API int tie_gemm_tc2(int out_dtype, const void* a, const void* w, void* out, int M, int N, int K, long long lda,
-                         long long ldw, long long ldo, int silu, int w_rows, int w_row0, cudaStream_t s);
+                         long long ldw, long long ldo, int silu, int w_rows, int w_row0, int bn, cudaStream_t s);
 
 TIE_API int tie_attention_rows(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                void* out, const int* seq_of_row, const int* query_start, const int* context_lens,

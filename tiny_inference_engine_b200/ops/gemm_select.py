@@ -122,6 +122,40 @@ def pair_takes(M: int, N: int) -> bool:
     return M >= PAIR_MIN_ROWS and N >= 256 and not _NO_PAIR and math.ceil(M / 128) * math.ceil(N / 128) > NUM_SMS
 
 
+PAIR_WIDTHS = (256, 224, 192, 160, 128)
+# Microseconds of a 256 x width tile per 64-deep k-block, measured at Qwen3-8B's widths: the MMAs of the full width,
+# and what staging the operands from L2 costs at any width (the 256 rows of `a` are fetched whatever the width:
+# narrow tiles are bound by that, which is why they only pay where they save a whole wave); and per tile the
+# prologue and epilogue that nothing hides.
+_PAIR_US_MMA, _PAIR_US_FEED, _PAIR_US_TILE = 0.45, 0.33, 3.0
+_pairs = None
+
+
+def resident_pairs() -> int:
+    """Pairs of SMs that hold the pair kernel at once (asked of the library once; 74 without a GPU, for planning)."""
+    global _pairs
+    if _pairs is None:
+        try:
+            _pairs = int(_library().tie_gemm_tc2_pairs()) or NUM_SMS // 2
+        except Exception:       # no GPU, no library: plans are still worth looking at
+            return NUM_SMS // 2
+    return _pairs
+
+
+@functools.lru_cache(maxsize=None)
+def pair_width(M: int, N: int, K: int, pairs: int) -> int:
+    """The tile width of the pair kernel for out[M, N] = a[M, K] w^T: the one whose waves of tiles over `pairs` pairs
+    of SMs take the least time by the estimate above; the widest on a tie."""
+    tiles_m, k_blocks = math.ceil(M / 256), math.ceil(K / 64)
+    best = None
+    for bn in PAIR_WIDTHS:
+        waves = math.ceil(tiles_m * math.ceil(N / bn) / pairs)
+        cost = waves * (k_blocks * max(_PAIR_US_MMA * bn / 256, _PAIR_US_FEED) + _PAIR_US_TILE)
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, bn)
+    return best[1]
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None, bn=None, splits=None, scratch=None,
             silu: bool = False, partial_scratch=None, deep=None, pair=None, checked: bool = False):
     """The tensor-core product; the tiling can be forced (tests). Returns `out`, or a SplitSum when
@@ -142,7 +176,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, transposed=None
         pair = transposed is None and bn is None and splits is None and pair_takes(M, N)
     if pair:
         _call("tie_gemm_tc2", dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
-              w.stride(0), out.stride(0), 1 if silu else 0, 0, 0, _stream())
+              w.stride(0), out.stride(0), 1 if silu else 0, 0, 0, bn if bn in PAIR_WIDTHS else pair_width(M, N, K, resident_pairs()),
+              _stream())
         return out
     t, b, s = plan(M, N, K)
     transposed = t if transposed is None else int(transposed)
@@ -250,6 +285,8 @@ class BoundGemm:
             if not t:
                 bn = max(bn, 32)
         real = _library().tie_gemm_tc_real_splits(self.K, splits) if splits > 1 else 1
+        if pair:
+            bn = pair_width(M, self.N, self.K, resident_pairs())
         p = (pair, t, bn, splits, int(not t or bn >= 128), real)
         self._plans[M] = p
         return p
@@ -275,7 +312,7 @@ class BoundGemm:
         code = 1 if out.dtype == torch.bfloat16 else 0
         if pair:
             _call("tie_gemm_tc2", code, a.data_ptr(), self.w_ptr, out.data_ptr(), M, self.N, self.K, a.stride(0), self.ldw,
-                  out.stride(0), 1 if self.silu else 0, self.packed_rows, self.row0, _stream())
+                  out.stride(0), 1 if self.silu else 0, self.packed_rows, self.row0, bn, _stream())
             return out
         leave = splits > 1 and partial_scratch is not None
         scratch = 0

@@ -30,7 +30,7 @@ _SIGNATURES = {
     "tie_sample": [P, L, I, I, P, P, P, P, P],
     "tie_sample_filtered": [P, L, I, I, P, P, P, P, P, P, I, P],
     "tie_gemm_tc": [I, P, P, P, I, I, I, L, L, L, I, I, I, P, I, I, I, I, I, P],
-    "tie_gemm_tc2": [I, P, P, P, I, I, I, L, L, L, I, I, I, P],
+    "tie_gemm_tc2": [I, P, P, P, I, I, I, L, L, L, I, I, I, I, P],
     "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_decode_tc": [P, L, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_attention_decode_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P, P],
@@ -68,6 +68,8 @@ def library() -> ctypes.CDLL:
         lib.tie_kernel_status.argtypes = []
         lib.tie_gemm_tc_real_splits.restype = c_int
         lib.tie_gemm_tc_real_splits.argtypes = [c_int, c_int]
+        lib.tie_gemm_tc2_pairs.restype = c_int
+        lib.tie_gemm_tc2_pairs.argtypes = []
         lib.tie_replay_launcher_id.restype = c_int
         lib.tie_replay_launcher_id.argtypes = [ctypes.c_char_p]
         lib.tie_replay_launcher_args.restype = c_int
