@@ -300,6 +300,34 @@ def test_a_mixer_with_state_of_its_own_under_the_engine_with_preemption_and_a_fa
     assert states.num_free == 3 and cache.num_free() == 6
 
 
+def test_decode_steps_of_a_model_with_state_are_captured_when_its_mixer_says_it_can_be():
+    """A mixer with state that reads the step through device tensors only says `graph_safe`; its model's decode steps
+    then run as CUDA graphs (with sequences that pad a batch, whose state slot is -1), and the tokens are those of
+    the plain restatement. The toy of the other tests reads the step on the host: its model stays out of graphs."""
+    from tiny_inference_engine_b200 import SamplingParams, ServingConfig, StepRunner, make_cache
+    from tiny_inference_engine_b200.engine import Engine, Scheduler, SchedulerConfig
+    from tiny_inference_engine_b200.parts import Model
+    from test_parts_gpu import DictSource
+    from toy_parts import running_mean_model
+    for on_device in (True, False):
+        spec, w, cfg, plain_forward = running_mean_model(on_device=on_device)
+        model = Model(spec, torch.float32).load(DictSource(w))
+        serving = ServingConfig(16, 4)
+        cache, states = make_cache(model, page_size=8, num_pages=32, max_requests=8)
+        runner = StepRunner(model, cache, serving.max_tokens_per_step, serving.max_seqs, serving.max_seqs, states=states)
+        assert runner.use_graphs == on_device
+        eng = Engine(model, cache, Scheduler(cache, SchedulerConfig(serving, policy="fcfs")), serving, states=states, runner=runner)
+        rng = np.random.default_rng(11)
+        prompts = [rng.integers(0, 256, n).tolist() for n in (6, 1, 11)]           # three requests: a batch of four is padded
+        got = eng.generate_batch(prompts, SamplingParams(max_tokens=9))
+        for p, g in zip(prompts, got):
+            toks = list(p)
+            for t in g:
+                assert t == int(plain_forward(toks)[-1].argmax())
+                toks.append(t)
+        assert (runner.graph_replays > 0) == on_device and states.num_free == 8
+
+
 def test_capacity_errors_cancel_and_callbacks(tiny_models):
     from tiny_inference_engine_b200 import CapacityError, InvalidArgument, SamplingParams
     from tiny_inference_engine_b200.engine import FinishReason, SeqState

@@ -15,10 +15,8 @@ from tiny_inference_engine_b200.parts.layer_runs import LayerRuns, walk_part
 
 
 @pytest.fixture(autouse=True)
-def low_addresses(monkeypatch):
-    """Host memory of a test process may lie below 4 GiB, where device memory never does: tell addresses from
-    sizes at 4,096 here (every size in these tests is smaller)."""
-    monkeypatch.setattr(replay, "_ADDRESS", 4096)
+def short_runs(monkeypatch):
+    """The tiny model has three layers: let three be a run."""
     monkeypatch.setattr(LayerRuns, "MIN_RUN", 3)
 
 
@@ -122,6 +120,10 @@ def test_a_plan_names_the_layers_own_tensors_by_slot_and_offset(tmp_path):
     # the same addresses in another layer's row of the table
     row = runs.table[0][2]
     assert int(row[p.slot[1]]) + int(p.offset[1]) == model.layers[2].mixer.w_k.data_ptr()
+    # which arguments are pointers is the launcher's own declaration, not a guess from their size: a 64-bit stride
+    # that happens to equal a tensor's address stays a number
+    p2 = replay.plan([("tie_rmsnorm_rows", (0, shared, w_k, layer.ffn_norm.weight.data_ptr(), 1e-5, shared, 96, 96, 7, 0))], spans)
+    assert p2.slot[2] == -1 and p2.words[2] == w_k and p2.slot[3] >= 0
     # a function that is no launcher of a layer, or a wrong number of arguments: no plan
     assert replay.plan([("tie_sample", (0,) * 9)], spans) is None
     assert replay.plan([("tie_silu_mul", (1, 2, 3))], spans) is None

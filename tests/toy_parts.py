@@ -40,11 +40,34 @@ def running_mean_mixer():
     return RunningMean
 
 
-def running_mean_model(seed=7):
+def running_mean_mixer_on_device():
+    """The same mixer for steps in which every request brings one token, written with device tensors of the step
+    only, so that it can say `graph_safe` and decode steps of its model are captured as CUDA graphs. Sequences that
+    pad a captured batch have state slot -1: they add nothing to any slot."""
+    base = running_mean_mixer()
+
+    class RunningMeanOnDevice(base):
+        graph_safe = True
+
+        def forward(self, h, ctx, cache, state):
+            if ctx.multi_rows > 0:
+                return super().forward(h, ctx, cache, state)
+            S = ctx.S
+            slots = ctx.state_slots[:S]
+            live = slots >= 0
+            at = slots.clamp(min=0).long()
+            state.index_add_(0, at, h.float() * live[:, None])
+            counts = (ctx.positions[:S] + 1).float()
+            return ((state[at] / counts[:, None]) @ self.w.T).to(h.dtype)
+
+    return RunningMeanOnDevice
+
+
+def running_mean_model(seed=7, on_device=False):
     """tiny-A with its second layer's attention replaced by the running mean: (spec, weights, config, plain forward)."""
     from tiny_inference_engine_b200.config import LayerSpec, ModelSpec, PartSpec, parse_qwen3_config, qwen3_spec
     from tiny_inference_engine_b200.parts import register_part
-    register_part("mixer", "running_mean", running_mean_mixer(), replace=True)
+    register_part("mixer", "running_mean", running_mean_mixer_on_device() if on_device else running_mean_mixer(), replace=True)
     cfg = plain.normalise_config(plain.TINY_A)
     w = plain.random_weights(cfg, seed, std=0.1)
     D = cfg["hidden_size"]

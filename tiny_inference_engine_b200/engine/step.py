@@ -31,7 +31,7 @@ import torch
 
 from .. import ops
 from ..cache.manager import CacheManager, RequestCache, blocks_for
-from ..errors import CapacityError, InvalidArgument
+from ..errors import CapacityError, InvalidArgument, TieError
 from ..ops import gemm_select
 from ..ops.library import check_device
 from ..sampling.params import SamplingParams
@@ -160,8 +160,11 @@ class StepRunner:
         self._ids_turn = 0
         self.layer_hook = None
         self.fail_hook = None     # tests: called after the batch is built, may raise
-        # Per-request state is updated by plain torch code in toy mixers: no graphs then.
-        self.use_graphs = use_graphs and (states is None or states.bytes_per_slot == 0)
+        # A mixer with state of its own may be plain torch code that reads the step on the host: decode steps are
+        # captured as graphs only if every such mixer says that it can be (`Mixer.graph_safe`).
+        stateful = [model.layers[e.layer].mixer for i, e in enumerate(model.spec.run_order)
+                    if states is not None and states.tensor(i) is not None]
+        self.use_graphs = use_graphs and all(getattr(m, "graph_safe", False) for m in stateful)
         self._graphs: dict[tuple, tuple] = {}
         self.graph_replays = 0
         self.kernels_in_graph: dict[tuple, int] = {}
@@ -261,7 +264,9 @@ class StepRunner:
         sb, mb, sampled, _ = key
         ctx = self.prepare(entries, sampling, pad_seqs=sb, table_len=mb, device_tokens=device_tokens)
         if key not in self._graphs:
-            # one eager run allocates every buffer and loads every kernel, then the capture
+            # The first step of a shape runs kernel by kernel: that allocates every buffer, loads every kernel and is
+            # the step's own execution (a second run would update the state of mixers that keep some a second
+            # time). The capture behind it records the same launches over the same buffers and executes nothing.
             logits = self.model.forward(ctx, self.cache, self.states)
             if sampled:
                 self._sample(ctx, logits)
@@ -275,17 +280,20 @@ class StepRunner:
             gc.disable()
             try:
                 with torch.cuda.graph(graph):
-                    logits = self.model.forward(ctx, self.cache, self.states)
+                    captured = self.model.forward(ctx, self.cache, self.states)
                     if sampled:
-                        self._sample(ctx, logits)
+                        self._sample(ctx, captured)
             finally:
                 if gc_was_on:
                     gc.enable()
+            if captured.data_ptr() != logits.data_ptr():
+                raise TieError("a decode step's logits moved between its first run and its capture")
             self.kernels_in_graph[key] = ops.library.launch_count() - before
-            self._graphs[key] = (graph, logits)
-        graph, logits = self._graphs[key]
-        graph.replay()
-        self.graph_replays += 1
+            self._graphs[key] = (graph, captured)
+        else:
+            graph, logits = self._graphs[key]
+            graph.replay()
+            self.graph_replays += 1
         S = len(entries)
         if sampling is None:
             return logits[:S]

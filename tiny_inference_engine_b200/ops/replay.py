@@ -3,8 +3,8 @@
 A step that is not a captured graph makes about eight launcher calls per layer from Python; for a
 few hundred tokens the GPU is done with a layer before the host has issued the next one. Layers
 that are built alike make the same calls with the same arguments except for the addresses of
-their own tensors. `record()` collects the calls of one layer; `plan()` marks every argument that
-points into one of that layer's tensors as (slot, offset within it); `run()` hands the list and a
+their own tensors. `record()` collects the calls of one layer; `plan()` marks every pointer argument (known
+from the launcher's declared signature) that points into one of that layer's tensors as (slot, offset within it); `run()` hands the list and a
 table of the following layers' addresses to `tie_replay_layers` (csrc/layer_replay.cu), which
 issues the same launchers with the same arguments: one call from Python for all of them.
 """
@@ -18,7 +18,6 @@ import numpy as np
 
 from . import library
 
-_ADDRESS = 1 << 32      # integer arguments from here on can only be addresses (sizes and strides are far smaller)
 
 
 @contextmanager
@@ -51,10 +50,11 @@ def plan(calls, spans) -> ReplayPlan | None:
     fn, begin, words, slot, offset = [], [0], [], [], []
     for name, args in calls:
         fid = lib.tie_replay_launcher_id(name.encode())
-        if fid < 0 or lib.tie_replay_launcher_args(fid) != len(args):
+        kinds = library._SIGNATURES.get(name)
+        if fid < 0 or lib.tie_replay_launcher_args(fid) != len(args) or kinds is None or len(kinds) != len(args):
             return None
         fn.append(fid)
-        for a in args:
+        for a, kind in zip(args, kinds):
             s, off = -1, 0
             if a is None:
                 w = 0
@@ -62,7 +62,7 @@ def plan(calls, spans) -> ReplayPlan | None:
                 w = int(np.float64(a).view(np.int64))
             else:
                 w = int(a)
-                if w >= _ADDRESS:
+                if kind is library.P and w != 0:        # a pointer by the launcher's own signature, not by its size
                     for i, (base, nbytes) in enumerate(spans):
                         if base <= w < base + nbytes:
                             s, off = i, w - base

@@ -87,6 +87,12 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # For a mixer that keeps state (`state_need`): True if its forward reads the step through the device tensors of
+    # `ctx` only (never `ctx.host`) and copes with the sequences that pad a captured batch (state slot -1, no keys):
+    # decode steps of a model with such mixers are then captured as CUDA graphs like those of a model without state.
+    # False (the default) keeps every step of the model out of graphs.
+    graph_safe = False
+
     def cache_need(self) -> CacheNeed | None:
         return None
 

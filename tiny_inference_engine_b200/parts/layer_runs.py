@@ -83,8 +83,6 @@ class LayerRuns:
             self._held += [weakref.ref(t) for t in tensors[:len(tensors) - planes]]
             if states is not None and states.tensor(i) is not None:
                 ok = False      # state of its own: one tensor per entry that is not on the layer
-            if any(t.data_ptr() < layer_replay._ADDRESS for t in tensors):
-                ok = False      # `plan` tells addresses from sizes by their magnitude
             sig = (type(model.layers[order[i].layer]), tuple(scalars), tuple((t.shape, t.stride(), t.dtype) for t in tensors),
                    view.group if view is not None else None, view.writes if view is not None else None)
             sigs.append(sig if ok else None)
