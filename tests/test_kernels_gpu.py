@@ -400,6 +400,16 @@ def test_sampling_kernels_refuse_rows_with_a_nan_or_nothing_finite(ops, one_cta)
     assert got == [-2 if r in refused else sample_host(z[r], params[r], 3) for r in range(R)]
 
 
+def test_the_constants_the_host_plans_with_are_the_kernels_own(ops):
+    from tiny_inference_engine_b200.ops.library import library
+    from tiny_inference_engine_b200.parts import attention as att
+    lib = library()
+    assert att.TMA_DECODE_TABLE_ENTRIES == lib.tie_attention_decode_limit(0)
+    assert att.MAX_SPLITS <= lib.tie_attention_decode_limit(1)
+    assert att.NUM_SMS == torch.cuda.get_device_properties(0).multi_processor_count
+    assert 1 <= lib.tie_gemm_tc2_pairs() <= att.NUM_SMS // 2
+
+
 def test_refusals_are_clear(ops):
     from tiny_inference_engine_b200.errors import InvalidArgument
     q = torch.zeros(1, 2 * 20, device="cuda")

@@ -323,6 +323,10 @@ static int launch_decode_tma(const CUtensorMap& km, const CUtensorMap& vm, const
 
 using namespace tie;
 
+// Limits of the kernel that the host plans splits with (parts/attention.py keeps copies; a test holds them equal):
+// 0 -> page ids of one split kept in shared memory, 1 -> the most splits of a sequence.
+TIE_API int tie_attention_decode_limit(int which) { return which == 0 ? kMaxTablePages : which == 1 ? 256 : -1; }
+
 // The sequences of seq_list bring one token each. scratch holds n_list * q_heads * max_splits *
 // (head_dim + 2) floats; counters holds n_list * kv_heads ints that are zero before the first
 // launch (the kernel leaves them zero). pages is the number of pages of the cache planes.

@@ -68,6 +68,8 @@ def library() -> ctypes.CDLL:
         lib.tie_kernel_status.argtypes = []
         lib.tie_gemm_tc_real_splits.restype = c_int
         lib.tie_gemm_tc_real_splits.argtypes = [c_int, c_int]
+        lib.tie_attention_decode_limit.restype = c_int
+        lib.tie_attention_decode_limit.argtypes = [c_int]
         lib.tie_gemm_tc2_pairs.restype = c_int
         lib.tie_gemm_tc2_pairs.argtypes = []
         lib.tie_replay_launcher_id.restype = c_int

@@ -21,10 +21,11 @@ from ..errors import InvalidArgument
 from ..weights.loader import TensorNeed
 from .base import CacheNeed, Mixer, build_part, register_part, to_compute
 
+from ..ops.gemm_select import NUM_SMS      # the SM count the split and tiling heuristics were tuned for (one B200)
+
 SPLIT_KEYS = 256       # keys per split for sequences that bring one token
-MAX_SPLITS = 64
-TMA_DECODE_TABLE_ENTRIES = 512     # csrc/attention_decode.cu: kMaxTablePages
-NUM_SMS = 148
+MAX_SPLITS = 64        # at most tie_attention_decode_limit(1) = 256
+TMA_DECODE_TABLE_ENTRIES = 512     # tie_attention_decode_limit(0) (csrc/attention_decode.cu: kMaxTablePages)
 
 
 class GQAttention(Mixer):
