@@ -384,6 +384,39 @@ def test_long_decoding_and_the_first_tokens(tiny_models, dtype):
     assert_logits_close(got, want, dtype, "600 decoded tokens")
 
 
+def test_decode_graphs_at_a_context_in_the_last_bucket_of_the_block_table(tmp_path):
+    """A model whose longest request has 40 pages (no power of two): max_seqs requests decode as one captured graph while
+    one of them is at a context of 38 pages. The graph's table length is the next power of two, 64, capped at the 40
+    the index buffer was sized for: the step fits, and its logits are the plain ones."""
+    from tiny_inference_engine_b200 import StepEntry, StepRunner, load_model, make_cache
+    cfg = dict(plain.TINY_A, max_position_embeddings=320)
+    w = sharp_weights_for(cfg)
+    plain.write_model_dir(tmp_path, cfg, w)
+    model = load_model(tmp_path, "float32")
+    page, seqs = 8, 4
+    cache, states = make_cache(model, page_size=page, num_pages=40 + 3 * 6 + 2, max_requests=seqs)
+    runner = StepRunner(model, cache, 320, seqs, seqs, states=states)
+    assert runner._table_cap == 40
+    rng = np.random.default_rng(12)
+    lengths = [300, 9, 33, 41]
+    toks = [rng.integers(0, cfg["vocab_size"], n + 3).tolist() for n in lengths]
+    reqs = [cache.new_request() for _ in lengths]
+    for r, t, n in zip(reqs, toks, lengths):
+        assert cache.reserve(r, n + 3)
+        runner.run([StepEntry(r, t[:n], 0, [])])
+    want = [plain.forward(w, cfg, t) for t in toks]
+    for step in range(3):
+        out = runner.run([StepEntry(r, [t[n + step]], n + step, [0]) for r, t, n in zip(reqs, toks, lengths)]).float().cpu().numpy()
+        for i, n in enumerate(lengths):
+            assert_logits_close(out[i:i + 1], want[i][n + step:n + step + 1], "float32", f"request {i}, step {step}")
+    assert runner.graph_replays >= 1 and all(key[1] == 40 for key in runner._graphs)
+
+
+def sharp_weights_for(cfg):
+    from conftest import sharp_weights
+    return sharp_weights(cfg, 5)
+
+
 def test_command_line_generates_the_plain_tokens(tiny_models):
     import subprocess
     import sys
