@@ -9,9 +9,11 @@
 // TOKENS_PER_STEP tokens a step) twice: with 256 pages -> OUT_DIR/greedy.txt, and with
 // SMALL_POOL_PAGES pages and no watermark (admission may use the last free page), so few that
 // it preempts -> OUT_DIR/greedy_small.txt, whose first line is "# preemptions N"
-// (tests/engine/test_engine_batching.cpp:58-75 is the test this follows).
+// (tests/engine/test_engine_batching.cpp:58-75 is the test this follows). The roomy run is
+// timed on the host -> OUT_DIR/timing.txt (one line; a record of this machine, compared by no test).
 #include <cstdio>
 #include <cstdlib>
+#include <chrono>
 #include <fstream>
 #include <iostream>
 #include <sstream>
@@ -62,7 +64,18 @@ static int64_t run_engine(CpuBackend& backend, const LoadedModel& weights, int32
     p.max_tokens = new_tokens[i];
     ids.push_back(engine.add_request(prompts[i], p));
   }
-  while (engine.has_work()) engine.step();
+  const auto t0 = std::chrono::steady_clock::now();
+  int64_t steps = 0;
+  while (engine.has_work()) { engine.step(); ++steps; }
+  const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  if (!small) {
+    int64_t prompt_tokens = 0, generated = 0;
+    for (size_t i = 0; i < prompts.size(); ++i) { prompt_tokens += int64_t(prompts[i].size()); generated += new_tokens[i]; }
+    std::ofstream t(path.substr(0, path.rfind('/')) + "/timing.txt");
+    t << "reference engine, CPU backend (scalar dot products, g++ -O2), all requests batched: " << steps << " steps, "
+      << prompt_tokens << " prompt tokens and " << generated << " generated tokens in " << ms << " ms = "
+      << double(generated) * 1e3 / ms << " generated tokens/s\n";
+  }
   std::ofstream g(path);
   if (small) g << "# preemptions " << engine.stats().preemptions << "\n";
   for (size_t i = 0; i < ids.size(); ++i) {
