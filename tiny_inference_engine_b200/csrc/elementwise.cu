@@ -498,94 +498,115 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restr
 }
 
 // The same for many tokens, where the kernel above is bound by the instructions it issues (about 250 a
-// head), not by memory. One block a token; a lane holds 8 neighbouring elements, so a head takes
-// LPH = DH / 8 lanes and a warp works on 32 / LPH heads at once; what does not depend on the head (the
-// lane's cos and sin, its norm weights, the token's place in the cache) is made once per thread.
-template <typename T, int DH>
-__global__ void __launch_bounds__(256) qk_norm_rope_append_rows_kernel(T* __restrict__ qkv, long long row_stride,
+// head), not by memory. A block works on TOK tokens, one after the other; a lane holds four neighbouring
+// elements of the first half of a head and the four that rotate with them in the second half, so a head takes
+// LPH = DH / 8 lanes, a warp works on 32 / LPH heads at once, and the rotation needs no exchange between lanes.
+// What does not depend on the head (the lane's norm weights, and per token its cos and sin and its place in the
+// cache) is made once.
+template <typename T, int DH, int TOK>
+__global__ void __launch_bounds__(256, 4) qk_norm_rope_append_rows_kernel(T* __restrict__ qkv, long long row_stride,
                                                                        const float* __restrict__ qw, const float* __restrict__ kw,
                                                                        float q_eps, float k_eps, const float* __restrict__ inv_freq,
                                                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                                                        T* __restrict__ k_cache, T* __restrict__ v_cache, int q_heads,
-                                                                       int kv_heads, int page_size, int heads_per_token) {
+                                                                       int kv_heads, int page_size, int heads_per_token, int tokens) {
   pdl_launch_dependents();
-  constexpr int E = 8, LPH = DH / E, HALF = DH / 2, WARP_HEADS = 32 / LPH;
-  using Slice = HeadSlice<T, E>;
-  __shared__ float cs[DH];   // the token's rotation: cos at [0, HALF), sin at [HALF, DH)
+  constexpr int Q = 4, HALF = DH / 2, LPH = HALF / Q, WARP_HEADS = 32 / LPH;
+  using Slice = HeadSlice<T, Q>;
+  __shared__ __align__(16) float cs[TOK][DH];   // a token's rotation: cos at [0, HALF), sin at [HALF, DH)
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long t = blockIdx.x;
+  const long long t0 = static_cast<long long>(blockIdx.x) * TOK;
   // positions, frequencies, slots and weights do not come from the kernel ahead
   if (inv_freq) {
-    const float pos = static_cast<float>(positions[t]);
-    for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf(pos * inv_freq[i], cs + HALF + i, cs + i);
+    for (int i = threadIdx.x; i < TOK * HALF; i += blockDim.x) {
+      const int tk = i / HALF, j = i % HALF;
+      if (t0 + tk < tokens) sincosf(static_cast<float>(positions[t0 + tk]) * inv_freq[j], &cs[tk][HALF + j], &cs[tk][j]);
+    }
   }
-  const int e0 = (lane % LPH) * E;        // this lane's elements of its head
-  float qwv[E], kwv[E];
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    qwv[e] = qw ? qw[e0 + e] : 1.0f;
-    kwv[e] = kw ? kw[e0 + e] : 1.0f;
-  }
-  const int slot = slots ? slots[t] : -1;
-  const long long cache_row = slot >= 0 ? static_cast<long long>(slot / page_size) * kv_heads * page_size + slot % page_size : 0;
+  const int e0 = (lane % LPH) * Q;        // this lane's elements of each half of its head
+  float4 one = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+  const float4 qw_lo = qw ? *reinterpret_cast<const float4*>(qw + e0) : one, qw_hi = qw ? *reinterpret_cast<const float4*>(qw + HALF + e0) : one;
+  const float4 kw_lo = kw ? *reinterpret_cast<const float4*>(kw + e0) : one, kw_hi = kw ? *reinterpret_cast<const float4*>(kw + HALF + e0) : one;
+  const int stride_heads = warps * WARP_HEADS;
   pdl_wait();
   __syncthreads();
-  float c[E], sn[E];   // x' = x * c + partner * sn, the sine with the sign of the lane's half
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    c[e] = inv_freq ? cs[e0 % HALF + e] : 1.0f;
-    sn[e] = inv_freq ? (e0 < HALF ? -cs[HALF + e0 % HALF + e] : cs[HALF + e0 % HALF + e]) : 0.0f;
-  }
-  for (int base = warp * WARP_HEADS; base < heads_per_token; base += warps * WARP_HEADS) {   // uniform over the warp
-    const int head = base + lane / LPH;
-    const bool is_q = head < q_heads;
-    const bool is_v = head >= q_heads + kv_heads;
-    T* src = qkv + t * row_stride + static_cast<long long>(head) * DH + e0;
-    T* dst = nullptr;
-    if (head < heads_per_token) {
-      if (is_q) {
-        dst = src;
-      } else if (slot >= 0) {
-        const int h = is_v ? head - q_heads - kv_heads : head - q_heads;
-        dst = (is_v ? v_cache : k_cache) + (cache_row + static_cast<long long>(h) * page_size) * DH + e0;
+#pragma unroll 1
+  for (int tk = 0; tk < TOK; ++tk) {
+    const long long t = t0 + tk;
+    if (t >= tokens) break;
+    const int slot = slots ? slots[t] : -1;
+    const long long cache_row = slot >= 0 ? static_cast<long long>(slot / page_size) * kv_heads * page_size + slot % page_size : 0;
+    float4 c = one, sn = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (inv_freq) {
+      c = *reinterpret_cast<const float4*>(&cs[tk][e0]);
+      sn = *reinterpret_cast<const float4*>(&cs[tk][HALF + e0]);
+    }
+    T* row = qkv + t * row_stride + e0;
+#pragma unroll 1
+    for (int base = warp * WARP_HEADS; base < heads_per_token; base += stride_heads) {   // uniform over the warp
+      const int head = base + lane / LPH;
+      const bool is_q = head < q_heads;
+      const bool is_v = head >= q_heads + kv_heads;
+      const T* src = row + static_cast<long long>(head) * DH;
+      T* dst = nullptr;
+      if (head < heads_per_token) {
+        if (is_q) {
+          dst = const_cast<T*>(src);
+        } else if (slot >= 0) {
+          const int h = is_v ? head - q_heads - kv_heads : head - q_heads;
+          dst = (is_v ? v_cache : k_cache) + (cache_row + static_cast<long long>(h) * page_size) * DH + e0;
+        }
       }
-    }
-    if (__all_sync(0xffffffffu, is_v || dst == nullptr)) {   // a warp of value heads only copies
-      if (dst != nullptr) *reinterpret_cast<Slice*>(dst) = *reinterpret_cast<const Slice*>(src);
-      continue;
-    }
-    float x[E];
-    if (dst != nullptr) {
-      const Slice in = *reinterpret_cast<const Slice*>(src);
+      Slice lo, hi;
+      if (dst != nullptr) {
+        lo = *reinterpret_cast<const Slice*>(src);
+        hi = *reinterpret_cast<const Slice*>(src + HALF);
+      }
+      if (__all_sync(0xffffffffu, is_v || dst == nullptr)) {   // a warp of value heads only copies
+        if (dst != nullptr) {
+          *reinterpret_cast<Slice*>(dst) = lo;
+          *reinterpret_cast<Slice*>(dst + HALF) = hi;
+        }
+        continue;
+      }
+      float a[Q], b[Q];
 #pragma unroll
-      for (int e = 0; e < E; ++e) x[e] = Elem<T>::load(in.v + e);
-    } else {
+      for (int e = 0; e < Q; ++e) {
+        a[e] = dst != nullptr ? Elem<T>::load(lo.v + e) : 0.0f;
+        b[e] = dst != nullptr ? Elem<T>::load(hi.v + e) : 0.0f;
+      }
+      float ss = 0.0f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) x[e] = 0.0f;
-    }
-    float ss = 0.0f;
+      for (int e = 0; e < Q; ++e) ss += a[e] * a[e] + b[e] * b[e];
 #pragma unroll
-    for (int e = 0; e < E; ++e) ss += x[e] * x[e];
+      for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (!is_v) {   // values are stored as they are
+        if ((is_q ? qw : kw) != nullptr) {
+          const float inv = 1.0f / sqrtf(ss / static_cast<float>(DH) + (is_q ? q_eps : k_eps));
+          const float4 wl = is_q ? qw_lo : kw_lo, wh = is_q ? qw_hi : kw_hi;
+          a[0] = (a[0] * inv) * wl.x, a[1] = (a[1] * inv) * wl.y, a[2] = (a[2] * inv) * wl.z, a[3] = (a[3] * inv) * wl.w;
+          b[0] = (b[0] * inv) * wh.x, b[1] = (b[1] * inv) * wh.y, b[2] = (b[2] * inv) * wh.z, b[3] = (b[3] * inv) * wh.w;
+        }
+        if (inv_freq != nullptr) {
+          const float cc[Q] = {c.x, c.y, c.z, c.w}, ssn[Q] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
-    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const bool normed = !is_v && (is_q ? qw : kw) != nullptr;   // values are stored as they are
-    const float inv = normed ? 1.0f / sqrtf(ss / static_cast<float>(DH) + (is_q ? q_eps : k_eps)) : 1.0f;
+          for (int e = 0; e < Q; ++e) {
+            const float x0 = a[e], x1 = b[e];
+            a[e] = x0 * cc[e] - x1 * ssn[e];
+            b[e] = x1 * cc[e] + x0 * ssn[e];
+          }
+        }
+      }
+      if (dst != nullptr) {
+        Slice out_lo, out_hi;
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const float w = is_q ? qwv[e] : kwv[e];
-      x[e] = normed ? (x[e] * inv) * w : x[e];
-    }
-    const bool rotated = !is_v && inv_freq != nullptr;
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const float other = __shfl_xor_sync(0xffffffffu, x[e], LPH / 2);
-      x[e] = rotated ? x[e] * c[e] + other * sn[e] : x[e];
-    }
-    if (dst != nullptr) {
-      Slice out;
-#pragma unroll
-      for (int e = 0; e < E; ++e) Elem<T>::store(out.v + e, x[e]);
-      *reinterpret_cast<Slice*>(dst) = out;
+        for (int e = 0; e < Q; ++e) {
+          Elem<T>::store(out_lo.v + e, a[e]);
+          Elem<T>::store(out_hi.v + e, b[e]);
+        }
+        *reinterpret_cast<Slice*>(dst) = out_lo;
+        *reinterpret_cast<Slice*>(dst + HALF) = out_hi;
+      }
     }
   }
 }
@@ -682,20 +703,31 @@ int launch_qk_norm_rope_append(void* qkv, long long stride, const float* part, l
                      stride % vec == 0 && reinterpret_cast<uintptr_t>(qkv) % slice == 0 && reinterpret_cast<uintptr_t>(kc) % slice == 0 &&
                      reinterpret_cast<uintptr_t>(vc) % slice == 0;
   // many tokens, nothing to sum: the kernel that issues the fewest instructions a head
-  const size_t wide = sizeof(T) * 8 > 16 ? 16 : sizeof(T) * 8;
-  const bool rows = whole && part == nullptr && tokens >= 256 && stride % 8 == 0 && reinterpret_cast<uintptr_t>(qkv) % wide == 0 &&
-                    reinterpret_cast<uintptr_t>(kc) % wide == 0 && reinterpret_cast<uintptr_t>(vc) % wide == 0;
+  const size_t half_slice = sizeof(T) * 4;
+  const bool rows = whole && part == nullptr && tokens >= 256 && stride % 4 == 0 && reinterpret_cast<uintptr_t>(qkv) % half_slice == 0 &&
+                    reinterpret_cast<uintptr_t>(kc) % half_slice == 0 && reinterpret_cast<uintptr_t>(vc) % half_slice == 0 &&
+                    reinterpret_cast<uintptr_t>(qw) % 16 == 0 && reinterpret_cast<uintptr_t>(kw) % 16 == 0;
   if (rows) {
     T* q = static_cast<T*>(qkv);
     T* k = static_cast<T*>(kc);
     T* v = static_cast<T*>(vc);
-#define TIE_QK_ROWS(D)                                                                                                       \
-  TIE_LAUNCH((qk_norm_rope_append_rows_kernel<T, D>), tokens, 256, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, slots, k, v, \
-             q_heads, kv_heads, page_size, heads_per_token)
+    // four tokens a block where there are blocks enough for every SM several times over: the weights are fetched once
+#define TIE_QK_ROWS_OF(D, TOK)                                                                                                          \
+  TIE_LAUNCH((qk_norm_rope_append_rows_kernel<T, D, TOK>), ceil_div(tokens, TOK), 256, 0, s, q, stride, qw, kw, q_eps, k_eps, inv_freq, pos, \
+             slots, k, v, q_heads, kv_heads, page_size, heads_per_token, tokens)
+#define TIE_QK_ROWS(D)                   \
+  do {                                   \
+    if (tokens >= 2048) {                \
+      TIE_QK_ROWS_OF(D, 4);              \
+    } else {                             \
+      TIE_QK_ROWS_OF(D, 1);              \
+    }                                    \
+  } while (0)
     if (head_dim == 64) TIE_QK_ROWS(64);
     else if (head_dim == 128) TIE_QK_ROWS(128);
     else TIE_QK_ROWS(256);
 #undef TIE_QK_ROWS
+#undef TIE_QK_ROWS_OF
     TIE_RETURN_LAUNCH("qk_norm_rope_append");
   }
   if (whole) {
