@@ -682,6 +682,93 @@ def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window)
             assert not counters.any()
 
 
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(8, 2, 128, 16, 0), (4, 4, 64, 8, 0), (16, 1, 128, 32, 0), (6, 2, 256, 16, 0),
+                                                  (8, 2, 128, 16, 100), (32, 2, 64, 64, 0)])
+@pytest.mark.parametrize("source", ["rows", "partial sums"])
+def test_decode_attention_that_prepares_its_own_heads(ops, Hq, Hkv, Dh, page, window, source):
+    """A step of single tokens, straight from the q/k/v product's output: the kernel norms and rotates its query
+    heads, makes the newest key and value, stores them and uses them. Equal, bit for bit, to the q/k norm + RoPE +
+    append kernel followed by the TMA-fed decode attention (outputs and both cache planes), and right against the
+    plain attention over keys that include the newest. Contexts that end at the first and the last key of a tile,
+    of a page and of a split, one of a single key, one empty (a sequence that pads a captured batch); the newest
+    key's slot holds junk before the step, and so do the slots behind it."""
+    from tiny_inference_engine_b200.ops import gemm_select
+    rng = np.random.default_rng(Hq + Dh + page)
+    contexts = [1, 64, 65, 300, 129, 0, 257, 256]
+    S = len(contexts)
+    kc, vc, bt, ks, vs = paged_cache(rng, "bfloat16", [max(c, 1) for c in contexts], Hkv, Dh, page, 128 * 16 // page)
+    width = (Hq + 2 * Hkv) * Dh
+    rows = as_stored(rng.standard_normal((S, width)), "bfloat16")
+    qw, kw = (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32), (1 + 0.2 * rng.standard_normal(Dh)).astype(np.float32)
+    inv = plain.rope_inv_freq(1e6, Dh)
+    pos = np.array([max(c - 1, 0) for c in contexts])
+    slots = np.array([bt[i, pos[i] // page] * page + pos[i] % page if contexts[i] > 0 else -1 for i in range(S)])
+    for i in range(S):                          # the newest key's slot, and the rest of its page, hold junk
+        if contexts[i] > 0:
+            kc[bt[i, pos[i] // page], :, pos[i] % page:] = 7.0
+            vc[bt[i, pos[i] // page], :, pos[i] % page:] = -7.0
+    qs = np.arange(S + 1)
+    meta = (dev(qs, torch.int32), dev(np.array(contexts), torch.int32), dev(bt, torch.int32))
+    seqs = dev(np.arange(S), torch.int32)
+    scale = 1.0 / np.sqrt(Dh)
+    partial = None
+    if source == "partial sums":                # three float partial sums whose sum, in order, is what the kernels see
+        parts = np.stack([rows * 0.5, rows * 0.25, rows * 0.25]).astype(np.float32)
+        partial = ops.SplitSum(dev(parts).reshape(-1), 3, S, width)
+    results = []
+    for fused in (False, True):
+        kcd, vcd = dev(kc, torch.bfloat16), dev(vc, torch.bfloat16)
+        qkv = dev(rows if partial is None else np.zeros_like(rows), torch.bfloat16)
+        out = torch.full((S, Hq * Dh), float("nan"), device="cuda", dtype=torch.bfloat16)
+        scratch = torch.empty(ops.attention_split_scratch_floats(S, Hq, Dh, 8), device="cuda")
+        counters = torch.zeros(S * Hkv, dtype=torch.int32, device="cuda")
+        for split_keys, max_splits in ((64, 8), (128, 3), (512, 1)):
+            if fused:
+                assert ops.attention_decode_prep_takes(qkv, Hq, Hkv, Dh, page, dev(inv))
+                ops.attention_decode_prep(qkv, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), kcd, vcd, out, *meta,
+                                          Hq, Hkv, Dh, scale, seqs, S, split_keys, max_splits, scratch, counters, window,
+                                          append=True, partial=partial)
+            else:
+                work = qkv.clone()
+                ops.qk_norm_rope_append(work, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), dev(slots, torch.int32),
+                                        kcd, vcd, Hq, Hkv, Dh, partial=partial)
+                ops.attention_decode_tma(work[:, :Hq * Dh], kcd, vcd, out, *meta, Hq, Hkv, Dh, scale, seqs, S, split_keys,
+                                         max_splits, scratch, counters, window)
+            torch.cuda.synchronize()
+            gemm_select.check_status()
+            assert not counters.any()
+            results.append((fused, split_keys, out.clone(), kcd.clone(), vcd.clone()))
+    half = len(results) // 2
+    for (_, sk, o0, k0, v0), (_, _, o1, k1, v1) in zip(results[:half], results[half:]):
+        assert torch.equal(o0, o1), f"outputs differ at split_keys={sk}"
+        assert torch.equal(k0, k1) and torch.equal(v0, v1), "cache planes differ"
+    # against the plain formulas: the newest key and value are among the keys
+    q, k, v = rows[:, :Hq * Dh], rows[:, Hq * Dh:(Hq + Hkv) * Dh], rows[:, (Hq + Hkv) * Dh:]
+    want_q = as_stored(plain.rope_neox(plain.rms_norm(q.reshape(S * Hq, Dh), qw, 1e-6).reshape(S, -1), pos, Hq, Dh, 1e6), "bfloat16")
+    want_k = as_stored(plain.rope_neox(plain.rms_norm(k.reshape(S * Hkv, Dh), kw, 1e-5).reshape(S, -1), pos, Hkv, Dh, 1e6), "bfloat16")
+    got = host(results[-1][2])
+    for i, c in enumerate(contexts):
+        if c == 0:
+            assert not got[i].any()
+            continue
+        keys = np.concatenate([ks[i][:c - 1], want_k[i].reshape(1, Hkv, Dh)])
+        vals = np.concatenate([vs[i][:c - 1], v[i].reshape(1, Hkv, Dh)])
+        want = dense_reference(want_q[i:i + 1], keys, vals, Hq, Hkv, Dh, 1, window)
+        assert rel_err(got[i:i + 1], want) < TOL["bfloat16"], f"context {c}"
+    # without the append (a layer that reads another layer's cache): the cache is read as it is and left as it is
+    kcd, vcd = results[4][3].clone(), results[4][4].clone()     # the planes as the run with 3 splits of 128 keys left them
+    before_k, before_v = kcd.clone(), vcd.clone()
+    out = torch.full((S, Hq * Dh), float("nan"), device="cuda", dtype=torch.bfloat16)
+    q_only = dev(rows, torch.bfloat16)[:, :Hq * Dh]
+    ops.attention_decode_prep(q_only, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), kcd, vcd, out, *meta,
+                              Hq, Hkv, Dh, scale, seqs, S, 128, 3, scratch, counters, window, append=False)
+    torch.cuda.synchronize()
+    gemm_select.check_status()
+    assert torch.equal(kcd, before_k) and torch.equal(vcd, before_v)
+    if partial is None:
+        assert torch.equal(out, results[4][2])
+
+
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 65, 255, 256, 511, 512, 1022, 1023])
 def test_tensor_core_attention_finds_one_far_key(ops, far):
     """As test_one_far_key_among_a_thousand_is_found, for the mma kernels: edges of pages (16),

@@ -21,6 +21,7 @@
 // depend on which CTA came last) and writes the output rows. With one split the output is
 // written directly. Every mbarrier wait is bounded; on expiry the status word gets a code.
 #include "attention_mma.cuh"
+#include "head_prep.cuh"
 #include "tma.cuh"
 #include "launchers.h"
 
@@ -42,9 +43,21 @@ struct DecodeArgs {
   long long q_stride;
   int max_blocks, q_heads, kv_heads, page_size, page_shift, window, split_keys, max_splits;
   float scale_log2;
+  // Only for the kernel that prepares its heads itself (PREP): the output of the q/k/v product, [T, (q_heads + 2 kv_heads)
+  // * head_dim] as bfloat16 rows (qkv) or as `part_splits` float partial sums (part + z * part_stride + t * part_ld + column),
+  // the head norms' weights (null: no norm), the rotation's frequencies (null: none), the tokens' positions, the cache
+  // planes to append the newest key and value to (append != 0).
+  const __nv_bfloat16* qkv;
+  const float* part;
+  long long qkv_stride, part_stride, part_ld;
+  int part_splits, append;
+  const float *qw, *kw, *inv_freq;
+  float q_eps, k_eps;
+  const int* positions;
+  __nv_bfloat16 *k_plane, *v_plane;
 };
 
-template <int DH, int STAGES>
+template <int DH, int STAGES, bool PREP>
 __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                       const __grid_constant__ CUtensorMap v_map, DecodeArgs a) {
   // Keys and values of earlier tokens, the tables and the lengths do not depend on the kernels just ahead in
@@ -64,6 +77,8 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   uint64_t* empty = full + STAGES;
   int* pages = reinterpret_cast<int*>(empty + STAGES);                 // page ids of this split
   int* flags = pages + kMaxTablePages;                                 // [0] abort, [1] last-arrival flag
+  [[maybe_unused]] float* cs = reinterpret_cast<float*>(flags + 4);    // PREP: the token's cos and sin
+  [[maybe_unused]] __nv_bfloat16* newest = reinterpret_cast<__nv_bfloat16*>(cs + DH);   // PREP: the newest key, then its value
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int li = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -126,7 +141,9 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
       for (int i = 0; i < n_tiles; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, abort_flag, a.status, 11)) break;
-        if (hi == pos && i == n_tiles - 1) pdl_wait();   // the tile with the newest key
+        // the tile with the newest key: written by the kernel ahead, unless this kernel appends it itself (then the
+        // copy in shared memory is patched once it has landed)
+        if (hi == pos && i == n_tiles - 1 && !(PREP && a.append)) pdl_wait();
         mbar_expect_tx(full + s, STAGE_BYTES);
         uint8_t* kdst = smem + s * STAGE_BYTES;
         for (int b = 0; b < boxes_per_tile; ++b) {
@@ -142,13 +159,64 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
     }
   } else {
     // Q: the G heads of the group, rows G..15 zero
-    pdl_wait();
     constexpr int CPR = DH / 8;
-    for (int id = threadIdx.x; id < 16 * CPR; id += 128) {
-      const int r = id / CPR, c = id % CPR;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < G) v = *reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t) * a.q_stride + static_cast<long long>(kvh * G + r) * DH + c * 8);
-      *reinterpret_cast<uint4*>(q_tile + RowLayout<DH>::at(r, c)) = v;
+    constexpr int VEC = DH / 32;
+    using Slice = HeadSlice<__nv_bfloat16, VEC>;
+    [[maybe_unused]] const bool appends = PREP && a.append != 0 && hi == pos;   // this split ends with the newest key
+    if constexpr (PREP) {
+      // the rotation depends on the step's own inputs only: made while the kernel ahead still runs
+      if (a.inv_freq) rotation_table(cs, static_cast<float>(a.positions[t]), a.inv_freq, DH / 2, threadIdx.x, 128);
+      for (int id = threadIdx.x; id < 16 * CPR; id += 128) {
+        const int r = id / CPR, c = id % CPR;
+        if (r >= G) *reinterpret_cast<uint4*>(q_tile + RowLayout<DH>::at(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      pdl_wait();
+      // A warp a head, as in the q/k norm + RoPE + append kernel: the group's query heads, and where this split ends
+      // with the newest key, that key's head (normed and rotated) and its value's (as it is).
+      const int heads = G + (appends ? 2 : 0);
+      for (int r = warp; r < heads; r += 4) {
+        const int head = r < G ? kvh * G + r : (r == G ? a.q_heads + kvh : a.q_heads + a.kv_heads + kvh);
+        const long long col = static_cast<long long>(head) * DH + lane * VEC;
+        float x[VEC];
+        if (a.part) {   // the sum of the split product's partial sums, in split order
+          using FloatSlice = HeadSlice<float, VEC>;
+          const float* psrc = a.part + static_cast<long long>(t) * a.part_ld + col;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) x[e] = 0.0f;
+#pragma unroll 4
+          for (int z = 0; z < a.part_splits; ++z) {
+            const FloatSlice p = *reinterpret_cast<const FloatSlice*>(psrc + static_cast<long long>(z) * a.part_stride);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) x[e] += p.v[e];
+          }
+        } else {
+          const Slice in = *reinterpret_cast<const Slice*>(a.qkv + static_cast<long long>(t) * a.qkv_stride + col);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) x[e] = __bfloat162float(in.v[e]);
+        }
+        if (r <= G) prepare_head<VEC>(x, r < G ? a.qw : a.kw, r < G ? a.q_eps : a.k_eps, a.inv_freq ? cs : nullptr, lane);
+        Slice out;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) out.v[e] = __float2bfloat16_rn(x[e]);
+        if (r < G) {
+          *reinterpret_cast<Slice*>(q_tile + RowLayout<DH>::at(r, (lane * VEC) >> 3) + ((lane * VEC * 2) & 15)) = out;
+        } else {
+          // the page of the newest key is among this split's pages; the same row the TMA boxes of that page start from
+          const int box = (pos - kt_first * kKeysPerTile) / box_rows;
+          const long long row = static_cast<long long>(pages[box] * a.kv_heads + kvh) * a.page_size + (pos & (a.page_size - 1));
+          *reinterpret_cast<Slice*>((r == G ? a.k_plane : a.v_plane) + row * DH + lane * VEC) = out;
+          *reinterpret_cast<Slice*>(newest + (r - G) * DH + lane * VEC) = out;
+        }
+      }
+    } else {
+      pdl_wait();
+      for (int id = threadIdx.x; id < 16 * CPR; id += 128) {
+        const int r = id / CPR, c = id % CPR;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < G) v = *reinterpret_cast<const uint4*>(a.q + static_cast<long long>(t) * a.q_stride + static_cast<long long>(kvh * G + r) * DH + c * 8);
+        *reinterpret_cast<uint4*>(q_tile + RowLayout<DH>::at(r, c)) = v;
+      }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four consumer warps
     uint32_t qf[DH / 16][4];
@@ -159,6 +227,18 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % STAGES;
       if (!mbar_wait(full + s, (i / STAGES) & 1, abort_flag, a.status, 12)) break;
+      if constexpr (PREP) {
+        // The tile came from the cache as it was before this step: the newest key's row gets what this kernel made,
+        // from the warp that works on that key (no other warp reads the row).
+        const int rr = pos - (kt_first + i) * kKeysPerTile;
+        if (appends && i == n_tiles - 1 && warp == (rr >> 4)) {
+          uint8_t* tile = smem + s * STAGE_BYTES;
+          const uint32_t at = L::at(rr, (lane * VEC) >> 3) + ((lane * VEC * 2) & 15);
+          *reinterpret_cast<Slice*>(tile + at) = *reinterpret_cast<const Slice*>(newest + lane * VEC);
+          *reinterpret_cast<Slice*>(tile + PLANE_BYTES + at) = *reinterpret_cast<const Slice*>(newest + DH + lane * VEC);
+          __syncwarp();
+        }
+      }
       const int key0 = (kt_first + i) * kKeysPerTile + warp * 16;   // this warp's 16 keys of the tile
       if (key0 <= hi && key0 + 15 >= lo) {
         const uint32_t k_tile = smem_u32(smem + s * STAGE_BYTES);
@@ -299,24 +379,65 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   if (threadIdx.x == 0) a.counters[li * a.kv_heads + kvh] = 0;   // ready for the next launch
 }
 
-template <int DH>
+template <int DH, bool PREP>
 static int launch_decode_tma(const CUtensorMap& km, const CUtensorMap& vm, const DecodeArgs& a, int n_list, cudaStream_t s) {
   constexpr int STAGES = DH >= 256 ? 2 : (DH == 128 ? 3 : 4);
   constexpr size_t ring = static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128;
   constexpr size_t combine = (4 * 16 * (DH + 2) + 6 * 16) * sizeof(float);          // the four warps' results and factors
   constexpr size_t weights = (3 * 16 * 256 + 16) * sizeof(float);                    // the last CTA's merge: 16 rows, 256 splits at most
   constexpr size_t merge = combine > weights ? combine : weights;
-  constexpr size_t smem = (ring > merge ? ring : merge) + 16 * DH * 2 + 2 * STAGES * 8 + (kMaxTablePages + 2) * 4 + 1024;
+  constexpr size_t prep = PREP ? DH * sizeof(float) + 2 * DH * 2 + 16 : 0;           // the rotation, the newest key and value
+  constexpr size_t smem = (ring > merge ? ring : merge) + 16 * DH * 2 + 2 * STAGES * 8 + (kMaxTablePages + 4) * 4 + prep + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_decode_tma_kernel<DH, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+    if (cudaFuncSetAttribute(attn_decode_tma_kernel<DH, STAGES, PREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
       set_error("attention_decode: cannot reserve %zu bytes of shared memory", smem);
       return kCudaError;
     }
     configured = true;
   }
-  TIE_LAUNCH((attn_decode_tma_kernel<DH, STAGES>), dim3(n_list, a.kv_heads, a.max_splits), kDecThreads, smem, s, km, vm, a);
+  TIE_LAUNCH((attn_decode_tma_kernel<DH, STAGES, PREP>), dim3(n_list, a.kv_heads, a.max_splits), kDecThreads, smem, s, km, vm, a);
   return kOk;
+}
+
+// What both entry points ask of their arguments, and the launch.
+static int decode_tma(DecodeArgs a, bool prep, const void* k_cache, const void* v_cache, int head_dim, int pages, int n_list,
+                      float scale, cudaStream_t s) {
+  const int q_heads = a.q_heads, kv_heads = a.kv_heads, page_size = a.page_size, split_keys = a.split_keys, max_splits = a.max_splits;
+  TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_decode: head_dim %d is not 64, 128 or 256", head_dim);
+  TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
+              "attention_decode: %d query heads over %d kv heads (at most 16 per group)", q_heads, kv_heads);
+  TIE_REQUIRE(page_size >= 8 && (page_size & (page_size - 1)) == 0, "attention_decode: page size %d is not a power of two from 8 up", page_size);
+  TIE_REQUIRE(split_keys > 0 && split_keys % kKeysPerTile == 0 && max_splits > 0 && a.scratch != nullptr && a.counters != nullptr,
+              "attention_decode: splits must be positive multiples of %d keys", kKeysPerTile);
+  const int box_rows = page_size < kKeysPerTile ? page_size : kKeysPerTile;
+  TIE_REQUIRE((split_keys / kKeysPerTile + 1) * (kKeysPerTile / box_rows) <= kMaxTablePages && max_splits <= 256,
+              "attention_decode: a split of %d keys over pages of %d (or %d splits) exceeds the kernel's tables", split_keys,
+              page_size, max_splits);
+  if (n_list == 0) return kOk;
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  CUtensorMap km, vm;
+  const long long rows = static_cast<long long>(pages) * kv_heads * page_size;
+  TIE_REQUIRE(make_map_bf16(&km, k_cache, rows, head_dim, head_dim, 64, box_rows) &&
+                  make_map_bf16(&vm, v_cache, rows, head_dim, head_dim, 64, box_rows),
+              "attention_decode: cuTensorMapEncodeTiled failed");
+  TIE_REQUIRE(status_word() != nullptr, "attention_decode: cannot allocate the status word");
+  a.status = status_word();
+  a.page_shift = shift;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  int st = kOk;
+  if (prep) {
+    if (head_dim == 64) st = launch_decode_tma<64, true>(km, vm, a, n_list, s);
+    else if (head_dim == 128) st = launch_decode_tma<128, true>(km, vm, a, n_list, s);
+    else st = launch_decode_tma<256, true>(km, vm, a, n_list, s);
+  } else {
+    if (head_dim == 64) st = launch_decode_tma<64, false>(km, vm, a, n_list, s);
+    else if (head_dim == 128) st = launch_decode_tma<128, false>(km, vm, a, n_list, s);
+    else st = launch_decode_tma<256, false>(km, vm, a, n_list, s);
+  }
+  if (st != kOk) return st;
+  TIE_RETURN_LAUNCH("attention_decode_tma");
 }
 
 }  // namespace tie
@@ -335,33 +456,47 @@ TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const vo
                                      int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
                                      int window, float scale, const int* seq_list, int n_list, int split_keys,
                                      int max_splits, float* scratch, int* counters, cudaStream_t s) {
-  TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_decode: head_dim %d is not 64, 128 or 256", head_dim);
-  TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
-              "attention_decode: %d query heads over %d kv heads (at most 16 per group)", q_heads, kv_heads);
-  TIE_REQUIRE(page_size >= 8 && (page_size & (page_size - 1)) == 0, "attention_decode: page size %d is not a power of two from 8 up", page_size);
   TIE_REQUIRE(q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0, "attention_decode: q rows must be 16-byte aligned");
-  TIE_REQUIRE(split_keys > 0 && split_keys % kKeysPerTile == 0 && max_splits > 0 && scratch != nullptr && counters != nullptr,
-              "attention_decode: splits must be positive multiples of %d keys", kKeysPerTile);
-  const int box_rows = page_size < kKeysPerTile ? page_size : kKeysPerTile;
-  TIE_REQUIRE((split_keys / kKeysPerTile + 1) * (kKeysPerTile / box_rows) <= kMaxTablePages && max_splits <= 256,
-              "attention_decode: a split of %d keys over pages of %d (or %d splits) exceeds the kernel's tables", split_keys,
-              page_size, max_splits);
-  if (n_list == 0) return kOk;
-  int shift = 0;
-  while ((1 << shift) < page_size) ++shift;
-  CUtensorMap km, vm;
-  const long long rows = static_cast<long long>(pages) * kv_heads * page_size;
-  TIE_REQUIRE(make_map_bf16(&km, k_cache, rows, head_dim, head_dim, 64, box_rows) &&
-                  make_map_bf16(&vm, v_cache, rows, head_dim, head_dim, 64, box_rows),
-              "attention_decode: cuTensorMapEncodeTiled failed");
-  TIE_REQUIRE(status_word() != nullptr, "attention_decode: cannot allocate the status word");
-  DecodeArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), query_start, context_lens, block_tables,
-               seq_list, scratch, counters, status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window,
-               split_keys, max_splits, scale * 1.4426950408889634f};
-  int st = kOk;
-  if (head_dim == 64) st = launch_decode_tma<64>(km, vm, a, n_list, s);
-  else if (head_dim == 128) st = launch_decode_tma<128>(km, vm, a, n_list, s);
-  else st = launch_decode_tma<256>(km, vm, a, n_list, s);
-  if (st != kOk) return st;
-  TIE_RETURN_LAUNCH("attention_decode_tma");
+  DecodeArgs a{};
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.query_start = query_start, a.context_lens = context_lens, a.block_tables = block_tables, a.seq_list = seq_list;
+  a.scratch = scratch, a.counters = counters, a.q_stride = q_stride;
+  a.max_blocks = max_blocks, a.q_heads = q_heads, a.kv_heads = kv_heads, a.page_size = page_size, a.window = window;
+  a.split_keys = split_keys, a.max_splits = max_splits;
+  return decode_tma(a, false, k_cache, v_cache, head_dim, pages, n_list, scale, s);
+}
+
+// The same attention for a step in which every sequence brings one token, straight from the output of the q/k/v
+// product: the kernel sums the product's partial sums (part, or reads the bfloat16 rows of qkv when part is null),
+// norms and rotates the group's query heads itself (what tie_qk_norm_rope_append does, bit for bit), and, with
+// append != 0, does the same for the newest key, stores it and its value in the cache planes and uses them. qw, kw
+// and inv_freq may be null (no norm, no rotation); the rotation covers the whole head. Rows of qkv and of the
+// partial sums: token t of sequence seq_list[i] is row query_start[seq_list[i]].
+TIE_API int tie_attention_decode_prep(const void* qkv, long long qkv_stride, const float* part, long long part_stride,
+                                      int part_splits, long long part_ld, const float* qw, const float* kw, float q_eps,
+                                      float k_eps, const float* inv_freq, const int* positions, int append, void* k_cache,
+                                      void* v_cache, void* out, const int* query_start, const int* context_lens,
+                                      const int* block_tables, int max_blocks, int q_heads, int kv_heads, int head_dim,
+                                      int page_size, int pages, int window, float scale, const int* seq_list, int n_list,
+                                      int split_keys, int max_splits, float* scratch, int* counters, cudaStream_t s) {
+  const int vec = head_dim / 32;
+  const size_t slice = static_cast<size_t>(vec) * 2 > 16 ? 16 : static_cast<size_t>(vec) * 2;
+  const size_t fslice = static_cast<size_t>(vec) * 4 > 16 ? 16 : static_cast<size_t>(vec) * 4;
+  TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_decode: head_dim %d is not 64, 128 or 256", head_dim);
+  TIE_REQUIRE(part != nullptr ? (part_splits >= 1 && reinterpret_cast<uintptr_t>(part) % fslice == 0 && part_stride % vec == 0 && part_ld % vec == 0)
+                              : (qkv != nullptr && reinterpret_cast<uintptr_t>(qkv) % slice == 0 && qkv_stride % vec == 0),
+              "attention_decode: the q/k/v rows (or their partial sums) must be aligned to %d elements", vec);
+  TIE_REQUIRE(positions != nullptr && reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0,
+              "attention_decode: positions and 16-byte aligned cache planes are needed");
+  DecodeArgs a{};
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.query_start = query_start, a.context_lens = context_lens, a.block_tables = block_tables, a.seq_list = seq_list;
+  a.scratch = scratch, a.counters = counters;
+  a.max_blocks = max_blocks, a.q_heads = q_heads, a.kv_heads = kv_heads, a.page_size = page_size, a.window = window;
+  a.split_keys = split_keys, a.max_splits = max_splits;
+  a.qkv = static_cast<const __nv_bfloat16*>(qkv), a.part = part, a.qkv_stride = qkv_stride, a.part_stride = part_stride, a.part_ld = part_ld;
+  a.part_splits = part_splits, a.append = append, a.qw = qw, a.kw = kw, a.inv_freq = inv_freq, a.q_eps = q_eps, a.k_eps = k_eps;
+  a.positions = positions, a.k_plane = static_cast<__nv_bfloat16*>(k_cache), a.v_plane = static_cast<__nv_bfloat16*>(v_cache);
+  return decode_tma(a, true, k_cache, v_cache, head_dim, pages, n_list, scale, s);
 }

@@ -7,6 +7,7 @@
 // embed :51-76, rms_norm :141-159, rope_neox :161-193, silu_mul :195-207, add :209-221,
 // gather_rows :223-233, kv_write :235-259. The fusions are this engine's own.
 #include "common.cuh"
+#include "head_prep.cuh"
 #include "launchers.h"
 
 namespace tie {
@@ -406,9 +407,6 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, long long row_st
 // The same for head sizes 64, 128 and 256 with the whole head rotated (or none of it):
 // a lane holds VEC = head_dim / 32 neighbouring elements (one vector load and store), lanes 0-15 the
 // first half of the head and lanes 16-31 the second, so a rotation pair is one shuffle apart.
-template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof(T) * VEC) HeadSlice {
-  T v[VEC];
-};
 
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, long long row_stride,
@@ -426,14 +424,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = blockIdx.x;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
-  if (inv_freq) {
-    const float pos = static_cast<float>(positions[t]);
-    for (int i = threadIdx.x; i < HALF; i += blockDim.x) {
-      const float angle = pos * inv_freq[i];
-      cs[i] = cosf(angle);
-      cs[HALF + i] = sinf(angle);
-    }
-  }
+  if (inv_freq) rotation_table(cs, static_cast<float>(positions[t]), inv_freq, HALF, threadIdx.x, blockDim.x);
   pdl_wait();
   __syncthreads();
   if (head >= heads_per_token) return;
@@ -472,25 +463,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_vec_kernel(T* __restr
     *reinterpret_cast<Slice*>(dst) = out;
     return;
   }
-  float ss = 0.0f;
-#pragma unroll
-  for (int e = 0; e < VEC; ++e) ss += x[e] * x[e];
-  const float* w = is_q ? qw : kw;
-  if (w) {
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / static_cast<float>(DH) + (is_q ? q_eps : k_eps));
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) x[e] = (x[e] * inv) * w[lane * VEC + e];
-  }
-  if (inv_freq) {
-    const int i0 = (lane & 15) * VEC;
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-      const float c = cs[i0 + e], sn = cs[HALF + i0 + e];
-      x[e] = lane < 16 ? x[e] * c - other * sn : x[e] * c + other * sn;
-    }
-  }
+  prepare_head<VEC>(x, is_q ? qw : kw, is_q ? q_eps : k_eps, inv_freq ? cs : nullptr, lane);
   Slice out;
 #pragma unroll
   for (int e = 0; e < VEC; ++e) Elem<T>::store(out.v + e, x[e]);

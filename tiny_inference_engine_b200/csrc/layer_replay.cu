@@ -63,10 +63,10 @@ const Launcher kLaunchers[] = {
     TIE_LAUNCHER(tie_gemm_simt),            TIE_LAUNCHER(tie_gemm_tc),              TIE_LAUNCHER(tie_gemm_tc2),
     TIE_LAUNCHER(tie_attention_rows),       TIE_LAUNCHER(tie_attention_split),      TIE_LAUNCHER(tie_attention_merge),
     TIE_LAUNCHER(tie_attention_prompt_tc),  TIE_LAUNCHER(tie_attention_decode_tc),  TIE_LAUNCHER(tie_attention_prompt_tma),
-    TIE_LAUNCHER(tie_attention_decode_tma), TIE_LAUNCHER(tie_attention_prompt_umma),
+    TIE_LAUNCHER(tie_attention_decode_tma), TIE_LAUNCHER(tie_attention_prompt_umma), TIE_LAUNCHER(tie_attention_decode_prep),
 };
 constexpr int kNumLaunchers = static_cast<int>(sizeof(kLaunchers) / sizeof(kLaunchers[0]));
-constexpr int kMaxArgs = 32;
+constexpr int kMaxArgs = 40;
 
 }  // namespace
 

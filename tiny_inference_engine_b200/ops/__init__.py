@@ -373,6 +373,55 @@ def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
          max_splits, scratch.data_ptr(), counters.data_ptr(), _stream())
 
 
+def attention_decode_prep_takes(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, page_size: int, inv_freq) -> bool:
+    """Whether the decode attention that prepares its own heads takes these operands: what the TMA-fed kernel takes,
+    and a rotation (if any) over the whole head."""
+    return (attention_decode_tma_takes(qkv, q_heads, kv_heads, head_dim, page_size)
+            and (inv_freq is None or 2 * inv_freq.numel() == head_dim))
+
+
+def attention_decode_prep(qkv, q_weight, k_weight, q_eps: float, k_eps: float, inv_freq, positions, k_cache, v_cache, out,
+                          query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, scale: float, seq_list,
+                          n_list: int, split_keys: int, max_splits: int, scratch, counters, window: int = 0,
+                          append: bool = True, partial: SplitSum | None = None) -> None:
+    """`attention_decode_tma` for a step in which every sequence brings one token, straight from the q/k/v product's
+    output: qkv [T, (q_heads + 2 kv_heads) * head_dim] (or q only, with `append` False), or the product's partial sums.
+    The kernel does what `qk_norm_rope_append` does to the group's query heads and, with `append`, to the newest
+    key and value, which it stores in the cache planes and uses; qkv itself is left as it is."""
+    _dev(qkv, q_weight, k_weight, inv_freq, positions, k_cache, v_cache, out, query_start, context_lens, block_tables,
+         seq_list, scratch, counters)
+    T = qkv.shape[0]
+    width = (q_heads + (2 * kv_heads if append else 0)) * head_dim
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= width and qkv.dtype == torch.bfloat16,
+          "attention_decode_prep: qkv must be bfloat16 rows of q (and k, v)")
+    _need(out.shape == (T, q_heads * head_dim) and out.is_contiguous() and out.dtype == torch.bfloat16,
+          "attention_decode_prep: out must be contiguous bfloat16 [T, q_heads * head_dim]")
+    _check_planes(k_cache, v_cache, kv_heads, head_dim)
+    _need(k_cache.dtype == torch.bfloat16, "attention_decode_prep: the cache must be bfloat16")
+    _need(positions.dtype == torch.int32 and positions.numel() == T, "attention_decode_prep: positions must be int32 [T]")
+    for w in (q_weight, k_weight):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == head_dim),
+              "attention_decode_prep: norm weights must be float32 [head_dim]")
+    _need(inv_freq is None or (inv_freq.dtype == torch.float32 and 2 * inv_freq.numel() == head_dim),
+          "attention_decode_prep: the rotation must cover the whole head")
+    _need(query_start.dtype == torch.int32 and context_lens.dtype == torch.int32 and block_tables.dtype == torch.int32
+          and block_tables.dim() == 2 and block_tables.stride(1) == 1, "attention: index tensors must be int32")
+    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
+    _need(scratch.dtype == torch.float32 and
+          scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, head_dim, max_splits),
+          "attention: scratch too small")
+    _need(counters.dtype == torch.int32 and counters.numel() >= n_list * kv_heads, "attention: counters too small")
+    if partial is not None:
+        _need(partial.M == T and partial.N == width, "attention_decode_prep: partial sums do not match the rows")
+    call("tie_attention_decode_prep", qkv.data_ptr(), qkv.stride(0), partial.partial.data_ptr() if partial else 0,
+         partial.stride if partial else 0, partial.splits if partial else 0, partial.N if partial else 0,
+         _ptr(q_weight), _ptr(k_weight), float(q_eps), float(k_eps), _ptr(inv_freq), positions.data_ptr(),
+         1 if append else 0, k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), query_start.data_ptr(),
+         context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads, head_dim,
+         k_cache.shape[2], k_cache.shape[0], int(window), float(scale), seq_list.data_ptr(), n_list, split_keys,
+         max_splits, scratch.data_ptr(), counters.data_ptr(), _stream())
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None, top_k=None,
            top_p=None, one_cta: bool = False) -> None:
     """out[r] = first maximum of row r (inv_temperature None or 0), or a draw from softmax(logits * inv_temperature)

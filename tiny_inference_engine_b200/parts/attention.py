@@ -108,8 +108,14 @@ class GQAttention(Mixer):
                                   ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K))
             got = (self.gemm_qkv if cache.writes else self.gemm_q)(
                 h, qkv, lambda n: ctx.ws.flat("attn.qkv.partial", n, torch.float32, self._capacity[0]))
+            partial = got if isinstance(got, ops.SplitSum) else None
+            if ctx.multi_rows == 0 and ops.attention_decode_prep_takes(qkv, Hq, Hkv, Dh, cache.k.shape[2], table):
+                # every sequence brings one token: the attention kernel prepares the heads itself
+                attn = ctx.ws.rows("attn.out", T, self.q_dim, self.dtype)
+                self.attend_single(None, attn, ctx, g, cache, prep=(qkv, qw, kw, q_eps, k_eps, table, partial))
+                return self.output(attn, ctx)
             ops.qk_norm_rope_append(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, g.slots, cache.k, cache.v, Hq, Hkv,
-                                    Dh, write_kv=cache.writes, partial=got if isinstance(got, ops.SplitSum) else None)
+                                    Dh, write_kv=cache.writes, partial=partial)
             q = qkv[:, :self.q_dim]
         else:
             # Any other norm or position encoding: separate products and the parts' own kernels.
@@ -131,7 +137,10 @@ class GQAttention(Mixer):
                 ops.kv_append(k, v, g.slots, cache.k, cache.v)
         attn = ctx.ws.rows("attn.out", T, self.q_dim, self.dtype)
         self.attend(q, attn, ctx, g, cache)
-        out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
+        return self.output(attn, ctx)
+
+    def output(self, attn, ctx):
+        out = ctx.ws.rows("mixer.out", attn.shape[0], self.hidden, self.dtype)
         if self._capacity is None:
             self._capacity = (ops.partial_capacity(ctx.ws.max_rows, self.gemm_qkv.N, self.gemm_qkv.K, split_many=False),
                               ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K))
@@ -156,34 +165,48 @@ class GQAttention(Mixer):
                 ops.attention_rows(q[:n], cache.k, cache.v, attn[:n], ctx.seq_of_row[:n], ctx.query_start,
                                    ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale, self.window)
         if ctx.single_count > 0:
-            longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
-            page = cache.k.shape[2]
-            if tc and ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, page):
-                lens = ctx.single_contexts if self.window <= 0 else None
-                key = ("decode_splits", longest, ctx.single_count, Hkv, page, lens is None)
-                memo = getattr(ctx, "memo", None)
-                splits = memo.get(key) if memo is not None else None
-                if splits is None:
-                    splits = decode_splits(longest, ctx.single_count, Hkv, page, lens)
-                    if memo is not None:
-                        memo[key] = splits
-                split_keys, max_splits = splits
-                scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
-                                      torch.float32)
-                counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * Hkv, torch.int32)
-                ops.attention_decode_tma(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq,
-                                         Hkv, Dh, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits,
-                                         scratch, counters, self.window)
-                return
-            split_keys = SPLIT_KEYS
-            while math.ceil(longest / split_keys) > MAX_SPLITS:
-                split_keys *= 2
-            max_splits = max(1, math.ceil(longest / split_keys))
+            self.attend_single(q, attn, ctx, g, cache, tc)
+
+    def attend_single(self, q, attn, ctx, g, cache, tc=True, prep=None):
+        """The sequences that bring one token. With `prep` (the q/k/v product's output, the head norms' weights and
+        eps, the rotation's frequencies, the product's partial sums or None) the TMA-fed kernel norms and rotates the
+        heads and appends the newest key and value itself; q is not used then."""
+        Hq, Hkv, Dh = self.heads, self.kv_heads, self.head_dim
+        longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
+        page = cache.k.shape[2]
+        if prep is not None or (tc and ops.attention_decode_tma_takes(q, Hq, Hkv, Dh, page)):
+            lens = ctx.single_contexts if self.window <= 0 else None
+            key = ("decode_splits", longest, ctx.single_count, Hkv, page, lens is None)
+            memo = getattr(ctx, "memo", None)
+            splits = memo.get(key) if memo is not None else None
+            if splits is None:
+                splits = decode_splits(longest, ctx.single_count, Hkv, page, lens)
+                if memo is not None:
+                    memo[key] = splits
+            split_keys, max_splits = splits
             scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
                                   torch.float32)
-            fn = ops.attention_decode_tc if tc else ops.attention_split
-            fn(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale,
-               ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, self.window)
+            counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * Hkv, torch.int32)
+            if prep is not None:
+                qkv, qw, kw, q_eps, k_eps, table, partial = prep
+                ops.attention_decode_prep(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, cache.k, cache.v, attn,
+                                          ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale,
+                                          ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, counters,
+                                          self.window, append=cache.writes, partial=partial)
+                return
+            ops.attention_decode_tma(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq,
+                                     Hkv, Dh, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits,
+                                     scratch, counters, self.window)
+            return
+        split_keys = SPLIT_KEYS
+        while math.ceil(longest / split_keys) > MAX_SPLITS:
+            split_keys *= 2
+        max_splits = max(1, math.ceil(longest / split_keys))
+        scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
+                              torch.float32)
+        fn = ops.attention_decode_tc if tc else ops.attention_split
+        fn(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale,
+           ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, self.window)
 
 
 def decode_splits(longest: int, sequences: int, kv_heads: int, page_size: int, contexts=None) -> tuple[int, int]:
