@@ -137,25 +137,25 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   for (int j = 0; j < DH / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
 
   if (warp == 4) {
-    if (lane == 0) {
-      for (int i = 0; i < n_tiles; ++i) {
-        const int s = i % STAGES;
-        if (!mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, abort_flag, a.status, 11)) break;
-        // the tile with the newest key: written by the kernel ahead, unless this kernel appends it itself (then the
-        // copy in shared memory is patched once it has landed)
-        if (hi == pos && i == n_tiles - 1 && !(PREP && a.append)) pdl_wait();
-        mbar_expect_tx(full + s, STAGE_BYTES);
-        uint8_t* kdst = smem + s * STAGE_BYTES;
-        for (int b = 0; b < boxes_per_tile; ++b) {
-          const int key = (kt_first + i) * kKeysPerTile + b * box_rows;
-          const int row = (pages[i * boxes_per_tile + b] * a.kv_heads + kvh) * a.page_size + (key & (a.page_size - 1));
-#pragma unroll
-          for (int h = 0; h < HALVES; ++h) {
-            tma_load_2d(kdst + h * (64 * 128) + b * box_rows * 128, &k_map, h * 64, row, full + s);
-            tma_load_2d(kdst + PLANE_BYTES + h * (64 * 128) + b * box_rows * 128, &v_map, h * 64, row, full + s);
-          }
-        }
+    // The whole warp walks the tiles: lane 0 arms the stage's barrier, then the lanes issue the tile's boxes side by
+    // side (one lane after the other would spend most of a tile's time computing addresses).
+    const int ops_per_tile = boxes_per_tile * HALVES * 2;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % STAGES;
+      if (!__all_sync(0xffffffffu, mbar_wait(empty + s, ((i / STAGES) & 1) ^ 1, abort_flag, a.status, 11) ? 1 : 0)) break;
+      // the tile with the newest key: written by the kernel ahead, unless this kernel appends it itself (then the
+      // copy in shared memory is patched once it has landed)
+      if (hi == pos && i == n_tiles - 1 && !(PREP && a.append)) pdl_wait();
+      if (lane == 0) mbar_expect_tx(full + s, STAGE_BYTES);
+      __syncwarp();
+      uint8_t* kdst = smem + s * STAGE_BYTES;
+      for (int op = lane; op < ops_per_tile; op += 32) {
+        const int b = op / (2 * HALVES), h = (op % (2 * HALVES)) >> 1, is_v = op & 1;
+        const int key = (kt_first + i) * kKeysPerTile + b * box_rows;
+        const int row = (pages[i * boxes_per_tile + b] * a.kv_heads + kvh) * a.page_size + (key & (a.page_size - 1));
+        tma_load_2d(kdst + is_v * PLANE_BYTES + h * (64 * 128) + b * box_rows * 128, is_v ? &v_map : &k_map, h * 64, row, full + s);
       }
+      __syncwarp();
     }
   } else {
     // Q: the G heads of the group, rows G..15 zero
