@@ -35,12 +35,14 @@ def ops():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_embed(ops, dtype):
+    """Widths that let a thread move 16 bytes of the table at a time, and one that does not."""
     rng = np.random.default_rng(0)
-    table = as_stored(rng.standard_normal((311, 72)), dtype)
-    ids = rng.integers(0, 311, 37)
-    out = torch.empty(37, 72, device="cuda")
-    ops.embed(dev(table, DT[dtype]), dev(ids, torch.int32), out)
-    assert np.array_equal(host(out), plain.embed(table, ids).astype(np.float32))
+    for width in (72, 75, 4096):
+        table = as_stored(rng.standard_normal((311, width)), dtype)
+        ids = rng.integers(0, 311, 37)
+        out = torch.full((37, width), float("nan"), device="cuda")
+        ops.embed(dev(table, DT[dtype]), dev(ids, torch.int32), out)
+        assert np.array_equal(host(out), plain.embed(table, ids).astype(np.float32))
 
 
 def test_scatter_ids(ops):

@@ -27,6 +27,19 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   // anyway); never read outside the table
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
   float* out = x + static_cast<size_t>(t) * dim;
+  // 16 bytes of the table a thread and step where rows and addresses allow it (a 64-column block never ends inside one)
+  constexpr int V = Vec16<T>::N;
+  if (dim % V == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0) {
+    for (int i = threadIdx.x * V; i < dim; i += blockDim.x * V) {
+      Vec16<T> v;
+      v.load(k_block_rows > 0 ? table + (static_cast<size_t>(i >> 6) * k_block_rows + id) * 64 + (i & 63)
+                              : table + static_cast<size_t>(id) * dim + i);
+#pragma unroll
+      for (int e = 0; e < V; e += 4)
+        *reinterpret_cast<float4*>(out + i + e) = make_float4(v.v[e], v.v[e + 1], v.v[e + 2], v.v[e + 3]);
+    }
+    return;
+  }
   if (k_block_rows > 0) {
     for (int i = threadIdx.x; i < dim; i += blockDim.x)
       out[i] = ld(table + (static_cast<size_t>(i >> 6) * k_block_rows + id) * 64 + (i & 63));
