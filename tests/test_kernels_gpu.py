@@ -674,13 +674,18 @@ def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window)
     if ops.attention_decode_tma_takes(qd, Hq, Hkv, Dh, page):
         from tiny_inference_engine_b200.ops import gemm_select
         counters = torch.zeros(3 * Hkv, dtype=torch.int32, device="cuda")
-        for split_keys, max_splits in ((64, 12), (512, 2), (1024, 1), (64, 12)):
+        # and with the splits of a sequence as one cluster that merges through shared memory (2, 4, 8, 16 splits; one
+        # of the sequences has a single key, so most of its cluster has nothing to add)
+        scratch = torch.empty(ops.attention_split_scratch_floats(3, Hq, Dh, 16), device="cuda")
+        for split_keys, max_splits, cluster in ((64, 12, False), (512, 2, False), (1024, 1, False), (64, 12, False), (64, 16, True),
+                                                (512, 2, True), (256, 4, True), (128, 8, True), (64, 16, True)):
             out[n_multi:] = float("nan")
             ops.attention_decode_tma(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, Hq, Hkv, Dh, scale,
-                                     dev(np.array([3, 4, 5]), torch.int32), 3, split_keys, max_splits, scratch, counters, window)
+                                     dev(np.array([3, 4, 5]), torch.int32), 3, split_keys, max_splits, scratch, counters, window,
+                                     cluster=cluster)
             torch.cuda.synchronize()
             gemm_select.check_status()
-            assert rel_err(host(out), want) < TOL["bfloat16"], f"split_keys={split_keys}"
+            assert rel_err(host(out), want) < TOL["bfloat16"], f"split_keys={split_keys} cluster={cluster}"
             assert not counters.any()
 
 
@@ -690,7 +695,8 @@ def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window)
 def test_decode_attention_that_prepares_its_own_heads(ops, Hq, Hkv, Dh, page, window, source):
     """A step of single tokens, straight from the q/k/v product's output: the kernel norms and rotates its query
     heads, makes the newest key and value, stores them and uses them. Equal, bit for bit, to the q/k norm + RoPE +
-    append kernel followed by the TMA-fed decode attention (outputs and both cache planes), and right against the
+    append kernel followed by the TMA-fed decode attention (outputs and both cache planes; with eight splits the
+    kernel under test merges them as a cluster through shared memory, the other through scratch memory), and right against the
     plain attention over keys that include the newest. Contexts that end at the first and the last key of a tile,
     of a page and of a split, one of a single key, one empty (a sequence that pads a captured batch); the newest
     key's slot holds junk before the step, and so do the slots behind it."""
@@ -729,7 +735,7 @@ def test_decode_attention_that_prepares_its_own_heads(ops, Hq, Hkv, Dh, page, wi
                 assert ops.attention_decode_prep_takes(qkv, Hq, Hkv, Dh, page, dev(inv))
                 ops.attention_decode_prep(qkv, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), kcd, vcd, out, *meta,
                                           Hq, Hkv, Dh, scale, seqs, S, split_keys, max_splits, scratch, counters, window,
-                                          append=True, partial=partial)
+                                          append=True, partial=partial, cluster=max_splits in ops.CLUSTER_SPLITS)
             else:
                 work = qkv.clone()
                 ops.qk_norm_rope_append(work, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), dev(slots, torch.int32),

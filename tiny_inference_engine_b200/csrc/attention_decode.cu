@@ -28,6 +28,7 @@
 namespace tie {
 
 constexpr int kDecThreads = 160;
+constexpr int kNoCluster = -7;         // launch_decode_tma: the GPU does not hold the launch's clusters at once
 constexpr int kMaxTablePages = 512;    // pages of one split that the CTA keeps in shared memory
 
 struct DecodeArgs {
@@ -57,7 +58,21 @@ struct DecodeArgs {
   __nv_bfloat16 *k_plane, *v_plane;
 };
 
-template <int DH, int STAGES, bool PREP>
+// A float into the shared memory of another CTA of the cluster (`mine`: the address in this CTA's own).
+__device__ __forceinline__ void send_float(const float* mine, uint32_t rank, float v) {
+  uint32_t addr;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(mine)), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// CLUSTER: the splits of a (sequence, kv head) are the CTAs of one thread-block cluster (grid z = cluster size =
+// a.max_splits, 2 to 16): each sends its results into the shared memory of the CTAs that merge (one row of the
+// group each), all meet at one cluster barrier, and the rows are merged from local shared memory, in split order; no
+// scratch, no counter, no fence. A CTA whose split holds no key walks the same path with nothing to add.
+template <int DH, int STAGES, bool PREP, bool CLUSTER>
 __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                       const __grid_constant__ CUtensorMap v_map, DecodeArgs a) {
   // Keys and values of earlier tokens, the tables and the lengths do not depend on the kernels just ahead in
@@ -79,6 +94,9 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   int* flags = pages + kMaxTablePages;                                 // [0] abort, [1] last-arrival flag
   [[maybe_unused]] float* cs = reinterpret_cast<float*>(flags + 4);    // PREP: the token's cos and sin
   [[maybe_unused]] __nv_bfloat16* newest = reinterpret_cast<__nv_bfloat16*>(cs + DH);   // PREP: the newest key, then its value
+  // CLUSTER: what the splits send for the rows this CTA merges, [16][RS] at most, and a row's weights. Memory of its own:
+  // a split that is through early sends while this CTA's ring is still in use.
+  [[maybe_unused]] float* inbox = reinterpret_cast<float*>(flags + 4) + (PREP ? 2 * DH : 0);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int li = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -96,15 +114,16 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   }
   const int lo0 = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   const int lo = lo0 + split * a.split_keys;
-  if (lo > pos) return;
+  const int n_splits = (pos - lo0) / a.split_keys + 1;     // the same in every CTA of the sequence
+  const bool no_keys = lo > pos;
+  if (no_keys && (!CLUSTER || n_splits == 1)) return;      // (with one split nobody meets at the cluster barrier)
   const int hi = min(pos, lo + a.split_keys - 1);
-  const int n_splits = (pos - lo0) / a.split_keys + 1;
   if (n_splits > a.max_splits) {   // the caller sized max_splits for shorter contexts: say so, write nothing
     if (threadIdx.x == 0 && split == 0) *reinterpret_cast<volatile int*>(a.status) = 13;
     return;
   }
   const int kt_first = lo / kKeysPerTile, kt_last = hi / kKeysPerTile;
-  const int n_tiles = kt_last - kt_first + 1;
+  const int n_tiles = no_keys ? 0 : kt_last - kt_first + 1;
   const int box_rows = min(a.page_size, kKeysPerTile);
   const int boxes_per_tile = kKeysPerTile / box_rows;
 
@@ -162,7 +181,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
     constexpr int CPR = DH / 8;
     constexpr int VEC = DH / 32;
     using Slice = HeadSlice<__nv_bfloat16, VEC>;
-    [[maybe_unused]] const bool appends = PREP && a.append != 0 && hi == pos;   // this split ends with the newest key
+    [[maybe_unused]] const bool appends = PREP && a.append != 0 && hi == pos && !no_keys;   // this split ends with the newest key
     if constexpr (PREP) {
       // the rotation depends on the step's own inputs only: made while the kernel ahead still runs
       if (a.inv_freq) rotation_table(cs, static_cast<float>(a.positions[t]), a.inv_freq, DH / 2, threadIdx.x, 128);
@@ -310,6 +329,52 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
     fac[5 * G + r] = ls;
   }
   __syncthreads();
+  if constexpr (CLUSTER) {
+    if (n_splits > 1) {
+      // Row r of the group is merged by the CTA r % C of the cluster (C = a.max_splits CTAs): every CTA sends its sums,
+      // maximum and row sum of that row into the owner's shared memory, all meet at one cluster barrier, and the
+      // owners merge what they were sent, in split order. Nobody reads another CTA's memory after the barrier, so
+      // every CTA may leave when it is through.
+      const int C = a.max_splits;
+      float* wgt = inbox + 16 * RS;              // [C] weights of the row being merged, then 1 / its sum
+      for (int id = threadIdx.x; id < G * RS; id += kDecThreads) {
+        const int r = id / RS, e = id % RS;
+        float v;
+        if (e < DH) {
+          v = 0.0f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) v += part[(w * 16 + r) * RS + e] * fac[r * 4 + w];
+        } else {
+          v = fac[(e == DH ? 4 : 5) * G + r];
+        }
+        send_float(inbox + ((r / C) * C + split) * RS + e, static_cast<uint32_t>(r % C), v);
+      }
+      cluster_barrier();
+      for (int r = split; r < G; r += C) {       // (uniform over the CTA)
+        const float* mine = inbox + (r / C) * C * RS;
+        if (threadIdx.x == 0) {
+          float mx = -INFINITY;
+          for (int i = 0; i < n_splits; ++i) mx = fmaxf(mx, mine[i * RS + DH]);
+          float ls = 0.0f;
+          for (int i = 0; i < n_splits; ++i) {
+            const float w = exp2f(mine[i * RS + DH] - mx);
+            wgt[i] = w;
+            ls += mine[i * RS + DH + 1] * w;
+          }
+          wgt[C] = ls > 0.0f ? 1.0f / ls : 0.0f;
+        }
+        __syncthreads();
+        for (int d = threadIdx.x; d < DH; d += kDecThreads) {
+          float o = 0.0f;
+#pragma unroll 4
+          for (int i = 0; i < n_splits; ++i) o = fmaf(mine[i * RS + d], wgt[i], o);
+          a.out[(static_cast<long long>(t) * a.q_heads + kvh * G + r) * DH + d] = __float2bfloat16_rn(o * wgt[C]);
+        }
+        __syncthreads();
+      }
+      return;
+    }
+  }
   float* split_out = a.scratch + ((static_cast<long long>(li) * a.q_heads + kvh * G) * a.max_splits + split) * RS;
   for (int id = threadIdx.x; id < G * DH; id += kDecThreads) {
     const int r = id / DH, d = id % DH;
@@ -379,29 +444,71 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   if (threadIdx.x == 0) a.counters[li * a.kv_heads + kvh] = 0;   // ready for the next launch
 }
 
-template <int DH, bool PREP>
+template <int DH, bool PREP, bool CLUSTER>
 static int launch_decode_tma(const CUtensorMap& km, const CUtensorMap& vm, const DecodeArgs& a, int n_list, cudaStream_t s) {
   constexpr int STAGES = DH >= 256 ? 2 : (DH == 128 ? 3 : 4);
   constexpr size_t ring = static_cast<size_t>(STAGES) * 2 * (DH / 64) * 64 * 128;
-  constexpr size_t combine = (4 * 16 * (DH + 2) + 6 * 16) * sizeof(float);          // the four warps' results and factors
+  // the four warps' results and factors
+  constexpr size_t combine = (4 * 16 * (DH + 2) + 6 * 16 + 0) * sizeof(float);
   constexpr size_t weights = (3 * 16 * 256 + 16) * sizeof(float);                    // the last CTA's merge: 16 rows, 256 splits at most
   constexpr size_t merge = combine > weights ? combine : weights;
   constexpr size_t prep = PREP ? DH * sizeof(float) + 2 * DH * 2 + 16 : 0;           // the rotation, the newest key and value
-  constexpr size_t smem = (ring > merge ? ring : merge) + 16 * DH * 2 + 2 * STAGES * 8 + (kMaxTablePages + 4) * 4 + prep + 1024;
+  constexpr size_t inbox = CLUSTER ? (16 * (DH + 2) + 32) * sizeof(float) : 0;        // what the splits send to the CTA that merges a row
+  constexpr size_t smem = (ring > merge ? ring : merge) + 16 * DH * 2 + 2 * STAGES * 8 + (kMaxTablePages + 4) * 4 + prep + inbox + 1024;
   static bool configured = false;
+  auto kernel = attn_decode_tma_kernel<DH, STAGES, PREP, CLUSTER>;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_decode_tma_kernel<DH, STAGES, PREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-      set_error("attention_decode: cannot reserve %zu bytes of shared memory", smem);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess ||
+        (CLUSTER && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)) {
+      set_error("attention_decode: cannot reserve %zu bytes of shared memory (or clusters of 16)", smem);
       return kCudaError;
     }
     configured = true;
   }
-  TIE_LAUNCH((attn_decode_tma_kernel<DH, STAGES, PREP>), dim3(n_list, a.kv_heads, a.max_splits), kDecThreads, smem, s, km, vm, a);
+  if constexpr (CLUSTER) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_list, a.kv_heads, a.max_splits);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 1;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = a.max_splits;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    // How many clusters of this size the GPU holds at once (asked once a size): with more than that in the launch,
+    // splits without keys would keep others waiting for a place, and the launch goes through scratch memory instead.
+    static int holds[17] = {};
+    if (holds[a.max_splits] == 0) {
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+      }
+      holds[a.max_splits] = n > 0 ? n : -1;
+    }
+    if (holds[a.max_splits] < n_list * a.kv_heads) return kNoCluster;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, km, vm, a);
+  } else {
+    TIE_LAUNCH(kernel, dim3(n_list, a.kv_heads, a.max_splits), kDecThreads, smem, s, km, vm, a);
+  }
   return kOk;
 }
 
+template <bool PREP, bool CLUSTER>
+static int launch_decode_tma_of(int head_dim, const CUtensorMap& km, const CUtensorMap& vm, const DecodeArgs& a, int n_list, cudaStream_t s) {
+  if (head_dim == 64) return launch_decode_tma<64, PREP, CLUSTER>(km, vm, a, n_list, s);
+  if (head_dim == 128) return launch_decode_tma<128, PREP, CLUSTER>(km, vm, a, n_list, s);
+  return launch_decode_tma<256, PREP, CLUSTER>(km, vm, a, n_list, s);
+}
+
 // What both entry points ask of their arguments, and the launch.
-static int decode_tma(DecodeArgs a, bool prep, const void* k_cache, const void* v_cache, int head_dim, int pages, int n_list,
+static int decode_tma(DecodeArgs a, bool prep, bool cluster, const void* k_cache, const void* v_cache, int head_dim, int pages, int n_list,
                       float scale, cudaStream_t s) {
   const int q_heads = a.q_heads, kv_heads = a.kv_heads, page_size = a.page_size, split_keys = a.split_keys, max_splits = a.max_splits;
   TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_decode: head_dim %d is not 64, 128 or 256", head_dim);
@@ -426,16 +533,17 @@ static int decode_tma(DecodeArgs a, bool prep, const void* k_cache, const void* 
   a.status = status_word();
   a.page_shift = shift;
   a.scale_log2 = scale * 1.4426950408889634f;
-  int st = kOk;
-  if (prep) {
-    if (head_dim == 64) st = launch_decode_tma<64, true>(km, vm, a, n_list, s);
-    else if (head_dim == 128) st = launch_decode_tma<128, true>(km, vm, a, n_list, s);
-    else st = launch_decode_tma<256, true>(km, vm, a, n_list, s);
-  } else {
-    if (head_dim == 64) st = launch_decode_tma<64, false>(km, vm, a, n_list, s);
-    else if (head_dim == 128) st = launch_decode_tma<128, false>(km, vm, a, n_list, s);
-    else st = launch_decode_tma<256, false>(km, vm, a, n_list, s);
-  }
+  // cluster: the splits of a sequence and kv head as one thread-block cluster (2, 4, 8 or 16 CTAs), which merges them
+  // through shared memory. The caller asks for it where every CTA of the launch is resident at once (a split without
+  // keys holds its place until its cluster is through). Else, or with TIE_NO_CLUSTER_ATTENTION=1: through scratch
+  // memory, merged by the CTA that finishes last.
+  static const bool clusters = getenv("TIE_NO_CLUSTER_ATTENTION") == nullptr || getenv("TIE_NO_CLUSTER_ATTENTION")[0] != '1';
+  TIE_REQUIRE(!cluster || max_splits == 2 || max_splits == 4 || max_splits == 8 || max_splits == 16,
+              "attention_decode: a cluster of %d splits (2, 4, 8 or 16)", max_splits);
+  cluster = cluster && clusters;
+  int st = kNoCluster;
+  if (cluster) st = prep ? launch_decode_tma_of<true, true>(head_dim, km, vm, a, n_list, s) : launch_decode_tma_of<false, true>(head_dim, km, vm, a, n_list, s);
+  if (st == kNoCluster) st = prep ? launch_decode_tma_of<true, false>(head_dim, km, vm, a, n_list, s) : launch_decode_tma_of<false, false>(head_dim, km, vm, a, n_list, s);
   if (st != kOk) return st;
   TIE_RETURN_LAUNCH("attention_decode_tma");
 }
@@ -450,12 +558,14 @@ TIE_API int tie_attention_decode_limit(int which) { return which == 0 ? kMaxTabl
 
 // The sequences of seq_list bring one token each. scratch holds n_list * q_heads * max_splits *
 // (head_dim + 2) floats; counters holds n_list * kv_heads ints that are zero before the first
-// launch (the kernel leaves them zero). pages is the number of pages of the cache planes.
+// launch (the kernel leaves them zero). pages is the number of pages of the cache planes. cluster != 0: the splits of
+// a sequence and kv head run as one thread-block cluster and merge through shared memory (max_splits 2, 4, 8 or 16;
+// scratch and counters are not touched); worth it where all n_list * kv_heads * max_splits CTAs are resident at once.
 TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
                                      const int* query_start, const int* context_lens, const int* block_tables,
                                      int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
                                      int window, float scale, const int* seq_list, int n_list, int split_keys,
-                                     int max_splits, float* scratch, int* counters, cudaStream_t s) {
+                                     int max_splits, float* scratch, int* counters, int cluster, cudaStream_t s) {
   TIE_REQUIRE(q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0, "attention_decode: q rows must be 16-byte aligned");
   DecodeArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q);
@@ -464,7 +574,7 @@ TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const vo
   a.scratch = scratch, a.counters = counters, a.q_stride = q_stride;
   a.max_blocks = max_blocks, a.q_heads = q_heads, a.kv_heads = kv_heads, a.page_size = page_size, a.window = window;
   a.split_keys = split_keys, a.max_splits = max_splits;
-  return decode_tma(a, false, k_cache, v_cache, head_dim, pages, n_list, scale, s);
+  return decode_tma(a, false, cluster != 0, k_cache, v_cache, head_dim, pages, n_list, scale, s);
 }
 
 // The same attention for a step in which every sequence brings one token, straight from the output of the q/k/v
@@ -479,7 +589,8 @@ TIE_API int tie_attention_decode_prep(const void* qkv, long long qkv_stride, con
                                       void* v_cache, void* out, const int* query_start, const int* context_lens,
                                       const int* block_tables, int max_blocks, int q_heads, int kv_heads, int head_dim,
                                       int page_size, int pages, int window, float scale, const int* seq_list, int n_list,
-                                      int split_keys, int max_splits, float* scratch, int* counters, cudaStream_t s) {
+                                      int split_keys, int max_splits, float* scratch, int* counters, int cluster,
+                                      cudaStream_t s) {
   const int vec = head_dim / 32;
   const size_t slice = static_cast<size_t>(vec) * 2 > 16 ? 16 : static_cast<size_t>(vec) * 2;
   const size_t fslice = static_cast<size_t>(vec) * 4 > 16 ? 16 : static_cast<size_t>(vec) * 4;
@@ -498,5 +609,5 @@ TIE_API int tie_attention_decode_prep(const void* qkv, long long qkv_stride, con
   a.qkv = static_cast<const __nv_bfloat16*>(qkv), a.part = part, a.qkv_stride = qkv_stride, a.part_stride = part_stride, a.part_ld = part_ld;
   a.part_splits = part_splits, a.append = append, a.qw = qw, a.kw = kw, a.inv_freq = inv_freq, a.q_eps = q_eps, a.k_eps = k_eps;
   a.positions = positions, a.k_plane = static_cast<__nv_bfloat16*>(k_cache), a.v_plane = static_cast<__nv_bfloat16*>(v_cache);
-  return decode_tma(a, true, k_cache, v_cache, head_dim, pages, n_list, scale, s);
+  return decode_tma(a, true, cluster != 0, k_cache, v_cache, head_dim, pages, n_list, scale, s);
 }

@@ -355,11 +355,16 @@ def attention_prompt_umma(q, k_cache, v_cache, out, query_start, context_lens, b
          max_queries, q_heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _stream())
 
 
+CLUSTER_SPLITS = (2, 4, 8, 16)      # how many splits the decode attention merges as one thread-block cluster
+
+
 def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim,
                          scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, counters,
-                         window: int = 0) -> None:
+                         window: int = 0, cluster: bool = False) -> None:
     """Attention of sequences that bring one token each, keys and values fed by TMA, splits merged by
-    the last CTA to finish. `counters` (int32 [>= n_list * kv_heads]) must be zero; it is left zero."""
+    the last CTA to finish. `counters` (int32 [>= n_list * kv_heads]) must be zero; it is left zero.
+    `cluster` (with max_splits in CLUSTER_SPLITS): the splits of a sequence and kv head run as one thread-block
+    cluster and merge through shared memory, which is faster where all the launch's CTAs are resident at once."""
     _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch, counters)
     _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
     _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
@@ -370,7 +375,7 @@ def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
     call("tie_attention_decode_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
          query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads,
          head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), seq_list.data_ptr(), n_list, split_keys,
-         max_splits, scratch.data_ptr(), counters.data_ptr(), _stream())
+         max_splits, scratch.data_ptr(), counters.data_ptr(), 1 if cluster else 0, _stream())
 
 
 def attention_decode_prep_takes(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, page_size: int, inv_freq) -> bool:
@@ -383,7 +388,7 @@ def attention_decode_prep_takes(qkv: torch.Tensor, q_heads: int, kv_heads: int, 
 def attention_decode_prep(qkv, q_weight, k_weight, q_eps: float, k_eps: float, inv_freq, positions, k_cache, v_cache, out,
                           query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, scale: float, seq_list,
                           n_list: int, split_keys: int, max_splits: int, scratch, counters, window: int = 0,
-                          append: bool = True, partial: SplitSum | None = None) -> None:
+                          append: bool = True, partial: SplitSum | None = None, cluster: bool = False) -> None:
     """`attention_decode_tma` for a step in which every sequence brings one token, straight from the q/k/v product's
     output: qkv [T, (q_heads + 2 kv_heads) * head_dim] (or q only, with `append` False), or the product's partial sums.
     The kernel does what `qk_norm_rope_append` does to the group's query heads and, with `append`, to the newest
@@ -419,7 +424,7 @@ def attention_decode_prep(qkv, q_weight, k_weight, q_eps: float, k_eps: float, i
          1 if append else 0, k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), query_start.data_ptr(),
          context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads, head_dim,
          k_cache.shape[2], k_cache.shape[0], int(window), float(scale), seq_list.data_ptr(), n_list, split_keys,
-         max_splits, scratch.data_ptr(), counters.data_ptr(), _stream())
+         max_splits, scratch.data_ptr(), counters.data_ptr(), 1 if cluster else 0, _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, inv_temperature=None, seeds=None, counters=None, top_k=None,

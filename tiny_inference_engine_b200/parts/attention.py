@@ -187,16 +187,19 @@ class GQAttention(Mixer):
             scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, Hq, Dh, MAX_SPLITS),
                                   torch.float32)
             counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * Hkv, torch.int32)
+            # the splits of a sequence as one cluster, merged through shared memory: where every CTA of the launch is
+            # resident at once (a split without keys keeps its place until its cluster is through)
+            cluster = max_splits in ops.CLUSTER_SPLITS and ctx.single_count * Hkv * max_splits <= 2 * NUM_SMS
             if prep is not None:
                 qkv, qw, kw, q_eps, k_eps, table, partial = prep
                 ops.attention_decode_prep(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, cache.k, cache.v, attn,
                                           ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale,
                                           ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, counters,
-                                          self.window, append=cache.writes, partial=partial)
+                                          self.window, append=cache.writes, partial=partial, cluster=cluster)
                 return
             ops.attention_decode_tma(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq,
                                      Hkv, Dh, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits,
-                                     scratch, counters, self.window)
+                                     scratch, counters, self.window, cluster=cluster)
             return
         split_keys = SPLIT_KEYS
         while math.ceil(longest / split_keys) > MAX_SPLITS:
