@@ -437,8 +437,15 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
     const float* src = base + static_cast<long long>(r) * a.max_splits * RS + d;
     const float* wr = wgt + r * a.max_splits;
     float o = 0.0f;
-#pragma unroll 4
-    for (int i = 0; i < n_splits; ++i) o = fmaf(__ldcg(src + i * RS), wr[i], o);
+    for (int i0 = 0; i0 < n_splits; i0 += 8) {   // eight loads in flight, added in split order
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = i0 + j < n_splits ? __ldcg(src + (i0 + j) * RS) : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (i0 + j < n_splits) o = fmaf(v[j], wr[i0 + j], o);
+      }
+    }
     a.out[(static_cast<long long>(t) * a.q_heads + kvh * G + r) * DH + d] = __float2bfloat16_rn(o * inv[r]);
   }
   if (threadIdx.x == 0) a.counters[li * a.kv_heads + kvh] = 0;   // ready for the next launch
