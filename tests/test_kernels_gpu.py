@@ -681,8 +681,8 @@ def test_tensor_core_attention_prompt_and_decode(ops, Hq, Hkv, Dh, page, window)
                                                 (512, 2, True), (256, 4, True), (128, 8, True), (64, 16, True)):
             out[n_multi:] = float("nan")
             ops.attention_decode_tma(qd, dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), out, *meta, Hq, Hkv, Dh, scale,
-                                     dev(np.array([3, 4, 5]), torch.int32), 3, split_keys, max_splits, scratch, counters, window,
-                                     cluster=cluster)
+                                     3 if cluster else dev(np.array([3, 4, 5]), torch.int32), 3, split_keys, max_splits, scratch,
+                                     counters, window, cluster=cluster)
             torch.cuda.synchronize()
             gemm_select.check_status()
             assert rel_err(host(out), want) < TOL["bfloat16"], f"split_keys={split_keys} cluster={cluster}"
@@ -733,9 +733,10 @@ def test_decode_attention_that_prepares_its_own_heads(ops, Hq, Hkv, Dh, page, wi
         for split_keys, max_splits in ((64, 8), (128, 3), (512, 1)):
             if fused:
                 assert ops.attention_decode_prep_takes(qkv, Hq, Hkv, Dh, page, dev(inv))
+                # (the sequences as "S in a row from 0 on" instead of a list, for every other split size)
                 ops.attention_decode_prep(qkv, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), kcd, vcd, out, *meta,
-                                          Hq, Hkv, Dh, scale, seqs, S, split_keys, max_splits, scratch, counters, window,
-                                          append=True, partial=partial, cluster=max_splits in ops.CLUSTER_SPLITS)
+                                          Hq, Hkv, Dh, scale, 0 if split_keys != 128 else seqs, S, split_keys, max_splits, scratch,
+                                          counters, window, append=True, partial=partial, cluster=max_splits in ops.CLUSTER_SPLITS)
             else:
                 work = qkv.clone()
                 ops.qk_norm_rope_append(work, dev(qw), dev(kw), 1e-6, 1e-5, dev(inv), dev(pos, torch.int32), dev(slots, torch.int32),

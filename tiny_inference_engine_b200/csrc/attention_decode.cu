@@ -37,7 +37,8 @@ struct DecodeArgs {
   const int* query_start;
   const int* context_lens;
   const int* block_tables;
-  const int* seq_list;
+  const int* seq_list;   // null: the sequences seq_first, seq_first + 1, ...
+  int seq_first;
   float* scratch;        // [n_list, q_heads, max_splits, head_dim + 2]
   int* counters;         // [n_list, kv_heads], zero between launches
   int* status;
@@ -100,8 +101,24 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int li = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-  const int seq = a.seq_list[li];
+  const int seq = a.seq_list ? a.seq_list[li] : a.seq_first + li;
   const int G = a.q_heads / a.kv_heads;
+  // Without a window a split's first key does not depend on the context length: the page ids of all the boxes the
+  // split may need are asked for together with the length (one round of loads instead of two in a row); entries
+  // beyond the sequence's own pages are never used.
+  constexpr int kAhead = (kMaxTablePages + kDecThreads - 1) / kDecThreads;
+  int ahead[kAhead];
+  const int box_rows_ = min(a.page_size, kKeysPerTile);
+  const int split_boxes = a.window > 0 ? 0 : (a.split_keys / kKeysPerTile) * (kKeysPerTile / box_rows_);
+  {
+    const int* table = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j) {
+      const int b = threadIdx.x + j * kDecThreads;
+      const int idx = (split * a.split_keys + b * box_rows_) >> a.page_shift;
+      ahead[j] = b < split_boxes && idx < a.max_blocks ? table[idx] : 0;
+    }
+  }
   const int t = a.query_start[seq];
   const int pos = a.context_lens[seq] - 1;
   if (pos < 0) {            // a padding sequence: no keys; split 0 writes zeros
@@ -139,12 +156,18 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
   }
   // page ids of the split's tiles (one per TMA box), zero beyond the table: page 0 is real memory
   // and keys beyond `hi` are masked, so what it holds does not matter as long as it is finite
-  {
+  if (a.window > 0) {
     const int* table = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
     const int first_key = kt_first * kKeysPerTile;
     for (int b = threadIdx.x; b < n_tiles * boxes_per_tile; b += kDecThreads) {
       const int idx = (first_key + b * box_rows) >> a.page_shift;
       pages[b] = idx < a.max_blocks ? table[idx] : 0;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j) {
+      const int b = threadIdx.x + j * kDecThreads;
+      if (b < split_boxes) pages[b] = ahead[j];
     }
   }
   __syncthreads();
@@ -563,7 +586,7 @@ using namespace tie;
 // 0 -> page ids of one split kept in shared memory, 1 -> the most splits of a sequence.
 TIE_API int tie_attention_decode_limit(int which) { return which == 0 ? kMaxTablePages : which == 1 ? 256 : -1; }
 
-// The sequences of seq_list bring one token each. scratch holds n_list * q_heads * max_splits *
+// The sequences of seq_list (null: seq_first, seq_first + 1, ...; one load less at the start of every CTA) bring one token each. scratch holds n_list * q_heads * max_splits *
 // (head_dim + 2) floats; counters holds n_list * kv_heads ints that are zero before the first
 // launch (the kernel leaves them zero). pages is the number of pages of the cache planes. cluster != 0: the splits of
 // a sequence and kv head run as one thread-block cluster and merge through shared memory (max_splits 2, 4, 8 or 16;
@@ -571,13 +594,14 @@ TIE_API int tie_attention_decode_limit(int which) { return which == 0 ? kMaxTabl
 TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
                                      const int* query_start, const int* context_lens, const int* block_tables,
                                      int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
-                                     int window, float scale, const int* seq_list, int n_list, int split_keys,
+                                     int window, float scale, const int* seq_list, int seq_first, int n_list,
+                                     int split_keys,
                                      int max_splits, float* scratch, int* counters, int cluster, cudaStream_t s) {
   TIE_REQUIRE(q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0, "attention_decode: q rows must be 16-byte aligned");
   DecodeArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.out = static_cast<__nv_bfloat16*>(out);
-  a.query_start = query_start, a.context_lens = context_lens, a.block_tables = block_tables, a.seq_list = seq_list;
+  a.query_start = query_start, a.context_lens = context_lens, a.block_tables = block_tables, a.seq_list = seq_list, a.seq_first = seq_first;
   a.scratch = scratch, a.counters = counters, a.q_stride = q_stride;
   a.max_blocks = max_blocks, a.q_heads = q_heads, a.kv_heads = kv_heads, a.page_size = page_size, a.window = window;
   a.split_keys = split_keys, a.max_splits = max_splits;
@@ -595,7 +619,8 @@ TIE_API int tie_attention_decode_prep(const void* qkv, long long qkv_stride, con
                                       float k_eps, const float* inv_freq, const int* positions, int append, void* k_cache,
                                       void* v_cache, void* out, const int* query_start, const int* context_lens,
                                       const int* block_tables, int max_blocks, int q_heads, int kv_heads, int head_dim,
-                                      int page_size, int pages, int window, float scale, const int* seq_list, int n_list,
+                                      int page_size, int pages, int window, float scale, const int* seq_list, int seq_first,
+                                      int n_list,
                                       int split_keys, int max_splits, float* scratch, int* counters, int cluster,
                                       cudaStream_t s) {
   const int vec = head_dim / 32;
@@ -609,7 +634,7 @@ TIE_API int tie_attention_decode_prep(const void* qkv, long long qkv_stride, con
               "attention_decode: positions and 16-byte aligned cache planes are needed");
   DecodeArgs a{};
   a.out = static_cast<__nv_bfloat16*>(out);
-  a.query_start = query_start, a.context_lens = context_lens, a.block_tables = block_tables, a.seq_list = seq_list;
+  a.query_start = query_start, a.context_lens = context_lens, a.block_tables = block_tables, a.seq_list = seq_list, a.seq_first = seq_first;
   a.scratch = scratch, a.counters = counters;
   a.max_blocks = max_blocks, a.q_heads = q_heads, a.kv_heads = kv_heads, a.page_size = page_size, a.window = window;
   a.split_keys = split_keys, a.max_splits = max_splits;

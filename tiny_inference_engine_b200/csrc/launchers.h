@@ -60,14 +60,16 @@ TIE_API int tie_attention_prompt_tma(const void* q, long long q_stride, const vo
 TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
                                      const int* query_start, const int* context_lens, const int* block_tables,
                                      int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
-                                     int window, float scale, const int* seq_list, int n_list, int split_keys,
-                                     int max_splits, float* scratch, int* counters, int cluster, cudaStream_t s);
+                                     int window, float scale, const int* seq_list, int seq_first, int n_list,
+                                     int split_keys, int max_splits, float* scratch, int* counters, int cluster,
+                                     cudaStream_t s);
 TIE_API int tie_attention_decode_prep(const void* qkv, long long qkv_stride, const float* part, long long part_stride,
                                       int part_splits, long long part_ld, const float* qw, const float* kw, float q_eps,
                                       float k_eps, const float* inv_freq, const int* positions, int append, void* k_cache,
                                       void* v_cache, void* out, const int* query_start, const int* context_lens,
                                       const int* block_tables, int max_blocks, int q_heads, int kv_heads, int head_dim,
-                                      int page_size, int pages, int window, float scale, const int* seq_list, int n_list,
+                                      int page_size, int pages, int window, float scale, const int* seq_list, int seq_first,
+                                      int n_list,
                                       int split_keys, int max_splits, float* scratch, int* counters, int cluster,
                                       cudaStream_t s);
 TIE_API int tie_attention_prompt_umma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,

@@ -364,17 +364,23 @@ def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
     """Attention of sequences that bring one token each, keys and values fed by TMA, splits merged by
     the last CTA to finish. `counters` (int32 [>= n_list * kv_heads]) must be zero; it is left zero.
     `cluster` (with max_splits in CLUSTER_SPLITS): the splits of a sequence and kv head run as one thread-block
-    cluster and merge through shared memory, which is faster where all the launch's CTAs are resident at once."""
+    cluster and merge through shared memory, which is faster where all the launch's CTAs are resident at once.
+    `seq_list`: int32 [n_list], or an int: the first of n_list sequences in a row (the kernel then has one load
+    less to wait for before it can ask for keys)."""
+    first = seq_list if isinstance(seq_list, int) else 0
+    seq_list = None if isinstance(seq_list, int) else seq_list
     _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch, counters)
-    _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
-    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
+    S = _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
+    _need((seq_list is None and 0 <= first and first + n_list <= S) or
+          (seq_list is not None and seq_list.dtype == torch.int32 and seq_list.numel() >= n_list),
+          "attention: seq_list must be int32 [n_list], or the first of n_list sequences in a row")
     _need(scratch.dtype == torch.float32 and
           scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, head_dim, max_splits),
           "attention: scratch too small")
     _need(counters.dtype == torch.int32 and counters.numel() >= n_list * kv_heads, "attention: counters too small")
     call("tie_attention_decode_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
          query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads,
-         head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), seq_list.data_ptr(), n_list, split_keys,
+         head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _ptr(seq_list), first, n_list, split_keys,
          max_splits, scratch.data_ptr(), counters.data_ptr(), 1 if cluster else 0, _stream())
 
 
@@ -393,6 +399,8 @@ def attention_decode_prep(qkv, q_weight, k_weight, q_eps: float, k_eps: float, i
     output: qkv [T, (q_heads + 2 kv_heads) * head_dim] (or q only, with `append` False), or the product's partial sums.
     The kernel does what `qk_norm_rope_append` does to the group's query heads and, with `append`, to the newest
     key and value, which it stores in the cache planes and uses; qkv itself is left as it is."""
+    first = seq_list if isinstance(seq_list, int) else 0
+    seq_list = None if isinstance(seq_list, int) else seq_list
     _dev(qkv, q_weight, k_weight, inv_freq, positions, k_cache, v_cache, out, query_start, context_lens, block_tables,
          seq_list, scratch, counters)
     T = qkv.shape[0]
@@ -411,7 +419,9 @@ def attention_decode_prep(qkv, q_weight, k_weight, q_eps: float, k_eps: float, i
           "attention_decode_prep: the rotation must cover the whole head")
     _need(query_start.dtype == torch.int32 and context_lens.dtype == torch.int32 and block_tables.dtype == torch.int32
           and block_tables.dim() == 2 and block_tables.stride(1) == 1, "attention: index tensors must be int32")
-    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
+    _need((seq_list is None and 0 <= first and first + n_list <= context_lens.numel()) or
+          (seq_list is not None and seq_list.dtype == torch.int32 and seq_list.numel() >= n_list),
+          "attention: seq_list must be int32 [n_list], or the first of n_list sequences in a row")
     _need(scratch.dtype == torch.float32 and
           scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, head_dim, max_splits),
           "attention: scratch too small")
@@ -423,7 +433,7 @@ def attention_decode_prep(qkv, q_weight, k_weight, q_eps: float, k_eps: float, i
          _ptr(q_weight), _ptr(k_weight), float(q_eps), float(k_eps), _ptr(inv_freq), positions.data_ptr(),
          1 if append else 0, k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), query_start.data_ptr(),
          context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads, head_dim,
-         k_cache.shape[2], k_cache.shape[0], int(window), float(scale), seq_list.data_ptr(), n_list, split_keys,
+         k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _ptr(seq_list), first, n_list, split_keys,
          max_splits, scratch.data_ptr(), counters.data_ptr(), 1 if cluster else 0, _stream())
 
 

@@ -33,8 +33,8 @@ _SIGNATURES = {
     "tie_gemm_tc2": [I, P, P, P, I, I, I, L, L, L, I, I, I, I, P],
     "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_decode_tc": [P, L, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
-    "tie_attention_decode_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P, I, P],
-    "tie_attention_decode_prep": [P, L, P, L, I, L, P, P, F, F, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, P, P, I, P],
+    "tie_attention_decode_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, I, P, P, I, P],
+    "tie_attention_decode_prep": [P, L, P, L, I, L, P, P, F, F, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, I, P, P, I, P],
     "tie_attention_prompt_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_prompt_umma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_merge": [I, P, P, P, I, I, I, P, I, I, I, P, P],

@@ -194,11 +194,11 @@ class GQAttention(Mixer):
                 qkv, qw, kw, q_eps, k_eps, table, partial = prep
                 ops.attention_decode_prep(qkv, qw, kw, q_eps, k_eps, table, ctx.positions, cache.k, cache.v, attn,
                                           ctx.query_start, ctx.context_lens, g.block_tables, Hq, Hkv, Dh, self.scale,
-                                          ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, counters,
+                                          ctx.multi_seqs, ctx.single_count, split_keys, max_splits, scratch, counters,
                                           self.window, append=cache.writes, partial=partial, cluster=cluster)
                 return
             ops.attention_decode_tma(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, Hq,
-                                     Hkv, Dh, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits,
+                                     Hkv, Dh, self.scale, ctx.multi_seqs, ctx.single_count, split_keys, max_splits,
                                      scratch, counters, self.window, cluster=cluster)
             return
         split_keys = SPLIT_KEYS
